@@ -1,0 +1,295 @@
+// Device codec shared by every low-bit kernel in this library (sm_100a).
+//
+// One thread owns GROUP = 8 consecutive elements.  A quantization block of
+// B = 8 * T elements (T a power of two <= 32) therefore lives in T adjacent
+// lanes of one warp, and its absmax is a width-T xor-shuffle reduction: no
+// shared memory, no block-wide barrier.  Packing happens in registers; eight
+// b-bit codes form one b-byte group that is stored with a single instruction
+// (b = 4: one 32-bit word per thread, 128 contiguous bytes per warp).
+//
+// Numerics follow the host quantizer bit for bit (bitscom_b200/quantization.py,
+// which restates reference python/bitscom/quantization.py:102-150 and
+// cpp/src/lowbit_cuda_kernels.cu:144-250): IEEE division, fp16 round trip of
+// the scale, half-to-even rounding, explicit __fmul_rn/__fadd_rn so that the
+// compiler cannot contract a multiply and an add into one fma.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace bcom {
+
+constexpr int GROUP = 8;  // elements per thread
+
+template <int BITS> struct Range {
+  static constexpr int qmin = BITS == 1 ? 0 : -(1 << (BITS - 1));
+  static constexpr int qmax = BITS == 1 ? 1 : (1 << (BITS - 1)) - 1;
+};
+
+// bytes occupied by one 8-element group on the wire
+template <int BITS> struct GroupBytes { static constexpr int value = BITS; };
+
+// ---------------------------------------------------------------------------
+// counter-based uniform stream: same arithmetic as quantization.sr_uniform
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float sr_uniform(uint32_t key, uint32_t idx) {
+  uint32_t h = idx * 0x9E3779B1u + key;
+  h ^= h >> 16;
+  h *= 0x21F0AAADu;
+  h ^= h >> 15;
+  h *= 0x735A2D97u;
+  h ^= h >> 15;
+  return (float)(h >> 8) * (1.0f / 16777216.0f);
+}
+
+// ---------------------------------------------------------------------------
+// typed 8-element loads / stores (vector form needs a 16-byte aligned address)
+// ---------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+template <typename T>
+__device__ __forceinline__ void load8_vec(const T* __restrict__ p, float (&v)[GROUP]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+    const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) v[i] = Elem<T>::to_f(h[i]);
+  }
+}
+
+// plain (coherent) variant for buffers that are written earlier in the same kernel
+template <typename T>
+__device__ __forceinline__ void load8_vec_coherent(const T* p, float (&v)[GROUP]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) v[i] = Elem<T>::to_f(h[i]);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void load8_guard(const T* p, long long base, long long n,
+                                            float (&v)[GROUP]) {
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i)
+    v[i] = (base + i < n) ? Elem<T>::to_f(p[base + i]) : 0.0f;
+}
+
+template <typename T>
+__device__ __forceinline__ void store8_vec(T* p, const float (&v)[GROUP]) {
+  if constexpr (sizeof(T) == 4) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    uint4 raw;
+    T* h = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) h[i] = Elem<T>::from_f(v[i]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store8_guard(T* p, long long base, long long n,
+                                             const float (&v)[GROUP]) {
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i)
+    if (base + i < n) p[base + i] = Elem<T>::from_f(v[i]);
+}
+
+// ---------------------------------------------------------------------------
+// block scale: width-T shuffle absmax, IEEE divide, fp16 round trip
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float absmax8(const float (&v)[GROUP]) {
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
+
+// All 32 lanes of the warp must call this. T = lanes per quantization block.
+__device__ __forceinline__ float block_absmax(float m, int lanes_per_block) {
+  for (int o = lanes_per_block >> 1; o > 0; o >>= 1)
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  return m;
+}
+
+template <int BITS>
+__device__ __forceinline__ __half scale_from_absmax(float m) {
+  float s = __fdiv_rn(m, (float)Range<BITS>::qmax);
+  if (!(m > 0.0f)) s = 1.0f;
+  return __float2half_rn(s);
+}
+
+// ---------------------------------------------------------------------------
+// quantize values with a given fp32(fp16 scale); returns signed codes in [qmin, qmax]
+// ---------------------------------------------------------------------------
+template <int BITS, bool SR>
+__device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t idx) {
+  const float n = __fdiv_rn(fabsf(x), sf);
+  float mag;
+  if constexpr (SR) {
+    const float lo = floorf(n);
+    const float p = fminf(fmaxf(__fsub_rn(n, lo), 0.0f), 1.0f);
+    mag = sr_uniform(key, idx) < p ? __fadd_rn(lo, 1.0f) : lo;
+  } else {
+    mag = rintf(n);
+  }
+  float s = mag;
+  if constexpr (BITS != 1) {
+    const float sign = (float)((x > 0.0f) - (x < 0.0f));
+    s = __fmul_rn(mag, sign);
+  }
+  const float c = fminf(fmaxf(s, (float)Range<BITS>::qmin), (float)Range<BITS>::qmax);
+  return (s != s) ? 0 : (int)c;  // NaN converts to 0, as on the host
+}
+
+template <int BITS, bool SR>
+__device__ __forceinline__ void quant8(const float (&x)[GROUP], float sf, uint32_t key,
+                                       uint32_t idx0, int (&q)[GROUP]) {
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) q[i] = quant1<BITS, SR>(x[i], sf, key, idx0 + i);
+}
+
+__device__ __forceinline__ void dequant8(const int (&q)[GROUP], float sf, float (&y)[GROUP]) {
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) y[i] = __fmul_rn((float)q[i], sf);
+}
+
+// ---------------------------------------------------------------------------
+// register packing of one 8-element group: BITS bytes, first element lowest
+// ---------------------------------------------------------------------------
+template <int BITS> struct Packed8 {
+  static constexpr int WORDS = (BITS + 3) / 4;  // 32-bit words, last may be partial
+  uint32_t w[WORDS];
+};
+
+template <int BITS>
+__device__ __forceinline__ Packed8<BITS> pack8(const int (&q)[GROUP]) {
+  Packed8<BITS> out;
+#pragma unroll
+  for (int i = 0; i < Packed8<BITS>::WORDS; ++i) out.w[i] = 0u;
+  constexpr uint32_t mask = BITS >= 32 ? 0xffffffffu : ((1u << BITS) - 1u);
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    const uint32_t code = (uint32_t)(q[i] - Range<BITS>::qmin) & mask;
+    const int bit = i * BITS;
+    out.w[bit >> 5] |= code << (bit & 31);
+    if ((bit & 31) + BITS > 32) out.w[(bit >> 5) + 1] |= code >> (32 - (bit & 31));
+  }
+  return out;
+}
+
+template <int BITS>
+__device__ __forceinline__ void unpack8(const Packed8<BITS>& in, int (&q)[GROUP]) {
+  constexpr uint32_t mask = (1u << BITS) - 1u;
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    const int bit = i * BITS;
+    uint32_t code = in.w[bit >> 5] >> (bit & 31);
+    if ((bit & 31) + BITS > 32) code |= in.w[(bit >> 5) + 1] << (32 - (bit & 31));
+    code &= mask;
+    if constexpr (BITS == 16) {
+      q[i] = (int)(int16_t)(uint16_t)(code + (uint32_t)Range<16>::qmin);  // int16 wrap
+    } else {
+      q[i] = (int)code + Range<BITS>::qmin;
+    }
+  }
+}
+
+// Store / load a full group at byte offset group_index * BITS. The widest naturally
+// aligned access is used: 1, 2, 4, 8 bytes, 3 x 4 bytes (12-bit), 16 bytes.
+template <int BITS>
+__device__ __forceinline__ void store_group(uint8_t* base, long long group_index,
+                                            const Packed8<BITS>& p) {
+  uint8_t* dst = base + group_index * BITS;
+  if constexpr (BITS == 1) {
+    *dst = (uint8_t)p.w[0];
+  } else if constexpr (BITS == 2) {
+    *reinterpret_cast<uint16_t*>(dst) = (uint16_t)p.w[0];
+  } else if constexpr (BITS == 4) {
+    *reinterpret_cast<uint32_t*>(dst) = p.w[0];
+  } else if constexpr (BITS == 8) {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(p.w[0], p.w[1]);
+  } else if constexpr (BITS == 12) {
+    uint32_t* d = reinterpret_cast<uint32_t*>(dst);
+    d[0] = p.w[0]; d[1] = p.w[1]; d[2] = p.w[2];
+  } else {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(p.w[0], p.w[1], p.w[2], p.w[3]);
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ Packed8<BITS> load_group(const uint8_t* base, long long group_index) {
+  Packed8<BITS> p;
+  const uint8_t* src = base + group_index * BITS;
+  if constexpr (BITS == 1) {
+    p.w[0] = *src;
+  } else if constexpr (BITS == 2) {
+    p.w[0] = *reinterpret_cast<const uint16_t*>(src);
+  } else if constexpr (BITS == 4) {
+    p.w[0] = *reinterpret_cast<const uint32_t*>(src);
+  } else if constexpr (BITS == 8) {
+    const uint2 v = *reinterpret_cast<const uint2*>(src);
+    p.w[0] = v.x; p.w[1] = v.y;
+  } else if constexpr (BITS == 12) {
+    const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
+    p.w[0] = s[0]; p.w[1] = s[1]; p.w[2] = s[2];
+  } else {
+    const uint4 v = *reinterpret_cast<const uint4*>(src);
+    p.w[0] = v.x; p.w[1] = v.y; p.w[2] = v.z; p.w[3] = v.w;
+  }
+  return p;
+}
+
+// Byte-wise tail variants: only the first `nbytes` bytes of the group exist.
+template <int BITS>
+__device__ __forceinline__ void store_group_bytes(uint8_t* base, long long group_index,
+                                                  const Packed8<BITS>& p, int nbytes) {
+  uint8_t* dst = base + group_index * BITS;
+  for (int i = 0; i < nbytes; ++i) dst[i] = (uint8_t)(p.w[i >> 2] >> ((i & 3) * 8));
+}
+
+template <int BITS>
+__device__ __forceinline__ Packed8<BITS> load_group_bytes(const uint8_t* base,
+                                                          long long group_index, int nbytes) {
+  Packed8<BITS> p;
+#pragma unroll
+  for (int i = 0; i < Packed8<BITS>::WORDS; ++i) p.w[i] = 0u;
+  const uint8_t* src = base + group_index * BITS;
+  for (int i = 0; i < nbytes; ++i) p.w[i >> 2] |= (uint32_t)src[i] << ((i & 3) * 8);
+  return p;
+}
+
+// wire bytes of `n` codes
+__host__ __device__ inline long long packed_nbytes(long long n, int bits) {
+  if (bits == 12) return 3 * ((n + 1) / 2);
+  if (bits == 16) return 2 * n;
+  return (n * bits + 7) / 8;
+}
+
+}  // namespace bcom

@@ -1,0 +1,51 @@
+"""Shared helpers for calling the native libraries through ctypes."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+from .. import _build
+
+DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def cuda_present() -> bool:
+    return torch.cuda.is_available()
+
+
+def load(name: str) -> Optional[ctypes.CDLL]:
+    """Load a native library.
+
+    Without a GPU the library is not needed and ``None`` is returned when it cannot be
+    loaded.  With a GPU a missing or broken library is an error: falling back to torch
+    ops silently would hide that the kernels are not running.
+    """
+    try:
+        return _build.load_library(name)
+    except Exception as exc:
+        if cuda_present() and os.environ.get("BITSCOM_ALLOW_FALLBACK", "0") != "1":
+            raise NativeError(
+                f"bitscom_b200: native library '{name}' could not be loaded on a GPU "
+                f"machine: {exc}") from exc
+        return None
+
+
+def stream_ptr(device: Optional[torch.device] = None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeError(f"{what} failed with CUDA error {code}")
