@@ -32,7 +32,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-shared"
 LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "bcom_codec": {"sources": ["codec_kernels.cu"], "deps": ["codec.cuh"], "flags": []},
     "bcom_comm": {"sources": ["fused_collectives.cu", "symm.cu"],
-                  "deps": ["codec.cuh", "symm.h", "no_alloc.h"], "flags": []},
+                  "deps": ["codec.cuh", "symm.h"], "flags": []},
     "bcom_llama": {"sources": ["gemm_tcgen05.cu", "attention.cu", "elementwise.cu"],
                    "deps": ["tc_common.cuh"], "flags": []},
 }

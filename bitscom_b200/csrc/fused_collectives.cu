@@ -1,0 +1,594 @@
+// Fused low-bit collectives for one NVSwitch domain (sm_100a): ONE kernel per bucket
+// chunk does what the reference spreads over ~20 ATen kernels per shard, four NCCL
+// send/recv groups and three host-synchronised phases
+// (cpp/src/process_group_lowbit.cc:641-861 phase 1, :1106-1251 phase 2, :1253-1293
+// restore; Python twin python/bitscom/api.py:703-875):
+//
+//   phase 1  [error-feedback add] -> block absmax -> fp16 scale -> nearest/stochastic
+//            rounding -> bit-pack -> store the packed shard j and its scales straight
+//            into rank j's receive slot over NVLink (peer stores); new residual
+//   flag 1   last CTA of the rank publishes epoch to every peer (st.release.sys)
+//   phase 2  wait for all sources; dequantize the W streams from LOCAL memory, fp32 sum
+//            in ascending source order; [stage-2 residual add]; re-quantize; push the
+//            packed reduced shard into every rank's gather slot
+//   flag 2   publish; wait for all owners
+//   phase 3  unpack + dequantize all W shards from local gather slots, cast, optional
+//            post-scale, write the bucket
+//
+// reduce-scatter = phases 1-2 without the re-quantize (writes the fp32 sum to `out`);
+// all-gather = phase 2 fed from `in` plus phase 3.  All three modes keep both flag
+// handshakes, which is what makes back-to-back calls safe without a separate barrier.
+//
+// Synchronisation rules: the grid is launched cooperatively (all CTAs co-resident);
+// arrival counters live in the rank's control page and are re-armed by the kernel
+// itself; every wait is bounded by a wall-clock budget and, when it expires, the
+// kernel records {code, phase, peer, rank, observed, expected} in a host-mapped status
+// record and returns instead of trapping.
+#include <cuda_runtime.h>
+
+#include "codec.cuh"
+#include "symm_internal.h"
+
+namespace bcom {
+
+constexpr int kCollThreads = 512;
+
+struct RankParams {
+  unsigned char* peer[BCOM_MAX_WORLD];
+  unsigned int* status;
+  const void* in;
+  void* out;
+  float* res1;
+  float* res2;
+  long long n, S, c0, L;
+  unsigned long long epoch;
+  unsigned long long timeout_ns;
+  size_t region_bytes;
+  size_t slot_stride;   // bytes between two sources' slots inside a region
+  size_t scale_off;     // offset of the fp16 scales inside a slot
+  int rank, world;
+  int lanes_per_block;  // block / 8
+  int mode;
+  unsigned int key1, key2;
+  float post_scale;
+};
+
+// ---------------------------------------------------------------------------
+// memory-model helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// L2-coherent loads for slots that peers wrote during this kernel
+template <int BITS>
+__device__ __forceinline__ Packed8<BITS> load_group_cg(const unsigned char* base, long long g) {
+  Packed8<BITS> p;
+  const unsigned char* src = base + g * BITS;
+  if constexpr (BITS == 1) {
+    p.w[0] = __ldcg(src);
+  } else if constexpr (BITS == 2) {
+    p.w[0] = __ldcg(reinterpret_cast<const unsigned short*>(src));
+  } else if constexpr (BITS == 4) {
+    p.w[0] = __ldcg(reinterpret_cast<const unsigned int*>(src));
+  } else {
+    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(src));
+    p.w[0] = v.x; p.w[1] = v.y;
+  }
+  return p;
+}
+__device__ __forceinline__ float load_scale_cg(const unsigned char* slot, size_t scale_off,
+                                               long long block_index) {
+  const unsigned short raw =
+      __ldcg(reinterpret_cast<const unsigned short*>(slot + scale_off) + block_index);
+  return __half2float(__ushort_as_half(raw));
+}
+
+// ---------------------------------------------------------------------------
+// arrive / publish / wait
+// ---------------------------------------------------------------------------
+// Every CTA of the rank calls this once its stores of the phase are issued.  The last
+// one to arrive re-arms the other phase's counter and publishes `epoch` in slot `rank`
+// of the flag array at `flag_off` on every peer.
+__device__ __forceinline__ void arrive_and_publish(const RankParams& p, int ncta,
+                                                   int arrive_off, int rearm_off, int flag_off) {
+  __threadfence_system();  // this thread's peer stores are performed
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    unsigned int* ctr = reinterpret_cast<unsigned int*>(p.peer[p.rank] + arrive_off);
+    const unsigned int seen = atomicAdd(ctr, 1u);
+    is_last = (seen + 1u == (unsigned int)ncta);
+    if (is_last) {
+      *reinterpret_cast<volatile unsigned int*>(p.peer[p.rank] + rearm_off) = 0u;
+      __threadfence_system();
+    }
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < p.world) {
+    unsigned long long* flag =
+        reinterpret_cast<unsigned long long*>(p.peer[threadIdx.x] + flag_off) + p.rank;
+    st_release_sys(flag, p.epoch);
+  }
+}
+
+// Waits until all `world` flags at `flag_off` of this rank's control page reach the
+// epoch.  Returns false after recording a timeout.
+__device__ __forceinline__ bool wait_flags(const RankParams& p, int flag_off, unsigned int code) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    const unsigned long long* flag =
+        reinterpret_cast<const unsigned long long*>(p.peer[p.rank] + flag_off) + threadIdx.x;
+    unsigned long long seen = ld_acquire_sys(flag);
+    if (seen < p.epoch) {
+      const unsigned long long t0 = global_timer_ns();
+      unsigned int spins = 0;
+      while ((seen = ld_acquire_sys(flag)) < p.epoch) {
+        if ((++spins & 63u) == 0u) {
+          if (global_timer_ns() - t0 > p.timeout_ns) break;
+          __nanosleep(64);
+        }
+      }
+      if (seen < p.epoch) {
+        failed = 1;
+        if (atomicCAS(p.status, 0u, code) == 0u) {
+          p.status[1] = code;
+          p.status[2] = threadIdx.x;
+          p.status[3] = (unsigned int)p.rank;
+          p.status[4] = (unsigned int)seen;
+          p.status[5] = (unsigned int)(seen >> 32);
+          p.status[6] = (unsigned int)p.epoch;
+          p.status[7] = (unsigned int)(p.epoch >> 32);
+          __threadfence_system();
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return failed == 0;
+}
+
+// ---------------------------------------------------------------------------
+// typed tensor access with tail / alignment handling
+// ---------------------------------------------------------------------------
+template <typename T, bool ALIGNED>
+__device__ __forceinline__ void load_vals(const T* base, long long idx, long long lim,
+                                          float (&v)[GROUP]) {
+  if (ALIGNED && lim >= GROUP) {
+    load8_vec_coherent(base + idx, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) v[i] = (i < lim) ? Elem<T>::to_f(base[idx + i]) : 0.0f;
+  }
+}
+
+template <typename T, bool ALIGNED>
+__device__ __forceinline__ void store_vals(T* base, long long idx, long long lim,
+                                           const float (&v)[GROUP]) {
+  if (ALIGNED && lim >= GROUP) {
+    store8_vec(base + idx, v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i)
+      if (i < lim) base[idx + i] = Elem<T>::from_f(v[i]);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float cast_roundtrip(float x, float post_scale) {
+  // result = cast to T, then (optionally) one multiply carried out on the T value
+  float y = Elem<T>::to_f(Elem<T>::from_f(x));
+  if (post_scale != 1.0f) y = __fmul_rn(y, post_scale);
+  return y;
+}
+
+// Quantize 8 values whose block absmax is shared by `lanes` adjacent lanes, push the
+// packed group and the scale to `slot` on each listed destination.
+template <int BITS>
+__device__ __forceinline__ void push_group(unsigned char* slot, size_t scale_off, long long g,
+                                           int lanes, const Packed8<BITS>& pk, __half sh) {
+  store_group<BITS>(slot, g, pk);
+  if ((g & (lanes - 1)) == 0)
+    reinterpret_cast<__half*>(slot + scale_off)[g / lanes] = sh;
+}
+
+// ---------------------------------------------------------------------------
+// the collective, as seen by one rank whose CTAs are numbered cta in [0, ncta)
+// ---------------------------------------------------------------------------
+template <typename T, int BITS, bool SR, bool ALIGNED>
+__device__ void run_rank(const RankParams& p, int cta, int ncta) {
+  const int tid = threadIdx.x;
+  const long long nthreads = (long long)ncta * blockDim.x;
+  const long long first = (long long)cta * blockDim.x + tid;
+  const int W = p.world;
+  const int lanes = p.lanes_per_block;
+  const long long Gs = (p.L + GROUP - 1) / GROUP;  // groups in this shard chunk
+  const long long Gp = (Gs + 31) & ~31LL;          // padded so warps never straddle shards
+  const long long shard_end = p.c0 + p.L;
+  unsigned char* const recv_region = p.peer[p.rank] + BCOM_CONTROL_BYTES;
+  unsigned char* const gather_region = recv_region + p.region_bytes;
+  const T* in = static_cast<const T*>(p.in);
+  T* out = static_cast<T*>(p.out);
+
+  // ---------------- phase 1: quantize every destination's shard and push it ----------
+  if (p.mode != BCOM_MODE_ALL_GATHER) {
+    const bool ef = p.res1 != nullptr;
+    const long long items = (long long)W * Gp;
+    for (long long it = first; it < items; it += nthreads) {
+      const int k = (int)(it / Gp);
+      const long long g = it - (long long)k * Gp;
+      const int j = (p.rank + k) % W;  // ranks start on different destinations
+      const long long off = p.c0 + g * GROUP;
+      const long long idx = (long long)j * p.S + off;
+      const bool live = g < Gs;
+      long long lim = live ? min(shard_end - off, p.n - idx) : 0;
+      if (lim < 0) lim = 0;
+      float v[GROUP];
+      load_vals<T, ALIGNED>(in, idx, lim, v);
+      if (ef) {
+        float r[GROUP];
+        load_vals<float, ALIGNED>(p.res1, idx, lim, r);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) v[i] = __fadd_rn(v[i], r[i]);
+      }
+      const float m = block_absmax(absmax8(v), lanes);
+      const __half sh = scale_from_absmax<BITS>(m);
+      const float sf = __half2float(sh);
+      if (!live) continue;
+      int q[GROUP];
+      quant8<BITS, SR>(v, sf, p.key1, (uint32_t)idx, q);
+      if (ef) {
+        float d[GROUP];
+        dequant8(q, sf, d);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(v[i], d[i]);
+        store_vals<float, ALIGNED>(p.res1, idx, lim, d);
+      }
+      unsigned char* slot =
+          p.peer[j] + BCOM_CONTROL_BYTES + (size_t)p.rank * p.slot_stride;
+      push_group<BITS>(slot, p.scale_off, g, lanes, pack8<BITS>(q), sh);
+    }
+  }
+  arrive_and_publish(p, ncta, BCOM_CTL_ARRIVE1, BCOM_CTL_ARRIVE2, BCOM_CTL_FLAG1);
+  if (!wait_flags(p, BCOM_CTL_FLAG1, BCOM_TIMEOUT_PHASE1_FLAGS)) return;
+
+  // ---------------- phase 2: reduce own shard, re-quantize, push to everybody ---------
+  {
+    const bool ef2 = p.res2 != nullptr;
+    for (long long g = first; g < Gp; g += nthreads) {
+      const bool live = g < Gs;
+      const long long off = p.c0 + g * GROUP;
+      long long lim = live ? min(shard_end - off, (long long)GROUP) : 0;
+      float acc[GROUP];
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) acc[i] = 0.0f;
+      if (p.mode == BCOM_MODE_ALL_GATHER) {
+        load_vals<T, ALIGNED>(in, off, lim, acc);
+      } else if (live) {
+        for (int src = 0; src < W; ++src) {  // ascending source order: part of the contract
+          const unsigned char* slot = recv_region + (size_t)src * p.slot_stride;
+          const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
+          const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
+          int q[GROUP];
+          unpack8<BITS>(pk, q);
+#pragma unroll
+          for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn((float)q[i], sf));
+        }
+      }
+      if (p.mode == BCOM_MODE_REDUCE_SCATTER) {
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < GROUP; ++i) acc[i] = cast_roundtrip<T>(acc[i], p.post_scale);
+          store_vals<T, ALIGNED>(out, off, lim, acc);
+        }
+        continue;
+      }
+      if (ef2) {
+        float r[GROUP];
+        load_vals<float, ALIGNED>(p.res2, off, lim, r);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
+      }
+      const float m = block_absmax(absmax8(acc), lanes);
+      const __half sh = scale_from_absmax<BITS>(m);
+      const float sf = __half2float(sh);
+      if (!live) continue;
+      int q[GROUP];
+      quant8<BITS, SR>(acc, sf, p.key2, (uint32_t)((long long)p.rank * p.S + off), q);
+      if (ef2) {
+        float d[GROUP];
+        dequant8(q, sf, d);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(acc[i], d[i]);
+        store_vals<float, ALIGNED>(p.res2, off, lim, d);
+      }
+      const Packed8<BITS> pk = pack8<BITS>(q);
+      for (int k = 0; k < W; ++k) {
+        const int t = (p.rank + k) % W;
+        unsigned char* slot = p.peer[t] + BCOM_CONTROL_BYTES + p.region_bytes +
+                              (size_t)p.rank * p.slot_stride;
+        push_group<BITS>(slot, p.scale_off, g, lanes, pk, sh);
+      }
+    }
+  }
+  arrive_and_publish(p, ncta, BCOM_CTL_ARRIVE2, BCOM_CTL_ARRIVE1, BCOM_CTL_FLAG2);
+  if (!wait_flags(p, BCOM_CTL_FLAG2, BCOM_TIMEOUT_PHASE2_FLAGS)) return;
+  if (p.mode == BCOM_MODE_REDUCE_SCATTER) return;
+
+  // ---------------- phase 3: dequantize all shards into the bucket --------------------
+  {
+    const long long items = (long long)W * Gs;
+    for (long long it = first; it < items; it += nthreads) {
+      const int k = (int)(it / Gs);
+      const long long g = it - (long long)k * Gs;
+      const int j = (p.rank + k) % W;
+      const long long off = p.c0 + g * GROUP;
+      const long long idx = (long long)j * p.S + off;
+      const long long lim = min(shard_end - off, p.n - idx);
+      if (lim <= 0) continue;
+      const unsigned char* slot = gather_region + (size_t)j * p.slot_stride;
+      const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
+      const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
+      int q[GROUP];
+      unpack8<BITS>(pk, q);
+      float y[GROUP];
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i)
+        y[i] = cast_roundtrip<T>(__fmul_rn((float)q[i], sf), p.post_scale);
+      store_vals<T, ALIGNED>(out, idx, lim, y);
+    }
+  }
+}
+
+template <typename T, int BITS, bool SR, bool ALIGNED>
+__global__ void __launch_bounds__(kCollThreads, 2)
+lowbit_collective_kernel(const RankParams p) {
+  run_rank<T, BITS, SR, ALIGNED>(p, blockIdx.x, gridDim.x);
+}
+
+// Same-device emulation of `world` ranks in ONE cooperative launch: CTA groups play the
+// ranks, so the whole flag protocol runs (and can be tested) on a single GPU.
+template <typename T, int BITS, bool SR, bool ALIGNED>
+__global__ void __launch_bounds__(kCollThreads, 2)
+lowbit_collective_emulated_kernel(const RankParams* all, int world) {
+  const int per_rank = gridDim.x / world;
+  const int r = blockIdx.x / per_rank;
+  if (r >= world) return;
+  __shared__ RankParams p;
+  if (threadIdx.x == 0) p = all[r];
+  __syncthreads();
+  run_rank<T, BITS, SR, ALIGNED>(p, blockIdx.x - r * per_rank, per_rank);
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef void (*RealKernel)(const RankParams);
+typedef void (*EmuKernel)(const RankParams*, int);
+
+template <typename T, int BITS>
+static void pick(bool sr, bool aligned, RealKernel* real, EmuKernel* emu) {
+  if (sr && aligned) {
+    *real = lowbit_collective_kernel<T, BITS, true, true>;
+    *emu = lowbit_collective_emulated_kernel<T, BITS, true, true>;
+  } else if (sr) {
+    *real = lowbit_collective_kernel<T, BITS, true, false>;
+    *emu = lowbit_collective_emulated_kernel<T, BITS, true, false>;
+  } else if (aligned) {
+    *real = lowbit_collective_kernel<T, BITS, false, true>;
+    *emu = lowbit_collective_emulated_kernel<T, BITS, false, true>;
+  } else {
+    *real = lowbit_collective_kernel<T, BITS, false, false>;
+    *emu = lowbit_collective_emulated_kernel<T, BITS, false, false>;
+  }
+}
+
+template <typename T>
+static bool pick_bits(int bits, bool sr, bool aligned, RealKernel* real, EmuKernel* emu) {
+  switch (bits) {
+    case 1: pick<T, 1>(sr, aligned, real, emu); return true;
+    case 2: pick<T, 2>(sr, aligned, real, emu); return true;
+    case 4: pick<T, 4>(sr, aligned, real, emu); return true;
+    case 8: pick<T, 8>(sr, aligned, real, emu); return true;
+    default: return false;
+  }
+}
+
+static bool pick_kernel(int dtype, int bits, bool sr, bool aligned, RealKernel* real,
+                        EmuKernel* emu) {
+  switch (dtype) {
+    case 0: return pick_bits<float>(bits, sr, aligned, real, emu);
+    case 1: return pick_bits<__half>(bits, sr, aligned, real, emu);
+    case 2: return pick_bits<__nv_bfloat16>(bits, sr, aligned, real, emu);
+    default: return false;
+  }
+}
+
+static bool block_ok(int block) {
+  if (block % GROUP) return false;
+  const int t = block / GROUP;
+  return t >= 1 && t <= 32 && (t & (t - 1)) == 0;
+}
+
+static int elem_size(int dtype) { return dtype == 0 ? 4 : 2; }
+
+struct SlotLayout {
+  size_t scale_off;
+  size_t stride;
+};
+
+// layout of one source's slot for a chunk of `L` elements
+static SlotLayout slot_layout(long long L, int bits, int block) {
+  const long long groups = ((L + GROUP - 1) / GROUP + 31) & ~31LL;
+  SlotLayout s;
+  s.scale_off = bcom_align_up((size_t)groups * bits, 256);
+  const size_t scale_bytes = bcom_align_up((size_t)((L + block - 1) / block + 32) * 2, 256);
+  s.stride = s.scale_off + scale_bytes;
+  return s;
+}
+
+static long long max_chunk(size_t region_bytes, int world, int bits, int block) {
+  // largest L (multiple of 256 elements) with world * stride(L) <= region_bytes
+  const double per_elem = bits / 8.0 + 2.0 / block;
+  long long L = (long long)((double)(region_bytes / world) / per_elem);
+  L = L / 256 * 256;
+  while (L > 0 && (size_t)world * slot_layout(L, bits, block).stride > region_bytes) L -= 256;
+  return L;
+}
+
+static bool is_aligned(const BcomCollArgs& a) {
+  auto ok = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  return a.S % GROUP == 0 && ok(a.in) && ok(a.out) && ok(a.res1) && ok(a.res2);
+}
+
+static int validate(const BcomComm* c, const BcomCollArgs& a) {
+  if (!c || a.n < 0 || a.S <= 0 || !block_ok(a.block)) return (int)cudaErrorInvalidValue;
+  if (a.n > (long long)c->world * a.S) return (int)cudaErrorInvalidValue;
+  if (a.mode < 0 || a.mode > 2) return (int)cudaErrorInvalidValue;
+  return 0;
+}
+
+static void fill_params(const BcomComm* c, const BcomCollArgs& a, long long c0, long long L,
+                        unsigned long long epoch, RankParams* p) {
+  for (int i = 0; i < BCOM_MAX_WORLD; ++i) p->peer[i] = i < c->world ? c->peer[i] : nullptr;
+  p->status = c->status_dev;
+  p->in = a.in;
+  p->out = a.out;
+  p->res1 = a.res1;
+  p->res2 = a.res2;
+  p->n = a.n;
+  p->S = a.S;
+  p->c0 = c0;
+  p->L = L;
+  p->epoch = epoch;
+  p->timeout_ns = c->timeout_ns;
+  p->region_bytes = c->region_bytes;
+  const SlotLayout lay = slot_layout(L, a.bits, a.block);
+  p->slot_stride = lay.stride;
+  p->scale_off = lay.scale_off;
+  p->rank = c->rank;
+  p->world = c->world;
+  p->lanes_per_block = a.block / GROUP;
+  p->mode = a.mode;
+  p->key1 = a.key1;
+  p->key2 = a.key2;
+  p->post_scale = a.post_scale;
+}
+
+static int ctas_for(const BcomComm* c, const BcomCollArgs& a, long long L, int resident_per_sm) {
+  const long long groups = ((L + GROUP - 1) / GROUP + 31) & ~31LL;
+  long long want = ((long long)c->world * groups + kCollThreads - 1) / kCollThreads;
+  long long cap = (long long)c->sm_count * resident_per_sm;
+  if (a.max_ctas > 0 && a.max_ctas < cap) cap = a.max_ctas;
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+}  // namespace bcom
+
+using namespace bcom;
+
+extern "C" {
+
+int bcom_collective_supported(int dtype, int bits, int block) {
+  RealKernel r;
+  EmuKernel e;
+  return (pick_kernel(dtype, bits, false, true, &r, &e) && block_ok(block)) ? 1 : 0;
+}
+
+long long bcom_comm_max_chunk(BcomComm* c, int bits, int block) {
+  if (!c || !block_ok(block)) return 0;
+  return max_chunk(c->region_bytes, c->world, bits, block);
+}
+
+int bcom_collective(BcomComm* c, const BcomCollArgs* args, void* stream) {
+  const BcomCollArgs& a = *args;
+  if (int err = validate(c, a)) return err;
+  RealKernel kernel;
+  EmuKernel unused;
+  if (!pick_kernel(a.dtype, a.bits, a.stochastic != 0, is_aligned(a), &kernel, &unused))
+    return (int)cudaErrorNotSupported;
+  int resident = 0;
+  cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+      &resident, (const void*)kernel, kCollThreads, 0);
+  if (err != cudaSuccess) return (int)err;
+  if (resident < 1) return (int)cudaErrorLaunchOutOfResources;
+  long long Lmax = max_chunk(c->region_bytes, c->world, a.bits, a.block);
+  if (Lmax <= 0) return (int)cudaErrorMemoryAllocation;
+  Lmax = Lmax / a.block * a.block;  // chunks start on quantization-block boundaries
+  if (Lmax <= 0) return (int)cudaErrorMemoryAllocation;
+  for (long long c0 = 0; c0 < a.S; c0 += Lmax) {
+    const long long L = a.S - c0 < Lmax ? a.S - c0 : Lmax;
+    RankParams p;
+    fill_params(c, a, c0, L, ++c->epoch, &p);
+    void* kargs[] = {&p};
+    err = cudaLaunchCooperativeKernel((const void*)kernel, dim3(ctas_for(c, a, L, resident)),
+                                      dim3(kCollThreads), kargs, 0, (cudaStream_t)stream);
+    if (err != cudaSuccess) return (int)err;
+  }
+  return 0;
+}
+
+int bcom_collective_emulated(BcomComm** comms, const BcomCollArgs* args, int world,
+                             void* stream) {
+  if (world < 1 || world > BCOM_MAX_WORLD) return (int)cudaErrorInvalidValue;
+  for (int r = 0; r < world; ++r)
+    if (int err = validate(comms[r], args[r])) return err;
+  const BcomCollArgs& a0 = args[0];
+  bool aligned = true;
+  for (int r = 0; r < world; ++r) aligned = aligned && is_aligned(args[r]);
+  RealKernel unused;
+  EmuKernel kernel;
+  if (!pick_kernel(a0.dtype, a0.bits, a0.stochastic != 0, aligned, &unused, &kernel))
+    return (int)cudaErrorNotSupported;
+  int resident = 0;
+  cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+      &resident, (const void*)kernel, kCollThreads, 0);
+  if (err != cudaSuccess) return (int)err;
+  if (resident < 1) return (int)cudaErrorLaunchOutOfResources;
+  BcomComm* c0comm = comms[0];
+  long long Lmax = max_chunk(c0comm->region_bytes, world, a0.bits, a0.block);
+  Lmax = Lmax / a0.block * a0.block;
+  if (Lmax <= 0) return (int)cudaErrorMemoryAllocation;
+  RankParams* dev_params = nullptr;
+  err = cudaMallocAsync((void**)&dev_params, sizeof(RankParams) * world, (cudaStream_t)stream);
+  if (err != cudaSuccess) return (int)err;
+  for (long long c0 = 0; c0 < a0.S; c0 += Lmax) {
+    const long long L = a0.S - c0 < Lmax ? a0.S - c0 : Lmax;
+    RankParams host[BCOM_MAX_WORLD];
+    for (int r = 0; r < world; ++r)
+      fill_params(comms[r], args[r], c0, L, ++comms[r]->epoch, &host[r]);
+    err = cudaMemcpyAsync(dev_params, host, sizeof(RankParams) * world, cudaMemcpyHostToDevice,
+                          (cudaStream_t)stream);
+    if (err != cudaSuccess) break;
+    // host[] is on the stack: make sure the copy has consumed it
+    err = cudaStreamSynchronize((cudaStream_t)stream);
+    if (err != cudaSuccess) break;
+    int per_rank = ctas_for(c0comm, a0, L, resident);
+    const int cap = c0comm->sm_count * resident / world;
+    if (per_rank > cap) per_rank = cap;
+    if (per_rank < 1) { err = cudaErrorLaunchOutOfResources; break; }
+    int w = world;
+    void* kargs[] = {&dev_params, &w};
+    err = cudaLaunchCooperativeKernel((const void*)kernel, dim3(per_rank * world),
+                                      dim3(kCollThreads), kargs, 0, (cudaStream_t)stream);
+    if (err != cudaSuccess) break;
+  }
+  cudaFreeAsync(dev_params, (cudaStream_t)stream);
+  return (int)err;
+}
+
+}  // extern "C"

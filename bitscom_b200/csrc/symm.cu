@@ -1,0 +1,115 @@
+// Host side of the symmetric-memory communicator: allocation, CUDA IPC mapping of the
+// peers' blocks, status record, reset.  See symm.h for the layout and the protocol.
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "symm_internal.h"
+
+#define BCOM_TRY(expr)                         \
+  do {                                         \
+    cudaError_t e__ = (expr);                  \
+    if (e__ != cudaSuccess) return (int)e__;   \
+  } while (0)
+
+extern "C" {
+
+int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out) {
+  if (!out || world < 1 || world > BCOM_MAX_WORLD || rank < 0 || rank >= world)
+    return (int)cudaErrorInvalidValue;
+  BcomComm* c = new (std::nothrow) BcomComm();
+  if (!c) return (int)cudaErrorMemoryAllocation;
+  std::memset(c, 0, sizeof(*c));
+  c->rank = rank;
+  c->world = world;
+  c->region_bytes = bcom_align_up(region_bytes, 4096);
+  c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes;
+  c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
+  cudaError_t err = cudaGetDevice(&c->device);
+  if (err == cudaSuccess)
+    err = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
+  if (err == cudaSuccess) err = cudaMalloc((void**)&c->local, c->total_bytes);
+  if (err == cudaSuccess) err = cudaMemset(c->local, 0, BCOM_CONTROL_BYTES);
+  if (err == cudaSuccess)
+    err = cudaHostAlloc((void**)&c->status_host, 8 * sizeof(unsigned int), cudaHostAllocMapped);
+  if (err == cudaSuccess) {
+    std::memset(c->status_host, 0, 8 * sizeof(unsigned int));
+    err = cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0);
+  }
+  if (err != cudaSuccess) {
+    if (c->local) cudaFree(c->local);
+    if (c->status_host) cudaFreeHost(c->status_host);
+    delete c;
+    return (int)err;
+  }
+  c->peer[rank] = c->local;
+  *out = c;
+  return 0;
+}
+
+int bcom_comm_destroy(BcomComm* c) {
+  if (!c) return 0;
+  cudaSetDevice(c->device);
+  cudaDeviceSynchronize();
+  for (int p = 0; p < c->world; ++p)
+    if (c->opened[p] && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
+  if (c->local) cudaFree(c->local);
+  if (c->status_host) cudaFreeHost(c->status_host);
+  delete c;
+  return 0;
+}
+
+int bcom_comm_ipc_handle(BcomComm* c, void* handle_out) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == BCOM_IPC_HANDLE_BYTES, "handle size");
+  cudaIpcMemHandle_t h;
+  BCOM_TRY(cudaIpcGetMemHandle(&h, c->local));
+  std::memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+
+int bcom_comm_open_peers(BcomComm* c, const void* handles) {
+  const unsigned char* hs = (const unsigned char*)handles;
+  for (int p = 0; p < c->world; ++p) {
+    if (p == c->rank) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, hs + (size_t)p * BCOM_IPC_HANDLE_BYTES, sizeof(h));
+    void* base = nullptr;
+    BCOM_TRY(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    c->peer[p] = (unsigned char*)base;
+    c->opened[p] = true;
+  }
+  return 0;
+}
+
+int bcom_comm_set_peer(BcomComm* c, int peer, void* base) {
+  if (peer < 0 || peer >= c->world) return (int)cudaErrorInvalidValue;
+  c->peer[peer] = (unsigned char*)base;
+  c->opened[peer] = false;
+  return 0;
+}
+
+void* bcom_comm_local_base(BcomComm* c) { return c->local; }
+size_t bcom_comm_region_bytes(BcomComm* c) { return c->region_bytes; }
+unsigned long long bcom_comm_epoch(BcomComm* c) { return c->epoch; }
+
+int bcom_comm_set_timeout_ms(BcomComm* c, double ms) {
+  if (ms <= 0) return (int)cudaErrorInvalidValue;
+  c->timeout_ns = (unsigned long long)(ms * 1.0e6);
+  return 0;
+}
+
+int bcom_comm_status(BcomComm* c, unsigned int out[8]) {
+  for (int i = 0; i < 8; ++i) out[i] = ((volatile unsigned int*)c->status_host)[i];
+  return 0;
+}
+
+int bcom_comm_reset(BcomComm* c, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  BCOM_TRY(cudaStreamSynchronize(st));
+  std::memset(c->status_host, 0, 8 * sizeof(unsigned int));
+  BCOM_TRY(cudaMemsetAsync(c->local + BCOM_CTL_ARRIVE1, 0, 16, st));
+  BCOM_TRY(cudaStreamSynchronize(st));
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,93 @@
+// Symmetric-memory communicator and fused low-bit collectives: C API.
+//
+// One communicator per (process group, device).  Every rank allocates one block of
+// device memory with the same layout
+//
+//     [ control 4 KiB | receive region | gather region ]
+//
+// and maps every peer's block (CUDA IPC between processes of one NVSwitch domain).
+// The fused kernel pushes packed shards into the *destination's* regions with plain
+// peer stores, so a consumer only ever reads its own HBM; cross-GPU ordering uses
+// monotonically increasing 64-bit epoch flags in the control page
+// (st.release.sys / ld.acquire.sys), never reset, and every wait is bounded.
+//
+// This replaces the reference's private NCCL communicator with grouped
+// ncclSend/ncclRecv (cpp/src/process_group_lowbit.cc:543-575,776-835,1179-1239).
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+#define BCOM_MAX_WORLD 16
+#define BCOM_CONTROL_BYTES 4096
+#define BCOM_IPC_HANDLE_BYTES 64
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct BcomComm BcomComm;
+
+// kernel status codes (status[0]); 0 = ok
+enum {
+  BCOM_OK = 0,
+  BCOM_TIMEOUT_PHASE1_FLAGS = 1,  // a peer never announced its packed shards
+  BCOM_TIMEOUT_PHASE2_FLAGS = 2,  // a peer never announced its reduced shard
+};
+
+enum { BCOM_MODE_ALL_REDUCE = 0, BCOM_MODE_REDUCE_SCATTER = 1, BCOM_MODE_ALL_GATHER = 2 };
+
+// One collective on one rank.  For all modes S is the shard length and the logical
+// full tensor has n <= world * S elements:
+//   all-reduce      in/out: [n]            res1: [world*S] or null   res2: [S] or null
+//   reduce-scatter  in: [world*S] out: [S] res1: [world*S] or null
+//   all-gather      in: [S] out: [world*S] res2: [S] or null
+typedef struct {
+  const void* in;
+  void* out;
+  float* res1;
+  float* res2;
+  long long n;
+  long long S;
+  int dtype;       // 0 fp32, 1 fp16, 2 bf16
+  int bits;        // 1, 2, 4, 8
+  int block;       // 8 * power of two, <= 256
+  int mode;        // BCOM_MODE_*
+  int stochastic;  // 0 nearest, 1 stochastic rounding
+  unsigned int key1;  // stage-1 random key
+  unsigned int key2;  // stage-2 random key
+  float post_scale;   // applied to the result after the cast to dtype
+  int max_ctas;       // 0 = library default
+  int reserved;
+} BcomCollArgs;
+
+int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out);
+int bcom_comm_destroy(BcomComm* comm);
+// 64-byte CUDA IPC handle of this rank's block
+int bcom_comm_ipc_handle(BcomComm* comm, void* handle_out);
+// handles: world * 64 bytes, in rank order (own entry ignored)
+int bcom_comm_open_peers(BcomComm* comm, const void* handles);
+// wire a peer by address (same-process emulation, or memory mapped by other means)
+int bcom_comm_set_peer(BcomComm* comm, int peer, void* base);
+void* bcom_comm_local_base(BcomComm* comm);
+size_t bcom_comm_region_bytes(BcomComm* comm);
+// largest shard chunk (elements) one launch can carry for this codec setting
+long long bcom_comm_max_chunk(BcomComm* comm, int bits, int block);
+// copies the 8-word status record; status[0] != 0 means the last kernels gave up
+int bcom_comm_status(BcomComm* comm, unsigned int out[8]);
+// clears status, flags stay; zeroes the local arrival counters (after an error)
+int bcom_comm_reset(BcomComm* comm, void* stream);
+int bcom_comm_set_timeout_ms(BcomComm* comm, double ms);
+unsigned long long bcom_comm_epoch(BcomComm* comm);
+
+// Launch the fused kernel(s) for one collective on this rank (one launch per chunk).
+int bcom_collective(BcomComm* comm, const BcomCollArgs* args, void* stream);
+// All ranks of a same-device emulation in one cooperative launch per chunk.
+int bcom_collective_emulated(BcomComm** comms, const BcomCollArgs* args, int world,
+                             void* stream);
+// 1 if (dtype, bits, block) is covered by the fused kernel
+int bcom_collective_supported(int dtype, int bits, int block);
+
+#ifdef __cplusplus
+}
+#endif

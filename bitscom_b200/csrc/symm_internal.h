@@ -1,0 +1,30 @@
+// Internal layout shared by symm.cu (host runtime) and fused_collectives.cu (kernels).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "symm.h"
+
+struct BcomComm {
+  int rank;
+  int world;
+  int device;
+  size_t region_bytes;      // bytes of each of the two data regions
+  size_t total_bytes;
+  unsigned char* local;     // this rank's block
+  unsigned char* peer[BCOM_MAX_WORLD];
+  bool opened[BCOM_MAX_WORLD];  // peer mapping came from cudaIpcOpenMemHandle
+  unsigned int* status_host;    // pinned, mapped
+  unsigned int* status_dev;
+  unsigned long long epoch;     // collective launches so far (same on every rank)
+  unsigned long long timeout_ns;
+  int sm_count;
+};
+
+// control page layout (byte offsets inside the block)
+#define BCOM_CTL_FLAG1 0      // u64[BCOM_MAX_WORLD]: peer p finished pushing phase-1 data
+#define BCOM_CTL_FLAG2 128    // u64[BCOM_MAX_WORLD]: peer p finished pushing phase-2 data
+#define BCOM_CTL_ARRIVE1 256  // u32: CTAs of this rank that finished phase 1
+#define BCOM_CTL_ARRIVE2 264  // u32: CTAs of this rank that finished phase 2
+
+static inline size_t bcom_align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }

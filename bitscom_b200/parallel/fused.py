@@ -1,0 +1,376 @@
+"""Fused low-bit collectives over symmetric memory (Python side).
+
+``FusedLowBitComm`` owns one native communicator (``csrc/symm.cu``): a block of device
+memory per rank with receive and gather regions, mapped into every peer through CUDA
+IPC, plus the flag/arrival words the fused sm_100a kernel synchronises on
+(``csrc/fused_collectives.cu``).  ``all_reduce`` / ``reduce_scatter`` / ``all_gather``
+enqueue ONE kernel per bucket chunk on the current stream; nothing else touches the
+wire.  It replaces the reference's chain of pack kernels and NCCL send/recv groups
+(``cpp/src/process_group_lowbit.cc:641-1293``).
+
+``EmulatedWorld`` wires W communicators on ONE device and plays all ranks in a single
+cooperative launch, which lets the whole protocol be tested on one GPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import socket
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _native
+from ..ops._native import DTYPE_CODE, NativeError, check, ptr
+from ..quantization import sr_key
+from ..utils import timing as _timing
+
+MODE_ALL_REDUCE, MODE_REDUCE_SCATTER, MODE_ALL_GATHER = 0, 1, 2
+FUSED_BITS = (1, 2, 4, 8)
+
+_STATUS_TEXT = {
+    1: "a peer never announced its packed shards (phase-1 flags)",
+    2: "a peer never announced its reduced shard (phase-2 flags)",
+}
+
+
+class CollArgs(ctypes.Structure):
+    _fields_ = [
+        ("inp", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("res1", ctypes.c_void_p), ("res2", ctypes.c_void_p),
+        ("n", ctypes.c_longlong), ("S", ctypes.c_longlong),
+        ("dtype", ctypes.c_int), ("bits", ctypes.c_int), ("block", ctypes.c_int),
+        ("mode", ctypes.c_int), ("stochastic", ctypes.c_int),
+        ("key1", ctypes.c_uint), ("key2", ctypes.c_uint),
+        ("post_scale", ctypes.c_float), ("max_ctas", ctypes.c_int),
+        ("reserved", ctypes.c_int),
+    ]
+
+
+_lib = None
+
+
+def _get():
+    global _lib
+    if _lib is None:
+        lib = _native.load("bcom_comm")
+        if lib is not None:
+            vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+            lib.bcom_comm_create.argtypes = [ci, ci, ctypes.c_size_t, ctypes.POINTER(vp)]
+            lib.bcom_comm_destroy.argtypes = [vp]
+            lib.bcom_comm_ipc_handle.argtypes = [vp, vp]
+            lib.bcom_comm_open_peers.argtypes = [vp, vp]
+            lib.bcom_comm_set_peer.argtypes = [vp, ci, vp]
+            lib.bcom_comm_local_base.argtypes = [vp]
+            lib.bcom_comm_local_base.restype = vp
+            lib.bcom_comm_region_bytes.argtypes = [vp]
+            lib.bcom_comm_region_bytes.restype = ctypes.c_size_t
+            lib.bcom_comm_max_chunk.argtypes = [vp, ci, ci]
+            lib.bcom_comm_max_chunk.restype = ll
+            lib.bcom_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint * 8)]
+            lib.bcom_comm_reset.argtypes = [vp, vp]
+            lib.bcom_comm_set_timeout_ms.argtypes = [vp, ctypes.c_double]
+            lib.bcom_comm_epoch.argtypes = [vp]
+            lib.bcom_comm_epoch.restype = ctypes.c_ulonglong
+            lib.bcom_collective.argtypes = [vp, ctypes.POINTER(CollArgs), vp]
+            lib.bcom_collective_emulated.argtypes = [
+                ctypes.POINTER(vp), ctypes.POINTER(CollArgs), ci, vp]
+            lib.bcom_collective_supported.argtypes = [ci, ci, ci]
+        _lib = lib if lib is not None else False
+    return _lib or None
+
+
+def available() -> bool:
+    return _native.cuda_present() and _get() is not None
+
+
+def default_region_bytes() -> int:
+    return int(float(os.environ.get("BITSCOM_SYMM_MB", "64")) * (1 << 20))
+
+
+def default_timeout_ms() -> float:
+    return float(os.environ.get("BITSCOM_TIMEOUT_MS", "30000"))
+
+
+class FusedCollectiveError(RuntimeError):
+    pass
+
+
+def _keys(stochastic: bool, seed: Optional[int]):
+    if not stochastic:
+        return 0, 0
+    if seed is None:
+        from ..ops.codec import fresh_seed
+
+        seed = fresh_seed()
+    return sr_key(seed, 0), sr_key(seed, 1)
+
+
+def _args(inp, out, res1, res2, n, S, dtype, bits, block, mode, stochastic, seed,
+          post_scale, max_ctas) -> CollArgs:
+    k1, k2 = _keys(stochastic, seed)
+    return CollArgs(
+        inp=inp.data_ptr(), out=out.data_ptr(),
+        res1=0 if res1 is None else res1.data_ptr(),
+        res2=0 if res2 is None else res2.data_ptr(),
+        n=int(n), S=int(S), dtype=DTYPE_CODE[dtype], bits=int(bits), block=int(block),
+        mode=mode, stochastic=int(bool(stochastic)), key1=k1, key2=k2,
+        post_scale=float(post_scale), max_ctas=int(max_ctas), reserved=0)
+
+
+class _NativeComm:
+    """Owner of one ``BcomComm*``."""
+
+    def __init__(self, rank: int, world: int, region_bytes: int, device: torch.device):
+        self.lib = _get()
+        if self.lib is None:
+            raise NativeError("fused collectives need the bcom_comm library and a GPU")
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            check(self.lib.bcom_comm_create(rank, world, region_bytes, ctypes.byref(handle)),
+                  "bcom_comm_create")
+        self.handle = handle
+
+    def ipc_handle(self) -> bytes:
+        buf = ctypes.create_string_buffer(64)
+        check(self.lib.bcom_comm_ipc_handle(self.handle, buf), "cudaIpcGetMemHandle")
+        return buf.raw
+
+    def open_peers(self, handles: List[bytes]) -> None:
+        blob = ctypes.create_string_buffer(b"".join(handles), 64 * self.world)
+        with torch.cuda.device(self.device):
+            check(self.lib.bcom_comm_open_peers(self.handle, blob), "cudaIpcOpenMemHandle")
+
+    def status(self) -> List[int]:
+        out = (ctypes.c_uint * 8)()
+        self.lib.bcom_comm_status(self.handle, ctypes.byref(out))
+        return list(out)
+
+    def reset(self) -> None:
+        with torch.cuda.device(self.device):
+            check(self.lib.bcom_comm_reset(
+                self.handle, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)),
+                "bcom_comm_reset")
+
+    def close(self) -> None:
+        if self.handle:
+            self.lib.bcom_comm_destroy(self.handle)
+            self.handle = None
+
+
+def _describe(status: List[int]) -> str:
+    code = status[0]
+    seen = status[4] | (status[5] << 32)
+    want = status[6] | (status[7] << 32)
+    return (f"fused low-bit collective gave up: {_STATUS_TEXT.get(code, f'code {code}')}; "
+            f"rank {status[3]} waited on peer {status[2]}, saw epoch {seen}, wanted {want}")
+
+
+class FusedLowBitComm:
+    """Fused collectives for one process group on one device."""
+
+    _cache: Dict[tuple, "FusedLowBitComm"] = {}
+
+    def __init__(self, group, device: torch.device, region_bytes: Optional[int] = None,
+                 timeout_ms: Optional[float] = None):
+        self.group = group
+        self.device = torch.device(device)
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > 16:
+            raise NativeError("fused collectives support at most 16 ranks")
+        hosts: List[Optional[str]] = [None] * self.world
+        dist.all_gather_object(hosts, socket.gethostname(), group=group)
+        if len(set(hosts)) != 1:
+            raise NativeError("fused collectives need all ranks on one NVSwitch domain")
+        self.native = _NativeComm(self.rank, self.world,
+                                  region_bytes or default_region_bytes(), self.device)
+        handles: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(handles, self.native.ipc_handle(), group=group)
+        self.native.open_peers(handles)
+        self.native.lib.bcom_comm_set_timeout_ms(self.native.handle,
+                                                 timeout_ms or default_timeout_ms())
+        self.side_stream = torch.cuda.Stream(device=self.device)
+        self.max_ctas = int(os.environ.get("BITSCOM_MAX_CTAS", "0"))
+        self.launches = 0
+        # every rank has mapped every peer before anybody launches
+        dist.barrier(group=group, device_ids=[self.device.index]
+                     if dist.get_backend(group) == "nccl" else None)
+
+    @classmethod
+    def for_group(cls, group, device) -> "FusedLowBitComm":
+        key = (id(group), torch.device(device).index)
+        comm = cls._cache.get(key)
+        if comm is None:
+            comm = cls._cache[key] = cls(group, device)
+        return comm
+
+    @classmethod
+    def drop_cache(cls) -> None:
+        for comm in cls._cache.values():
+            comm.native.close()
+        cls._cache.clear()
+
+    # -- capabilities / status --------------------------------------------------------
+    def supports(self, dtype: torch.dtype, bitwidth: int, block_size: int) -> bool:
+        return dtype in DTYPE_CODE and bool(self.native.lib.bcom_collective_supported(
+            DTYPE_CODE[dtype], int(bitwidth), int(block_size)))
+
+    def check_status(self) -> None:
+        """Raise if a kernel of this communicator gave up waiting; re-arm afterwards."""
+        status = self.native.status()
+        if status[0] != 0:
+            self.native.reset()
+            _timing.add("fused_timeouts")
+            raise FusedCollectiveError(_describe(status))
+
+    def set_timeout_ms(self, ms: float) -> None:
+        self.native.lib.bcom_comm_set_timeout_ms(self.native.handle, float(ms))
+
+    # -- launch -------------------------------------------------------------------------
+    def _launch(self, args: CollArgs, async_op: bool, keep):
+        from ..api import _CudaEventWork
+
+        self.check_status()
+        cur = torch.cuda.current_stream(self.device)
+        stream = cur
+        if async_op:
+            stream = self.side_stream
+            stream.wait_stream(cur)
+        with torch.cuda.device(self.device):
+            check(self.native.lib.bcom_collective(
+                self.native.handle, ctypes.byref(args), ctypes.c_void_p(stream.cuda_stream)),
+                "bcom_collective")
+        self.launches += 1
+        _timing.add("fused_launches")
+        if not async_op:
+            return None
+        done = torch.cuda.Event()
+        done.record(stream)
+        for t in keep:
+            if t is not None:
+                t.record_stream(stream)
+        return _CudaEventWork(done, keepalive=list(keep), on_complete=self.check_status)
+
+    def all_reduce(self, tensor: torch.Tensor, *, bitwidth: int, block_size: int,
+                   stochastic: bool = False, seed: Optional[int] = None, ef=None,
+                   stage2: bool = False, post_scale: float = 1.0, async_op: bool = False):
+        """In-place low-bit sum of a contiguous CUDA tensor over the group."""
+        from ..api import ShardPlan
+
+        n = int(tensor.numel())
+        if n == 0:
+            return None
+        plan = ShardPlan(self.world, n)
+        res1 = res2 = None
+        if ef is not None:
+            ef.ensure(plan, tensor.device, stage2)
+            res1, res2 = ef.stage1, (ef.stage2 if stage2 else None)
+        args = _args(tensor, tensor, res1, res2, n, plan.shard_len, tensor.dtype, bitwidth,
+                     block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, self.max_ctas)
+        _timing.add("fused_allreduce_elems", n)
+        return self._launch(args, async_op, (tensor, res1, res2))
+
+    def reduce_scatter(self, output: torch.Tensor, input: torch.Tensor, *, bitwidth: int,
+                       block_size: int, stochastic: bool = False, seed: Optional[int] = None,
+                       ef=None, post_scale: float = 1.0, async_op: bool = False):
+        """``output[S] = sum over ranks of dequant(quant(input[rank*S:(rank+1)*S]))``."""
+        from ..api import ShardPlan
+
+        S = int(output.numel())
+        if int(input.numel()) != S * self.world or input.dtype != output.dtype:
+            raise ValueError("reduce_scatter needs input [world*S] and output [S] of one dtype")
+        res1 = None
+        if ef is not None:
+            ef.ensure(ShardPlan(self.world, S * self.world), input.device, False)
+            res1 = ef.stage1
+        args = _args(input, output, res1, None, S * self.world, S, input.dtype, bitwidth,
+                     block_size, MODE_REDUCE_SCATTER, stochastic, seed, post_scale,
+                     self.max_ctas)
+        return self._launch(args, async_op, (input, output, res1))
+
+    def all_gather(self, output: torch.Tensor, input: torch.Tensor, *, bitwidth: int,
+                   block_size: int, stochastic: bool = False, seed: Optional[int] = None,
+                   ef=None, post_scale: float = 1.0, async_op: bool = False):
+        """``output[j*S:(j+1)*S] = dequant(quant(rank j's input[S]))`` on every rank."""
+        S = int(input.numel())
+        if int(output.numel()) != S * self.world or input.dtype != output.dtype:
+            raise ValueError("all_gather needs input [S] and output [world*S] of one dtype")
+        res2 = None
+        if ef is not None:
+            if ef.stage2 is None or ef.stage2.numel() != S:
+                ef.stage2 = torch.zeros(S, dtype=torch.float32, device=input.device)
+            res2 = ef.stage2
+        args = _args(input, output, None, res2, S * self.world, S, input.dtype, bitwidth,
+                     block_size, MODE_ALL_GATHER, stochastic, seed, post_scale, self.max_ctas)
+        return self._launch(args, async_op, (input, output, res2))
+
+
+class EmulatedWorld:
+    """W ranks on one device, run by one cooperative kernel launch per chunk."""
+
+    def __init__(self, world: int, device="cuda:0", region_bytes: int = 8 << 20,
+                 timeout_ms: float = 2000.0):
+        self.world = world
+        self.device = torch.device(device)
+        self.comms = [_NativeComm(r, world, region_bytes, self.device) for r in range(world)]
+        lib = self.comms[0].lib
+        for a in self.comms:
+            for b in self.comms:
+                if a is not b:
+                    lib.bcom_comm_set_peer(a.handle, b.rank, lib.bcom_comm_local_base(b.handle))
+            lib.bcom_comm_set_timeout_ms(a.handle, float(timeout_ms))
+        self.lib = lib
+
+    def close(self):
+        for c in self.comms:
+            c.close()
+
+    def status(self) -> List[List[int]]:
+        return [c.status() for c in self.comms]
+
+    def reset(self):
+        for c in self.comms:
+            c.reset()
+
+    def max_chunk(self, bits: int, block: int) -> int:
+        return int(self.lib.bcom_comm_max_chunk(self.comms[0].handle, bits, block))
+
+    def _run(self, arg_list: List[CollArgs]) -> None:
+        handles = (ctypes.c_void_p * self.world)(*[c.handle for c in self.comms])
+        args = (CollArgs * self.world)(*arg_list)
+        with torch.cuda.device(self.device):
+            check(self.lib.bcom_collective_emulated(
+                handles, args, self.world,
+                ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)),
+                "bcom_collective_emulated")
+
+    def all_reduce(self, tensors: List[torch.Tensor], *, bitwidth: int, block_size: int,
+                   stochastic: bool = False, seed: Optional[int] = None,
+                   res1: Optional[List[torch.Tensor]] = None,
+                   res2: Optional[List[torch.Tensor]] = None, post_scale: float = 1.0):
+        n = int(tensors[0].numel())
+        S = -(-n // self.world)
+        self._run([
+            _args(t, t, res1[r] if res1 else None, res2[r] if res2 else None, n, S, t.dtype,
+                  bitwidth, block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, 0)
+            for r, t in enumerate(tensors)])
+
+    def reduce_scatter(self, outputs, inputs, *, bitwidth, block_size, stochastic=False,
+                       seed=None, res1=None):
+        S = int(outputs[0].numel())
+        self._run([
+            _args(i, o, res1[r] if res1 else None, None, S * self.world, S, i.dtype, bitwidth,
+                  block_size, MODE_REDUCE_SCATTER, stochastic, seed, 1.0, 0)
+            for r, (i, o) in enumerate(zip(inputs, outputs))])
+
+    def all_gather(self, outputs, inputs, *, bitwidth, block_size, stochastic=False, seed=None,
+                   res2=None):
+        S = int(inputs[0].numel())
+        self._run([
+            _args(i, o, None, res2[r] if res2 else None, S * self.world, S, i.dtype, bitwidth,
+                  block_size, MODE_ALL_GATHER, stochastic, seed, 1.0, 0)
+            for r, (i, o) in enumerate(zip(inputs, outputs))])
