@@ -33,7 +33,7 @@ LIBRARIES: Dict[str, Dict[str, List[str]]] = {
     "bcom_codec": {"sources": ["codec_kernels.cu"], "deps": ["codec.cuh"], "flags": []},
     "bcom_comm": {"sources": ["fused_collectives.cu", "symm.cu"],
                   "deps": ["codec.cuh", "symm.h"], "flags": []},
-    "bcom_llama": {"sources": ["gemm_tcgen05.cu", "attention.cu", "elementwise.cu"],
+    "bcom_llama": {"sources": ["gemm_tcgen05.cu", "attention_tcgen05.cu", "elementwise.cu"],
                    "deps": ["tc_common.cuh"], "flags": []},
 }
 

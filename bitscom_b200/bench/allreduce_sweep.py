@@ -76,7 +76,7 @@ def main(argv=None):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     world = dist.get_world_size()
 
-    from bitscom_b200.api import ErrorFeedbackState
+    from bitscom_b200.api import ErrorFeedbackState, ShardPlan
     from bitscom_b200.parallel.fused import FusedLowBitComm
 
     comm = FusedLowBitComm.for_group(dist.group.WORLD, torch.device("cuda", local))
@@ -97,6 +97,9 @@ def main(argv=None):
                     "nccl_fp32eq_gbs": n * 4 / nccl_ms / 1e6}
             for bits in args.bits:
                 efs = [None if args.no_ef else ErrorFeedbackState() for _ in bufs]
+                for e in efs:  # residuals exist before anything is timed
+                    if e is not None:
+                        e.ensure(ShardPlan(world, n), bufs[0].device, True)
                 index = {b.data_ptr(): e for b, e in zip(bufs, efs)}
 
                 def run(t, bits=bits, index=index):

@@ -1,0 +1,136 @@
+"""Small single-GPU workloads for profiling one kernel at a time (ncu-sized).
+
+    python -m bitscom_b200.bench.kernel_profile fused   --elems 33554432 --bits 4 --world 2
+    python -m bitscom_b200.bench.kernel_profile codec   --elems 67108864 --bits 4
+    python -m bitscom_b200.bench.kernel_profile gemm    --m 4096 --n 4096 --k 4096
+
+Each case warms up, then times a few launches with CUDA events (inputs larger than L2,
+or rotated so that L2 does not hold them) and prints one JSON line with the achieved
+bandwidth / throughput and its fraction of the measured peaks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(
+        os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+def _timed(fn, iters):
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    for i in range(iters):
+        fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def fused(args):
+    from bitscom_b200.parallel import fused as F
+
+    hbm, _, tag = _peaks()
+    W, n = args.world, args.elems
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    world = F.EmulatedWorld(W, "cuda:0", region_bytes=args.region_mb << 20)
+    S = -(-n // W)
+    bufs = [(torch.randn(n, device="cuda") * 1e-3).to(dtype) for _ in range(W)]
+    ef = not args.no_ef
+    res1 = [torch.zeros(S * W, device="cuda") for _ in range(W)] if ef else None
+    res2 = [torch.zeros(S, device="cuda") for _ in range(W)] if ef else None
+
+    def run(i):
+        world.all_reduce(bufs, bitwidth=args.bits, block_size=256, stochastic=not args.nearest,
+                         seed=i, res1=res1, res2=res2)
+
+    for i in range(args.warmup):
+        run(i)
+    ms = _timed(run, args.iters)
+    assert all(s[0] == 0 for s in world.status())
+    esize = 4 if dtype == torch.float32 else 2
+    pk = args.bits / 8 + 2 / 256
+    per_rank = n * (esize + (8 if ef else 0) + pk) + W * S * pk * 2 + (S * 8 if ef else 0) \
+        + n * (pk + esize)
+    total = per_rank * W  # all emulated ranks share one GPU's HBM
+    print(json.dumps({"case": "fused_allreduce_emulated", "world": W, "elems": n,
+                      "dtype": args.dtype, "bits": args.bits, "ef": ef, "ms": ms,
+                      "hbm_bytes": total, "gbs": total / ms / 1e6,
+                      "frac_hbm": total / ms / 1e6 / hbm, "peaks": tag}))
+    world.close()
+
+
+def codec(args):
+    from bitscom_b200.ops import codec as C
+
+    hbm, _, tag = _peaks()
+    n = args.elems
+    x = torch.randn(n, device="cuda") * 1e-3
+    if args.dtype == "bf16":
+        x = x.to(torch.bfloat16)
+    p, s = C.blockwise_quantize_pack(x, args.bits, 256)
+    for _ in range(args.warmup):
+        C.blockwise_quantize_pack(x, args.bits, 256)
+    ms_q = _timed(lambda i: C.blockwise_quantize_pack(x, args.bits, 256), args.iters)
+    ms_d = _timed(lambda i: C.blockwise_unpack_dequantize(p, s, args.bits, n, 256, x.dtype),
+                  args.iters)
+    nbytes = n * x.element_size() + p.numel() + s.numel() * 2
+    print(json.dumps({"case": "codec", "elems": n, "dtype": args.dtype, "bits": args.bits,
+                      "quantize_ms": ms_q, "quantize_gbs": nbytes / ms_q / 1e6,
+                      "quantize_frac_hbm": nbytes / ms_q / 1e6 / hbm,
+                      "dequantize_ms": ms_d, "dequantize_gbs": nbytes / ms_d / 1e6,
+                      "dequantize_frac_hbm": nbytes / ms_d / 1e6 / hbm, "peaks": tag}))
+
+
+def gemm(args):
+    from bitscom_b200.ops import gemm as G
+
+    _, tflops, tag = _peaks()
+    M, N, K = args.m, args.n, args.k
+    copies = max(1, min(8, (256 << 20) // max(1, (M * K + N * K) * 2)))
+    As = [(torch.randn(M, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
+    Bs = [(torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
+    for i in range(args.warmup):
+        G.gemm(As[i % copies], Bs[i % copies])
+    ms = _timed(lambda i: G.gemm(As[i % copies], Bs[i % copies]), args.iters)
+    G.check_status()
+    ms_ref = _timed(lambda i: torch.matmul(As[i % copies], Bs[i % copies].t()), args.iters)
+    tf = 2 * M * N * K / ms / 1e9
+    print(json.dumps({"case": "gemm_tcgen05", "M": M, "N": N, "K": K, "ms": ms, "tflops": tf,
+                      "frac_bf16_peak": tf / tflops, "torch_matmul_ms": ms_ref,
+                      "torch_tflops": 2 * M * N * K / ms_ref / 1e9, "peaks": tag}))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["fused", "codec", "gemm"])
+    ap.add_argument("--elems", type=int, default=1 << 25)
+    ap.add_argument("--bits", type=int, default=4)
+    ap.add_argument("--world", type=int, default=2)
+    ap.add_argument("--dtype", default="fp32")
+    ap.add_argument("--region-mb", type=int, default=64)
+    ap.add_argument("--no-ef", action="store_true")
+    ap.add_argument("--nearest", action="store_true")
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+    {"fused": fused, "codec": codec, "gemm": gemm}[args.case](args)
+
+
+if __name__ == "__main__":
+    main()

@@ -26,6 +26,9 @@
 // record and returns instead of trapping.
 #include <cuda_runtime.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "codec.cuh"
 #include "symm_internal.h"
 
@@ -497,6 +500,22 @@ static int ctas_for(const BcomComm* c, const BcomCollArgs& a, long long L, int r
   return (int)want;
 }
 
+// resident CTAs per SM of a kernel, asked once per kernel
+static cudaError_t resident_ctas(const void* kernel, int* out) {
+  static std::mutex mu;
+  static std::unordered_map<const void*, int> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(kernel);
+  if (it != cache.end()) {
+    *out = it->second;
+    return cudaSuccess;
+  }
+  cudaError_t err =
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(out, kernel, kCollThreads, 0);
+  if (err == cudaSuccess) cache[kernel] = *out;
+  return err;
+}
+
 }  // namespace bcom
 
 using namespace bcom;
@@ -522,8 +541,7 @@ int bcom_collective(BcomComm* c, const BcomCollArgs* args, void* stream) {
   if (!pick_kernel(a.dtype, a.bits, a.stochastic != 0, is_aligned(a), &kernel, &unused))
     return (int)cudaErrorNotSupported;
   int resident = 0;
-  cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-      &resident, (const void*)kernel, kCollThreads, 0);
+  cudaError_t err = resident_ctas((const void*)kernel, &resident);
   if (err != cudaSuccess) return (int)err;
   if (resident < 1) return (int)cudaErrorLaunchOutOfResources;
   long long Lmax = max_chunk(c->region_bytes, c->world, a.bits, a.block);

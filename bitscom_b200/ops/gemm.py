@@ -1,0 +1,122 @@
+"""bf16 GEMM on tcgen05 tensor cores (``csrc/gemm_tcgen05.cu``) and the linear layer
+built from it.  ``torch.matmul`` (cuBLAS) is the library call this replaces; the
+reference trainer's model is plain ``nn.Linear``
+(``benchmarks/train_llama7b_dp_pp_lowbit.py:222-238``)."""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _native
+from ._native import NativeError, check, ptr, stream_ptr
+
+_lib = None
+
+
+def _get():
+    global _lib
+    if _lib is None:
+        lib = _native.load("bcom_llama")
+        if lib is not None:
+            vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+            lib.bcom_gemm_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ll, ll, ll, ci, ci, ci, ci,
+                                           ci, vp]
+            lib.bcom_gemm_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
+        _lib = lib if lib is not None else False
+    return _lib or None
+
+
+def available() -> bool:
+    return _native.cuda_present() and _get() is not None
+
+
+_STATUS = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "accumulator hand-off"}
+
+
+def check_status(clear: bool = True) -> None:
+    """Raise if a GEMM kernel gave up on one of its bounded waits (synchronises)."""
+    out = (ctypes.c_uint * 4)()
+    check(_get().bcom_gemm_status(ctypes.byref(out), int(clear)), "bcom_gemm_status")
+    if out[0]:
+        raise NativeError(f"tcgen05 GEMM timed out in the {_STATUS.get(out[0], out[0])} "
+                          f"(cta {out[1]}, thread {out[2]})")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
+         b_mn_major: bool = False, out: Optional[torch.Tensor] = None,
+         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
+         max_ctas: int = 0) -> torch.Tensor:
+    """``C[M, N] (+)= A x B`` with bf16 operands and fp32 accumulation.
+
+    ``a``: ``[M, K]`` (K-major) or, with ``a_mn_major``, stored ``[K, M]``.
+    ``b``: ``[N, K]`` (K-major) or, with ``b_mn_major``, stored ``[K, N]``.
+    Operands are 2-D with unit stride in the last dimension; row strides are free.
+    """
+    lib = _get()
+    if lib is None:
+        raise NativeError("tcgen05 GEMM needs the bcom_llama library and a GPU")
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm expects bf16 operands")
+    if a.dim() != 2 or b.dim() != 2 or a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("gemm expects 2-D operands with a contiguous last dimension")
+    K, M = (a.shape[0], a.shape[1]) if a_mn_major else (a.shape[1], a.shape[0])
+    Kb, N = (b.shape[0], b.shape[1]) if b_mn_major else (b.shape[1], b.shape[0])
+    if K != Kb:
+        raise ValueError(f"reduction dimensions differ: {K} vs {Kb}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs an output tensor")
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16,
+                                                                      torch.float32):
+        raise ValueError("bad output tensor")
+    with torch.cuda.device(a.device):
+        check(lib.bcom_gemm_bf16(
+            ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32),
+            int(accumulate), int(max_ctas), stream_ptr(a.device)), "bcom_gemm_bf16")
+    return out
+
+
+class LinearFunction(torch.autograd.Function):
+    """``y = x W^T`` for ``x [tokens, in]`` and ``W [out, in]``, all three GEMMs on tcgen05.
+
+    The weight gradient is accumulated in fp32 into ``weight.main_grad`` when the
+    parameter has that attribute (gradient accumulation over micro-batches and the flat
+    fp32 bucket the low-bit all-reduce works on); otherwise it is returned in bf16.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dx[T, in] = dy[T, out] x W[out, in]: B is stored [K=out, N=in]
+            dx = gemm(dy2, weight, b_mn_major=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            # dW[out, in] = dy^T x: both operands stored [K=T, *]
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=main, accumulate=True)
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_mn_major=True, b_mn_major=True)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    return LinearFunction.apply(x, weight)

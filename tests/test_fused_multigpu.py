@@ -58,7 +58,7 @@ def _worker(rank, world, n, bits, dtype, iters):
     dense = full.float().clone()
     dist.all_reduce(dense)
     rel = (back.float() - dense).norm() / dense.norm()
-    assert rel < 0.5, rel
+    assert rel < {2: 2.5, 4: 0.5}[bits], rel
 
 
 @pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
