@@ -40,7 +40,8 @@ __device__ __forceinline__ float sr_uniform(uint32_t key, uint32_t idx) {
   h ^= h >> 15;
   h *= 0x735A2D97u;
   h ^= h >> 15;
-  return (float)(h >> 8) * (1.0f / 16777216.0f);
+  // 23 random bits as the mantissa of a float in [1, 2): no int-to-float conversion
+  return __uint_as_float(0x3F800000u | (h >> 9)) - 1.0f;
 }
 
 // ---------------------------------------------------------------------------
@@ -148,24 +149,40 @@ __device__ __forceinline__ __half scale_from_absmax(float m) {
 // ---------------------------------------------------------------------------
 // quantize values with a given fp32(fp16 scale); returns signed codes in [qmin, qmax]
 // ---------------------------------------------------------------------------
+// The kernels are instruction-issue bound, not DRAM bound, so the inner loop avoids the
+// quarter-rate conversion unit entirely: floor / round-half-even / float->int / int->float
+// are done with the 2^23 "magic number" adds, which are exact for the code range.
+constexpr float kTwo23 = 8388608.0f;        // 2^23
+constexpr float kMagic = 12582912.0f;       // 1.5 * 2^23: (c + kMagic) holds int c in its mantissa
+constexpr int kMagicBits = 0x4B400000;
+
+// Quantizes one value. Returns the signed code; *cf receives the same code as a float
+// (never -0), which is what dequantization multiplies by the scale.
 template <int BITS, bool SR>
-__device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t idx) {
+__device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t idx, float* cf) {
   const float n = __fdiv_rn(fabsf(x), sf);
   float mag;
   if constexpr (SR) {
-    const float lo = floorf(n);
-    const float p = fminf(fmaxf(__fsub_rn(n, lo), 0.0f), 1.0f);
+    const float lo = __fsub_rn(__fadd_rd(n, kTwo23), kTwo23);  // floor(n) for 0 <= n < 2^23
+    const float p = __fsub_rn(n, lo);                          // in [0, 1) for finite n
     mag = sr_uniform(key, idx) < p ? __fadd_rn(lo, 1.0f) : lo;
   } else {
-    mag = rintf(n);
+    mag = __fsub_rn(__fadd_rn(n, kTwo23), kTwo23);             // round half to even
   }
   float s = mag;
-  if constexpr (BITS != 1) {
-    const float sign = (float)((x > 0.0f) - (x < 0.0f));
-    s = __fmul_rn(mag, sign);
-  }
-  const float c = fminf(fmaxf(s, (float)Range<BITS>::qmin), (float)Range<BITS>::qmax);
-  return (s != s) ? 0 : (int)c;  // NaN converts to 0, as on the host
+  if constexpr (BITS != 1)
+    s = __uint_as_float(__float_as_uint(mag) | (__float_as_uint(x) & 0x80000000u));
+  float c = fminf(fmaxf(s, (float)Range<BITS>::qmin), (float)Range<BITS>::qmax);
+  c = (s != s) ? 0.0f : c;  // NaN (0/0 when the fp16 scale underflows) converts to 0
+  const float t = __fadd_rn(c, kMagic);
+  *cf = __fsub_rn(t, kMagic);
+  return __float_as_int(t) - kMagicBits;
+}
+
+template <int BITS, bool SR>
+__device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t idx) {
+  float unused;
+  return quant1<BITS, SR>(x, sf, key, idx, &unused);
 }
 
 template <int BITS, bool SR>
@@ -173,6 +190,18 @@ __device__ __forceinline__ void quant8(const float (&x)[GROUP], float sf, uint32
                                        uint32_t idx0, int (&q)[GROUP]) {
 #pragma unroll
   for (int i = 0; i < GROUP; ++i) q[i] = quant1<BITS, SR>(x[i], sf, key, idx0 + i);
+}
+
+// Quantize + dequantize in one go: q gets the codes, d the dequantized values.
+template <int BITS, bool SR>
+__device__ __forceinline__ void quant8_dq(const float (&x)[GROUP], float sf, uint32_t key,
+                                          uint32_t idx0, int (&q)[GROUP], float (&d)[GROUP]) {
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    float cf;
+    q[i] = quant1<BITS, SR>(x[i], sf, key, idx0 + i, &cf);
+    d[i] = __fmul_rn(cf, sf);
+  }
 }
 
 __device__ __forceinline__ void dequant8(const int (&q)[GROUP], float sf, float (&y)[GROUP]) {
@@ -218,6 +247,22 @@ __device__ __forceinline__ void unpack8(const Packed8<BITS>& in, int (&q)[GROUP]
     } else {
       q[i] = (int)code + Range<BITS>::qmin;
     }
+  }
+}
+
+// Unpack straight to float code values (code + qmin) without an int-to-float conversion:
+// OR the code into the mantissa of 2^23 and subtract 2^23 - qmin.
+template <int BITS>
+__device__ __forceinline__ void unpack8f(const Packed8<BITS>& in, float (&v)[GROUP]) {
+  constexpr uint32_t mask = (1u << BITS) - 1u;
+  constexpr float bias = 8388608.0f - (float)Range<BITS>::qmin;
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    const int bit = i * BITS;
+    uint32_t code = in.w[bit >> 5] >> (bit & 31);
+    if ((bit & 31) + BITS > 32) code |= in.w[(bit >> 5) + 1] << (32 - (bit & 31));
+    code &= mask;
+    v[i] = __fsub_rn(__uint_as_float(0x4B000000u | code), bias);
   }
 }
 

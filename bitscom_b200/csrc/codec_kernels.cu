@@ -94,10 +94,10 @@ blockwise_unpack_dequantize_fast(const uint8_t* __restrict__ packed,
                                  : load_group_bytes<BITS>(packed, g,
                                                           (int)packed_nbytes(n - base, BITS));
     const float sf = __half2float(scales[g / lanes_per_block]);
-    int q[GROUP];
-    unpack8<BITS>(p, q);
     float y[GROUP];
-    dequant8(q, sf, y);
+    unpack8f<BITS>(p, y);
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) y[i] = __fmul_rn(y[i], sf);
     if (full) {
       store8_vec(out + base, y);
     } else {

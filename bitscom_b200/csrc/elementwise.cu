@@ -1,0 +1,519 @@
+// Bandwidth-bound kernels of the Llama / GPT-2 trainers (sm_100a): RMSNorm, RoPE,
+// SwiGLU, fused softmax cross-entropy, embedding, and a flat fused AdamW.  Every one
+// makes a single pass over its operands with 16-byte accesses and keeps row statistics
+// in registers / shared memory; the torch-eager equivalents (several kernels and
+// temporaries each) are the baseline they replace.  The reference trainer gets these
+// ops from torch (benchmarks/train_llama7b_dp_pp_lowbit.py:158-165,248).
+//
+// C linkage, raw pointers + stream, async, cudaError_t returned as int.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ew {
+
+typedef __nv_bfloat16 bf16;
+
+struct alignas(16) Bf8 {
+  bf16 v[8];
+};
+
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+  const Bf8 raw = *reinterpret_cast<const Bf8*>(p);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(raw.v[i]);
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
+  Bf8 raw;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) raw.v[i] = __float2bfloat16_rn(f[i]);
+  *reinterpret_cast<Bf8*>(p) = raw;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// block-wide sum for up to 1024 threads; every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* scratch /*[33]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < (blockDim.x + 31) / 32 ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < (blockDim.x + 31) / 32 ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w        (H % 8 == 0)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                   float* __restrict__ rstd_out, int rows, int H, float eps) {
+  __shared__ float scratch[33];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const bf16* xr = x + (size_t)row * H;
+    float ss = 0.0f;
+    for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+      float f[8];
+      load8(xr + c, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (threadIdx.x == 0) rstd_out[row] = rstd;
+    bf16* yr = y + (size_t)row * H;
+    for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+      float f[8], g[8];
+      load8(xr + c, f);
+      load8(w + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * g[i];
+      store8(yr + c, f);
+    }
+  }
+}
+
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw += sum_rows dy * x * rstd (fp32)
+// Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dw partial in registers
+// (thread t owns columns t*8 + k*blockDim*8), adding it to dw once at the end.
+template <int MAX_ITERS>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                   const bf16* __restrict__ w, const float* __restrict__ rstd,
+                   bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
+  __shared__ float scratch[33];
+  float acc[MAX_ITERS][8];
+#pragma unroll
+  for (int k = 0; k < MAX_ITERS; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[k][i] = 0.0f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const bf16* xr = x + (size_t)row * H;
+    const bf16* gr = dy + (size_t)row * H;
+    const float rs = rstd[row];
+    float dot = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (threadIdx.x + k * blockDim.x) * 8;
+      if (c < H) {
+        float fx[8], fg[8], fw[8];
+        load8(xr + c, fx);
+        load8(gr + c, fg);
+        load8(w + c, fw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          dot += fg[i] * fw[i] * fx[i];
+          acc[k][i] += fg[i] * fx[i] * rs;
+        }
+      }
+    }
+    dot = block_sum(dot, scratch);
+    const float coef = dot * rs * rs * rs / (float)H;
+    bf16* dr = dx + (size_t)row * H;
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (threadIdx.x + k * blockDim.x) * 8;
+      if (c < H) {
+        float fx[8], fg[8], fw[8];
+        load8(xr + c, fx);
+        load8(gr + c, fg);
+        load8(w + c, fw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) fx[i] = fg[i] * fw[i] * rs - fx[i] * coef;
+        store8(dr + c, fx);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < MAX_ITERS; ++k) {
+    const int c = (threadIdx.x + k * blockDim.x) * 8;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(dw + c + i, acc[k][i]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RoPE (rotate-half convention), in place on a [tokens, heads, head_dim] slice of a
+// wider row: element (t, h, d) sits at x[t * row_stride + h * head_dim + d].
+// cos/sin: [seq, head_dim/2] fp32; position of token t is t % seq.
+// sign = +1 forward, -1 backward (the transposed rotation).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rope_kernel(bf16* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+            long long tokens, int heads, int head_dim, long long row_stride, int seq, float sign) {
+  const int half = head_dim / 2;
+  const int vec_per_head = half / 8;
+  const long long total = tokens * heads * vec_per_head;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec_per_head);
+    const long long th = i / vec_per_head;
+    const int h = (int)(th % heads);
+    const long long t = th / heads;
+    const int pos = (int)(t % seq);
+    bf16* base = x + t * row_stride + (long long)h * head_dim + v * 8;
+    float a[8], b[8];
+    load8(base, a);
+    load8(base + half, b);
+    const float* c = cos_t + (size_t)pos * half + v * 8;
+    const float* s = sin_t + (size_t)pos * half + v * 8;
+    float ra[8], rb[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float cs = c[k], sn = s[k] * sign;
+      ra[k] = a[k] * cs - b[k] * sn;
+      rb[k] = b[k] * cs + a[k] * sn;
+    }
+    store8(base, ra);
+    store8(base + half, rb);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU on a fused [tokens, 2F] projection (gate | up): h = silu(gate) * up
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, long long tokens, int F) {
+  const int vec = F / 8;
+  const long long total = tokens * vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec;
+    const int c = (int)(i - t * vec) * 8;
+    float g[8], u[8];
+    load8(gu + t * 2 * F + c, g);
+    load8(gu + t * 2 * F + F + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.0f + __expf(-g[k])) * u[k];
+    store8(h + t * F + c, g);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dh,
+                  bf16* __restrict__ dgu, long long tokens, int F) {
+  const int vec = F / 8;
+  const long long total = tokens * vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec;
+    const int c = (int)(i - t * vec) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + t * 2 * F + c, g);
+    load8(gu + t * 2 * F + F + c, u);
+    load8(dh + t * F + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sg = 1.0f / (1.0f + __expf(-g[k]));
+      const float silu = g[k] * sg;
+      dg[k] = d[k] * u[k] * (sg + silu * (1.0f - sg));
+      du[k] = d[k] * silu;
+    }
+    store8(dgu + t * 2 * F + c, dg);
+    store8(dgu + t * 2 * F + F + c, du);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Fused softmax cross-entropy: one CTA per row of logits [rows, V] (V % 8 == 0).
+// loss_out[row] = logsumexp - logit[target] (0 for ignored rows); the logits are
+// overwritten in place by dlogits = (softmax - onehot) * grad_scale[0].
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+cross_entropy_kernel(bf16* __restrict__ logits, const long long* __restrict__ targets,
+                     float* __restrict__ loss_out, const float* __restrict__ grad_scale,
+                     int rows, int V, long long ignore_index) {
+  __shared__ float scratch[33];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    bf16* lr = logits + (size_t)row * V;
+    const long long tgt = targets[row];
+    float m = -INFINITY;
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+      float f[8];
+      load8(lr + c, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, f[i]);
+    }
+    m = block_max(m, scratch);
+    float s = 0.0f;
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+      float f[8];
+      load8(lr + c, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += __expf(f[i] - m);
+    }
+    s = block_sum(s, scratch);
+    const bool ignored = tgt == ignore_index || tgt < 0 || tgt >= V;
+    const float lse = m + logf(s);
+    if (threadIdx.x == 0)
+      loss_out[row] = ignored ? 0.0f : lse - __bfloat162float(lr[tgt]);
+    __syncthreads();  // the target logit is read before anybody overwrites it
+    const float scale = ignored ? 0.0f : grad_scale[0];
+    const float inv = 1.0f / s;
+    for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+      float f[8];
+      load8(lr + c, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float p = __expf(f[i] - m) * inv;
+        if (c + i == tgt) p -= 1.0f;
+        f[i] = p * scale;
+      }
+      store8(lr + c, f);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Embedding lookup and its gradient (fp32 accumulation with atomics)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ table,
+                     bf16* __restrict__ out, long long tokens, int H, int vocab) {
+  const int vec = H / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < tokens * vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec;
+    const int c = (int)(i - t * vec) * 8;
+    long long id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    *reinterpret_cast<Bf8*>(out + t * H + c) =
+        *reinterpret_cast<const Bf8*>(table + id * H + c);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+embedding_bwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ dout,
+                     float* __restrict__ dtable, long long tokens, int H, int vocab) {
+  const int vec = H / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < tokens * vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec;
+    const int c = (int)(i - t * vec) * 8;
+    const long long id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    float f[8];
+    load8(dout + t * H + c, f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) atomicAdd(dtable + id * H + c + k, f[k]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Flat fused AdamW over fp32 master weights; also refreshes the bf16 working copy and
+// (optionally) zeroes the gradient for the next step.  n % 4 == 0 buffers, 16-B aligned.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+adamw_kernel(float* __restrict__ master, bf16* __restrict__ param_bf16, float* __restrict__ grad,
+             float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq, long long n, float lr,
+             float beta1, float beta2, float eps, float weight_decay, float bias1, float bias2,
+             float grad_scale, int zero_grad) {
+  const long long vecs = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vecs;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 p = reinterpret_cast<float4*>(master)[i];
+    float4 g = reinterpret_cast<float4*>(grad)[i];
+    float4 m = reinterpret_cast<float4*>(exp_avg)[i];
+    float4 v = reinterpret_cast<float4*>(exp_avg_sq)[i];
+    float* pp = &p.x; float* gg = &g.x; float* mm = &m.x; float* vv = &v.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = gg[k] * grad_scale;
+      mm[k] = beta1 * mm[k] + (1.0f - beta1) * gk;
+      vv[k] = beta2 * vv[k] + (1.0f - beta2) * gk * gk;
+      const float mhat = mm[k] / bias1;
+      const float vhat = vv[k] / bias2;
+      pp[k] = pp[k] * (1.0f - lr * weight_decay) - lr * mhat / (sqrtf(vhat) + eps);
+    }
+    reinterpret_cast<float4*>(master)[i] = p;
+    reinterpret_cast<float4*>(exp_avg)[i] = m;
+    reinterpret_cast<float4*>(exp_avg_sq)[i] = v;
+    if (zero_grad) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (param_bf16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(p.z, p.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(param_bf16)[i] = packed;
+    }
+  }
+}
+
+// SGD with momentum over flat fp32 buffers (ResNet DDP trainer)
+__global__ void __launch_bounds__(256)
+sgd_momentum_kernel(float* __restrict__ param, float* __restrict__ grad, float* __restrict__ mom,
+                    long long n, float lr, float momentum, float weight_decay, float grad_scale,
+                    int zero_grad) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float g = grad[i] * grad_scale + weight_decay * param[i];
+    const float b = momentum * mom[i] + g;
+    mom[i] = b;
+    param[i] -= lr * b;
+    if (zero_grad) grad[i] = 0.0f;
+  }
+}
+
+static int grid_for(long long work, int threads) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long long g = (work + threads - 1) / threads;
+  const long long cap = (long long)sms * 8;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace ew
+
+using namespace ew;
+
+extern "C" {
+
+int bcom_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int rows, int H,
+                     float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8) return (int)cudaErrorInvalidValue;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  rmsnorm_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)x, (const bf16*)w, (bf16*)y, (float*)rstd, rows, H, eps);
+  return (int)cudaGetLastError();
+}
+
+int bcom_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
+                     void* dw_fp32, int rows, int H, void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8) return (int)cudaErrorInvalidValue;
+  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  const int iters = (H / 8 + 255) / 256;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (iters <= 1)
+    rmsnorm_bwd_kernel<1><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+                                                (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
+                                                rows, H);
+  else if (iters <= 2)
+    rmsnorm_bwd_kernel<2><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+                                                (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
+                                                rows, H);
+  else if (iters <= 4)
+    rmsnorm_bwd_kernel<4><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+                                                (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
+                                                rows, H);
+  else
+    return (int)cudaErrorInvalidValue;  // H up to 8192
+  return (int)cudaGetLastError();
+}
+
+int bcom_rope(void* x, const void* cos_t, const void* sin_t, long long tokens, int heads,
+              int head_dim, long long row_stride, int seq, int backward, void* stream) {
+  if (tokens <= 0) return 0;
+  if (head_dim % 16 || row_stride % 8) return (int)cudaErrorInvalidValue;
+  const long long total = tokens * heads * (head_dim / 16);
+  rope_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>(
+      (bf16*)x, (const float*)cos_t, (const float*)sin_t, tokens, heads, head_dim, row_stride,
+      seq, backward ? -1.0f : 1.0f);
+  return (int)cudaGetLastError();
+}
+
+int bcom_swiglu_fwd(const void* gate_up, void* h, long long tokens, int F, void* stream) {
+  if (tokens <= 0) return 0;
+  if (F % 8) return (int)cudaErrorInvalidValue;
+  swiglu_fwd_kernel<<<grid_for(tokens * (F / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)gate_up, (bf16*)h, tokens, F);
+  return (int)cudaGetLastError();
+}
+
+int bcom_swiglu_bwd(const void* gate_up, const void* dh, void* dgate_up, long long tokens, int F,
+                    void* stream) {
+  if (tokens <= 0) return 0;
+  if (F % 8) return (int)cudaErrorInvalidValue;
+  swiglu_bwd_kernel<<<grid_for(tokens * (F / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)gate_up, (const bf16*)dh, (bf16*)dgate_up, tokens, F);
+  return (int)cudaGetLastError();
+}
+
+int bcom_cross_entropy(void* logits, const void* targets, void* loss_out, const void* grad_scale,
+                       int rows, int V, long long ignore_index, void* stream) {
+  if (rows <= 0) return 0;
+  if (V % 8) return (int)cudaErrorInvalidValue;
+  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  cross_entropy_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
+      (bf16*)logits, (const long long*)targets, (float*)loss_out, (const float*)grad_scale, rows,
+      V, ignore_index);
+  return (int)cudaGetLastError();
+}
+
+int bcom_embedding_fwd(const void* ids, const void* table, void* out, long long tokens, int H,
+                       int vocab, void* stream) {
+  if (tokens <= 0) return 0;
+  if (H % 8) return (int)cudaErrorInvalidValue;
+  embedding_fwd_kernel<<<grid_for(tokens * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const long long*)ids, (const bf16*)table, (bf16*)out, tokens, H, vocab);
+  return (int)cudaGetLastError();
+}
+
+int bcom_embedding_bwd(const void* ids, const void* dout, void* dtable_fp32, long long tokens,
+                       int H, int vocab, void* stream) {
+  if (tokens <= 0) return 0;
+  if (H % 8) return (int)cudaErrorInvalidValue;
+  embedding_bwd_kernel<<<grid_for(tokens * (H / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const long long*)ids, (const bf16*)dout, (float*)dtable_fp32, tokens, H, vocab);
+  return (int)cudaGetLastError();
+}
+
+int bcom_adamw(void* master, void* param_bf16, void* grad, void* exp_avg, void* exp_avg_sq,
+               long long n, float lr, float beta1, float beta2, float eps, float weight_decay,
+               int step, float grad_scale, int zero_grad, void* stream) {
+  if (n <= 0) return 0;
+  if (n % 4) return (int)cudaErrorInvalidValue;
+  const float bias1 = 1.0f - powf(beta1, (float)step);
+  const float bias2 = 1.0f - powf(beta2, (float)step);
+  adamw_kernel<<<grid_for(n / 4, 256), 256, 0, (cudaStream_t)stream>>>(
+      (float*)master, (bf16*)param_bf16, (float*)grad, (float*)exp_avg, (float*)exp_avg_sq, n, lr,
+      beta1, beta2, eps, weight_decay, bias1, bias2, grad_scale, zero_grad);
+  return (int)cudaGetLastError();
+}
+
+int bcom_sgd_momentum(void* param, void* grad, void* mom, long long n, float lr, float momentum,
+                      float weight_decay, float grad_scale, int zero_grad, void* stream) {
+  if (n <= 0) return 0;
+  sgd_momentum_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      (float*)param, (float*)grad, (float*)mom, n, lr, momentum, weight_decay, grad_scale,
+      zero_grad);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -228,40 +228,40 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   // ---------------- phase 1: quantize every destination's shard and push it ----------
   if (p.mode != BCOM_MODE_ALL_GATHER) {
     const bool ef = p.res1 != nullptr;
-    const long long items = (long long)W * Gp;
-    for (long long it = first; it < items; it += nthreads) {
-      const int k = (int)(it / Gp);
-      const long long g = it - (long long)k * Gp;
+    for (int k = 0; k < W; ++k) {
       const int j = (p.rank + k) % W;  // ranks start on different destinations
-      const long long off = p.c0 + g * GROUP;
-      const long long idx = (long long)j * p.S + off;
-      const bool live = g < Gs;
-      long long lim = live ? min(shard_end - off, p.n - idx) : 0;
-      if (lim < 0) lim = 0;
-      float v[GROUP];
-      load_vals<T, ALIGNED>(in, idx, lim, v);
-      if (ef) {
-        float r[GROUP];
-        load_vals<float, ALIGNED>(p.res1, idx, lim, r);
+      unsigned char* slot = p.peer[j] + BCOM_CONTROL_BYTES + (size_t)p.rank * p.slot_stride;
+      const long long shard0 = (long long)j * p.S;
+      for (long long g = first; g < Gp; g += nthreads) {
+        const long long off = p.c0 + g * GROUP;
+        const long long idx = shard0 + off;
+        const bool live = g < Gs;
+        long long lim = live ? min(shard_end - off, p.n - idx) : 0;
+        if (lim < 0) lim = 0;
+        float v[GROUP];
+        load_vals<T, ALIGNED>(in, idx, lim, v);
+        if (ef) {
+          float r[GROUP];
+          load_vals<float, ALIGNED>(p.res1, idx, lim, r);
 #pragma unroll
-        for (int i = 0; i < GROUP; ++i) v[i] = __fadd_rn(v[i], r[i]);
-      }
-      const float m = block_absmax(absmax8(v), lanes);
-      const __half sh = scale_from_absmax<BITS>(m);
-      const float sf = __half2float(sh);
-      if (!live) continue;
-      int q[GROUP];
-      quant8<BITS, SR>(v, sf, p.key1, (uint32_t)idx, q);
-      if (ef) {
-        float d[GROUP];
-        dequant8(q, sf, d);
+          for (int i = 0; i < GROUP; ++i) v[i] = __fadd_rn(v[i], r[i]);
+        }
+        const float m = block_absmax(absmax8(v), lanes);
+        const __half sh = scale_from_absmax<BITS>(m);
+        const float sf = __half2float(sh);
+        if (!live) continue;
+        int q[GROUP];
+        if (ef) {
+          float d[GROUP];
+          quant8_dq<BITS, SR>(v, sf, p.key1, (uint32_t)idx, q, d);
 #pragma unroll
-        for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(v[i], d[i]);
-        store_vals<float, ALIGNED>(p.res1, idx, lim, d);
+          for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(v[i], d[i]);
+          store_vals<float, ALIGNED>(p.res1, idx, lim, d);
+        } else {
+          quant8<BITS, SR>(v, sf, p.key1, (uint32_t)idx, q);
+        }
+        push_group<BITS>(slot, p.scale_off, g, lanes, pack8<BITS>(q), sh);
       }
-      unsigned char* slot =
-          p.peer[j] + BCOM_CONTROL_BYTES + (size_t)p.rank * p.slot_stride;
-      push_group<BITS>(slot, p.scale_off, g, lanes, pack8<BITS>(q), sh);
     }
   }
   arrive_and_publish(p, ncta, BCOM_CTL_ARRIVE1, BCOM_CTL_ARRIVE2, BCOM_CTL_FLAG1);
@@ -284,10 +284,10 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
           const unsigned char* slot = recv_region + (size_t)src * p.slot_stride;
           const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
           const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
-          int q[GROUP];
-          unpack8<BITS>(pk, q);
+          float c[GROUP];
+          unpack8f<BITS>(pk, c);
 #pragma unroll
-          for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn((float)q[i], sf));
+          for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(c[i], sf));
         }
       }
       if (p.mode == BCOM_MODE_REDUCE_SCATTER) {
@@ -309,13 +309,15 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
       const float sf = __half2float(sh);
       if (!live) continue;
       int q[GROUP];
-      quant8<BITS, SR>(acc, sf, p.key2, (uint32_t)((long long)p.rank * p.S + off), q);
+      const uint32_t idx2 = (uint32_t)((long long)p.rank * p.S + off);
       if (ef2) {
         float d[GROUP];
-        dequant8(q, sf, d);
+        quant8_dq<BITS, SR>(acc, sf, p.key2, idx2, q, d);
 #pragma unroll
         for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(acc[i], d[i]);
         store_vals<float, ALIGNED>(p.res2, off, lim, d);
+      } else {
+        quant8<BITS, SR>(acc, sf, p.key2, idx2, q);
       }
       const Packed8<BITS> pk = pack8<BITS>(q);
       for (int k = 0; k < W; ++k) {
@@ -331,25 +333,21 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   if (p.mode == BCOM_MODE_REDUCE_SCATTER) return;
 
   // ---------------- phase 3: dequantize all shards into the bucket --------------------
-  {
-    const long long items = (long long)W * Gs;
-    for (long long it = first; it < items; it += nthreads) {
-      const int k = (int)(it / Gs);
-      const long long g = it - (long long)k * Gs;
-      const int j = (p.rank + k) % W;
+  for (int k = 0; k < W; ++k) {
+    const int j = (p.rank + k) % W;
+    const unsigned char* slot = gather_region + (size_t)j * p.slot_stride;
+    const long long shard0 = (long long)j * p.S;
+    for (long long g = first; g < Gs; g += nthreads) {
       const long long off = p.c0 + g * GROUP;
-      const long long idx = (long long)j * p.S + off;
+      const long long idx = shard0 + off;
       const long long lim = min(shard_end - off, p.n - idx);
       if (lim <= 0) continue;
-      const unsigned char* slot = gather_region + (size_t)j * p.slot_stride;
       const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
       const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
-      int q[GROUP];
-      unpack8<BITS>(pk, q);
       float y[GROUP];
+      unpack8f<BITS>(pk, y);
 #pragma unroll
-      for (int i = 0; i < GROUP; ++i)
-        y[i] = cast_roundtrip<T>(__fmul_rn((float)q[i], sf), p.post_scale);
+      for (int i = 0; i < GROUP; ++i) y[i] = cast_roundtrip<T>(__fmul_rn(y[i], sf), p.post_scale);
       store_vals<T, ALIGNED>(out, idx, lim, y);
     }
   }

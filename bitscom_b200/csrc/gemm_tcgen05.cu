@@ -344,20 +344,23 @@ int bcom_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
                    int accumulate, int max_ctas, void* stream) {
   using namespace gemm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8)) || (N % 8)) return (int)cudaErrorInvalidValue;
-  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15))
-    return (int)cudaErrorInvalidValue;
+  // argument errors get codes of their own (1001..1005) so that they cannot be mistaken
+  // for a CUDA error
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8)) || (N % 8)) return 1001;
+  if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return 1002;
+  (void)cudaGetLastError();  // do not inherit an error left behind by an earlier call
   CUtensorMap tmA, tmB;
-  bool ok = a_mn_major ? make_map(&tmA, A, K, M, lda, 64, BK) : make_map(&tmA, A, M, K, lda, BK, BM);
-  ok = ok && (b_mn_major ? make_map(&tmB, B, K, N, ldb, 64, BK) : make_map(&tmB, B, N, K, ldb, BK, BN));
-  if (!ok) return (int)cudaErrorInvalidValue;
+  if (!(a_mn_major ? make_map(&tmA, A, K, M, lda, 64, BK) : make_map(&tmA, A, M, K, lda, BK, BM)))
+    return 1003;
+  if (!(b_mn_major ? make_map(&tmB, B, K, N, ldb, 64, BK) : make_map(&tmB, B, N, K, ldb, BK, BN)))
+    return 1004;
   Kernel kernel = pick(a_mn_major != 0, b_mn_major != 0, out_fp32 != 0, accumulate != 0);
   static std::mutex mu;
   {
     std::lock_guard<std::mutex> lock(mu);
     cudaError_t err = cudaFuncSetAttribute((const void*)kernel,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (err != cudaSuccess) return (int)err;
+    if (err != cudaSuccess) return 1005;
   }
   Params p;
   p.C = C;

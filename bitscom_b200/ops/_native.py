@@ -46,6 +46,18 @@ def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_ARG_ERRORS = {
+    1001: "a leading dimension or N is not a multiple of 8 elements",
+    1002: "an operand is not 16-byte aligned",
+    1003: "the tensor map of A could not be encoded",
+    1004: "the tensor map of B could not be encoded",
+    1005: "the kernel's shared-memory attribute could not be set",
+}
+
+
 def check(code: int, what: str) -> None:
-    if code != 0:
-        raise NativeError(f"{what} failed with CUDA error {code}")
+    if code == 0:
+        return
+    if code in _ARG_ERRORS:
+        raise NativeError(f"{what}: {_ARG_ERRORS[code]}")
+    raise NativeError(f"{what} failed with CUDA error {code}")

@@ -93,8 +93,11 @@ class LinearFunction(torch.autograd.Function):
     def forward(ctx, x, weight):
         ctx.save_for_backward(x, weight)
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, weight)
-        return y.view(*x.shape[:-1], weight.shape[0])
+        # allocate with the final shape: the result must not be a view, later kernels
+        # (RoPE, cross-entropy) update it in place
+        y = torch.empty(*x.shape[:-1], weight.shape[0], dtype=x.dtype, device=x.device)
+        gemm(x2, weight, out=y.view(-1, weight.shape[0]))
+        return y
 
     @staticmethod
     def backward(ctx, dy):

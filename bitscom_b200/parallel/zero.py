@@ -1,0 +1,70 @@
+"""ZeRO-1 style sharded optimizer on low-bit collectives.
+
+Every rank keeps the whole bf16 model but only ``1/W`` of the fp32 master weights and
+optimizer moments.  One step is
+
+  low-bit reduce-scatter of the flat fp32 gradient  ->  each rank holds the summed
+      gradient of its shard (error feedback on the sender side),
+  fused AdamW on the shard,
+  low-bit all-gather of the updated shard into the flat parameter buffer (error
+      feedback on the owner side, so quantization error of the broadcast parameters is
+      carried to the next step instead of accumulating).
+
+The reference has only the low-bit reduce-scatter primitive in its C++ backend
+(``cpp/src/process_group_lowbit.cc:1670-1777``) and forwards all-gather to NCCL; sharded
+training on top of both is new here.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import nn as K
+from .flat import FlatParameters
+
+
+class ShardedAdamW:
+    def __init__(self, flat: FlatParameters, lowbit_group, *, lr=1e-4, betas=(0.9, 0.999),
+                 eps=1e-8, weight_decay=0.01, param_bits_group=None):
+        self.flat = flat
+        self.group = lowbit_group              # gradients: reduce-scatter
+        self.pgroup = param_bits_group or lowbit_group  # parameters: all-gather
+        self.world = lowbit_group.world_size
+        self.rank = lowbit_group.rank
+        n = flat.numel
+        if n % (self.world * 256):
+            raise ValueError("flat buffer must be padded to world * 256 elements")
+        self.shard = n // self.world
+        lo = self.rank * self.shard
+        dev = flat.params.device
+        self.master_shard = flat.params[lo:lo + self.shard].float().clone()
+        self.grad_shard = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+        self.opt = K.FlatAdamW(self.master_shard, self.grad_shard, None, lr=lr, betas=betas,
+                               eps=eps, weight_decay=weight_decay)
+        self.new_params = torch.empty(self.shard, dtype=torch.float32, device=dev)
+        self.gathered = torch.empty(n, dtype=torch.float32, device=dev)
+
+    def step(self) -> None:
+        flat = self.flat
+        if self.world > 1:
+            self.group.reduce_scatter_lowbit(self.grad_shard, flat.grads, ef_key="zero_grads")
+        else:
+            self.grad_shard.copy_(flat.grads)
+        self.opt.step(grad_scale=1.0 / self.world, zero_grad=True)
+        flat.grads.zero_()
+        if self.world > 1:
+            self.pgroup.all_gather_lowbit(self.gathered, self.master_shard,
+                                          ef_key="zero_params")
+            flat.params.copy_(self.gathered)
+        else:
+            flat.params.copy_(self.master_shard)
+
+    def state_dict(self):
+        return {"opt": self.opt.state_dict(), "master_shard": self.master_shard}
+
+    def load_state_dict(self, sd):
+        self.opt.load_state_dict(sd["opt"])
+        self.master_shard.copy_(sd["master_shard"])

@@ -1,0 +1,293 @@
+"""Llama DP x PP trainer (shape of the reference's
+``benchmarks/train_llama7b_dp_pp_lowbit.py``): a (dp, pp) mesh with pp the fast
+dimension, one pipeline stage per rank, AdamW, data-parallel gradient all-reduce through
+``LowBitGroup``.  Differences, all deliberate:
+
+* the model is this repo's own (``bitscom_b200.models.llama``), bf16 compute with fp32
+  master weights and fp32 gradient accumulation, on hand-written sm_100a kernels;
+* the schedule is 1F1B (``parallel.pp_schedule``), not GPipe;
+* gradients are synchronised per layer-sized slice of the flat gradient buffer with the
+  fused low-bit kernel on a side stream while the last micro-batch is still in backward,
+  with error feedback, instead of one exposed synchronous call per parameter;
+* data is synthetic (uniform token ids), staged in pinned host memory.
+
+Launch with torchrun (one process per GPU) or run single-process for one GPU:
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m bitscom_b200.trainer.llama_dp_pp --pp_size 2 --bitwidth 4 --max_steps 10
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..api import LowBitGroup
+from ..models.llama import LlamaConfig, LlamaStage
+from ..ops import nn as K
+from ..parallel.hooks import GradBucketSync
+from ..parallel.pp_schedule import PipelineRunner
+
+
+@dataclass
+class TrainerConfig:
+    pp_size: int = 1
+    micro_batches: int = 4
+    micro_batch_size: int = 1
+    seq_length: int = 2048
+    bitwidth: int = 4
+    block_size: int = 256
+    stochastic_rounding: bool = False
+    error_feedback: bool = True
+    stage2_error_feedback: bool = False
+    dp_sync: str = "pipeline_a"   # "pipeline_a" | "flat" | "dense"
+    local_size: int = 1           # ranks per local group of pipeline-A
+    overlap: bool = True
+    lr: float = 1e-4
+    weight_decay: float = 0.01
+    seed: int = 0
+
+
+def _init_distributed() -> Tuple[int, int, int]:
+    if "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        rank = int(os.environ["RANK"])
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        torch.cuda.set_device(local)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, dist.get_world_size(), local
+    torch.cuda.set_device(0)
+    return 0, 1, 0
+
+
+class LlamaTrainer:
+    def __init__(self, model_cfg: LlamaConfig, cfg: TrainerConfig):
+        self.cfg, self.model_cfg = cfg, model_cfg
+        self.rank, self.world, self.local = _init_distributed()
+        if self.world % cfg.pp_size:
+            raise RuntimeError(f"world_size {self.world} must be divisible by pp_size "
+                               f"{cfg.pp_size}")
+        self.pp, self.dp = cfg.pp_size, self.world // cfg.pp_size
+        self.pp_rank, self.dp_rank = self.rank % self.pp, self.rank // self.pp
+        self.device = torch.device("cuda", self.local)
+
+        # groups: every rank creates all of them in the same order
+        self.pp_group = self.dp_group = None
+        if self.world > 1:
+            for d in range(self.dp):
+                g = dist.new_group([d * self.pp + p for p in range(self.pp)])
+                if d == self.dp_rank:
+                    self.pp_group = g
+            for p in range(self.pp):
+                g = dist.new_group([d * self.pp + p for d in range(self.dp)])
+                if p == self.pp_rank:
+                    self.dp_group = g
+
+        self.model = LlamaStage(model_cfg, self.pp_rank, self.pp, self.device,
+                                seed=cfg.seed)
+        flat = self.model.flat
+        self.opt = K.FlatAdamW(flat.master, flat.grads, flat.params, lr=cfg.lr,
+                               weight_decay=cfg.weight_decay)
+        self.runner = PipelineRunner(
+            self.pp_rank, self.pp, self.pp_group,
+            prev_rank=self.rank - 1 if self.pp_rank > 0 else None,
+            next_rank=self.rank + 1 if self.pp_rank < self.pp - 1 else None,
+            act_shape=(cfg.micro_batch_size * cfg.seq_length, model_cfg.hidden_size),
+            device=self.device) if self.pp > 1 else None
+
+        self.sync: Optional[GradBucketSync] = None
+        if self.dp > 1:
+            self.lowbit = LowBitGroup(
+                bitwidth=cfg.bitwidth, process_group=self.dp_group,
+                block_size=cfg.block_size, stochastic_rounding=cfg.stochastic_rounding,
+                error_feedback=cfg.error_feedback,
+                stage2_error_feedback=cfg.stage2_error_feedback, sr_seed=cfg.seed + 17)
+            local_group = inter_group = None
+            mode = cfg.dp_sync
+            if mode == "pipeline_a":
+                local_group, inter_group = self._hierarchy(cfg.local_size)
+            self.sync = GradBucketSync(
+                self.lowbit, flat.grads, self._sync_ranges(), mode=mode,
+                local_group=local_group, inter_group=inter_group, overlap=cfg.overlap)
+        self.step_count = 0
+        self._pinned: Optional[torch.Tensor] = None
+
+    # -- topology helpers --------------------------------------------------------------
+    def _hierarchy(self, local_size: int):
+        """Local groups of ``local_size`` consecutive DP ranks and the group of their
+        leaders.  ``local_size == 1`` is the degenerate hierarchy the reference's own
+        pipeline-A test uses (``tests/test_pipeline_a_correctness.py:16-22``)."""
+        dp_ranks = [d * self.pp + self.pp_rank for d in range(self.dp)]
+        if local_size <= 1:
+            return None, None  # handled as flat low-bit over the whole DP group
+        local = inter = None
+        for p in range(self.pp):
+            ranks = [d * self.pp + p for d in range(self.dp)]
+            for i in range(0, self.dp, local_size):
+                g = dist.new_group(ranks[i:i + local_size])
+                if p == self.pp_rank and self.rank in ranks[i:i + local_size]:
+                    local = g
+            g = dist.new_group(ranks[::local_size])
+            if p == self.pp_rank:
+                inter = g
+        return local, inter
+
+    def _sync_ranges(self) -> List[Tuple[int, int]]:
+        """One slice per transformer layer (plus embedding / head), in the order backward
+        finishes them: last layer first."""
+        flat = self.model.flat
+        names = list(flat.offsets)
+        groups: List[Tuple[int, int]] = []
+        cur_key, start = None, 0
+        for name in names + [None]:
+            key = name.split(".")[0] if name is not None else None
+            off = flat.offsets[name][0] if name is not None else flat.numel
+            if cur_key is not None and key != cur_key:
+                groups.append((start, off - start))
+                start = off
+            cur_key = key
+        return list(reversed(groups))
+
+    # -- data ---------------------------------------------------------------------------
+    def synthetic_batch(self, step: int, pinned: bool = True) -> torch.Tensor:
+        """Uniform token ids ``[micro_batches, micro_batch_size, seq]`` for this DP rank."""
+        c = self.cfg
+        g = torch.Generator().manual_seed(1000003 * (step + 1) + self.dp_rank)
+        ids = torch.randint(1, self.model_cfg.vocab_size,
+                            (c.micro_batches, c.micro_batch_size, c.seq_length), generator=g)
+        return ids.pin_memory() if pinned else ids
+
+    # -- one optimizer step ---------------------------------------------------------------
+    def train_step(self, ids_host_or_dev: torch.Tensor) -> Optional[torch.Tensor]:
+        """``ids``: ``[micro_batches, micro_batch_size, seq]`` int64, pinned host or device.
+        Returns the mean loss as a device scalar on the last stage, else ``None``."""
+        c = self.cfg
+        ids = ids_host_or_dev.to(self.device, non_blocking=True)
+        model = self.model
+        scale = 1.0 / c.micro_batches
+        losses: List[torch.Tensor] = []
+
+        # hooks that fire when a layer's input gradient exists, i.e. the layer's weight
+        # gradients of the LAST micro-batch are complete
+        hook_state = {"armed": False}
+
+        def forward_fn(mb: int, x: Optional[torch.Tensor]):
+            if not model.is_first:
+                model.set_shape(c.micro_batch_size, c.seq_length)
+            inp = ids[mb] if model.is_first else x
+            tgt = ids[mb] if model.is_last else None
+            if model.is_last:
+                return model(inp, targets=tgt, ignore_index=0, loss_scale=scale)
+            return model(inp)
+
+        if self.runner is None:
+            for mb in range(c.micro_batches):
+                loss = forward_fn(mb, None)
+                losses.append(loss.detach())
+                loss.backward()
+        else:
+            losses = self.runner.run(c.micro_batches, forward_fn)
+
+        if self.sync is not None:
+            self.sync.finish()
+        self.opt.step(grad_scale=1.0, zero_grad=True)
+        self.step_count += 1
+        if model.is_last:
+            return torch.stack(losses).sum()
+        return None
+
+    # -- checkpoint -----------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        sd = {"step": self.step_count, "opt": self.opt.state_dict(),
+              "params": self.model.flat.params}
+        if self.sync is not None:
+            sd["lowbit"] = self.lowbit.state_dict()
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = int(sd["step"])
+        self.opt.load_state_dict(sd["opt"])
+        self.model.flat.params.copy_(sd["params"])
+        if self.sync is not None and "lowbit" in sd:
+            self.lowbit.load_state_dict(sd["lowbit"])
+
+    def tokens_per_step(self) -> int:
+        c = self.cfg
+        return self.dp * c.micro_batches * c.micro_batch_size * c.seq_length
+
+
+def smoke_step(device) -> None:
+    """One tiny forward + backward + optimizer step of the flagship model."""
+    cfg = LlamaConfig.tiny(attention=_default_attention())
+    model = LlamaStage(cfg, device=device, seed=1)
+    ids = torch.randint(1, cfg.vocab_size, (2, 128), device=device)
+    loss = model(ids, targets=ids)
+    loss.backward()
+    K.FlatAdamW(model.flat.master, model.flat.grads, model.flat.params, lr=1e-3).step()
+    torch.cuda.synchronize()
+    assert torch.isfinite(loss).item()
+
+
+def _default_attention() -> str:
+    try:
+        from ..ops import attention as A
+
+        return "tcgen05" if A.available() else "sdpa"
+    except Exception:
+        return "sdpa"
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--pp_size", type=int, default=1)
+    ap.add_argument("--micro_batches", type=int, default=4)
+    ap.add_argument("--batch_size", type=int, default=1, help="sequences per micro-batch")
+    ap.add_argument("--seq_length", type=int, default=2048)
+    ap.add_argument("--bitwidth", type=int, default=4)
+    ap.add_argument("--backend", default="lowbit", choices=["lowbit", "nccl"])
+    ap.add_argument("--stochastic_rounding", action="store_true")
+    ap.add_argument("--no_error_feedback", action="store_true")
+    ap.add_argument("--dp_sync", default="pipeline_a", choices=["pipeline_a", "flat", "dense"])
+    ap.add_argument("--local_size", type=int, default=1)
+    ap.add_argument("--max_steps", type=int, default=10)
+    ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
+    ap.add_argument("--output_dir", default=None, help="write a checkpoint here at the end")
+    args = ap.parse_args(argv)
+
+    mcfg = LlamaConfig.llama7b() if args.model == "llama7b" else LlamaConfig.tiny()
+    mcfg.attention = _default_attention()
+    if args.model == "tiny":
+        args.seq_length = min(args.seq_length, mcfg.max_seq)
+    tcfg = TrainerConfig(
+        pp_size=args.pp_size, micro_batches=args.micro_batches,
+        micro_batch_size=args.batch_size, seq_length=args.seq_length, bitwidth=args.bitwidth,
+        stochastic_rounding=args.stochastic_rounding,
+        error_feedback=not args.no_error_feedback,
+        dp_sync="dense" if args.backend == "nccl" else args.dp_sync,
+        local_size=args.local_size, lr=args.lr)
+    trainer = LlamaTrainer(mcfg, tcfg)
+    for step in range(args.max_steps):
+        t0 = time.perf_counter()
+        loss = trainer.train_step(trainer.synthetic_batch(step))
+        if loss is not None:
+            print(json.dumps({"step": step, "loss": float(loss.item()),
+                              "step_s": time.perf_counter() - t0}), flush=True)
+    if args.output_dir:
+        from ..utils.checkpoint import save_checkpoint
+
+        save_checkpoint(args.output_dir, trainer.state_dict(), trainer.rank)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,85 @@
+"""1F1B schedule: action order, activation memory bound, and a deadlock-freedom check of
+the point-to-point plan (every posted batch must find its matching batch on the peer)."""
+
+import pytest
+
+from bitscom_b200.parallel.pp_schedule import (build_1f1b, communication_plan,
+                                               max_live_microbatches)
+
+
+@pytest.mark.parametrize("stages,mbs", [(1, 4), (2, 4), (4, 8), (4, 2), (8, 16), (3, 5)])
+def test_1f1b_order_and_memory(stages, mbs):
+    for s in range(stages):
+        acts = build_1f1b(s, stages, mbs)
+        assert sorted(i for k, i in acts if k == "F") == list(range(mbs))
+        assert [i for k, i in acts if k == "B"] == list(range(mbs))
+        seen = set()
+        for k, i in acts:
+            if k == "F":
+                seen.add(i)
+            else:
+                assert i in seen  # backward only after its forward
+        assert max_live_microbatches(acts) <= min(stages - s, mbs)
+
+
+def _simulate(stages, mbs):
+    """Play all stages' plans with NCCL's grouping rule: the operations of one batch run
+    concurrently and complete one by one as the peer's CURRENT batch offers the matching
+    operation; a stage moves on when its batch is empty.  Returns, per stage, the
+    micro-batches whose activations / gradients it received, in arrival order."""
+    plans = [[(k, mb, c) for k, mb, c in communication_plan(s, stages, mbs) if c.any()]
+             for s in range(stages)]
+    pos = [0] * stages
+    got_fwd = [[] for _ in range(stages)]
+    got_bwd = [[] for _ in range(stages)]
+
+    def pending_ops(s):
+        if pos[s] >= len(plans[s]):
+            return None
+        _, mb, c = plans[s][pos[s]]
+        ops = set()
+        if c.send_next:
+            ops.add(("send", s + 1, mb))
+        if c.send_prev:
+            ops.add(("send", s - 1, mb))
+        if c.recv_prev:
+            ops.add(("recv", s - 1, None))
+        if c.recv_next:
+            ops.add(("recv", s + 1, None))
+        return ops
+
+    pending = [pending_ops(s) for s in range(stages)]
+    for _ in range(20 * stages * mbs + 20):
+        if all(p is None for p in pending):
+            return got_fwd, got_bwd
+        progressed = False
+        for s in range(stages):
+            if not pending[s]:
+                continue
+            for op in list(pending[s]):
+                kind, peer, mb = op
+                if kind != "send" or pending[peer] is None:
+                    continue
+                match = ("recv", s, None)
+                if match in pending[peer]:
+                    pending[peer].discard(match)
+                    pending[s].discard(op)
+                    (got_fwd if peer == s + 1 else got_bwd)[peer].append(mb)
+                    progressed = True
+        for s in range(stages):
+            if pending[s] is not None and not pending[s]:
+                pos[s] += 1
+                pending[s] = pending_ops(s)
+                progressed = True
+        if not progressed:
+            raise AssertionError(f"deadlock: {pending}")
+    raise AssertionError("simulation did not terminate")
+
+
+@pytest.mark.parametrize("stages,mbs", [(2, 4), (2, 1), (4, 8), (4, 4), (4, 2), (3, 7), (8, 16)])
+def test_p2p_plan_is_deadlock_free_and_ordered(stages, mbs):
+    got_fwd, got_bwd = _simulate(stages, mbs)
+    for s in range(1, stages):
+        assert got_fwd[s] == list(range(mbs))       # activations arrive in order
+    for s in range(stages - 1):
+        assert got_bwd[s] == list(range(mbs))       # gradients arrive in order
