@@ -1,0 +1,696 @@
+// Causal flash attention, forward and backward, on tcgen05 tensor cores (sm_100a),
+// head_dim 128, operating directly on the fused, RoPE-rotated projection
+// qkv[tokens, 3 * heads * 128] (bf16) through TMA tensor maps: no q/k/v copies.
+//
+// TMEM gives every thread one accumulator ROW (thread t <-> TMEM lane t), so row maxima,
+// row sums and the softmax need no cross-thread reduction at all.
+//
+// forward   one CTA per (batch, head, 128 query rows), 2 CTAs per SM.
+//           per 64-key block:  S = Q K^T (tcgen05.mma, smem x smem -> TMEM)
+//                              rows of S -> registers (tcgen05.ld), online softmax,
+//                              P (bf16) -> 128B-swizzled smem
+//                              O_blk = P V (V consumed MN-major straight from its row-major
+//                              tile), rows of O_blk -> registers, O = O * alpha + O_blk
+//           the next K / V tile is requested the moment the MMA that read the previous one
+//           has completed, so TMA runs under the softmax.
+// backward  one CTA per (batch, head, 128 keys), looping over the 128-row query blocks at
+//           or below the diagonal; everything is kept transposed (rows = keys):
+//             S^T = K Q^T, dP^T = V dO^T                       -> TMEM
+//             P^T = exp2(S^T * c - lse), dS^T = P^T o (dP^T - D) * scale   -> smem (bf16)
+//             dV += P^T dO, dK += dS^T Q   (accumulate in TMEM over all query blocks)
+//             dQ  = dS K                    -> TMEM -> fp32 atomics into a dQ buffer
+//           One smem tile serves as K-major operand of one product and MN-major operand of
+//           another (same bytes, different descriptor), so each of Q, K, V, dO is loaded once.
+//
+// The library baseline is torch SDPA / flash_attn; the reference trainer takes attention
+// from its external model package.  All mbarrier waits are bounded (status word + drain).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace attn {
+
+constexpr int HD = 128;           // head dim
+constexpr int BQ = 128;           // query rows per CTA (forward) / per iteration (backward)
+constexpr int BKF = 64;           // keys per iteration, forward
+constexpr int BKB = 128;          // keys per CTA, backward
+constexpr int kThreads = 128;
+constexpr unsigned long long kBudgetNs = 2000000000ull;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ unsigned int g_status[4];
+
+__device__ __forceinline__ void record_fail(unsigned int code) {
+  if (atomicCAS(&g_status[0], 0u, code) == 0u) {
+    g_status[1] = blockIdx.x;
+    g_status[2] = threadIdx.x;
+  }
+}
+
+// byte offset of the 16-byte unit `c8` (0..7) of row `r` inside a 128B-swizzled tile whose
+// rows are 128 bytes; `rows` rows form one 64-column chunk
+__device__ __forceinline__ uint32_t swz(int r, int c8) {
+  return (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// UMMA descriptors for the two ways a [rows x 128-col] two-chunk tile is consumed.
+// K-major: MN = rows, K = columns. Chunk c (64 columns) starts at c * rows * 128.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int rows, int kstep) {
+  const int chunk = kstep >> 2;  // 4 k-steps of 16 elements per 64-column chunk
+  return tc::make_smem_desc_sw128(base + chunk * rows * 128 + (kstep & 3) * 32, 16, 1024);
+}
+// MN-major: MN = columns, K = rows. k-step advances 16 rows; chunks are `rows * 128` apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int rows, int kstep) {
+  return tc::make_smem_desc_sw128(base + kstep * 16 * 128, rows * 128, 1024);
+}
+
+struct FwdParams {
+  __nv_bfloat16* out;   // [tokens, heads * HD]
+  float* lse2;          // [batch, heads, seq], log2 domain
+  int batch, seq, heads;
+  float scale_log2;     // softmax scale * log2(e)
+};
+
+struct FwdShared {
+  uint64_t bar_q, bar_k, bar_v, bar_s, bar_o;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+constexpr int FWD_Q_BYTES = BQ * HD * 2;    // 32 KiB
+constexpr int FWD_K_BYTES = BKF * HD * 2;   // 16 KiB
+constexpr int FWD_P_BYTES = BQ * BKF * 2;   // 16 KiB
+constexpr int FWD_SMEM = FWD_Q_BYTES + 2 * FWD_K_BYTES + FWD_P_BYTES + 1024 + 128;
+
+__global__ void __launch_bounds__(kThreads, 2)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 128}
+                     const __grid_constant__ CUtensorMap tm_kv,   // box {64, 64}
+                     const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + FWD_Q_BYTES;
+  uint8_t* sV = sK + FWD_K_BYTES;
+  uint8_t* sP = sV + FWD_K_BYTES;
+  FwdShared* sh = reinterpret_cast<FwdShared*>(sP + FWD_P_BYTES);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int qblocks = p.seq / BQ;
+  // heavy (late) query blocks first
+  const int qb = qblocks - 1 - (int)(blockIdx.x % qblocks);
+  const int bh = blockIdx.x / qblocks;
+  const int h = bh % p.heads, b = bh / p.heads;
+  const int H = p.heads * HD;
+  const int row0 = b * p.seq + qb * BQ;          // first token row of this query block
+  const int q_col = h * HD, k_col = H + h * HD, v_col = 2 * H + h * HD;
+  const int nblocks = (qb * BQ + BQ) / BKF;      // causal: keys 0 .. q0 + 127
+
+  if (tid == 0) {
+    tc::mbar_init(&sh->bar_q, 1);
+    tc::mbar_init(&sh->bar_k, 1);
+    tc::mbar_init(&sh->bar_v, 1);
+    tc::mbar_init(&sh->bar_s, 1);
+    tc::mbar_init(&sh->bar_o, 1);
+    sh->abort = 0;
+    tc::fence_mbar_init();
+  }
+  if (warp == 0) tc::tmem_alloc(&sh->tmem_base, 256);
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tS = tmem, tO = tmem + 64;
+  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+
+  auto load_k = [&](int j) {
+    tc::mbar_expect_tx(&sh->bar_k, FWD_K_BYTES);
+    tc::tma_load_2d(sK, &tm_kv, &sh->bar_k, k_col, b * p.seq + j * BKF);
+    tc::tma_load_2d(sK + BKF * 128, &tm_kv, &sh->bar_k, k_col + 64, b * p.seq + j * BKF);
+  };
+  auto load_v = [&](int j) {
+    tc::mbar_expect_tx(&sh->bar_v, FWD_K_BYTES);
+    tc::tma_load_2d(sV, &tm_kv, &sh->bar_v, v_col, b * p.seq + j * BKF);
+    tc::tma_load_2d(sV + BKF * 128, &tm_kv, &sh->bar_v, v_col + 64, b * p.seq + j * BKF);
+  };
+
+  if (tid == 0) {
+    tc::mbar_expect_tx(&sh->bar_q, FWD_Q_BYTES);
+    tc::tma_load_2d(sQ, &tm_q, &sh->bar_q, q_col, row0);
+    tc::tma_load_2d(sQ + BQ * 128, &tm_q, &sh->bar_q, q_col + 64, row0);
+    load_k(0);
+    load_v(0);
+  }
+
+  constexpr uint32_t idesc_s = tc::make_idesc_bf16(BQ, BKF, false, false);
+  constexpr uint32_t idesc_o = tc::make_idesc_bf16(BQ, HD, false, true);
+  const uint32_t aQ = tc::smem_u32(sQ), aK = tc::smem_u32(sK), aV = tc::smem_u32(sV),
+                 aP = tc::smem_u32(sP);
+
+  float o[HD];
+#pragma unroll
+  for (int i = 0; i < HD; ++i) o[i] = 0.0f;
+  float m_run = -INFINITY, l_run = 0.0f;
+  const int q_idx = qb * BQ + tid;  // position of this thread's query inside the sequence
+
+  if (!tc::mbar_wait(&sh->bar_q, 0, kBudgetNs)) { sh->abort = 1; record_fail(1); }
+
+  for (int j = 0; j < nblocks; ++j) {
+    const uint32_t par = (uint32_t)j & 1u;
+    // ---- S = Q K^T ----
+    if (tid == 0) {
+      if (!tc::mbar_wait(&sh->bar_k, par, kBudgetNs)) { sh->abort = 1; record_fail(2); }
+      tc::tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        tc::umma_bf16(tS, desc_kmajor(aQ, BQ, ks), desc_kmajor(aK, BKF, ks), idesc_s, ks != 0);
+      tc::umma_commit(&sh->bar_s);
+    }
+    if (!tc::mbar_wait(&sh->bar_s, par, kBudgetNs)) { sh->abort = 1; record_fail(3); }
+    tc::tc_fence_after_sync();
+    if (tid == 0 && j + 1 < nblocks) load_k(j + 1);  // K tile is free again
+
+    // ---- online softmax on this thread's row ----
+    float s[BKF];
+    {
+      uint32_t r[32];
+      tc::tmem_ld_32x32(tS + lane_addr, r);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]) * p.scale_log2;
+      tc::tmem_ld_32x32(tS + lane_addr + 32, r);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(r[i]) * p.scale_log2;
+    }
+    const int k0 = j * BKF;
+    if (k0 + BKF - 1 > qb * BQ) {  // block touches the diagonal
+#pragma unroll
+      for (int i = 0; i < BKF; ++i)
+        if (k0 + i > q_idx) s[i] = -INFINITY;
+    }
+    float m_blk = m_run;
+#pragma unroll
+    for (int i = 0; i < BKF; ++i) m_blk = fmaxf(m_blk, s[i]);
+    const float alpha = exp2f(m_run - m_blk);  // first block: exp2(-inf) = 0
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < BKF; ++i) {
+      s[i] = exp2f(s[i] - m_blk);
+      sum += s[i];
+    }
+    l_run = l_run * alpha + sum;
+    m_run = m_blk;
+#pragma unroll
+    for (int c8 = 0; c8 < BKF / 8; ++c8) {
+      uint4 v;
+      v.x = pack_bf16(s[c8 * 8 + 0], s[c8 * 8 + 1]);
+      v.y = pack_bf16(s[c8 * 8 + 2], s[c8 * 8 + 3]);
+      v.z = pack_bf16(s[c8 * 8 + 4], s[c8 * 8 + 5]);
+      v.w = pack_bf16(s[c8 * 8 + 6], s[c8 * 8 + 7]);
+      *reinterpret_cast<uint4*>(sP + swz(tid, c8)) = v;
+    }
+    tc::fence_proxy_async();       // generic-proxy smem writes -> visible to the MMA
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (sh->abort) break;
+
+    // ---- O_blk = P V ----
+    if (tid == 0) {
+      if (!tc::mbar_wait(&sh->bar_v, par, kBudgetNs)) { sh->abort = 1; record_fail(4); }
+      tc::tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < BKF / 16; ++ks)
+        tc::umma_bf16(tO, desc_kmajor(aP, BQ, ks), desc_mnmajor(aV, BKF, ks), idesc_o, ks != 0);
+      tc::umma_commit(&sh->bar_o);
+    }
+    if (!tc::mbar_wait(&sh->bar_o, par, kBudgetNs)) { sh->abort = 1; record_fail(5); }
+    tc::tc_fence_after_sync();
+    if (tid == 0 && j + 1 < nblocks) load_v(j + 1);  // V tile is free again
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t r[32];
+      tc::tmem_ld_32x32(tO + lane_addr + c * 32, r);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
+    }
+    tc::tc_fence_before_sync();
+  }
+
+  // ---- epilogue ----
+  if (!sh->abort) {
+    const float inv = 1.0f / l_run;
+    __nv_bfloat16* dst = p.out + (size_t)(row0 + tid) * H + q_col;
+#pragma unroll
+    for (int c8 = 0; c8 < HD / 8; ++c8) {
+      uint4 v;
+      v.x = pack_bf16(o[c8 * 8 + 0] * inv, o[c8 * 8 + 1] * inv);
+      v.y = pack_bf16(o[c8 * 8 + 2] * inv, o[c8 * 8 + 3] * inv);
+      v.z = pack_bf16(o[c8 * 8 + 4] * inv, o[c8 * 8 + 5] * inv);
+      v.w = pack_bf16(o[c8 * 8 + 6] * inv, o[c8 * 8 + 7] * inv);
+      reinterpret_cast<uint4*>(dst)[c8] = v;
+    }
+    p.lse2[((size_t)b * p.heads + h) * p.seq + q_idx] = m_run + log2f(l_run);
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tmem, 256);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------
+struct BwdParams {
+  __nv_bfloat16* dqkv;   // [tokens, 3 * heads * HD]; K and V thirds written here
+  float* dq_acc;         // [tokens, heads * HD] fp32, zero on entry
+  const float* lse2;     // [batch, heads, seq]
+  const float* delta;    // [batch, heads, seq]  rowsum(dO o O)
+  int batch, seq, heads;
+  float scale_log2;      // scale * log2(e)
+  float scale;           // softmax scale
+};
+
+struct BwdShared {
+  uint64_t bar_kv, bar_q, bar_1, bar_2;
+  uint32_t tmem_base;
+  volatile int abort;
+  float lse[BQ];
+  float delta[BQ];
+};
+
+constexpr int TILE = 128 * HD * 2;  // 32 KiB: every backward tile is 128 x 128 bf16
+constexpr int BWD_SMEM = 6 * TILE + 1024 + sizeof(BwdShared) + 64;
+
+__global__ void __launch_bounds__(kThreads, 1)
+attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 128} over qkv
+                     const __grid_constant__ CUtensorMap tm_do,    // box {64, 128} over dO
+                     const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE;
+  uint8_t* sQ = sV + TILE;
+  uint8_t* sDO = sQ + TILE;
+  uint8_t* sPT = sDO + TILE;
+  uint8_t* sDS = sPT + TILE;
+  BwdShared* sh = reinterpret_cast<BwdShared*>(sDS + TILE);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int kblocks = p.seq / BKB;
+  const int kb = (int)(blockIdx.x % kblocks);  // early key blocks (most work) first
+  const int bh = blockIdx.x / kblocks;
+  const int h = bh % p.heads, b = bh / p.heads;
+  const int H = p.heads * HD;
+  const int key0 = b * p.seq + kb * BKB;
+  const int q_col = h * HD, k_col = H + h * HD, v_col = 2 * H + h * HD;
+  const int nq = kblocks - kb;  // query blocks kb .. kblocks-1 (BQ == BKB)
+
+  if (tid == 0) {
+    tc::mbar_init(&sh->bar_kv, 1);
+    tc::mbar_init(&sh->bar_q, 1);
+    tc::mbar_init(&sh->bar_1, 1);
+    tc::mbar_init(&sh->bar_2, 1);
+    sh->abort = 0;
+    tc::fence_mbar_init();
+  }
+  if (warp == 0) tc::tmem_alloc(&sh->tmem_base, 512);
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tST = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 384, tDQ = tmem;
+  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+
+  auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int col, int row) {
+    tc::tma_load_2d(dst, map, bar, col, row);
+    tc::tma_load_2d(dst + 128 * 128, map, bar, col + 64, row);
+  };
+  auto load_q = [&](int qi) {
+    const int row = b * p.seq + (kb + qi) * BQ;
+    tc::mbar_expect_tx(&sh->bar_q, 2 * TILE);
+    load_tile(sQ, &tm_qkv, &sh->bar_q, q_col, row);
+    load_tile(sDO, &tm_do, &sh->bar_q, q_col, row);
+  };
+
+  if (tid == 0) {
+    tc::mbar_expect_tx(&sh->bar_kv, 2 * TILE);
+    load_tile(sK, &tm_qkv, &sh->bar_kv, k_col, key0);
+    load_tile(sV, &tm_qkv, &sh->bar_kv, v_col, key0);
+    load_q(0);
+  }
+
+  constexpr uint32_t idesc_kk = tc::make_idesc_bf16(128, 128, false, false);  // both K-major
+  constexpr uint32_t idesc_kn = tc::make_idesc_bf16(128, 128, false, true);   // B MN-major
+  constexpr uint32_t idesc_nn = tc::make_idesc_bf16(128, 128, true, true);    // both MN-major
+  const uint32_t aK = tc::smem_u32(sK), aV = tc::smem_u32(sV), aQ = tc::smem_u32(sQ),
+                 aDO = tc::smem_u32(sDO), aPT = tc::smem_u32(sPT), aDS = tc::smem_u32(sDS);
+  const int key_idx = kb * BKB + tid;  // this thread's key position inside the sequence
+
+  if (!tc::mbar_wait(&sh->bar_kv, 0, kBudgetNs)) { sh->abort = 1; record_fail(11); }
+
+  for (int qi = 0; qi < nq; ++qi) {
+    const uint32_t par = (uint32_t)qi & 1u;
+    const int qpos0 = (kb + qi) * BQ;  // first query position of this block
+    // row statistics of the 128 queries of this block
+    {
+      const size_t base = ((size_t)b * p.heads + h) * p.seq + qpos0;
+      sh->lse[tid] = p.lse2[base + tid];
+      sh->delta[tid] = p.delta[base + tid];
+    }
+    // ---- S^T = K Q^T and dP^T = V dO^T ----
+    if (tid == 0) {
+      if (!tc::mbar_wait(&sh->bar_q, par, kBudgetNs)) { sh->abort = 1; record_fail(12); }
+      tc::tc_fence_after_sync();
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        tc::umma_bf16(tST, desc_kmajor(aK, 128, ks), desc_kmajor(aQ, 128, ks), idesc_kk, ks != 0);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        tc::umma_bf16(tDP, desc_kmajor(aV, 128, ks), desc_kmajor(aDO, 128, ks), idesc_kk,
+                      ks != 0);
+      tc::umma_commit(&sh->bar_1);
+    }
+    __syncthreads();  // lse / delta visible
+    if (!tc::mbar_wait(&sh->bar_1, par, kBudgetNs)) { sh->abort = 1; record_fail(13); }
+    tc::tc_fence_after_sync();
+
+    // ---- P^T and dS^T for this thread's key row, 32 query columns at a time ----
+    const bool diagonal = qi == 0;
+#pragma unroll 1
+    for (int c = 0; c < BQ / 32; ++c) {
+      uint32_t rs[32], rd[32];
+      tc::tmem_ld_32x32(tST + lane_addr + c * 32, rs);
+      tc::tmem_ld_32x32(tDP + lane_addr + c * 32, rd);
+      tc::tmem_wait_ld();
+      float pt[32], ds[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int qq = c * 32 + i;
+        float pv = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - sh->lse[qq]);
+        if (diagonal && key_idx > qpos0 + qq) pv = 0.0f;
+        pt[i] = pv;
+        ds[i] = pv * (__uint_as_float(rd[i]) - sh->delta[qq]) * p.scale;
+      }
+      const int chunk = c >> 1;            // 64-column chunk of the tile
+      const int c8_0 = (c & 1) * 4;        // first 16-byte unit inside the chunk
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint4 v, w;
+        v.x = pack_bf16(pt[u * 8 + 0], pt[u * 8 + 1]);
+        v.y = pack_bf16(pt[u * 8 + 2], pt[u * 8 + 3]);
+        v.z = pack_bf16(pt[u * 8 + 4], pt[u * 8 + 5]);
+        v.w = pack_bf16(pt[u * 8 + 6], pt[u * 8 + 7]);
+        w.x = pack_bf16(ds[u * 8 + 0], ds[u * 8 + 1]);
+        w.y = pack_bf16(ds[u * 8 + 2], ds[u * 8 + 3]);
+        w.z = pack_bf16(ds[u * 8 + 4], ds[u * 8 + 5]);
+        w.w = pack_bf16(ds[u * 8 + 6], ds[u * 8 + 7]);
+        const uint32_t off = chunk * 128 * 128 + swz(tid, c8_0 + u);
+        *reinterpret_cast<uint4*>(sPT + off) = v;
+        *reinterpret_cast<uint4*>(sDS + off) = w;
+      }
+    }
+    tc::fence_proxy_async();
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (sh->abort) break;
+
+    // ---- dV += P^T dO, dK += dS^T Q, dQ = dS K ----
+    if (tid == 0) {
+      tc::tc_fence_after_sync();
+      const uint32_t acc = qi != 0;
+#pragma unroll
+      for (int ks = 0; ks < BQ / 16; ++ks)
+        tc::umma_bf16(tDV, desc_kmajor(aPT, 128, ks), desc_mnmajor(aDO, 128, ks), idesc_kn,
+                      acc | (ks != 0));
+#pragma unroll
+      for (int ks = 0; ks < BQ / 16; ++ks)
+        tc::umma_bf16(tDK, desc_kmajor(aDS, 128, ks), desc_mnmajor(aQ, 128, ks), idesc_kn,
+                      acc | (ks != 0));
+#pragma unroll
+      for (int ks = 0; ks < BKB / 16; ++ks)
+        tc::umma_bf16(tDQ, desc_mnmajor(aDS, 128, ks), desc_mnmajor(aK, 128, ks), idesc_nn,
+                      ks != 0);
+      tc::umma_commit(&sh->bar_2);
+    }
+    if (!tc::mbar_wait(&sh->bar_2, par, kBudgetNs)) { sh->abort = 1; record_fail(14); }
+    tc::tc_fence_after_sync();
+    if (tid == 0 && qi + 1 < nq) load_q(qi + 1);  // Q and dO tiles are free again
+
+    // ---- dQ rows (thread t <-> query row t) into the fp32 buffer ----
+    {
+      float* dst = p.dq_acc + (size_t)(b * p.seq + qpos0 + tid) * H + q_col;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(tDQ + lane_addr + c * 32, r);
+        tc::tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          atomicAdd(reinterpret_cast<float4*>(dst + c * 32 + i),
+                    make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                                __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
+      }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();  // everybody has read dQ before the next S^T overwrites its columns
+    if (sh->abort) break;
+  }
+
+  // ---- dK, dV rows (thread t <-> key row t) ----
+  if (!sh->abort) {
+    tc::tc_fence_after_sync();
+    __nv_bfloat16* dk = p.dqkv + (size_t)(key0 + tid) * 3 * H + k_col;
+    __nv_bfloat16* dv = p.dqkv + (size_t)(key0 + tid) * 3 * H + v_col;
+#pragma unroll 1
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t r[32];
+      tc::tmem_ld_32x32(tDK + lane_addr + c * 32, r);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(r[u * 8 + 0]), __uint_as_float(r[u * 8 + 1]));
+        v.y = pack_bf16(__uint_as_float(r[u * 8 + 2]), __uint_as_float(r[u * 8 + 3]));
+        v.z = pack_bf16(__uint_as_float(r[u * 8 + 4]), __uint_as_float(r[u * 8 + 5]));
+        v.w = pack_bf16(__uint_as_float(r[u * 8 + 6]), __uint_as_float(r[u * 8 + 7]));
+        reinterpret_cast<uint4*>(dk + c * 32)[u] = v;
+      }
+      tc::tmem_ld_32x32(tDV + lane_addr + c * 32, r);
+      tc::tmem_wait_ld();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint4 v;
+        v.x = pack_bf16(__uint_as_float(r[u * 8 + 0]), __uint_as_float(r[u * 8 + 1]));
+        v.y = pack_bf16(__uint_as_float(r[u * 8 + 2]), __uint_as_float(r[u * 8 + 3]));
+        v.z = pack_bf16(__uint_as_float(r[u * 8 + 4]), __uint_as_float(r[u * 8 + 5]));
+        v.w = pack_bf16(__uint_as_float(r[u * 8 + 6]), __uint_as_float(r[u * 8 + 7]));
+        reinterpret_cast<uint4*>(dv + c * 32)[u] = v;
+      }
+    }
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tmem, 512);
+  }
+}
+
+// delta[b, h, s] = sum_d dO * O   (one warp per (token, head))
+__global__ void __launch_bounds__(256)
+attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                       float* __restrict__ delta, int batch, int seq, int heads) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long total = (long long)batch * seq * heads;
+  if (warp_id >= total) return;
+  const int h = (int)(warp_id % heads);
+  const long long tok = warp_id / heads;
+  const size_t off = (size_t)tok * heads * HD + (size_t)h * HD + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(o + off);
+  const uint2 g = *reinterpret_cast<const uint2*>(d_o + off);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(g2[i]);
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int w = 16; w > 0; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
+  if (lane == 0) {
+    const int b = (int)(tok / seq), sp = (int)(tok % seq);
+    delta[((size_t)b * heads + h) * seq + sp] = s;
+  }
+}
+
+// dqkv[:, 0:H] = bf16(dq_acc); dq_acc is left zeroed for the next call
+__global__ void __launch_bounds__(256)
+attention_dq_finish_kernel(float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv,
+                           long long tokens, int H) {
+  const long long vecs = tokens * (H / 4);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vecs;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / (H / 4);
+    const int c = (int)(i - t * (H / 4)) * 4;
+    float4* src = reinterpret_cast<float4*>(dq_acc + t * H + c);
+    const float4 v = *src;
+    *src = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint2 o;
+    o.x = pack_bf16(v.x, v.y);
+    o.y = pack_bf16(v.z, v.w);
+    *reinterpret_cast<uint2*>(dqkv + t * 3 * H + c) = o;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
+                    int box_cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "bitscom_b200: attention tensor map failed (%d): ptr=%p rows=%lld cols=%lld\n",
+            (int)r, ptr, rows, cols);
+  return (int)r;
+}
+
+}  // namespace attn
+
+extern "C" {
+
+// qkv: [batch*seq, 3*heads*128] bf16 (q | k | v, RoPE already applied); out: [batch*seq,
+// heads*128] bf16; lse2: [batch, heads, seq] fp32.  seq must be a multiple of 128.
+int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int seq, int heads,
+                       int head_dim, float scale, void* stream) {
+  using namespace attn;
+  if (head_dim != HD || seq % BQ || batch <= 0 || heads <= 0) return 1001;
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return 1002;
+  (void)cudaFree(nullptr);
+  (void)cudaGetLastError();
+  const long long tokens = (long long)batch * seq;
+  const int W = 3 * heads * HD;
+  CUtensorMap tm_q, tm_kv;
+  if (make_map(&tm_q, qkv, tokens, W, 64, BQ)) return 1003;
+  if (make_map(&tm_kv, qkv, tokens, W, 64, BKF)) return 1004;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute((const void*)attention_fwd_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
+  });
+  if (attr_err != cudaSuccess) return 1005;
+  FwdParams p;
+  p.out = (__nv_bfloat16*)out;
+  p.lse2 = (float*)lse2;
+  p.batch = batch;
+  p.seq = seq;
+  p.heads = heads;
+  p.scale_log2 = scale * kLog2e;
+  const int grid = batch * heads * (seq / BQ);
+  attention_fwd_kernel<<<grid, kThreads, FWD_SMEM, (cudaStream_t)stream>>>(tm_q, tm_kv, p);
+  return (int)cudaGetLastError();
+}
+
+// d_out: [batch*seq, heads*128]; dqkv (written): [batch*seq, 3*heads*128];
+// dq_acc: fp32 [batch*seq, heads*128] scratch, must be zero on entry and is zero on exit;
+// delta: fp32 [batch, heads, seq] scratch.
+int bcom_attention_bwd(const void* qkv, const void* out, const void* d_out, const void* lse2,
+                       void* dqkv, void* dq_acc, void* delta, int batch, int seq, int heads,
+                       int head_dim, float scale, void* stream) {
+  using namespace attn;
+  if (head_dim != HD || seq % BQ || batch <= 0 || heads <= 0) return 1001;
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)d_out & 15) || ((uintptr_t)dqkv & 15)) return 1002;
+  (void)cudaFree(nullptr);
+  (void)cudaGetLastError();
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long tokens = (long long)batch * seq;
+  const int H = heads * HD;
+  CUtensorMap tm_qkv, tm_do;
+  if (make_map(&tm_qkv, qkv, tokens, 3 * H, 64, 128)) return 1003;
+  if (make_map(&tm_do, d_out, tokens, H, 64, 128)) return 1004;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+  });
+  if (attr_err != cudaSuccess) return 1005;
+  {
+    const long long warps = tokens * heads;
+    const int grid = (int)((warps * 32 + 255) / 256);
+    attention_delta_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)out,
+                                                 (const __nv_bfloat16*)d_out, (float*)delta,
+                                                 batch, seq, heads);
+  }
+  BwdParams p;
+  p.dqkv = (__nv_bfloat16*)dqkv;
+  p.dq_acc = (float*)dq_acc;
+  p.lse2 = (const float*)lse2;
+  p.delta = (const float*)delta;
+  p.batch = batch;
+  p.seq = seq;
+  p.heads = heads;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  const int grid = batch * heads * (seq / BKB);
+  attention_bwd_kernel<<<grid, kThreads, BWD_SMEM, st>>>(tm_qkv, tm_do, p);
+  attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>((float*)dq_acc, (__nv_bfloat16*)dqkv, tokens,
+                                                     H);
+  return (int)cudaGetLastError();
+}
+
+int bcom_attention_status(unsigned int out[4], int clear) {
+  cudaError_t err = cudaMemcpyFromSymbol(out, attn::g_status, sizeof(unsigned int) * 4);
+  if (err == cudaSuccess && clear) {
+    unsigned int zero[4] = {0, 0, 0, 0};
+    err = cudaMemcpyToSymbol(attn::g_status, zero, sizeof(zero));
+  }
+  return (int)err;
+}
+
+}  // extern "C"

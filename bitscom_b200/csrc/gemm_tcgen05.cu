@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -301,18 +302,26 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 row-major matrix [rows, cols] with leading dimension ld (elements)
-static bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
-                     long long ld, int box_cols, int box_rows) {
+// 2-D bf16 row-major matrix [rows, cols] with leading dimension ld (elements).
+// Returns the driver's result code (0 = ok, -1 = entry point missing).
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
+                    long long ld, int box_cols, int box_rows) {
   EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
+  if (!fn) return -1;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr,
+            "bitscom_b200: cuTensorMapEncodeTiled failed (%d): ptr=%p rows=%lld cols=%lld "
+            "ld=%lld box=%dx%d\n",
+            (int)r, ptr, rows, cols, ld, box_cols, box_rows);
+  return (int)r;
 }
 
 typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const Params);
@@ -350,9 +359,12 @@ int bcom_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return 1002;
   (void)cudaGetLastError();  // do not inherit an error left behind by an earlier call
   CUtensorMap tmA, tmB;
-  if (!(a_mn_major ? make_map(&tmA, A, K, M, lda, 64, BK) : make_map(&tmA, A, M, K, lda, BK, BM)))
+  // the tensor-map encoder is a driver call: make sure this thread (it may be an autograd
+  // worker) has the device's primary context bound
+  (void)cudaFree(nullptr);
+  if (a_mn_major ? make_map(&tmA, A, K, M, lda, 64, BK) : make_map(&tmA, A, M, K, lda, BK, BM))
     return 1003;
-  if (!(b_mn_major ? make_map(&tmB, B, K, N, ldb, 64, BK) : make_map(&tmB, B, N, K, ldb, BK, BN)))
+  if (b_mn_major ? make_map(&tmB, B, K, N, ldb, 64, BK) : make_map(&tmB, B, N, K, ldb, BK, BN))
     return 1004;
   Kernel kernel = pick(a_mn_major != 0, b_mn_major != 0, out_fp32 != 0, accumulate != 0);
   static std::mutex mu;

@@ -1,0 +1,119 @@
+"""GPT-2 decoder (medium by default: 24 layers, d_model 1024, 16 heads, vocab 50257,
+sequence 1024) for the sharded-training workload.  Linear layers run on the tcgen05 GEMM
+(``ops.gemm``); LayerNorm, GELU and the head_dim-64 attention come from torch (the
+hand-written attention kernel covers head_dim 128).  Parameters are views of one flat
+buffer so that ZeRO-style sharding is a contiguous range per rank.  The reference's GPT-2
+benchmark uses a 4-layer, 256-wide HF model (``benchmarks/multimodel_stochastic_e2e_curve
+.py:534-539``); there is no sharded trainer in the reference."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import gemm as G
+from ..ops import nn as K
+from ..parallel.flat import FlatParameters
+
+
+@dataclass
+class GPT2Config:
+    vocab_size: int = 50257
+    n_layer: int = 24
+    d_model: int = 1024
+    n_head: int = 16
+    seq: int = 1024
+    init_std: float = 0.02
+
+    @property
+    def padded_vocab(self) -> int:
+        return -(-self.vocab_size // 256) * 256
+
+    @staticmethod
+    def medium(**kw) -> "GPT2Config":
+        return GPT2Config(**kw)
+
+    @staticmethod
+    def tiny(**kw) -> "GPT2Config":
+        base = dict(vocab_size=512, n_layer=2, d_model=256, n_head=4, seq=128)
+        base.update(kw)
+        return GPT2Config(**base)
+
+
+class GPT2(torch.nn.Module):
+    def __init__(self, cfg: GPT2Config, device="cuda", seed: int = 0, pad_to: int = 256):
+        super().__init__()
+        self.cfg = cfg
+        D, V = cfg.d_model, cfg.padded_vocab
+        shapes: Dict[str, Tuple[int, ...]] = {"wte": (V, D), "wpe": (cfg.seq, D)}
+        for i in range(cfg.n_layer):
+            shapes[f"h{i}.ln1_w"] = (D,)
+            shapes[f"h{i}.ln1_b"] = (D,)
+            shapes[f"h{i}.wqkv"] = (3 * D, D)
+            shapes[f"h{i}.bqkv"] = (3 * D,)
+            shapes[f"h{i}.wo"] = (D, D)
+            shapes[f"h{i}.bo"] = (D,)
+            shapes[f"h{i}.ln2_w"] = (D,)
+            shapes[f"h{i}.ln2_b"] = (D,)
+            shapes[f"h{i}.wfc"] = (4 * D, D)
+            shapes[f"h{i}.bfc"] = (4 * D,)
+            shapes[f"h{i}.wproj"] = (D, 4 * D)
+            shapes[f"h{i}.bproj"] = (D,)
+        shapes["lnf_w"] = (D,)
+        shapes["lnf_b"] = (D,)
+        self.flat = FlatParameters(shapes, device, pad_to=pad_to)
+        self.p = torch.nn.ParameterDict(
+            {n.replace(".", "_"): self.flat.make_parameter(n) for n in shapes})
+        gen = torch.Generator(device=self.flat.params.device).manual_seed(seed)
+        with torch.no_grad():
+            for name, view in self.flat.named_views():
+                if name.endswith("_w") and "ln" in name:
+                    view.fill_(1.0)
+                elif name.split(".")[-1].startswith("b") or name.endswith("_b"):
+                    view.zero_()
+                else:
+                    view.copy_(torch.randn(view.shape, device=view.device, generator=gen)
+                               * cfg.init_std)
+        self.flat.sync_master_from_params()
+
+    def _w(self, name):
+        return self.p[name.replace(".", "_")]
+
+    def _bias_grad_hook(self, name):
+        return self._w(name)
+
+    def forward(self, ids: torch.Tensor, targets: Optional[torch.Tensor] = None):
+        cfg = self.cfg
+        B, S = ids.shape
+        D, nh = cfg.d_model, cfg.n_head
+        x = K.embedding(ids.reshape(-1), self._w("wte")) + self._w("wpe")[:S].repeat(B, 1)
+        for i in range(cfg.n_layer):
+            h = F.layer_norm(x, (D,), self._w(f"h{i}.ln1_w"), self._w(f"h{i}.ln1_b"))
+            qkv = G.linear(h, self._w(f"h{i}.wqkv")) + self._w(f"h{i}.bqkv")
+            q, k, v = (qkv[:, j * D:(j + 1) * D].view(B, S, nh, D // nh).transpose(1, 2)
+                       for j in range(3))
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            a = a.transpose(1, 2).reshape(B * S, D)
+            x = x + G.linear(a, self._w(f"h{i}.wo")) + self._w(f"h{i}.bo")
+            h = F.layer_norm(x, (D,), self._w(f"h{i}.ln2_w"), self._w(f"h{i}.ln2_b"))
+            h = F.gelu(G.linear(h, self._w(f"h{i}.wfc")) + self._w(f"h{i}.bfc"),
+                       approximate="tanh")
+            x = x + G.linear(h, self._w(f"h{i}.wproj")) + self._w(f"h{i}.bproj")
+        x = F.layer_norm(x, (D,), self._w("lnf_w"), self._w("lnf_b"))
+        logits = G.linear(x, self._w("wte"))
+        if targets is None:
+            return logits.view(B, S, -1)
+        shifted = torch.full_like(targets, -100)
+        shifted[:, :-1] = targets[:, 1:]
+        return K.cross_entropy(logits, shifted.reshape(-1), ignore_index=-100)
+
+    def collect_autograd_grads(self) -> None:
+        """Parameters updated by torch ops (LayerNorm, biases, position embedding) receive
+        ``.grad``; fold them into the flat fp32 gradient buffer."""
+        for p in self.p.values():
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.float())
+                p.grad = None

@@ -1,0 +1,125 @@
+"""GPT-2 medium, ZeRO-1 style sharded training on low-bit collectives (bf16 compute).
+
+24 layers, d_model 1024, 16 heads, vocab 50257, sequence 1024, micro-batch 8 per GPU,
+synthetic uniform token ids.  Each step: forward/backward on the full bf16 model, low-bit
+reduce-scatter of the flat fp32 gradient (4-bit + error feedback), AdamW on the local
+shard of fp32 master weights, low-bit all-gather of the updated parameters (8-bit by
+default: parameters tolerate less noise than gradients; ``--param-bits 4`` for the 4-bit
+setting).  ``--mode nccl`` uses dense NCCL reduce-scatter / all-gather.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m bitscom_b200.trainer.gpt2_sharded --steps 10
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..api import LowBitGroup
+from ..models.gpt2 import GPT2, GPT2Config
+from ..ops import nn as K
+from ..parallel.zero import ShardedAdamW
+
+
+class DenseShardedAdamW:
+    """NCCL baseline with the same sharding."""
+
+    def __init__(self, flat, world, rank, lr):
+        self.flat, self.world, self.rank = flat, world, rank
+        self.shard = flat.numel // world
+        lo = rank * self.shard
+        self.master = flat.params[lo:lo + self.shard].float().clone()
+        self.grad = torch.zeros_like(self.master)
+        self.opt = K.FlatAdamW(self.master, self.grad, None, lr=lr)
+        self.full = torch.empty(flat.numel, dtype=torch.float32, device=self.master.device)
+
+    def step(self):
+        dist.reduce_scatter_tensor(self.grad, self.flat.grads)
+        self.opt.step(grad_scale=1.0 / self.world)
+        self.flat.grads.zero_()
+        dist.all_gather_into_tensor(self.full, self.master)
+        self.flat.params.copy_(self.full)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--grad-bits", type=int, default=4)
+    ap.add_argument("--param-bits", type=int, default=8)
+    ap.add_argument("--mode", default="lowbit", choices=["lowbit", "nccl"])
+    ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
+    ap.add_argument("--out", default="gpurun_out/gpt2_sharded.jsonl")
+    args = ap.parse_args(argv)
+
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = GPT2Config.medium() if args.model == "medium" else GPT2Config.tiny()
+    model = GPT2(cfg, dev, seed=0, pad_to=256 * max(world, 1))
+    flat = model.flat
+    if args.mode == "lowbit" and world > 1:
+        ggrp = LowBitGroup(bitwidth=args.grad_bits, block_size=256, error_feedback=True)
+        pgrp = LowBitGroup(bitwidth=args.param_bits, block_size=256, error_feedback=True)
+        opt = ShardedAdamW(flat, ggrp, lr=3e-4, param_bits_group=pgrp)
+    elif world > 1:
+        opt = DenseShardedAdamW(flat, world, rank, 3e-4)
+    else:
+        opt = K.FlatAdamW(flat.master, flat.grads, flat.params, lr=3e-4)
+    g = torch.Generator().manual_seed(5 + rank)
+
+    def step():
+        ids = torch.randint(0, cfg.vocab_size, (args.micro_batch, cfg.seq), generator=g)
+        ids = ids.pin_memory().to(dev, non_blocking=True)
+        loss = model(ids, targets=ids)
+        loss.backward()
+        model.collect_autograd_grads()
+        opt.step()
+        return loss.detach()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    first = last = None
+    for i in range(args.steps):
+        last = step()
+        if i == 0:
+            first = last
+    e.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([s.elapsed_time(e) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        tokens = world * args.micro_batch * cfg.seq
+        row = {"workload": "gpt2_medium_sharded" if args.model == "medium" else "gpt2_tiny",
+               "mode": args.mode, "world": world, "grad_bits": args.grad_bits,
+               "param_bits": args.param_bits, "ms_per_step": float(ms.item()),
+               "tokens_per_s": tokens / float(ms.item()) * 1e3,
+               "loss_first": float(first.item()), "loss_last": float(last.item())}
+        print(json.dumps(row), flush=True)
+        if args.out:
+            os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+            with open(args.out, "a") as f:
+                f.write(json.dumps(row) + "\n")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -9,11 +9,15 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 
-def _entry(rank, world, backend, init_file, fn, args, errq):
+def _entry(rank, world, backend, init_file, fn, args, errq, lowbit_options=None):
     try:
         os.environ["TORCH_DISTRIBUTED_DEBUG"] = "OFF"
-        if backend == "nccl":
+        if backend in ("nccl", "lowbit"):
             torch.cuda.set_device(rank)
+        if backend == "lowbit":
+            import bitscom_b200
+
+            bitscom_b200.init(**(lowbit_options or {}))
         dist.init_process_group(backend, init_method=f"file://{init_file}", rank=rank,
                                 world_size=world)
         fn(rank, world, *args)
@@ -24,14 +28,14 @@ def _entry(rank, world, backend, init_file, fn, args, errq):
         raise
 
 
-def run_ranks(fn, world, *args, backend="gloo", timeout=300):
+def run_ranks(fn, world, *args, backend="gloo", timeout=300, lowbit_options=None):
     """Run ``fn(rank, world, *args)`` in ``world`` processes; raise on any failure."""
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     with tempfile.TemporaryDirectory() as tmp:
         init_file = os.path.join(tmp, "rendezvous")
         procs = [ctx.Process(target=_entry,
-                             args=(r, world, backend, init_file, fn, args, errq))
+                             args=(r, world, backend, init_file, fn, args, errq, lowbit_options))
                  for r in range(world)]
         for p in procs:
             p.start()

@@ -70,6 +70,25 @@ def test_strided_operands():
     _check(out, a.float() @ b.float().t(), 512)
 
 
+def test_gemm_from_a_worker_thread():
+    import threading
+
+    a, b = _mk(512, 768, 11), _mk(768, 1024, 12)
+    box = {}
+
+    def work():
+        try:
+            box["out"] = G.gemm(a, b, b_mn_major=True)
+        except Exception as exc:  # surfaced in the main thread
+            box["err"] = exc
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "err" not in box, box.get("err")
+    _check(box["out"], a.float() @ b.float(), 768)
+
+
 def test_linear_autograd_matches_torch():
     x = _mk(512, 1024, 7).requires_grad_()
     w = _mk(768, 1024, 8).requires_grad_()
