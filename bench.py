@@ -143,6 +143,11 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         if last is not None and not isinstance(last, float):
             last = float(last.item())
+        if world > 1:  # the loss lives on the last pipeline stage; rank 0 reports it
+            box = torch.tensor([last if (last is not None and trainer.dp_rank == 0) else 0.0],
+                               device=dev)
+            dist.all_reduce(box)
+            last = float(box.item())
         return float(ms.item()), last
 
     for i in range(args.warmup):

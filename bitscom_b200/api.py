@@ -396,12 +396,26 @@ class LowBitGroup:
         self._fused_comms: Dict[int, object] = {}
 
     # -- backend progress / scheduled handles (reference api.py:363-391) -----------
+    def _backend_attr(self, name: str):
+        """An extra method of the lowbit backend: on the group object itself, or on the
+        CUDA backend behind a ``ProcessGroup`` wrapper."""
+        fn = getattr(self.pg, name, None)
+        if fn is not None:
+            return fn
+        getter = getattr(self.pg, "_get_backend", None)
+        if getter is None:
+            return None
+        try:
+            return getattr(getter(torch.device("cuda")), name, None)
+        except Exception:
+            return None
+
     def progress_lowbit(self, block: bool = False) -> bool:
-        fn = getattr(self.pg, "progress_lowbit", None)
+        fn = self._backend_attr("progress_lowbit")
         return bool(fn(bool(block))) if fn is not None else False
 
     def schedule_lowbit_allreduce(self, tensor: torch.Tensor):
-        fn = getattr(self.pg, "schedule_lowbit_allreduce", None)
+        fn = self._backend_attr("schedule_lowbit_allreduce")
         if fn is None:
             raise RuntimeError("lowbit backend does not expose schedule_lowbit_allreduce")
         return fn(tensor)
@@ -410,7 +424,7 @@ class LowBitGroup:
         fn = getattr(handle, method, None)
         if fn is not None:
             return bool(fn())
-        fn = getattr(self.pg, pg_method, None)
+        fn = self._backend_attr(pg_method)
         if fn is None:
             raise RuntimeError(f"lowbit backend does not expose {label}")
         return bool(fn(handle))

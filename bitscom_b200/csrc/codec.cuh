@@ -33,15 +33,25 @@ template <int BITS> struct GroupBytes { static constexpr int value = BITS; };
 // ---------------------------------------------------------------------------
 // counter-based uniform stream: same arithmetic as quantization.sr_uniform
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float sr_uniform(uint32_t key, uint32_t idx) {
-  uint32_t h = idx * 0x9E3779B1u + key;
+// One 32-bit hash serves TWO consecutive elements (16 random bits each): element idx
+// uses the low half of hash(idx >> 1) when idx is even, the high half when odd.
+__device__ __forceinline__ uint32_t sr_hash(uint32_t key, uint32_t pair) {
+  uint32_t h = pair * 0x9E3779B1u + key;
   h ^= h >> 16;
   h *= 0x21F0AAADu;
   h ^= h >> 15;
   h *= 0x735A2D97u;
   h ^= h >> 15;
-  // 23 random bits as the mantissa of a float in [1, 2): no int-to-float conversion
-  return __uint_as_float(0x3F800000u | (h >> 9)) - 1.0f;
+  return h;
+}
+// 16 random bits as the top mantissa bits of a float in [1, 2): u = bits * 2^-16 exactly,
+// without an int-to-float conversion
+__device__ __forceinline__ float sr_u16(uint32_t bits16) {
+  return __uint_as_float(0x3F800000u | (bits16 << 7)) - 1.0f;
+}
+__device__ __forceinline__ float sr_uniform(uint32_t key, uint32_t idx) {
+  const uint32_t h = sr_hash(key, idx >> 1);
+  return sr_u16((idx & 1u) ? (h >> 16) : (h & 0xFFFFu));
 }
 
 // ---------------------------------------------------------------------------
@@ -156,16 +166,36 @@ constexpr float kTwo23 = 8388608.0f;        // 2^23
 constexpr float kMagic = 12582912.0f;       // 1.5 * 2^23: (c + kMagic) holds int c in its mantissa
 constexpr int kMagicBits = 0x4B400000;
 
-// Quantizes one value. Returns the signed code; *cf receives the same code as a float
-// (never -0), which is what dequantization multiplies by the scale.
+// Correctly rounded a / sf for many numerators and one denominator: y = RN(1/sf) once,
+// then q0 = RN(a*y), r = a - q0*sf (exact, fma), q = RN(q0 + r*y).  With y correctly
+// rounded and q0 within one ulp this is the IEEE quotient (Markstein); sf is an fp16 value,
+// so its significand is never all ones, the one case the argument excludes.  sf == 0 (the
+// fp16 scale underflowed) takes the plain IEEE divide so that inf / NaN come out as on the
+// host.
+struct Divider {
+  float sf, y;
+  __device__ __forceinline__ explicit Divider(float s) {
+    sf = s;
+    y = __frcp_rn(s);
+  }
+  __device__ __forceinline__ float operator()(float a) const {
+    if (__builtin_expect(sf == 0.0f, 0)) return __fdiv_rn(a, sf);
+    const float q0 = __fmul_rn(a, y);
+    const float r = __fmaf_rn(-q0, sf, a);
+    return __fmaf_rn(r, y, q0);
+  }
+};
+
+// Quantizes one value given n = |x| / sf and its uniform draw. Returns the signed code;
+// *cf receives the same code as a float (never -0), which is what dequantization
+// multiplies by the scale.
 template <int BITS, bool SR>
-__device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t idx, float* cf) {
-  const float n = __fdiv_rn(fabsf(x), sf);
+__device__ __forceinline__ int quant_core(float x, float n, float u, float* cf) {
   float mag;
   if constexpr (SR) {
     const float lo = __fsub_rn(__fadd_rd(n, kTwo23), kTwo23);  // floor(n) for 0 <= n < 2^23
     const float p = __fsub_rn(n, lo);                          // in [0, 1) for finite n
-    mag = sr_uniform(key, idx) < p ? __fadd_rn(lo, 1.0f) : lo;
+    mag = u < p ? __fadd_rn(lo, 1.0f) : lo;
   } else {
     mag = __fsub_rn(__fadd_rn(n, kTwo23), kTwo23);             // round half to even
   }
@@ -180,28 +210,51 @@ __device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t 
 }
 
 template <int BITS, bool SR>
+__device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t idx, float* cf) {
+  const float n = __fdiv_rn(fabsf(x), sf);
+  float u = 0.0f;
+  if constexpr (SR) u = sr_uniform(key, idx);
+  return quant_core<BITS, SR>(x, n, u, cf);
+}
+
+template <int BITS, bool SR>
 __device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t idx) {
   float unused;
   return quant1<BITS, SR>(x, sf, key, idx, &unused);
 }
 
-template <int BITS, bool SR>
-__device__ __forceinline__ void quant8(const float (&x)[GROUP], float sf, uint32_t key,
-                                       uint32_t idx0, int (&q)[GROUP]) {
-#pragma unroll
-  for (int i = 0; i < GROUP; ++i) q[i] = quant1<BITS, SR>(x[i], sf, key, idx0 + i);
-}
-
-// Quantize + dequantize in one go: q gets the codes, d the dequantized values.
+// Quantize + dequantize a group of 8 starting at index idx0: q gets the codes,
+// d the dequantized values (code * sf).
 template <int BITS, bool SR>
 __device__ __forceinline__ void quant8_dq(const float (&x)[GROUP], float sf, uint32_t key,
                                           uint32_t idx0, int (&q)[GROUP], float (&d)[GROUP]) {
+  const Divider div(sf);
 #pragma unroll
-  for (int i = 0; i < GROUP; ++i) {
-    float cf;
-    q[i] = quant1<BITS, SR>(x[i], sf, key, idx0 + i, &cf);
-    d[i] = __fmul_rn(cf, sf);
+  for (int i = 0; i < GROUP; i += 2) {
+    float u0 = 0.0f, u1 = 0.0f;
+    if constexpr (SR) {
+      if ((idx0 & 1u) == 0u) {  // the usual case: both elements share one hash
+        const uint32_t h = sr_hash(key, (idx0 + i) >> 1);
+        u0 = sr_u16(h & 0xFFFFu);
+        u1 = sr_u16(h >> 16);
+      } else {
+        u0 = sr_uniform(key, idx0 + i);
+        u1 = sr_uniform(key, idx0 + i + 1);
+      }
+    }
+    float c0, c1;
+    q[i] = quant_core<BITS, SR>(x[i], div(fabsf(x[i])), u0, &c0);
+    q[i + 1] = quant_core<BITS, SR>(x[i + 1], div(fabsf(x[i + 1])), u1, &c1);
+    d[i] = __fmul_rn(c0, sf);
+    d[i + 1] = __fmul_rn(c1, sf);
   }
+}
+
+template <int BITS, bool SR>
+__device__ __forceinline__ void quant8(const float (&x)[GROUP], float sf, uint32_t key,
+                                       uint32_t idx0, int (&q)[GROUP]) {
+  float d[GROUP];
+  quant8_dq<BITS, SR>(x, sf, key, idx0, q, d);
 }
 
 __device__ __forceinline__ void dequant8(const int (&q)[GROUP], float sf, float (&y)[GROUP]) {

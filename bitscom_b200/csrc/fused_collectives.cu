@@ -228,21 +228,26 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   // ---------------- phase 1: quantize every destination's shard and push it ----------
   if (p.mode != BCOM_MODE_ALL_GATHER) {
     const bool ef = p.res1 != nullptr;
+    const int gs = (int)Gs, gp = (int)Gp, gfirst = (int)first, gstride = (int)nthreads;
     for (int k = 0; k < W; ++k) {
       const int j = (p.rank + k) % W;  // ranks start on different destinations
       unsigned char* slot = p.peer[j] + BCOM_CONTROL_BYTES + (size_t)p.rank * p.slot_stride;
-      const long long shard0 = (long long)j * p.S;
-      for (long long g = first; g < Gp; g += nthreads) {
-        const long long off = p.c0 + g * GROUP;
-        const long long idx = shard0 + off;
-        const bool live = g < Gs;
-        long long lim = live ? min(shard_end - off, p.n - idx) : 0;
-        if (lim < 0) lim = 0;
+      const long long base_idx = (long long)j * p.S + p.c0;   // first element of the chunk
+      // real elements of this shard chunk: the rest of the chunk is zero padding
+      long long valid_ll = min(shard_end - p.c0, p.n - base_idx);
+      const int valid = (int)max(0LL, min(valid_ll, (long long)gs * GROUP));
+      const T* src = in + base_idx;
+      float* res = ef ? p.res1 + base_idx : nullptr;
+      const uint32_t idx_lo = (uint32_t)base_idx;
+      for (int g = gfirst; g < gp; g += gstride) {
+        const int e0 = g * GROUP;
+        const bool live = g < gs;
+        const int lim = live ? min(max(valid - e0, 0), GROUP) : 0;
         float v[GROUP];
-        load_vals<T, ALIGNED>(in, idx, lim, v);
+        load_vals<T, ALIGNED>(src, e0, lim, v);
         if (ef) {
           float r[GROUP];
-          load_vals<float, ALIGNED>(p.res1, idx, lim, r);
+          load_vals<float, ALIGNED>(res, e0, lim, r);
 #pragma unroll
           for (int i = 0; i < GROUP; ++i) v[i] = __fadd_rn(v[i], r[i]);
         }
@@ -253,12 +258,12 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
         int q[GROUP];
         if (ef) {
           float d[GROUP];
-          quant8_dq<BITS, SR>(v, sf, p.key1, (uint32_t)idx, q, d);
+          quant8_dq<BITS, SR>(v, sf, p.key1, idx_lo + (uint32_t)e0, q, d);
 #pragma unroll
           for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(v[i], d[i]);
-          store_vals<float, ALIGNED>(p.res1, idx, lim, d);
+          store_vals<float, ALIGNED>(res, e0, lim, d);
         } else {
-          quant8<BITS, SR>(v, sf, p.key1, (uint32_t)idx, q);
+          quant8<BITS, SR>(v, sf, p.key1, idx_lo + (uint32_t)e0, q);
         }
         push_group<BITS>(slot, p.scale_off, g, lanes, pack8<BITS>(q), sh);
       }
@@ -333,22 +338,28 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   if (p.mode == BCOM_MODE_REDUCE_SCATTER) return;
 
   // ---------------- phase 3: dequantize all shards into the bucket --------------------
-  for (int k = 0; k < W; ++k) {
-    const int j = (p.rank + k) % W;
-    const unsigned char* slot = gather_region + (size_t)j * p.slot_stride;
-    const long long shard0 = (long long)j * p.S;
-    for (long long g = first; g < Gs; g += nthreads) {
-      const long long off = p.c0 + g * GROUP;
-      const long long idx = shard0 + off;
-      const long long lim = min(shard_end - off, p.n - idx);
-      if (lim <= 0) continue;
-      const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
-      const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
-      float y[GROUP];
-      unpack8f<BITS>(pk, y);
+  {
+    const int gs = (int)Gs, gfirst = (int)first, gstride = (int)nthreads;
+    for (int k = 0; k < W; ++k) {
+      const int j = (p.rank + k) % W;
+      const unsigned char* slot = gather_region + (size_t)j * p.slot_stride;
+      const long long base_idx = (long long)j * p.S + p.c0;
+      const long long valid_ll = min(shard_end - p.c0, p.n - base_idx);
+      const int valid = (int)max(0LL, min(valid_ll, (long long)gs * GROUP));
+      T* dst = out + base_idx;
+      for (int g = gfirst; g < gs; g += gstride) {
+        const int e0 = g * GROUP;
+        const int lim = min(valid - e0, GROUP);
+        if (lim <= 0) continue;
+        const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
+        const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
+        float y[GROUP];
+        unpack8f<BITS>(pk, y);
 #pragma unroll
-      for (int i = 0; i < GROUP; ++i) y[i] = cast_roundtrip<T>(__fmul_rn(y[i], sf), p.post_scale);
-      store_vals<T, ALIGNED>(out, idx, lim, y);
+        for (int i = 0; i < GROUP; ++i)
+          y[i] = cast_roundtrip<T>(__fmul_rn(y[i], sf), p.post_scale);
+        store_vals<T, ALIGNED>(dst, e0, lim, y);
+      }
     }
   }
 }

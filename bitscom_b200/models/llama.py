@@ -161,6 +161,10 @@ class LlamaStage(torch.nn.Module):
             x = inp
         self._shape = (batch, seq)
         for i in range(*self.layer_range):
+            if self.on_layer_backward is not None and x.requires_grad:
+                # fires once the gradient w.r.t. this layer's input exists, i.e. the layer's
+                # own weight gradients have been enqueued
+                x.register_hook(self._make_hook(i))
             x = self.layer(i, x, batch, seq)
         if not self.is_last:
             return x
@@ -174,6 +178,17 @@ class LlamaStage(torch.nn.Module):
         shifted = torch.full_like(targets, ignore_index)
         shifted[:, :-1] = targets[:, 1:]
         return K.cross_entropy(logits, shifted.reshape(-1), ignore_index, loss_scale)
+
+    def _make_hook(self, layer_index: int):
+        cb = self.on_layer_backward
+
+        def hook(grad):
+            cb(layer_index)
+            return None
+
+        return hook
+
+    on_layer_backward = None  # optional callable(layer_index), set by the trainer
 
     def set_shape(self, batch: int, seq: int) -> None:
         self._shape = (batch, seq)

@@ -83,20 +83,22 @@ def sr_key(seed: int, stream: int = 0) -> int:
 
 
 def sr_uniform(key: int, index: torch.Tensor) -> torch.Tensor:
-    """fp32 uniforms in [0, 1) with 23 random bits, one per element index.
+    """fp32 uniforms in [0, 1) with 16 random bits, one per element index.
 
-    ``h = idx * 0x9E3779B1 + key`` followed by two xorshift-multiply rounds on
-    32 bits; the top 23 bits scaled by 2^-23 (on the device they become the
-    mantissa of a float in [1, 2)).  ``index`` is an int64 tensor and is reduced
-    mod 2^32.
+    One 32-bit hash serves two consecutive elements: ``h = (idx >> 1) * 0x9E3779B1 + key``
+    followed by two xorshift-multiply rounds; even indices take the low 16 bits, odd
+    indices the high 16 bits, scaled by 2^-16.  ``index`` is an int64 tensor and is
+    reduced mod 2^32.
     """
-    h = ((index.to(torch.int64) & _U32) * 0x9E3779B1 + int(key)) & _U32
+    idx = index.to(torch.int64) & _U32
+    h = ((idx >> 1) * 0x9E3779B1 + int(key)) & _U32
     h = h ^ (h >> 16)
     h = (h * 0x21F0AAAD) & _U32
     h = h ^ (h >> 15)
     h = (h * 0x735A2D97) & _U32
     h = h ^ (h >> 15)
-    return (h >> 9).to(torch.float32) * (1.0 / 8388608.0)
+    bits = torch.where((idx & 1) == 1, h >> 16, h & 0xFFFF)
+    return bits.to(torch.float32) * (1.0 / 65536.0)
 
 
 def _draw_uniform(like: torch.Tensor, sr_seed: Optional[int], sr_offset: int,

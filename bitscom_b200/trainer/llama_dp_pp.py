@@ -145,15 +145,31 @@ class LlamaTrainer:
         flat = self.model.flat
         names = list(flat.offsets)
         groups: List[Tuple[int, int]] = []
+        keys: List[str] = []
         cur_key, start = None, 0
         for name in names + [None]:
             key = name.split(".")[0] if name is not None else None
             off = flat.offsets[name][0] if name is not None else flat.numel
             if cur_key is not None and key != cur_key:
                 groups.append((start, off - start))
+                keys.append(cur_key)
                 start = off
             cur_key = key
-        return list(reversed(groups))
+        groups.reverse()
+        keys.reverse()
+        self._range_index = {k: i for i, k in enumerate(keys)}
+        return groups
+
+    def _layer_done(self, layer: int) -> None:
+        """Backward of the last micro-batch has passed ``layer``: its slice, and the
+        head / final norm when it is the stage's last layer, are final."""
+        if self.sync is None:
+            return
+        if layer == self.model.layer_range[1] - 1:
+            for key in ("lm_head", "final_norm"):
+                if key in self._range_index:
+                    self.sync.on_ready(self._range_index[key])
+        self.sync.on_ready(self._range_index[f"l{layer}"])
 
     # -- data ---------------------------------------------------------------------------
     def synthetic_batch(self, step: int, pinned: bool = True) -> torch.Tensor:
@@ -174,11 +190,11 @@ class LlamaTrainer:
         scale = 1.0 / c.micro_batches
         losses: List[torch.Tensor] = []
 
-        # hooks that fire when a layer's input gradient exists, i.e. the layer's weight
-        # gradients of the LAST micro-batch are complete
-        hook_state = {"armed": False}
+        last_mb = c.micro_batches - 1
 
         def forward_fn(mb: int, x: Optional[torch.Tensor]):
+            model.on_layer_backward = self._layer_done if (
+                mb == last_mb and self.sync is not None and c.overlap) else None
             if not model.is_first:
                 model.set_shape(c.micro_batch_size, c.seq_length)
             inp = ids[mb] if model.is_first else x
@@ -195,6 +211,7 @@ class LlamaTrainer:
         else:
             losses = self.runner.run(c.micro_batches, forward_fn)
 
+        model.on_layer_backward = None
         if self.sync is not None:
             self.sync.finish()
         self.opt.step(grad_scale=1.0, zero_grad=True)
