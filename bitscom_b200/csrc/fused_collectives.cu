@@ -50,7 +50,8 @@ struct RankParams {
   size_t slot_stride;   // bytes between two sources' slots inside a region
   size_t scale_off;     // offset of the fp16 scales inside a slot
   int rank, world;
-  int lanes_per_block;  // block / 8
+  int lanes_per_block;  // block / 8 (a power of two)
+  int lanes_log2;
   int mode;
   unsigned int key1, key2;
   float post_scale;
@@ -201,10 +202,11 @@ __device__ __forceinline__ float cast_roundtrip(float x, float post_scale) {
 // packed group and the scale to `slot` on each listed destination.
 template <int BITS>
 __device__ __forceinline__ void push_group(unsigned char* slot, size_t scale_off, long long g,
-                                           int lanes, const Packed8<BITS>& pk, __half sh) {
+                                           int lanes, int lanes_log2, const Packed8<BITS>& pk,
+                                           __half sh) {
   store_group<BITS>(slot, g, pk);
   if ((g & (lanes - 1)) == 0)
-    reinterpret_cast<__half*>(slot + scale_off)[g / lanes] = sh;
+    reinterpret_cast<__half*>(slot + scale_off)[g >> lanes_log2] = sh;
 }
 
 // ---------------------------------------------------------------------------
@@ -217,6 +219,7 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   const long long first = (long long)cta * blockDim.x + tid;
   const int W = p.world;
   const int lanes = p.lanes_per_block;
+  const int llog = p.lanes_log2;
   const long long Gs = (p.L + GROUP - 1) / GROUP;  // groups in this shard chunk
   const long long Gp = (Gs + 31) & ~31LL;          // padded so warps never straddle shards
   const long long shard_end = p.c0 + p.L;
@@ -265,7 +268,7 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
         } else {
           quant8<BITS, SR>(v, sf, p.key1, idx_lo + (uint32_t)e0, q);
         }
-        push_group<BITS>(slot, p.scale_off, g, lanes, pack8<BITS>(q), sh);
+        push_group<BITS>(slot, p.scale_off, g, lanes, llog, pack8<BITS>(q), sh);
       }
     }
   }
@@ -285,14 +288,29 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
       if (p.mode == BCOM_MODE_ALL_GATHER) {
         load_vals<T, ALIGNED>(in, off, lim, acc);
       } else if (live) {
-        for (int src = 0; src < W; ++src) {  // ascending source order: part of the contract
-          const unsigned char* slot = recv_region + (size_t)src * p.slot_stride;
-          const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
-          const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
-          float c[GROUP];
-          unpack8f<BITS>(pk, c);
+        // issue the loads of up to 8 sources back to back, then accumulate in ascending
+        // source order (the order is part of the wire contract)
+        for (int s0 = 0; s0 < W; s0 += 8) {
+          Packed8<BITS> pk[8];
+          float sc[8];
 #pragma unroll
-          for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(c[i], sf));
+          for (int u = 0; u < 8; ++u) {
+            if (s0 + u < W) {
+              const unsigned char* slot = recv_region + (size_t)(s0 + u) * p.slot_stride;
+              pk[u] = load_group_cg<BITS>(slot, g);
+              sc[u] = load_scale_cg(slot, p.scale_off, g >> llog);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (s0 + u < W) {
+              float c[GROUP];
+              unpack8f<BITS>(pk[u], c);
+#pragma unroll
+              for (int i = 0; i < GROUP; ++i)
+                acc[i] = __fadd_rn(acc[i], __fmul_rn(c[i], sc[u]));
+            }
+          }
         }
       }
       if (p.mode == BCOM_MODE_REDUCE_SCATTER) {
@@ -329,7 +347,7 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
         const int t = (p.rank + k) % W;
         unsigned char* slot = p.peer[t] + BCOM_CONTROL_BYTES + p.region_bytes +
                               (size_t)p.rank * p.slot_stride;
-        push_group<BITS>(slot, p.scale_off, g, lanes, pk, sh);
+        push_group<BITS>(slot, p.scale_off, g, lanes, llog, pk, sh);
       }
     }
   }
@@ -352,7 +370,7 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
         const int lim = min(valid - e0, GROUP);
         if (lim <= 0) continue;
         const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
-        const float sf = load_scale_cg(slot, p.scale_off, g / lanes);
+        const float sf = load_scale_cg(slot, p.scale_off, g >> llog);
         float y[GROUP];
         unpack8f<BITS>(pk, y);
 #pragma unroll
@@ -493,6 +511,8 @@ static void fill_params(const BcomComm* c, const BcomCollArgs& a, long long c0, 
   p->rank = c->rank;
   p->world = c->world;
   p->lanes_per_block = a.block / GROUP;
+  p->lanes_log2 = 0;
+  while ((1 << p->lanes_log2) < p->lanes_per_block) ++p->lanes_log2;
   p->mode = a.mode;
   p->key1 = a.key1;
   p->key2 = a.key2;

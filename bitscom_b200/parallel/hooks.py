@@ -106,7 +106,7 @@ def make_ddp_hook_state(lowbit_group, average: bool = True) -> _HookState:
     return _HookState(lowbit_group, average)
 
 
-def lowbit_ddp_comm_hook(state: _HookState, bucket) -> "torch.futures.Future[torch.Tensor]":
+def lowbit_ddp_comm_hook(state, bucket):  # unannotated: DDP compares annotations by identity
     """DDP communication hook: low-bit all-reduce of the bucket on a side stream.
 
     The returned future is CUDA-aware: its completion event is recorded on the side
