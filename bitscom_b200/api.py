@@ -506,6 +506,19 @@ class LowBitGroup:
             st.load_state_dict(v)
             self._ef_states[k] = st
 
+    def check_consistency(self) -> None:
+        """Collective: every rank of the group must have been built with the same codec
+        options, otherwise packed shards of different sizes would meet on the wire.
+        Raises ``RuntimeError`` on every rank when they differ."""
+        mine = (self.bitwidth, self.block_size, self.stochastic_rounding, self.error_feedback,
+                self.stage2_error_feedback, self.sr_seed)
+        everyone = [None] * self.world_size
+        dist.all_gather_object(everyone, mine, group=self.pg)
+        if any(o != everyone[0] for o in everyone):
+            raise RuntimeError(
+                "LowBitGroup options differ between ranks: "
+                + "; ".join(f"rank {r}: {o}" for r, o in enumerate(everyone)))
+
     # -- engine selection ------------------------------------------------------------
     def _fused_comm(self, tensor: torch.Tensor, group):
         """The fused communicator of ``group`` if this tensor can use it, else None."""
