@@ -29,10 +29,11 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-shared"
               "--expt-relaxed-constexpr"]
 
 # library name -> (sources, extra flags)
-LIBRARIES: Dict[str, Dict[str, List[str]]] = {
+LIBRARIES: Dict[str, dict] = {
     "bcom_codec": {"sources": ["codec_kernels.cu"], "deps": ["codec.cuh"], "flags": []},
     "bcom_comm": {"sources": ["fused_collectives.cu", "symm.cu"],
                   "deps": ["codec.cuh", "symm.h"], "flags": []},
+    "bcom_cpu": {"sources": ["cpu_codec.cc"], "deps": [], "flags": [], "host_only": True},
     "bcom_llama": {"sources": ["gemm_tcgen05.cu", "attention_tcgen05.cu", "elementwise.cu"],
                    "deps": ["tc_common.cuh"], "flags": []},
 }
@@ -85,13 +86,20 @@ def build_library(name: str, verbose: bool = False, force: bool = False) -> str:
     so = lib_path(name)
     if not force and is_current(name):
         return so
-    nvcc = nvcc_path()
-    if nvcc is None:
-        raise RuntimeError("nvcc not found; cannot build " + name)
     os.makedirs(LIBDIR, exist_ok=True)
-    cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + spec["flags"] + ["-I", CSRC]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
+    if spec.get("host_only"):
+        cxx = shutil.which("g++") or shutil.which("c++")
+        if cxx is None:
+            raise RuntimeError("g++ not found; cannot build " + name)
+        # -ffp-contract=off: the codec must round every operation like the host quantizer
+        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-I", CSRC]
+    else:
+        nvcc = nvcc_path()
+        if nvcc is None:
+            raise RuntimeError("nvcc not found; cannot build " + name)
+        cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + spec["flags"] + ["-I", CSRC]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
     cmd += ["-o", so + ".tmp"] + sources
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
@@ -119,7 +127,7 @@ def load_library(name: str) -> ctypes.CDLL:
             return _loaded[name]
         so = lib_path(name)
         if not is_current(name):
-            if nvcc_path() is not None:
+            if nvcc_path() is not None or LIBRARIES[name].get("host_only"):
                 build_library(name)
             elif not os.path.exists(so):
                 raise RuntimeError(f"{so} is missing and nvcc is not available")
