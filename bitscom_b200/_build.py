@@ -59,7 +59,7 @@ def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + spec["flags"]).encode())
     for path in _existing(spec["sources"]) + _existing(spec["deps"]):
-        h.update(path.encode())
+        h.update(os.path.basename(path).encode())  # not the absolute path: the tree moves
         with open(path, "rb") as f:
             h.update(f.read())
     return h.hexdigest()
@@ -100,15 +100,18 @@ def build_library(name: str, verbose: bool = False, force: bool = False) -> str:
         cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + spec["flags"] + ["-I", CSRC]
         if verbose:
             cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", so + ".tmp"] + sources
+    tmp = f"{so}.{os.getpid()}.tmp"  # several ranks may build at once: private file, atomic rename
+    cmd += ["-o", tmp] + sources
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed for {name}:\n{proc.stdout}\n{proc.stderr}")
+        raise RuntimeError(f"compiler failed for {name}:\n{proc.stdout}\n{proc.stderr}")
     if verbose:
         sys.stderr.write(proc.stderr)
-    os.replace(so + ".tmp", so)
-    with open(so + ".sha", "w") as f:
+    os.replace(tmp, so)
+    stamp_tmp = f"{so}.sha.{os.getpid()}.tmp"
+    with open(stamp_tmp, "w") as f:
         f.write(_digest(name))
+    os.replace(stamp_tmp, so + ".sha")
     return so
 
 

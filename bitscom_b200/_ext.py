@@ -46,7 +46,7 @@ def build_backend_extension(verbose: bool = False) -> str:
     from torch.utils import cpp_extension
 
     _build.build_library("bcom_comm")
-    build_dir = os.path.join(_build.LIBDIR, "_build_" + NAME)
+    build_dir = os.path.join(_build.LIBDIR, f"_build_{NAME}_{os.getpid()}")
     os.makedirs(build_dir, exist_ok=True)
     nccl_inc = []
     for base in sys.path:
@@ -63,8 +63,10 @@ def build_backend_extension(verbose: bool = False) -> str:
         with_cuda=True, is_python_module=False)
     built = os.path.join(build_dir, NAME + ".so")
     os.replace(built, _so_path())
-    with open(_so_path() + ".sha", "w") as f:
+    stamp_tmp = f"{_so_path()}.sha.{os.getpid()}.tmp"
+    with open(stamp_tmp, "w") as f:
         f.write(_digest())
+    os.replace(stamp_tmp, _so_path() + ".sha")
     return _so_path()
 
 

@@ -113,9 +113,78 @@ def gemm(args):
                       "torch_tflops": 2 * M * N * K / ms_ref / 1e9, "peaks": tag}))
 
 
+def attention(args):
+    from bitscom_b200.ops import attention as A
+
+    _, tflops, tag = _peaks()
+    B, S, nh, hd = args.batch, args.seq, args.heads, 128
+    H = nh * hd
+    qkv = (torch.randn(B * S, 3 * H, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    d_out = (torch.randn(B * S, H, device="cuda") * 0.5).to(torch.bfloat16)
+    for _ in range(args.warmup):
+        A.attention(qkv, B, S, nh, hd).backward(d_out)
+    outs = []
+    ms_f = _timed(lambda i: outs.append(A.attention(qkv, B, S, nh, hd)), args.iters)
+    ms_b = _timed(lambda i: outs[i].backward(d_out), args.iters)
+    A.check_status()
+    flops = 4.0 * B * nh * S * S * hd / 2
+    q, k, v = (qkv.detach()[:, i * H:(i + 1) * H].view(B, S, nh, hd).transpose(1, 2)
+               for i in range(3))
+    ms_ref = _timed(lambda i: torch.nn.functional.scaled_dot_product_attention(
+        q, k, v, is_causal=True), args.iters)
+    print(json.dumps({"case": "attention_tcgen05", "batch": B, "seq": S, "heads": nh,
+                      "fwd_ms": ms_f, "fwd_tflops": flops / ms_f / 1e9,
+                      "fwd_frac_bf16_peak": flops / ms_f / 1e9 / tflops,
+                      "bwd_ms": ms_b, "bwd_tflops": 2.5 * flops / ms_b / 1e9,
+                      "bwd_frac_bf16_peak": 2.5 * flops / ms_b / 1e9 / tflops,
+                      "sdpa_fwd_ms": ms_ref, "peaks": tag}))
+
+
+def elementwise(args):
+    from bitscom_b200.ops import nn as K
+
+    hbm, _, tag = _peaks()
+    T, H, F, V = args.tokens, 4096, 11008, 32000
+    rows = []
+
+    def bf(*shape):
+        return (torch.randn(*shape, device="cuda") * 0.5).to(torch.bfloat16)
+
+    x, w = bf(T, H).requires_grad_(), bf(H).requires_grad_()
+    w.main_grad = torch.zeros(H, device="cuda")
+    dy = bf(T, H)
+    y = K.rmsnorm(x, w)
+    ms = _timed(lambda i: K.rmsnorm(x, w), args.iters)
+    rows.append(("rmsnorm_fwd", ms, 2 * T * H * 2))
+    ms = _timed(lambda i: K.rmsnorm(x, w).backward(dy), args.iters) - ms
+    rows.append(("rmsnorm_bwd", ms, 3 * T * H * 2))
+    gu, dh = bf(T, 2 * F).requires_grad_(), bf(T, F)
+    ms_f = _timed(lambda i: K.swiglu(gu), args.iters)
+    rows.append(("swiglu_fwd", ms_f, 3 * T * F * 2))
+    ms = _timed(lambda i: K.swiglu(gu).backward(dh), args.iters) - ms_f
+    rows.append(("swiglu_bwd", ms, 5 * T * F * 2))
+    logits = bf(T, V)
+    tgt = torch.randint(1, V, (T,), device="cuda")
+    ms = _timed(lambda i: K.cross_entropy(logits, tgt, 0), args.iters)
+    rows.append(("cross_entropy_fwd_bwd", ms, 4 * T * V * 2))
+    n = 1 << 28
+    master, grad = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    opt = K.FlatAdamW(master, grad, torch.empty(n, device="cuda", dtype=torch.bfloat16))
+    opt.step()
+    ms = _timed(lambda i: opt.step(), args.iters)
+    rows.append(("adamw_flat", ms, n * 34))
+    print(json.dumps({"case": "elementwise", "tokens": T, "peaks": tag, "kernels": [
+        {"name": nm, "ms": ms, "gbs": b / ms / 1e6, "frac_hbm": b / ms / 1e6 / hbm}
+        for nm, ms, b in rows]}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["fused", "codec", "gemm"])
+    ap.add_argument("case", choices=["fused", "codec", "gemm", "attention", "elementwise"])
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--elems", type=int, default=1 << 25)
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--world", type=int, default=2)
@@ -129,7 +198,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
-    {"fused": fused, "codec": codec, "gemm": gemm}[args.case](args)
+    {"fused": fused, "codec": codec, "gemm": gemm, "attention": attention,
+     "elementwise": elementwise}[args.case](args)
 
 
 if __name__ == "__main__":

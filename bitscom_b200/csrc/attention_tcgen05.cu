@@ -39,7 +39,8 @@ constexpr int HD = 128;           // head dim
 constexpr int BQ = 128;           // query rows per CTA (forward) / per iteration (backward)
 constexpr int BKF = 64;           // keys per iteration, forward
 constexpr int BKB = 128;          // keys per CTA, backward
-constexpr int kThreads = 128;
+constexpr int kThreads = 128;      // forward
+constexpr int kBwdThreads = 256;   // backward: two warps share each TMEM lane quarter
 constexpr unsigned long long kBudgetNs = 2000000000ull;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -295,7 +296,7 @@ struct BwdShared {
 constexpr int TILE = 128 * HD * 2;  // 32 KiB: every backward tile is 128 x 128 bf16
 constexpr int BWD_SMEM = 6 * TILE + 1024 + sizeof(BwdShared) + 64;
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 128} over qkv
                      const __grid_constant__ CUtensorMap tm_do,    // box {64, 128} over dO
                      const BwdParams p) {
@@ -311,6 +312,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   BwdShared* sh = reinterpret_cast<BwdShared*>(sDS + TILE);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  // Warps w and w + 4 may read the same 32 TMEM lanes; they split the columns. `row` is the
+  // key row (and later the query row of dQ) this thread owns, `half` its column half.
+  const int row = ((warp & 3) << 5) | (tid & 31);
+  const int half = warp >> 2;
   const int kblocks = p.seq / BKB;
   const int kb = (int)(blockIdx.x % kblocks);  // early key blocks (most work) first
   const int bh = blockIdx.x / kblocks;
@@ -334,7 +339,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   tc::tc_fence_after_sync();
   const uint32_t tmem = sh->tmem_base;
   const uint32_t tST = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 384, tDQ = tmem;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
   auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int col, int row) {
     tc::tma_load_2d(dst, map, bar, col, row);
@@ -359,7 +364,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   constexpr uint32_t idesc_nn = tc::make_idesc_bf16(128, 128, true, true);    // both MN-major
   const uint32_t aK = tc::smem_u32(sK), aV = tc::smem_u32(sV), aQ = tc::smem_u32(sQ),
                  aDO = tc::smem_u32(sDO), aPT = tc::smem_u32(sPT), aDS = tc::smem_u32(sDS);
-  const int key_idx = kb * BKB + tid;  // this thread's key position inside the sequence
+  const int key_idx = kb * BKB + row;  // this thread's key position inside the sequence
 
   if (!tc::mbar_wait(&sh->bar_kv, 0, kBudgetNs)) { sh->abort = 1; record_fail(11); }
 
@@ -369,8 +374,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
     // row statistics of the 128 queries of this block
     {
       const size_t base = ((size_t)b * p.heads + h) * p.seq + qpos0;
-      sh->lse[tid] = p.lse2[base + tid];
-      sh->delta[tid] = p.delta[base + tid];
+      if (tid < BQ) {
+        sh->lse[tid] = p.lse2[base + tid];
+        sh->delta[tid] = p.delta[base + tid];
+      }
     }
     // ---- S^T = K Q^T and dP^T = V dO^T ----
     if (tid == 0) {
@@ -392,7 +399,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
     // ---- P^T and dS^T for this thread's key row, 32 query columns at a time ----
     const bool diagonal = qi == 0;
 #pragma unroll 1
-    for (int c = 0; c < BQ / 32; ++c) {
+    for (int c = half * (BQ / 64); c < (half + 1) * (BQ / 64); ++c) {
       uint32_t rs[32], rd[32];
       tc::tmem_ld_32x32(tST + lane_addr + c * 32, rs);
       tc::tmem_ld_32x32(tDP + lane_addr + c * 32, rd);
@@ -419,7 +426,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
         w.y = pack_bf16(ds[u * 8 + 2], ds[u * 8 + 3]);
         w.z = pack_bf16(ds[u * 8 + 4], ds[u * 8 + 5]);
         w.w = pack_bf16(ds[u * 8 + 6], ds[u * 8 + 7]);
-        const uint32_t off = chunk * 128 * 128 + swz(tid, c8_0 + u);
+        const uint32_t off = chunk * 128 * 128 + swz(row, c8_0 + u);
         *reinterpret_cast<uint4*>(sPT + off) = v;
         *reinterpret_cast<uint4*>(sDS + off) = w;
       }
@@ -453,9 +460,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
 
     // ---- dQ rows (thread t <-> query row t) into the fp32 buffer ----
     {
-      float* dst = p.dq_acc + (size_t)(b * p.seq + qpos0 + tid) * H + q_col;
+      float* dst = p.dq_acc + (size_t)(b * p.seq + qpos0 + row) * H + q_col;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t r[32];
         tc::tmem_ld_32x32(tDQ + lane_addr + c * 32, r);
         tc::tmem_wait_ld();
@@ -474,10 +481,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   // ---- dK, dV rows (thread t <-> key row t) ----
   if (!sh->abort) {
     tc::tc_fence_after_sync();
-    __nv_bfloat16* dk = p.dqkv + (size_t)(key0 + tid) * 3 * H + k_col;
-    __nv_bfloat16* dv = p.dqkv + (size_t)(key0 + tid) * 3 * H + v_col;
+    __nv_bfloat16* dk = p.dqkv + (size_t)(key0 + row) * 3 * H + k_col;
+    __nv_bfloat16* dv = p.dqkv + (size_t)(key0 + row) * 3 * H + v_col;
 #pragma unroll 1
-    for (int c = 0; c < HD / 32; ++c) {
+    for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
       uint32_t r[32];
       tc::tmem_ld_32x32(tDK + lane_addr + c * 32, r);
       tc::tmem_wait_ld();
@@ -678,7 +685,7 @@ int bcom_attention_bwd(const void* qkv, const void* out, const void* d_out, cons
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   const int grid = batch * heads * (seq / BKB);
-  attention_bwd_kernel<<<grid, kThreads, BWD_SMEM, st>>>(tm_qkv, tm_do, p);
+  attention_bwd_kernel<<<grid, kBwdThreads, BWD_SMEM, st>>>(tm_qkv, tm_do, p);
   attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>((float*)dq_acc, (__nv_bfloat16*)dqkv, tokens,
                                                      H);
   return (int)cudaGetLastError();

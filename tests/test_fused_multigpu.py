@@ -23,6 +23,8 @@ def _input(rank, n, it, dtype):
 def _worker(rank, world, n, bits, dtype, iters):
     from bitscom_b200 import LowBitGroup
 
+    torch.set_num_threads(1)  # every rank replays the golden model on the CPU
+
     group = LowBitGroup(bitwidth=bits, error_feedback=True, stage2_error_feedback=True,
                         stochastic_rounding=True, sr_seed=5, fused=True)
     state = SimState()
@@ -72,4 +74,4 @@ def test_all_gpus_all_reduce_bit_exact():
     n_gpus = torch.cuda.device_count() if torch.cuda.is_available() else 0
     if n_gpus < 4:
         pytest.skip("needs 4 or more GPUs")
-    run_ranks(_worker, n_gpus, 1 << 20, 4, torch.float32, 2, backend="nccl")
+    run_ranks(_worker, n_gpus, 1 << 17, 4, torch.float32, 2, backend="nccl", timeout=600)
