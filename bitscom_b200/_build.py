@@ -35,7 +35,7 @@ LIBRARIES: Dict[str, dict] = {
                   "deps": ["codec.cuh", "symm.h"], "flags": []},
     "bcom_cpu": {"sources": ["cpu_codec.cc"], "deps": [], "flags": [], "host_only": True},
     "bcom_llama": {"sources": ["gemm_tcgen05.cu", "attention_tcgen05.cu", "elementwise.cu"],
-                   "deps": ["tc_common.cuh"], "flags": []},
+                   "deps": ["tc_common.cuh", "no_alloc.h"], "flags": []},
 }
 
 _lock = threading.Lock()

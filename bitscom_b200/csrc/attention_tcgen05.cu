@@ -701,3 +701,106 @@ int bcom_attention_status(unsigned int out[4], int clear) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the backward pass (declared in no_alloc.h).
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace attn {
+
+// Scratch that ships inside the library image: [ dQ accumulator | row statistics ].
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[BCOM_NO_ALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static void* g_scratch_addr[kMaxDevices];
+static std::mutex g_scratch_mu;
+
+// Device address of the scratch array on the current device; looked up once per device.
+static cudaError_t no_alloc_scratch_ptr(unsigned char** out) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    err = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
+    if (err != cudaSuccess) return err;
+    g_scratch_addr[dev] = p;
+  }
+  *out = static_cast<unsigned char*>(g_scratch_addr[dev]);
+  return cudaSuccess;
+}
+
+}  // namespace attn
+
+extern "C" {
+
+unsigned long long bcom_no_alloc_scratch_bytes(void) { return BCOM_NO_ALLOC_SCRATCH_BYTES; }
+
+int bcom_attention_bwd_no_alloc(const void* qkv, const void* out, const void* d_out,
+                                const void* lse2, void* dqkv, int batch, int seq, int heads,
+                                int head_dim, float scale, void* stream) {
+  using namespace attn;
+  if (head_dim != HD || seq % BQ || batch <= 0 || heads <= 0) return 1001;
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)d_out & 15) || ((uintptr_t)dqkv & 15)) return 1002;
+  const long long tokens = (long long)batch * seq;
+  const int H = heads * HD;
+  const unsigned long long dq_bytes = 4ull * (unsigned long long)tokens * (unsigned long long)H;
+  const unsigned long long delta_bytes =
+      (4ull * (unsigned long long)tokens * (unsigned long long)heads + 255ull) & ~255ull;
+  if (dq_bytes + delta_bytes > BCOM_NO_ALLOC_SCRATCH_BYTES) {
+    fprintf(stderr,
+            "bitscom_b200: bcom_attention_bwd_no_alloc needs %llu bytes of scratch for "
+            "batch=%d seq=%d heads=%d but the built-in array holds %u; use "
+            "bcom_attention_bwd with caller-provided buffers\n",
+            dq_bytes + delta_bytes, batch, seq, heads, BCOM_NO_ALLOC_SCRATCH_BYTES);
+    return 1006;
+  }
+  unsigned char* scratch = nullptr;
+  cudaError_t err = no_alloc_scratch_ptr(&scratch);  // also binds this thread's context
+  if (err != cudaSuccess) return (int)err;
+  (void)cudaGetLastError();
+  cudaStream_t st = (cudaStream_t)stream;
+  float* dq_acc = reinterpret_cast<float*>(scratch);
+  float* delta = reinterpret_cast<float*>(scratch + dq_bytes);
+  // the accumulator must start at zero; the array still holds the previous call's data
+  err = cudaMemsetAsync(dq_acc, 0, dq_bytes, st);
+  if (err != cudaSuccess) return (int)err;
+
+  CUtensorMap tm_qkv, tm_do;
+  if (make_map(&tm_qkv, qkv, tokens, 3 * H, 64, 128)) return 1003;
+  if (make_map(&tm_do, d_out, tokens, H, 64, 128)) return 1004;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+  });
+  if (attr_err != cudaSuccess) return 1005;
+  {
+    const long long warps = tokens * heads;
+    const int grid = (int)((warps * 32 + 255) / 256);
+    attention_delta_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)out,
+                                                 (const __nv_bfloat16*)d_out, delta, batch, seq,
+                                                 heads);
+  }
+  BwdParams p;
+  p.dqkv = (__nv_bfloat16*)dqkv;
+  p.dq_acc = dq_acc;
+  p.lse2 = (const float*)lse2;
+  p.delta = delta;
+  p.batch = batch;
+  p.seq = seq;
+  p.heads = heads;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  const int grid = batch * heads * (seq / BKB);
+  attention_bwd_kernel<<<grid, kBwdThreads, BWD_SMEM, st>>>(tm_qkv, tm_do, p);
+  attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"
