@@ -103,6 +103,10 @@ int bcom_comm_status(BcomComm* c, unsigned int out[8]) {
   return 0;
 }
 
+// Host address of the 8-word status record (pinned, written by the kernels): lets a caller
+// poll status[0] without a library call.
+void* bcom_comm_status_host(BcomComm* c) { return c->status_host; }
+
 int bcom_comm_reset(BcomComm* c, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   BCOM_TRY(cudaStreamSynchronize(st));

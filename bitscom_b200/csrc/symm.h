@@ -75,6 +75,8 @@ size_t bcom_comm_region_bytes(BcomComm* comm);
 long long bcom_comm_max_chunk(BcomComm* comm, int bits, int block);
 // copies the 8-word status record; status[0] != 0 means the last kernels gave up
 int bcom_comm_status(BcomComm* comm, unsigned int out[8]);
+// host address of that record (pinned memory the kernels write), for polling without a call
+void* bcom_comm_status_host(BcomComm* comm);
 // clears status, flags stay; zeroes the local arrival counters (after an error)
 int bcom_comm_reset(BcomComm* comm, void* stream);
 int bcom_comm_set_timeout_ms(BcomComm* comm, double ms);

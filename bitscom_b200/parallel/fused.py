@@ -70,6 +70,8 @@ def _get():
             lib.bcom_comm_max_chunk.argtypes = [vp, ci, ci]
             lib.bcom_comm_max_chunk.restype = ll
             lib.bcom_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint * 8)]
+            lib.bcom_comm_status_host.argtypes = [vp]
+            lib.bcom_comm_status_host.restype = vp
             lib.bcom_comm_reset.argtypes = [vp, vp]
             lib.bcom_comm_set_timeout_ms.argtypes = [vp, ctypes.c_double]
             lib.bcom_comm_epoch.argtypes = [vp]
@@ -133,6 +135,12 @@ class _NativeComm:
             check(self.lib.bcom_comm_create(rank, world, region_bytes, ctypes.byref(handle)),
                   "bcom_comm_create")
         self.handle = handle
+        # live view of the pinned status record: word 0 != 0 means a kernel gave up
+        self._status_view = (ctypes.c_uint * 8).from_address(
+            self.lib.bcom_comm_status_host(handle))
+
+    def failed(self) -> bool:
+        return self._status_view[0] != 0
 
     def ipc_handle(self) -> bytes:
         buf = ctypes.create_string_buffer(64)
@@ -221,6 +229,8 @@ class FusedLowBitComm:
 
     def check_status(self) -> None:
         """Raise if a kernel of this communicator gave up waiting; re-arm afterwards."""
+        if not self.native.failed():
+            return
         status = self.native.status()
         if status[0] != 0:
             self.native.reset()
@@ -234,16 +244,22 @@ class FusedLowBitComm:
     def _launch(self, args: CollArgs, async_op: bool, keep):
         from ..api import _CudaEventWork
 
-        self.check_status()
+        if self.native.failed():
+            self.check_status()
         cur = torch.cuda.current_stream(self.device)
         stream = cur
         if async_op:
             stream = self.side_stream
             stream.wait_stream(cur)
-        with torch.cuda.device(self.device):
-            check(self.native.lib.bcom_collective(
-                self.native.handle, ctypes.byref(args), ctypes.c_void_p(stream.cuda_stream)),
-                "bcom_collective")
+        if torch.cuda.current_device() == self.device.index:
+            rc = self.native.lib.bcom_collective(
+                self.native.handle, ctypes.byref(args), ctypes.c_void_p(stream.cuda_stream))
+        else:
+            with torch.cuda.device(self.device):
+                rc = self.native.lib.bcom_collective(
+                    self.native.handle, ctypes.byref(args), ctypes.c_void_p(stream.cuda_stream))
+        if rc:
+            check(rc, "bcom_collective")
         self.launches += 1
         _timing.add("fused_launches")
         if not async_op:
@@ -271,7 +287,6 @@ class FusedLowBitComm:
             res1, res2 = ef.stage1, (ef.stage2 if stage2 else None)
         args = _args(tensor, tensor, res1, res2, n, plan.shard_len, tensor.dtype, bitwidth,
                      block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, self.max_ctas)
-        _timing.add("fused_allreduce_elems", n)
         return self._launch(args, async_op, (tensor, res1, res2))
 
     def reduce_scatter(self, output: torch.Tensor, input: torch.Tensor, *, bitwidth: int,
