@@ -8,7 +8,8 @@ Config: 32 layers, hidden 4096, 32 heads, FFN 11008 SwiGLU, RMSNorm, RoPE, vocab
 sequence 2048, bf16 compute with fp32 master weights, AdamW.  N = 1 runs one stage; N >= 2
 runs PP = 2 with 1F1B over NCCL p2p and DP = N / 2 with the 4-bit low-bit gradient
 all-reduce (error feedback on).  Per-GPU work is fixed as N grows (weak scaling): each
-data-parallel replica processes 4 * PP micro-batches of one sequence per step.
+data-parallel replica processes 4 * PP micro-batches of two sequences per step (16384
+tokens per GPU per step).
 
 Two timed regions of K steps each, both bracketed by barrier + synchronize and timed
 with CUDA events (max over ranks):
@@ -113,7 +114,7 @@ def run_ours(args):
     mcfg.attention = args.attention or _default_attention()
     seq = 2048 if args.model == "llama7b" else 256
     tcfg = TrainerConfig(pp_size=pp, micro_batches=args.micro_batches or 4 * pp,
-                         micro_batch_size=1, seq_length=seq, bitwidth=4,
+                         micro_batch_size=args.micro_batch_size, seq_length=seq, bitwidth=4,
                          error_feedback=True, dp_sync=args.dp_sync, local_size=args.local_size)
     trainer = LlamaTrainer(mcfg, tcfg)
     rank, dev = trainer.rank, trainer.device
@@ -231,6 +232,7 @@ def main():
     ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
     ap.add_argument("--pp", type=int, default=0)
     ap.add_argument("--micro-batches", type=int, default=0)
+    ap.add_argument("--micro-batch-size", type=int, default=2, help="sequences per micro-batch")
     ap.add_argument("--attention", default=None, choices=[None, "tcgen05", "sdpa"])
     ap.add_argument("--dp-sync", default="pipeline_a", choices=["pipeline_a", "flat", "dense"])
     ap.add_argument("--local-size", type=int, default=1)

@@ -102,10 +102,27 @@ def gemm(args):
     copies = max(1, min(8, (256 << 20) // max(1, (M * K + N * K) * 2)))
     As = [(torch.randn(M, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
     Bs = [(torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
+    if args.wgrad:
+        # weight-gradient form: dW[M, N] += dY^T X with dY stored [K, M], X stored [K, N]
+        As = [(torch.randn(K, M, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
+        Bs = [(torch.randn(K, N, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
+        acc = torch.zeros(M, N, device="cuda")
+
+        def run(i):
+            G.gemm(As[i % copies], Bs[i % copies], a_mn_major=True, b_mn_major=True, out=acc,
+                   accumulate=True)
+    else:
+        def run(i):
+            G.gemm(As[i % copies], Bs[i % copies])
     for i in range(args.warmup):
-        G.gemm(As[i % copies], Bs[i % copies])
-    ms = _timed(lambda i: G.gemm(As[i % copies], Bs[i % copies]), args.iters)
+        run(i)
+    ms = _timed(run, args.iters)
     G.check_status()
+    if args.wgrad:
+        tf = 2 * M * N * K / ms / 1e9
+        print(json.dumps({"case": "gemm_tcgen05_wgrad_fp32_accumulate", "M": M, "N": N, "K": K,
+                          "ms": ms, "tflops": tf, "frac_bf16_peak": tf / tflops, "peaks": tag}))
+        return
     ms_ref = _timed(lambda i: torch.matmul(As[i % copies], Bs[i % copies].t()), args.iters)
     tf = 2 * M * N * K / ms / 1e9
     print(json.dumps({"case": "gemm_tcgen05", "M": M, "N": N, "K": K, "ms": ms, "tflops": tf,
@@ -200,6 +217,7 @@ def main(argv=None):
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--wgrad", action="store_true")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)

@@ -106,7 +106,7 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
 // Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dw partial in registers
 // (thread t owns columns t*8 + k*blockDim*8), adding it to dw once at the end.
 template <int MAX_ITERS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                    const bf16* __restrict__ w, const float* __restrict__ rstd,
                    bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
@@ -417,23 +417,24 @@ int bcom_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* r
                      void* dw_fp32, int rows, int H, void* stream) {
   if (rows <= 0) return 0;
   if (H % 8) return (int)cudaErrorInvalidValue;
-  const int grid = rows < 148 * 4 ? rows : 148 * 4;
-  const int iters = (H / 8 + 255) / 256;
+  // few, fat CTAs: every CTA ends with H atomic adds into dw, so their number matters
+  const int grid = rows < 148 * 2 ? rows : 148 * 2;
+  const int iters = (H / 8 + 511) / 512;
   cudaStream_t st = (cudaStream_t)stream;
   if (iters <= 1)
-    rmsnorm_bwd_kernel<1><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+    rmsnorm_bwd_kernel<1><<<grid, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
                                                 (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
                                                 rows, H);
   else if (iters <= 2)
-    rmsnorm_bwd_kernel<2><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+    rmsnorm_bwd_kernel<2><<<grid, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
                                                 (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
                                                 rows, H);
   else if (iters <= 4)
-    rmsnorm_bwd_kernel<4><<<grid, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+    rmsnorm_bwd_kernel<4><<<grid, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
                                                 (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
                                                 rows, H);
   else
-    return (int)cudaErrorInvalidValue;  // H up to 8192
+    return (int)cudaErrorInvalidValue;  // H up to 16384
   return (int)cudaGetLastError();
 }
 
