@@ -528,11 +528,13 @@ class LowBitGroup:
             return None
         comm = self._fused_comms.get(id(group))
         if comm is None:
-            try:
-                from .parallel.fused import FusedLowBitComm
+            from .parallel.fused import FusedLowBitComm, FusedUnavailable
 
+            try:
                 comm = FusedLowBitComm.for_group(group, tensor.device)
-            except Exception:
+            except FusedUnavailable:
+                # benign: several hosts / too many ranks.  A missing native library is not
+                # caught here: on a GPU machine it must fail loudly.
                 if self.fused is True:
                     raise
                 comm = False

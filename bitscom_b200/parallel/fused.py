@@ -100,6 +100,12 @@ class FusedCollectiveError(RuntimeError):
     pass
 
 
+class FusedUnavailable(RuntimeError):
+    """The group cannot use the fused path for a benign reason (ranks on several hosts, too
+    many ranks); callers fall back to NCCL collectives.  A missing or broken native library is
+    NOT this: it raises ``NativeError``."""
+
+
 def _keys(stochastic: bool, seed: Optional[int]):
     if not stochastic:
         return 0, 0
@@ -189,11 +195,11 @@ class FusedLowBitComm:
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         if self.world > 16:
-            raise NativeError("fused collectives support at most 16 ranks")
+            raise FusedUnavailable("fused collectives support at most 16 ranks")
         hosts: List[Optional[str]] = [None] * self.world
         dist.all_gather_object(hosts, socket.gethostname(), group=group)
         if len(set(hosts)) != 1:
-            raise NativeError("fused collectives need all ranks on one NVSwitch domain")
+            raise FusedUnavailable("fused collectives need all ranks on one NVSwitch domain")
         self.native = _NativeComm(self.rank, self.world,
                                   region_bytes or default_region_bytes(), self.device)
         handles: List[Optional[bytes]] = [None] * self.world

@@ -54,7 +54,7 @@ class GradBucketSync:
             dist.all_reduce(bucket, group=self.group.pg)
             if self.post_scale != 1.0:
                 bucket.mul_(self.post_scale)
-        elif self.mode == "pipeline_a":
+        elif self.mode == "pipeline_a" and self.local_group is not None:
             self.group.all_reduce(bucket, local_group=self.local_group,
                                   inter_group=self.inter_group, chunk_size=self.chunk_size,
                                   ef_key=key)

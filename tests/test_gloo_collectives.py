@@ -132,3 +132,27 @@ def _pipeline_singleton_worker(rank, world):
 
 def test_pipeline_a_singleton_local_groups():
     run_ranks(_pipeline_singleton_worker, 2)
+
+
+def _bucket_sync_worker(rank, world):
+    from bitscom_b200.parallel.hooks import GradBucketSync
+
+    group = LowBitGroup(bitwidth=4, error_feedback=True)
+    n = 5000
+    ranges = [(3000, 2000), (0, 3000)]          # backward order: last slice first
+    flat = torch.zeros(n)
+    sync = GradBucketSync(group, flat, ranges, mode="flat")
+    states = [SimState(), SimState()]
+    for it in range(3):
+        everyone = [_rank_input(r, n, it) for r in range(world)]
+        flat.copy_(everyone[rank])
+        sync.on_ready(0)                          # slice 0 is final early ...
+        sync.finish()                             # ... the rest at the end
+        for idx, (start, length) in enumerate(ranges):
+            want = simulate_all_reduce([e[start:start + length] for e in everyone], 4, 256,
+                                       state=states[idx])[rank] * (1.0 / world)
+            assert torch.equal(flat[start:start + length], want), (it, idx)
+
+
+def test_grad_bucket_sync_matches_model_with_per_bucket_residuals():
+    run_ranks(_bucket_sync_worker, 2)
