@@ -28,15 +28,20 @@ def _peaks():
     return 6650.0, 1590.0, "of fallback"
 
 
-def _timed(fn, iters):
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    s.record()
-    for i in range(iters):
-        fn(i)
-    e.record()
-    torch.cuda.synchronize()
-    return s.elapsed_time(e) / iters
+def _timed(fn, iters, reps=3):
+    """Mean time of ``iters`` back-to-back launches, median over ``reps`` repetitions (one
+    slow launch on a cold box would otherwise dominate a five-launch mean)."""
+    means = []
+    for r in range(reps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for i in range(iters):
+            fn(r * iters + i)  # a running index: a case may consume one item per call
+        e.record()
+        torch.cuda.synchronize()
+        means.append(s.elapsed_time(e) / iters)
+    return sorted(means)[len(means) // 2]
 
 
 def fused(args):

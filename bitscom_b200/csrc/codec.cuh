@@ -55,7 +55,7 @@ __device__ __forceinline__ float sr_uniform(uint32_t key, uint32_t idx) {
 }
 
 // ---------------------------------------------------------------------------
-// typed 8-element loads / stores (vector form needs a 16-byte aligned address)
+// typed 8-element loads / stores (vector form: 32-byte aligned fp32, 16-byte aligned 2-byte types)
 // ---------------------------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<float> {
@@ -71,13 +71,33 @@ template <> struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
 
+// fp32 groups move as ONE 256-bit access (ld/st.global.v8.f32, sm_100): every store
+// instruction then writes whole 32-byte sectors, which two 128-bit stores per thread do not
+// (each would write half of every sector it touches).  The address must be 32-byte aligned
+// for fp32 and 16-byte aligned for the 2-byte types; the launchers check that.
+__device__ __forceinline__ void ld256_nc(const float* p, float (&v)[GROUP]) {
+  asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]),
+                 "=f"(v[6]), "=f"(v[7])
+               : "l"(p));
+}
+__device__ __forceinline__ void ld256(const float* p, float (&v)[GROUP]) {
+  asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]),
+                 "=f"(v[6]), "=f"(v[7])
+               : "l"(p)
+               : "memory");
+}
+__device__ __forceinline__ void st256(float* p, const float (&v)[GROUP]) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v[0]),
+               "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
+}
+
 template <typename T>
 __device__ __forceinline__ void load8_vec(const T* __restrict__ p, float (&v)[GROUP]) {
   if constexpr (sizeof(T) == 4) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    ld256_nc(reinterpret_cast<const float*>(p), v);
   } else {
     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
     const T* h = reinterpret_cast<const T*>(&raw);
@@ -90,10 +110,7 @@ __device__ __forceinline__ void load8_vec(const T* __restrict__ p, float (&v)[GR
 template <typename T>
 __device__ __forceinline__ void load8_vec_coherent(const T* p, float (&v)[GROUP]) {
   if constexpr (sizeof(T) == 4) {
-    const float4 a = *reinterpret_cast<const float4*>(p);
-    const float4 b = *(reinterpret_cast<const float4*>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    ld256(reinterpret_cast<const float*>(p), v);
   } else {
     const uint4 raw = *reinterpret_cast<const uint4*>(p);
     const T* h = reinterpret_cast<const T*>(&raw);
@@ -113,8 +130,7 @@ __device__ __forceinline__ void load8_guard(const T* p, long long base, long lon
 template <typename T>
 __device__ __forceinline__ void store8_vec(T* p, const float (&v)[GROUP]) {
   if constexpr (sizeof(T) == 4) {
-    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
-    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    st256(reinterpret_cast<float*>(p), v);
   } else {
     uint4 raw;
     T* h = reinterpret_cast<T*>(&raw);
@@ -223,30 +239,46 @@ __device__ __forceinline__ int quant1(float x, float sf, uint32_t key, uint32_t 
   return quant1<BITS, SR>(x, sf, key, idx, &unused);
 }
 
-// Quantize + dequantize a group of 8 starting at index idx0: q gets the codes,
-// d the dequantized values (code * sf).
+// Quantize + dequantize a group of 8 starting at index idx0: q gets the codes, d the
+// dequantized values (code * sf).  The two rare cases (underflowed scale, odd first index)
+// are decided once per group, so the per-element code is branch-free.
 template <int BITS, bool SR>
 __device__ __forceinline__ void quant8_dq(const float (&x)[GROUP], float sf, uint32_t key,
                                           uint32_t idx0, int (&q)[GROUP], float (&d)[GROUP]) {
-  const Divider div(sf);
+  float n[GROUP];
+  if (__builtin_expect(sf == 0.0f, 0)) {
 #pragma unroll
-  for (int i = 0; i < GROUP; i += 2) {
-    float u0 = 0.0f, u1 = 0.0f;
-    if constexpr (SR) {
-      if ((idx0 & 1u) == 0u) {  // the usual case: both elements share one hash
-        const uint32_t h = sr_hash(key, (idx0 + i) >> 1);
-        u0 = sr_u16(h & 0xFFFFu);
-        u1 = sr_u16(h >> 16);
-      } else {
-        u0 = sr_uniform(key, idx0 + i);
-        u1 = sr_uniform(key, idx0 + i + 1);
-      }
+    for (int i = 0; i < GROUP; ++i) n[i] = __fdiv_rn(fabsf(x[i]), sf);
+  } else {
+    const float y = __frcp_rn(sf);  // see Divider: correctly rounded quotients
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) {
+      const float a = fabsf(x[i]);
+      const float q0 = __fmul_rn(a, y);
+      n[i] = __fmaf_rn(__fmaf_rn(-q0, sf, a), y, q0);
     }
-    float c0, c1;
-    q[i] = quant_core<BITS, SR>(x[i], div(fabsf(x[i])), u0, &c0);
-    q[i + 1] = quant_core<BITS, SR>(x[i + 1], div(fabsf(x[i + 1])), u1, &c1);
-    d[i] = __fmul_rn(c0, sf);
-    d[i + 1] = __fmul_rn(c1, sf);
+  }
+  float u[GROUP];
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) u[i] = 0.0f;
+  if constexpr (SR) {
+    if ((idx0 & 1u) == 0u) {  // the usual case: two elements share one hash
+#pragma unroll
+      for (int i = 0; i < GROUP; i += 2) {
+        const uint32_t h = sr_hash(key, (idx0 + i) >> 1);
+        u[i] = sr_u16(h & 0xFFFFu);
+        u[i + 1] = sr_u16(h >> 16);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) u[i] = sr_uniform(key, idx0 + i);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    float cf;
+    q[i] = quant_core<BITS, SR>(x[i], n[i], u[i], &cf);
+    d[i] = __fmul_rn(cf, sf);
   }
 }
 

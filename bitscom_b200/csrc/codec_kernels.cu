@@ -331,7 +331,9 @@ int bcom_blockwise_quantize_pack(const void* x, int dtype, long long n, int bits
                                  void* packed, void* scales, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-  const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)packed & 15) == 0;
+  // 8-element groups move as one access: 32 bytes for fp32, 16 bytes for fp16 / bf16
+  const uintptr_t in_mask = dtype == kF32 ? 31 : 15;
+  const bool aligned = ((uintptr_t)x & in_mask) == 0 && ((uintptr_t)packed & 15) == 0;
   if (fast_block(block) && aligned) {
     const long long groups = (n + GROUP - 1) / GROUP;
     const int grid = grid_for(groups, kThreads, sm_count() * 8);
@@ -364,7 +366,8 @@ int bcom_blockwise_unpack_dequantize(const void* packed, const void* scales, int
                                      void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-  const bool aligned = ((uintptr_t)out & 15) == 0 && ((uintptr_t)packed & 15) == 0;
+  const uintptr_t out_mask = dtype == kF32 ? 31 : 15;
+  const bool aligned = ((uintptr_t)out & out_mask) == 0 && ((uintptr_t)packed & 15) == 0;
   if (fast_block(block) && aligned) {
     const long long groups = (n + GROUP - 1) / GROUP;
     const int grid = grid_for(groups, kThreads, sm_count() * 8);

@@ -478,9 +478,13 @@ static long long max_chunk(size_t region_bytes, int world, int bits, int block) 
   return L;
 }
 
+// Vector path: shards start on 8-element boundaries and every tensor base is aligned to one
+// 8-element group (32 bytes for fp32 tensors and the fp32 residuals, 16 bytes for 2-byte types).
 static bool is_aligned(const BcomCollArgs& a) {
-  auto ok = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
-  return a.S % GROUP == 0 && ok(a.in) && ok(a.out) && ok(a.res1) && ok(a.res2);
+  const uintptr_t tmask = a.dtype == 0 ? 31 : 15;
+  auto ok = [](const void* p, uintptr_t mask) { return ((uintptr_t)p & mask) == 0; };
+  return a.S % GROUP == 0 && ok(a.in, tmask) && ok(a.out, tmask) && ok(a.res1, 31) &&
+         ok(a.res2, 31);
 }
 
 static int validate(const BcomComm* c, const BcomCollArgs& a) {
