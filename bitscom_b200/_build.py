@@ -92,7 +92,8 @@ def build_library(name: str, verbose: bool = False, force: bool = False) -> str:
         if cxx is None:
             raise RuntimeError("g++ not found; cannot build " + name)
         # -ffp-contract=off: the codec must round every operation like the host quantizer
-        cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-I", CSRC]
+        cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-ffp-contract=off",
+               "-fno-math-errno", "-fno-trapping-math", "-I", CSRC]
     else:
         nvcc = nvcc_path()
         if nvcc is None:

@@ -214,7 +214,15 @@ def run_train(name: str, arm: str, args, rank: int, world: int, device) -> Dict[
         acts = [torch.profiler.ProfilerActivity.CPU]
         if cuda:
             acts.append(torch.profiler.ProfilerActivity.CUDA)
-        ctx = torch.profiler.profile(activities=acts, record_shapes=True)
+        os.makedirs(args.out_dir, exist_ok=True)
+        trace_path = os.path.join(args.out_dir, f"trace_{name}_{arm}_bw{args.bitwidth}.json")
+        # a schedule makes the profiler emit one "ProfilerStep#k" range per step, which is
+        # what the stable-window analyser cuts on
+        ctx = torch.profiler.profile(
+            activities=acts, record_shapes=True,
+            schedule=torch.profiler.schedule(wait=0, warmup=0,
+                                             active=min(steps, args.profile_steps), repeat=1),
+            on_trace_ready=lambda p: p.export_chrome_trace(trace_path))
     losses: List[float] = []
     elapsed = 0.0
     with ctx as prof:
@@ -245,10 +253,7 @@ def run_train(name: str, arm: str, args, rank: int, world: int, device) -> Dict[
             if profile and step <= args.profile_steps:
                 prof.step()
     if profile:
-        os.makedirs(args.out_dir, exist_ok=True)
-        path = os.path.join(args.out_dir, f"trace_{name}_{arm}_bw{args.bitwidth}.json")
-        prof.export_chrome_trace(path)
-        print(f"saved trace: {path}")
+        print(f"saved trace: {trace_path}")
     safe = max(elapsed, 1e-9)
     return {"losses": losses, "avg_step_time_ms": safe / max(len(losses), 1) * 1e3,
             "throughput_samples_per_s": batch * len(losses) * world / safe}

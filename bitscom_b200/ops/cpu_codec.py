@@ -21,8 +21,9 @@ def _get():
             vp, ll, ci, cu = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_uint
             lib.bcom_cpu_packed_nbytes.argtypes = [ll, ci]
             lib.bcom_cpu_packed_nbytes.restype = ll
-            lib.bcom_cpu_blockwise_quantize_pack.argtypes = [vp, ll, ci, ci, ci, cu, cu, vp, vp]
-            lib.bcom_cpu_blockwise_unpack_dequantize.argtypes = [vp, vp, ci, ll, ci, vp]
+            lib.bcom_cpu_blockwise_quantize_pack_mt.argtypes = [vp, ll, ci, ci, ci, cu, cu, vp,
+                                                                vp, ci]
+            lib.bcom_cpu_blockwise_unpack_dequantize_mt.argtypes = [vp, vp, ci, ll, ci, vp, ci]
             _lib = lib
         except Exception:
             _lib = False
@@ -47,9 +48,10 @@ def blockwise_quantize_pack(x: torch.Tensor, bitwidth: int, block_size: int,
     if stochastic and sr_seed is None:
         raise ValueError("the C++ CPU codec needs a seed for stochastic rounding")
     key = sr_key(sr_seed, sr_stream) if stochastic else 0
-    rc = lib.bcom_cpu_blockwise_quantize_pack(
+    rc = lib.bcom_cpu_blockwise_quantize_pack_mt(
         flat.data_ptr(), n, bitwidth, block_size, int(bool(stochastic)), key,
-        int(sr_offset) & 0xFFFFFFFF, packed.data_ptr(), scales.data_ptr())
+        int(sr_offset) & 0xFFFFFFFF, packed.data_ptr(), scales.data_ptr(),
+        torch.get_num_threads())
     if rc:
         raise ValueError("bad arguments for the CPU codec")
     return packed, scales
@@ -61,8 +63,9 @@ def blockwise_unpack_dequantize(packed: torch.Tensor, scales: torch.Tensor, bitw
     packed = packed.contiguous().view(-1)
     scales = scales.contiguous().view(-1)
     out = torch.empty(numel, dtype=torch.float32)
-    rc = lib.bcom_cpu_blockwise_unpack_dequantize(packed.data_ptr(), scales.data_ptr(), bitwidth,
-                                                  numel, block_size, out.data_ptr())
+    rc = lib.bcom_cpu_blockwise_unpack_dequantize_mt(
+        packed.data_ptr(), scales.data_ptr(), bitwidth, numel, block_size, out.data_ptr(),
+        torch.get_num_threads())
     if rc:
         raise ValueError("bad arguments for the CPU codec")
     return out

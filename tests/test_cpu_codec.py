@@ -54,3 +54,32 @@ def test_faster_than_torch_ops_on_cpu():
     t_cpp = (time.perf_counter() - t0) / 3
     print(f"CPU 1 Mi elements 4-bit: torch ops {t_torch * 1e3:.2f} ms, C++ {t_cpp * 1e3:.2f} ms")
     assert t_cpp < t_torch * 2
+
+
+@pytest.mark.parametrize("bits", [1, 4, 12])
+@pytest.mark.parametrize("block", [8, 256, 1000])
+def test_threaded_path_and_special_values_are_bit_exact(bits, block):
+    """Large tensors are split over threads; infinities, zero blocks, tiny blocks and NaN
+    (which selects scale 1.0 for its block, as in the host quantizer) stay bit-exact."""
+    old = torch.get_num_threads()
+    torch.set_num_threads(4)
+    try:
+        n = (1 << 19) + 37
+        g = torch.Generator().manual_seed(bits * 1000 + block)
+        x = torch.randn(n, generator=g) * torch.rand(n, generator=g).pow(4)
+        x[5], x[4000], x[300000] = float("inf"), float("-inf"), 0.0
+        x[100 * block:101 * block] = 0.0
+        x[200 * block:201 * block] = 1e-9
+        x[7 * block + 3] = float("nan")
+        for sr in (False, True):
+            q, s = Q.quantize_tensor_blockwise(x, bits, block_size=block, stochastic_rounding=sr,
+                                               sr_seed=7, sr_offset=11)
+            want_p, _ = Q.pack_lowbit(q, bits)
+            p, sc = C.blockwise_quantize_pack(x, bits, block, sr, 7, 11)
+            assert torch.equal(sc.view(torch.int16), s.view(torch.int16))
+            assert torch.equal(p, want_p)
+            d = C.blockwise_unpack_dequantize(p, sc, bits, n, block)
+            want_d = Q.dequantize_tensor_blockwise(q, s, block_size=block).view(-1)
+            assert torch.equal(torch.nan_to_num(d, nan=7.0), torch.nan_to_num(want_d, nan=7.0))
+    finally:
+        torch.set_num_threads(old)
