@@ -151,17 +151,26 @@ __device__ __forceinline__ void store8_guard(T* p, long long base, long long n,
 // ---------------------------------------------------------------------------
 // block scale: width-T shuffle absmax, IEEE divide, fp16 round trip
 // ---------------------------------------------------------------------------
+// max that returns NaN when either operand is NaN (fmaxf would drop it).  The host
+// quantizer's amax propagates NaN, and a NaN absmax then selects the scale 1.0 for its block
+// (reference python/bitscom/quantization.py:126-131), so the block maximum must keep it.
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
 __device__ __forceinline__ float absmax8(const float (&v)[GROUP]) {
   float m = 0.0f;
 #pragma unroll
-  for (int i = 0; i < GROUP; ++i) m = fmaxf(m, fabsf(v[i]));
+  for (int i = 0; i < GROUP; ++i) m = max_nan(m, fabsf(v[i]));
   return m;
 }
 
 // All 32 lanes of the warp must call this. T = lanes per quantization block.
 __device__ __forceinline__ float block_absmax(float m, int lanes_per_block) {
   for (int o = lanes_per_block >> 1; o > 0; o >>= 1)
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
   return m;
 }
 

@@ -132,7 +132,8 @@ blockwise_quantize_pack_generic(const T* __restrict__ x, long long n, int block,
     const long long start = b * block;
     const long long stop = min(start + (long long)block, n);
     float m = 0.0f;
-    for (long long i = start + lane; i < stop; i += 32) m = fmaxf(m, fabsf(Elem<T>::to_f(x[i])));
+    for (long long i = start + lane; i < stop; i += 32)
+      m = max_nan(m, fabsf(Elem<T>::to_f(x[i])));
     m = block_absmax(m, 32);
     const __half sh = scale_from_absmax<BITS>(m);
     const float sf = __half2float(sh);
@@ -192,7 +193,7 @@ absmax_kernel(const T* __restrict__ x, long long n, unsigned int* __restrict__ a
   float m = 0.0f;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
-    m = fmaxf(m, fabsf(Elem<T>::to_f(x[i])));
+    m = max_nan(m, fabsf(Elem<T>::to_f(x[i])));
   m = block_absmax(m, 32);
   __shared__ float part[kThreads / 32];
   if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;

@@ -53,6 +53,23 @@ def test_blockwise_unaligned_view_and_zero_blocks():
         assert torch.equal(p.cpu(), pc) and torch.equal(s.cpu(), sc)
 
 
+@pytest.mark.parametrize("block,n", [(256, 4096), (100, 1234)])
+def test_nan_and_inf_blocks_match_the_host_quantizer(block, n):
+    """A NaN makes its block's absmax NaN, which selects the scale 1.0; an infinity makes the
+    scale infinite.  Both must come out as on the host (fast and generic kernels)."""
+    x = torch.randn(n)
+    x[3], x[block + 5], x[n - 2] = float("nan"), float("inf"), float("nan")
+    for bits in (2, 4, 8):
+        if not codec.supports_blockwise(bits, block):
+            continue
+        for sr in (False, True):
+            kw = dict(block_size=block, stochastic_rounding=sr, sr_seed=5 if sr else None)
+            p, s, _ = Q.quantize_pack_tensor_blockwise(x.cuda(), bits, **kw)
+            pc, sc, _ = Q.quantize_pack_tensor_blockwise(x, bits, **kw)
+            assert torch.equal(s.cpu().view(torch.int16), sc.view(torch.int16))
+            assert torch.equal(p.cpu(), pc)
+
+
 @pytest.mark.parametrize("bits", [1, 2, 4, 8])
 def test_seeded_stochastic_rounding_bit_exact(bits):
     x = torch.randn(10000) * 0.1

@@ -1,0 +1,32 @@
+"""setup.py: version, and the compile-command list covers every native source."""
+
+import os
+import subprocess
+import sys
+
+import bitscom_b200
+from bitscom_b200 import _build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_setup_reports_package_version():
+    out = subprocess.run([sys.executable, "setup.py", "--version"], cwd=ROOT,
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.strip().splitlines()[-1] == bitscom_b200.__version__
+
+
+def test_compile_commands_cover_all_sources():
+    code = ("import sys, json; sys.argv=['setup.py','--version']; "
+            "ns={'__name__':'setup_probe','__file__':'setup.py'}; "
+            "src=open('setup.py').read().split('\\nsetup(\\n')[0]; exec(compile(src,'setup.py','exec'),ns); "
+            "print(json.dumps([e['file'] for e in ns['compile_commands']()]))")
+    out = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True,
+                         timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    import json
+
+    files = {os.path.basename(f) for f in json.loads(out.stdout.strip().splitlines()[-1])}
+    want = {s for spec in _build.LIBRARIES.values() for s in spec["sources"]} | {"backend.cc"}
+    assert want <= files
