@@ -1,6 +1,8 @@
 // Causal flash attention, forward and backward, on tcgen05 tensor cores (sm_100a),
-// head_dim 128, operating directly on the fused, RoPE-rotated projection
-// qkv[tokens, 3 * heads * 128] (bf16) through TMA tensor maps: no q/k/v copies.
+// head_dim 128 (Llama) or 64 (GPT-2), operating directly on the fused projection
+// qkv[tokens, 3 * heads * head_dim] (bf16, RoPE already applied where the model has it)
+// through TMA tensor maps: no q/k/v copies.  The kernels are templates on the head dim; a
+// [rows x head_dim] tile is head_dim / 64 chunks of 64 columns (one 128-byte swizzle row).
 //
 // TMEM gives every thread one accumulator ROW (thread t <-> TMEM lane t), so row maxima,
 // row sums and the softmax need no cross-thread reduction at all.
@@ -35,7 +37,6 @@
 
 namespace attn {
 
-constexpr int HD = 128;           // head dim
 constexpr int BQ = 128;           // query rows per CTA (forward) / per iteration (backward)
 constexpr int BKF = 64;           // keys per iteration, forward
 constexpr int BKB = 128;          // keys per CTA, backward
@@ -64,7 +65,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// UMMA descriptors for the two ways a [rows x 128-col] two-chunk tile is consumed.
+// UMMA descriptors for the two ways a [rows x (64 * chunks)-col] tile is consumed.
 // K-major: MN = rows, K = columns. Chunk c (64 columns) starts at c * rows * 128.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int rows, int kstep) {
   const int chunk = kstep >> 2;  // 4 k-steps of 16 elements per 64-column chunk
@@ -88,11 +89,15 @@ struct FwdShared {
   volatile int abort;
 };
 
-constexpr int FWD_Q_BYTES = BQ * HD * 2;    // 32 KiB
-constexpr int FWD_K_BYTES = BKF * HD * 2;   // 16 KiB
 constexpr int FWD_P_BYTES = BQ * BKF * 2;   // 16 KiB
-constexpr int FWD_SMEM = FWD_Q_BYTES + 2 * FWD_K_BYTES + FWD_P_BYTES + 1024 + 128;
+template <int HD> struct Fwd {
+  static constexpr int Q_BYTES = BQ * HD * 2;    // 32 KiB at head_dim 128
+  static constexpr int K_BYTES = BKF * HD * 2;   // 16 KiB at head_dim 128
+  static constexpr int SMEM = Q_BYTES + 2 * K_BYTES + FWD_P_BYTES + 1024 + 128;
+  static constexpr int TMEM_COLS = HD == 128 ? 256 : 128;  // S (64) + O (HD), power of two
+};
 
+template <int HD>
 __global__ void __launch_bounds__(kThreads, 2)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 128}
                      const __grid_constant__ CUtensorMap tm_kv,   // box {64, 64}
@@ -100,6 +105,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 12
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int FWD_Q_BYTES = Fwd<HD>::Q_BYTES, FWD_K_BYTES = Fwd<HD>::K_BYTES;
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + FWD_Q_BYTES;
   uint8_t* sV = sK + FWD_K_BYTES;
@@ -126,7 +132,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 12
     sh->abort = 0;
     tc::fence_mbar_init();
   }
-  if (warp == 0) tc::tmem_alloc(&sh->tmem_base, 256);
+  if (warp == 0) tc::tmem_alloc(&sh->tmem_base, Fwd<HD>::TMEM_COLS);
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
@@ -136,19 +142,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 12
 
   auto load_k = [&](int j) {
     tc::mbar_expect_tx(&sh->bar_k, FWD_K_BYTES);
-    tc::tma_load_2d(sK, &tm_kv, &sh->bar_k, k_col, b * p.seq + j * BKF);
-    tc::tma_load_2d(sK + BKF * 128, &tm_kv, &sh->bar_k, k_col + 64, b * p.seq + j * BKF);
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c)
+      tc::tma_load_2d(sK + c * BKF * 128, &tm_kv, &sh->bar_k, k_col + 64 * c,
+                      b * p.seq + j * BKF);
   };
   auto load_v = [&](int j) {
     tc::mbar_expect_tx(&sh->bar_v, FWD_K_BYTES);
-    tc::tma_load_2d(sV, &tm_kv, &sh->bar_v, v_col, b * p.seq + j * BKF);
-    tc::tma_load_2d(sV + BKF * 128, &tm_kv, &sh->bar_v, v_col + 64, b * p.seq + j * BKF);
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c)
+      tc::tma_load_2d(sV + c * BKF * 128, &tm_kv, &sh->bar_v, v_col + 64 * c,
+                      b * p.seq + j * BKF);
   };
 
   if (tid == 0) {
     tc::mbar_expect_tx(&sh->bar_q, FWD_Q_BYTES);
-    tc::tma_load_2d(sQ, &tm_q, &sh->bar_q, q_col, row0);
-    tc::tma_load_2d(sQ + BQ * 128, &tm_q, &sh->bar_q, q_col + 64, row0);
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c)
+      tc::tma_load_2d(sQ + c * BQ * 128, &tm_q, &sh->bar_q, q_col + 64 * c, row0);
     load_k(0);
     load_v(0);
   }
@@ -268,7 +279,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 12
   __syncthreads();
   if (warp == 0) {
     tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tmem, 256);
+    tc::tmem_dealloc(tmem, Fwd<HD>::TMEM_COLS);
   }
 }
 
@@ -293,9 +304,13 @@ struct BwdShared {
   float delta[BQ];
 };
 
-constexpr int TILE = 128 * HD * 2;  // 32 KiB: every backward tile is 128 x 128 bf16
-constexpr int BWD_SMEM = 6 * TILE + 1024 + sizeof(BwdShared) + 64;
+constexpr int TILE_SQ = 128 * 128 * 2;  // P^T and dS^T: 128 keys x 128 queries, 32 KiB
+template <int HD> struct Bwd {
+  static constexpr int TILE = 128 * HD * 2;  // K, V, Q, dO: 128 rows x HD (32 KiB at 128)
+  static constexpr int SMEM = 4 * TILE + 2 * TILE_SQ + 1024 + sizeof(BwdShared) + 64;
+};
 
+template <int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 128} over qkv
                      const __grid_constant__ CUtensorMap tm_do,    // box {64, 128} over dO
@@ -303,13 +318,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int TILE = Bwd<HD>::TILE;
   uint8_t* sK = smem;
   uint8_t* sV = sK + TILE;
   uint8_t* sQ = sV + TILE;
   uint8_t* sDO = sQ + TILE;
   uint8_t* sPT = sDO + TILE;
-  uint8_t* sDS = sPT + TILE;
-  BwdShared* sh = reinterpret_cast<BwdShared*>(sDS + TILE);
+  uint8_t* sDS = sPT + TILE_SQ;
+  BwdShared* sh = reinterpret_cast<BwdShared*>(sDS + TILE_SQ);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   // Warps w and w + 4 may read the same 32 TMEM lanes; they split the columns. `row` is the
@@ -338,12 +354,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem = sh->tmem_base;
-  const uint32_t tST = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 384, tDQ = tmem;
+  // S^T and dP^T: 128 columns each; dV and dK: HD columns each; dQ reuses S^T's columns
+  const uint32_t tST = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 256 + HD,
+                 tDQ = tmem;
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
   auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int col, int row) {
-    tc::tma_load_2d(dst, map, bar, col, row);
-    tc::tma_load_2d(dst + 128 * 128, map, bar, col + 64, row);
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c)
+      tc::tma_load_2d(dst + c * 128 * 128, map, bar, col + 64 * c, row);
   };
   auto load_q = [&](int qi) {
     const int row = b * p.seq + (kb + qi) * BQ;
@@ -360,8 +379,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   }
 
   constexpr uint32_t idesc_kk = tc::make_idesc_bf16(128, 128, false, false);  // both K-major
-  constexpr uint32_t idesc_kn = tc::make_idesc_bf16(128, 128, false, true);   // B MN-major
-  constexpr uint32_t idesc_nn = tc::make_idesc_bf16(128, 128, true, true);    // both MN-major
+  constexpr uint32_t idesc_kn = tc::make_idesc_bf16(128, HD, false, true);    // B MN-major
+  constexpr uint32_t idesc_nn = tc::make_idesc_bf16(128, HD, true, true);     // both MN-major
   const uint32_t aK = tc::smem_u32(sK), aV = tc::smem_u32(sV), aQ = tc::smem_u32(sQ),
                  aDO = tc::smem_u32(sDO), aPT = tc::smem_u32(sPT), aDS = tc::smem_u32(sDS);
   const int key_idx = kb * BKB + row;  // this thread's key position inside the sequence
@@ -518,7 +537,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
   }
 }
 
-// delta[b, h, s] = sum_d dO * O   (one warp per (token, head))
+// delta[b, h, s] = sum_d dO * O   (one warp per (token, head), HD / 32 elements per lane)
+template <int HD>
 __global__ void __launch_bounds__(256)
 attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                        float* __restrict__ delta, int batch, int seq, int heads) {
@@ -528,14 +548,13 @@ attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
   if (warp_id >= total) return;
   const int h = (int)(warp_id % heads);
   const long long tok = warp_id / heads;
-  const size_t off = (size_t)tok * heads * HD + (size_t)h * HD + lane * 4;
-  const uint2 a = *reinterpret_cast<const uint2*>(o + off);
-  const uint2 g = *reinterpret_cast<const uint2*>(d_o + off);
-  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+  constexpr int PAIRS = HD / 64;  // bf16 pairs per lane
+  const size_t off = (size_t)tok * heads * HD + (size_t)h * HD + lane * (2 * PAIRS);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(o + off);
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(d_o + off);
   float s = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < PAIRS; ++i) {
     const float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(g2[i]);
     s += x.x * y.x + x.y * y.y;
   }
@@ -606,19 +625,10 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
   return (int)r;
 }
 
-}  // namespace attn
-
-extern "C" {
-
-// qkv: [batch*seq, 3*heads*128] bf16 (q | k | v, RoPE already applied); out: [batch*seq,
-// heads*128] bf16; lse2: [batch, heads, seq] fp32.  seq must be a multiple of 128.
-int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int seq, int heads,
-                       int head_dim, float scale, void* stream) {
-  using namespace attn;
-  if (head_dim != HD || seq % BQ || batch <= 0 || heads <= 0) return 1001;
-  if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return 1002;
-  (void)cudaFree(nullptr);
-  (void)cudaGetLastError();
+// ---- launchers, one instantiation per head dim ------------------------------------
+template <int HD>
+static int launch_fwd(const void* qkv, void* out, void* lse2, int batch, int seq, int heads,
+                      float scale, cudaStream_t st) {
   const long long tokens = (long long)batch * seq;
   const int W = 3 * heads * HD;
   CUtensorMap tm_q, tm_kv;
@@ -627,8 +637,8 @@ int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int se
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute((const void*)attention_fwd_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
+    attr_err = cudaFuncSetAttribute((const void*)attention_fwd_kernel<HD>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd<HD>::SMEM);
   });
   if (attr_err != cudaSuccess) return 1005;
   FwdParams p;
@@ -639,22 +649,14 @@ int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int se
   p.heads = heads;
   p.scale_log2 = scale * kLog2e;
   const int grid = batch * heads * (seq / BQ);
-  attention_fwd_kernel<<<grid, kThreads, FWD_SMEM, (cudaStream_t)stream>>>(tm_q, tm_kv, p);
+  attention_fwd_kernel<HD><<<grid, kThreads, Fwd<HD>::SMEM, st>>>(tm_q, tm_kv, p);
   return (int)cudaGetLastError();
 }
 
-// d_out: [batch*seq, heads*128]; dqkv (written): [batch*seq, 3*heads*128];
-// dq_acc: fp32 [batch*seq, heads*128] scratch, must be zero on entry and is zero on exit;
-// delta: fp32 [batch, heads, seq] scratch.
-int bcom_attention_bwd(const void* qkv, const void* out, const void* d_out, const void* lse2,
-                       void* dqkv, void* dq_acc, void* delta, int batch, int seq, int heads,
-                       int head_dim, float scale, void* stream) {
-  using namespace attn;
-  if (head_dim != HD || seq % BQ || batch <= 0 || heads <= 0) return 1001;
-  if (((uintptr_t)qkv & 15) || ((uintptr_t)d_out & 15) || ((uintptr_t)dqkv & 15)) return 1002;
-  (void)cudaFree(nullptr);
-  (void)cudaGetLastError();
-  cudaStream_t st = (cudaStream_t)stream;
+template <int HD>
+static int launch_bwd(const void* qkv, const void* out, const void* d_out, const void* lse2,
+                      void* dqkv, float* dq_acc, float* delta, int batch, int seq, int heads,
+                      float scale, cudaStream_t st) {
   const long long tokens = (long long)batch * seq;
   const int H = heads * HD;
   CUtensorMap tm_qkv, tm_do;
@@ -663,32 +665,73 @@ int bcom_attention_bwd(const void* qkv, const void* out, const void* d_out, cons
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel<HD>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd<HD>::SMEM);
   });
   if (attr_err != cudaSuccess) return 1005;
   {
     const long long warps = tokens * heads;
     const int grid = (int)((warps * 32 + 255) / 256);
-    attention_delta_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)out,
-                                                 (const __nv_bfloat16*)d_out, (float*)delta,
-                                                 batch, seq, heads);
+    attention_delta_kernel<HD><<<grid, 256, 0, st>>>((const __nv_bfloat16*)out,
+                                                     (const __nv_bfloat16*)d_out, delta, batch,
+                                                     seq, heads);
   }
   BwdParams p;
   p.dqkv = (__nv_bfloat16*)dqkv;
-  p.dq_acc = (float*)dq_acc;
+  p.dq_acc = dq_acc;
   p.lse2 = (const float*)lse2;
-  p.delta = (const float*)delta;
+  p.delta = delta;
   p.batch = batch;
   p.seq = seq;
   p.heads = heads;
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   const int grid = batch * heads * (seq / BKB);
-  attention_bwd_kernel<<<grid, kBwdThreads, BWD_SMEM, st>>>(tm_qkv, tm_do, p);
-  attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>((float*)dq_acc, (__nv_bfloat16*)dqkv, tokens,
-                                                     H);
+  attention_bwd_kernel<HD><<<grid, kBwdThreads, Bwd<HD>::SMEM, st>>>(tm_qkv, tm_do, p);
+  attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
   return (int)cudaGetLastError();
+}
+
+static bool shape_ok(int batch, int seq, int heads, int head_dim) {
+  return (head_dim == 64 || head_dim == 128) && seq % BQ == 0 && batch > 0 && heads > 0;
+}
+
+}  // namespace attn
+
+extern "C" {
+
+// qkv: [batch*seq, 3*heads*head_dim] bf16 (q | k | v, RoPE already applied); out: [batch*seq,
+// heads*head_dim] bf16; lse2: [batch, heads, seq] fp32.  head_dim is 64 or 128 and seq a
+// multiple of 128.
+int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int seq, int heads,
+                       int head_dim, float scale, void* stream) {
+  using namespace attn;
+  if (!shape_ok(batch, seq, heads, head_dim)) return 1001;
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return 1002;
+  (void)cudaFree(nullptr);
+  (void)cudaGetLastError();
+  cudaStream_t st = (cudaStream_t)stream;
+  return head_dim == 128 ? launch_fwd<128>(qkv, out, lse2, batch, seq, heads, scale, st)
+                         : launch_fwd<64>(qkv, out, lse2, batch, seq, heads, scale, st);
+}
+
+// d_out: [batch*seq, heads*head_dim]; dqkv (written): [batch*seq, 3*heads*head_dim];
+// dq_acc: fp32 [batch*seq, heads*head_dim] scratch, must be zero on entry and is zero on exit;
+// delta: fp32 [batch, heads, seq] scratch.
+int bcom_attention_bwd(const void* qkv, const void* out, const void* d_out, const void* lse2,
+                       void* dqkv, void* dq_acc, void* delta, int batch, int seq, int heads,
+                       int head_dim, float scale, void* stream) {
+  using namespace attn;
+  if (!shape_ok(batch, seq, heads, head_dim)) return 1001;
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)d_out & 15) || ((uintptr_t)dqkv & 15)) return 1002;
+  (void)cudaFree(nullptr);
+  (void)cudaGetLastError();
+  cudaStream_t st = (cudaStream_t)stream;
+  return head_dim == 128
+             ? launch_bwd<128>(qkv, out, d_out, lse2, dqkv, (float*)dq_acc, (float*)delta, batch,
+                               seq, heads, scale, st)
+             : launch_bwd<64>(qkv, out, d_out, lse2, dqkv, (float*)dq_acc, (float*)delta, batch,
+                              seq, heads, scale, st);
 }
 
 int bcom_attention_status(unsigned int out[4], int clear) {
@@ -744,10 +787,10 @@ int bcom_attention_bwd_no_alloc(const void* qkv, const void* out, const void* d_
                                 const void* lse2, void* dqkv, int batch, int seq, int heads,
                                 int head_dim, float scale, void* stream) {
   using namespace attn;
-  if (head_dim != HD || seq % BQ || batch <= 0 || heads <= 0) return 1001;
+  if (head_dim != 128 || seq % BQ || batch <= 0 || heads <= 0) return 1001;
   if (((uintptr_t)qkv & 15) || ((uintptr_t)d_out & 15) || ((uintptr_t)dqkv & 15)) return 1002;
   const long long tokens = (long long)batch * seq;
-  const int H = heads * HD;
+  const int H = heads * 128;
   const unsigned long long dq_bytes = 4ull * (unsigned long long)tokens * (unsigned long long)H;
   const unsigned long long delta_bytes =
       (4ull * (unsigned long long)tokens * (unsigned long long)heads + 255ull) & ~255ull;
@@ -769,38 +812,8 @@ int bcom_attention_bwd_no_alloc(const void* qkv, const void* out, const void* d_
   // the accumulator must start at zero; the array still holds the previous call's data
   err = cudaMemsetAsync(dq_acc, 0, dq_bytes, st);
   if (err != cudaSuccess) return (int)err;
-
-  CUtensorMap tm_qkv, tm_do;
-  if (make_map(&tm_qkv, qkv, tokens, 3 * H, 64, 128)) return 1003;
-  if (make_map(&tm_do, d_out, tokens, H, 64, 128)) return 1004;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
-  });
-  if (attr_err != cudaSuccess) return 1005;
-  {
-    const long long warps = tokens * heads;
-    const int grid = (int)((warps * 32 + 255) / 256);
-    attention_delta_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)out,
-                                                 (const __nv_bfloat16*)d_out, delta, batch, seq,
-                                                 heads);
-  }
-  BwdParams p;
-  p.dqkv = (__nv_bfloat16*)dqkv;
-  p.dq_acc = dq_acc;
-  p.lse2 = (const float*)lse2;
-  p.delta = delta;
-  p.batch = batch;
-  p.seq = seq;
-  p.heads = heads;
-  p.scale = scale;
-  p.scale_log2 = scale * kLog2e;
-  const int grid = batch * heads * (seq / BKB);
-  attention_bwd_kernel<<<grid, kBwdThreads, BWD_SMEM, st>>>(tm_qkv, tm_do, p);
-  attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
-  return (int)cudaGetLastError();
+  return launch_bwd<128>(qkv, out, d_out, lse2, dqkv, dq_acc, delta, batch, seq, heads, scale,
+                         st);
 }
 
 }  // extern "C"

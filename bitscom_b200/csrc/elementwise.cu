@@ -1,5 +1,5 @@
-// Bandwidth-bound kernels of the Llama / GPT-2 trainers (sm_100a): RMSNorm, RoPE,
-// SwiGLU, fused softmax cross-entropy, embedding, and a flat fused AdamW.  Every one
+// Bandwidth-bound kernels of the Llama / GPT-2 trainers (sm_100a): RMSNorm, LayerNorm, RoPE,
+// SwiGLU, bias + GELU, fused softmax cross-entropy, embedding, and a flat fused AdamW.  Every one
 // makes a single pass over its operands with 16-byte accesses and keeps row statistics
 // in registers / shared memory; the torch-eager equivalents (several kernels and
 // temporaries each) are the baseline they replace.  The reference trainer gets these
@@ -161,6 +161,200 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
       for (int i = 0; i < 8; ++i) atomicAdd(dw + c + i, acc[k][i]);
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm (GPT-2): y = (x - mean) * rstd * w + b.  One warp per row, the row held in
+// registers between the statistics and the output (one read of x).  H <= 32 * 8 * MAX_ITERS
+// (the launchers instantiate 2 and 4: H up to 1024).
+// ---------------------------------------------------------------------------
+template <int MAX_ITERS>
+__global__ void __launch_bounds__(256)
+layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                     const bf16* __restrict__ b, bf16* __restrict__ y,
+                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int H,
+                     float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_cta) {
+    const bf16* xr = x + (size_t)row * H;
+    float f[MAX_ITERS][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (lane + k * 32) * 8;
+      if (c < H) {
+        load8(xr + c, f[k]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += f[k][i];
+      }
+    }
+    const float mean = warp_sum(sum) / (float)H;
+    float var = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (lane + k * 32) * 8;
+      if (c < H) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = f[k][i] - mean;
+          var += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(var) / (float)H + eps);
+    if (lane == 0) {
+      mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    bf16* yr = y + (size_t)row * H;
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (lane + k * 32) * 8;
+      if (c < H) {
+        float g[8], bb[8], o[8];
+        load8(w + c, g);
+        load8(b + c, bb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (f[k][i] - mean) * rstd * g[i] + bb[i];
+        store8(yr + c, o);
+      }
+    }
+  }
+}
+
+// g = dy * w; dx = rstd * (g - mean(g) - xhat * mean(g * xhat));
+// dw += sum_rows dy * xhat, db += sum_rows dy (fp32 atomics, one set per warp at the end).
+template <int MAX_ITERS>
+__global__ void __launch_bounds__(256)
+layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                     const bf16* __restrict__ w, const float* __restrict__ mean,
+                     const float* __restrict__ rstd, bf16* __restrict__ dx,
+                     float* __restrict__ dw, float* __restrict__ db, int rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  float aw[MAX_ITERS][8], ab[MAX_ITERS][8], fw[MAX_ITERS][8];
+#pragma unroll
+  for (int k = 0; k < MAX_ITERS; ++k) {
+    const int c = (lane + k * 32) * 8;
+    if (c < H) load8(w + c, fw[k]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) aw[k][i] = ab[k][i] = 0.0f;
+  }
+  for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_cta) {
+    const bf16* xr = x + (size_t)row * H;
+    const bf16* gr = dy + (size_t)row * H;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[MAX_ITERS][8], g[MAX_ITERS][8];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (lane + k * 32) * 8;
+      if (c < H) {
+        float fx[8], fg[8];
+        load8(xr + c, fx);
+        load8(gr + c, fg);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[k][i] = (fx[i] - mu) * rs;
+          g[k][i] = fg[i] * fw[k][i];
+          s1 += g[k][i];
+          s2 += g[k][i] * xh[k][i];
+          aw[k][i] += fg[i] * xh[k][i];
+          ab[k][i] += fg[i];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / (float)H;
+    s2 = warp_sum(s2) / (float)H;
+    bf16* dr = dx + (size_t)row * H;
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (lane + k * 32) * 8;
+      if (c < H) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rs * (g[k][i] - s1 - xh[k][i] * s2);
+        store8(dr + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < MAX_ITERS; ++k) {
+    const int c = (lane + k * 32) * 8;
+    if (c < H) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        atomicAdd(dw + c + i, aw[k][i]);
+        atomicAdd(db + c + i, ab[k][i]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// bias + GELU (tanh form) on a [rows, C] GEMM output: y = gelu(x + bias).
+// Backward recomputes from x and bias: dx = dy * gelu'(x + bias), dbias += colsum(dx).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_fast(float v) {
+  float r;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+constexpr float kGeluK = 0.7978845608028654f;  // sqrt(2 / pi)
+constexpr float kGeluC = 0.044715f;
+
+__global__ void __launch_bounds__(256)
+bias_gelu_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ bias,
+                     bf16* __restrict__ y, long long rows, int C) {
+  const int vec = C / 8;
+  const long long total = rows * vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % vec) * 8;
+    float u[8], bb[8];
+    load8(x + i * 8, u);
+    load8(bias + c, bb);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float v = u[k] + bb[k];
+      u[k] = 0.5f * v * (1.0f + tanh_fast(kGeluK * (v + kGeluC * v * v * v)));
+    }
+    store8(y + i * 8, u);
+  }
+}
+
+// grid: (C / (8 * blockDim.x) column tiles, row strips).  Thread t of a column tile owns 8
+// columns and walks its strip's rows, so the bias gradient needs 8 atomics per thread.
+__global__ void __launch_bounds__(256)
+bias_gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                     const bf16* __restrict__ bias, bf16* __restrict__ dx,
+                     float* __restrict__ dbias, long long rows, int C) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= C) return;
+  float bb[8], acc[8];
+  load8(bias + c, bb);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+  for (long long r = blockIdx.y; r < rows; r += gridDim.y) {
+    float u[8], d[8];
+    load8(x + r * C + c, u);
+    load8(dy + r * C + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float v = u[k] + bb[k];
+      const float t = tanh_fast(kGeluK * (v + kGeluC * v * v * v));
+      const float dg = 0.5f * (1.0f + t) +
+                       0.5f * v * (1.0f - t * t) * kGeluK * (1.0f + 3.0f * kGeluC * v * v);
+      d[k] *= dg;
+      acc[k] += d[k];
+    }
+    store8(dx + r * C + c, d);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) atomicAdd(dbias + c + k, acc[k]);
 }
 
 // ---------------------------------------------------------------------------
@@ -435,6 +629,72 @@ int bcom_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* r
                                                 rows, H);
   else
     return (int)cudaErrorInvalidValue;  // H up to 16384
+  return (int)cudaGetLastError();
+}
+
+// LayerNorm over rows of H <= 1024 elements (H % 8 == 0; one warp keeps a row in
+// registers); mean / rstd: fp32 [rows].
+int bcom_layernorm_fwd(const void* x, const void* w, const void* b, void* y, void* mean,
+                       void* rstd, int rows, int H, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8 || H > 1024) return (int)cudaErrorInvalidValue;
+  const int warps = 8;
+  const int want = (rows + warps - 1) / warps;
+  const int grid = want < 148 * 8 ? want : 148 * 8;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int iters = (H / 8 + 31) / 32;
+#define BCOM_LN_FWD(N)                                                                       \
+  layernorm_fwd_kernel<N><<<grid, warps * 32, 0, st>>>(                                       \
+      (const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y, (float*)mean, (float*)rstd,  \
+      rows, H, eps)
+  if (iters <= 2) BCOM_LN_FWD(2);
+  else BCOM_LN_FWD(4);
+#undef BCOM_LN_FWD
+  return (int)cudaGetLastError();
+}
+
+// dw / db: fp32 [H], accumulated into (not overwritten).
+int bcom_layernorm_bwd(const void* dy, const void* x, const void* w, const void* mean,
+                       const void* rstd, void* dx, void* dw_fp32, void* db_fp32, int rows, int H,
+                       void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 8 || H > 1024) return (int)cudaErrorInvalidValue;
+  const int warps = 8;
+  const int want = (rows + warps - 1) / warps;
+  const int grid = want < 148 ? want : 148;  // every warp ends with 2 * H atomics
+  cudaStream_t st = (cudaStream_t)stream;
+  const int iters = (H / 8 + 31) / 32;
+#define BCOM_LN_BWD(N)                                                                        \
+  layernorm_bwd_kernel<N><<<grid, warps * 32, 0, st>>>(                                        \
+      (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean, (const float*)rstd, \
+      (bf16*)dx, (float*)dw_fp32, (float*)db_fp32, rows, H)
+  if (iters <= 2) BCOM_LN_BWD(2);
+  else BCOM_LN_BWD(4);
+#undef BCOM_LN_BWD
+  return (int)cudaGetLastError();
+}
+
+int bcom_bias_gelu_fwd(const void* x, const void* bias, void* y, long long rows, int C,
+                       void* stream) {
+  if (rows <= 0) return 0;
+  if (C % 8) return (int)cudaErrorInvalidValue;
+  bias_gelu_fwd_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)x, (const bf16*)bias, (bf16*)y, rows, C);
+  return (int)cudaGetLastError();
+}
+
+// dbias: fp32 [C], accumulated into.
+int bcom_bias_gelu_bwd(const void* dy, const void* x, const void* bias, void* dx,
+                       void* dbias_fp32, long long rows, int C, void* stream) {
+  if (rows <= 0) return 0;
+  if (C % 8) return (int)cudaErrorInvalidValue;
+  const int threads = 128;
+  const int col_tiles = (C / 8 + threads - 1) / threads;
+  int strips = (148 * 8 + col_tiles - 1) / col_tiles;
+  if (strips > rows) strips = (int)rows;
+  if (strips > 65535) strips = 65535;
+  bias_gelu_bwd_kernel<<<dim3(col_tiles, strips), threads, 0, (cudaStream_t)stream>>>(
+      (const bf16*)dy, (const bf16*)x, (const bf16*)bias, (bf16*)dx, (float*)dbias_fp32, rows, C);
   return (int)cudaGetLastError();
 }
 

@@ -1,7 +1,7 @@
 """GPT-2 decoder (medium by default: 24 layers, d_model 1024, 16 heads, vocab 50257,
 sequence 1024) for the sharded-training workload.  Linear layers run on the tcgen05 GEMM
-(``ops.gemm``); LayerNorm, GELU and the head_dim-64 attention come from torch (the
-hand-written attention kernel covers head_dim 128).  Parameters are views of one flat
+(``ops.gemm``), attention on the tcgen05 flash kernel (head_dim 64), LayerNorm and
+bias + GELU on the hand-written elementwise kernels.  Parameters are views of one flat
 buffer so that ZeRO-style sharding is a contiguous range per rank.  The reference's GPT-2
 benchmark uses a 4-layer, 256-wide HF model (``benchmarks/multimodel_stochastic_e2e_curve
 .py:534-539``); there is no sharded trainer in the reference."""
@@ -14,6 +14,7 @@ from typing import Dict, Optional, Tuple
 import torch
 import torch.nn.functional as F
 
+from ..ops import attention as A
 from ..ops import gemm as G
 from ..ops import nn as K
 from ..parallel.flat import FlatParameters
@@ -90,19 +91,25 @@ class GPT2(torch.nn.Module):
         B, S = ids.shape
         D, nh = cfg.d_model, cfg.n_head
         x = K.embedding(ids.reshape(-1), self._w("wte")) + self._w("wpe")[:S].repeat(B, 1)
+        hd = D // nh
+        fused_attn = A.available() and A.supported(S, hd)
+        ln = K.layernorm if K.layernorm_supported(x) else (
+            lambda t, w, b: F.layer_norm(t, (D,), w, b))
         for i in range(cfg.n_layer):
-            h = F.layer_norm(x, (D,), self._w(f"h{i}.ln1_w"), self._w(f"h{i}.ln1_b"))
+            h = ln(x, self._w(f"h{i}.ln1_w"), self._w(f"h{i}.ln1_b"))
             qkv = G.linear(h, self._w(f"h{i}.wqkv")) + self._w(f"h{i}.bqkv")
-            q, k, v = (qkv[:, j * D:(j + 1) * D].view(B, S, nh, D // nh).transpose(1, 2)
-                       for j in range(3))
-            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-            a = a.transpose(1, 2).reshape(B * S, D)
+            if fused_attn:
+                a = A.attention(qkv, B, S, nh, hd)
+            else:
+                q, k, v = (qkv[:, j * D:(j + 1) * D].view(B, S, nh, hd).transpose(1, 2)
+                           for j in range(3))
+                a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+                a = a.transpose(1, 2).reshape(B * S, D)
             x = x + G.linear(a, self._w(f"h{i}.wo")) + self._w(f"h{i}.bo")
-            h = F.layer_norm(x, (D,), self._w(f"h{i}.ln2_w"), self._w(f"h{i}.ln2_b"))
-            h = F.gelu(G.linear(h, self._w(f"h{i}.wfc")) + self._w(f"h{i}.bfc"),
-                       approximate="tanh")
+            h = ln(x, self._w(f"h{i}.ln2_w"), self._w(f"h{i}.ln2_b"))
+            h = K.bias_gelu(G.linear(h, self._w(f"h{i}.wfc")), self._w(f"h{i}.bfc"))
             x = x + G.linear(h, self._w(f"h{i}.wproj")) + self._w(f"h{i}.bproj")
-        x = F.layer_norm(x, (D,), self._w("lnf_w"), self._w("lnf_b"))
+        x = ln(x, self._w("lnf_w"), self._w("lnf_b"))
         logits = G.linear(x, self._w("wte"))
         if targets is None:
             return logits.view(B, S, -1)

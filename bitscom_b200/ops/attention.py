@@ -1,5 +1,6 @@
-"""Causal flash attention on tcgen05 (``csrc/attention_tcgen05.cu``), consuming the fused
-RoPE-rotated ``qkv`` projection in place.  Library baseline: torch SDPA."""
+"""Causal flash attention on tcgen05 (``csrc/attention_tcgen05.cu``), head_dim 128 (Llama)
+or 64 (GPT-2), consuming the fused ``qkv`` projection in place.  Library baseline: torch
+SDPA."""
 
 from __future__ import annotations
 
@@ -36,7 +37,7 @@ def available() -> bool:
 
 
 def supported(seq: int, head_dim: int) -> bool:
-    return head_dim == 128 and seq % 128 == 0
+    return head_dim in (64, 128) and seq % 128 == 0
 
 
 def check_status(clear: bool = True) -> None:
@@ -60,7 +61,7 @@ class AttentionFunction(torch.autograd.Function):
         if lib is None:
             raise NativeError("attention kernel needs the bcom_llama library and a GPU")
         if not supported(seq, head_dim):
-            raise ValueError("tcgen05 attention needs head_dim 128 and seq % 128 == 0")
+            raise ValueError("tcgen05 attention needs head_dim 64 or 128 and seq % 128 == 0")
         H = heads * head_dim
         q2 = qkv.view(batch * seq, 3 * H)
         out = torch.empty(batch * seq, H, dtype=qkv.dtype, device=qkv.device)

@@ -1,5 +1,6 @@
 """Autograd wrappers over the bandwidth-bound trainer kernels (``csrc/elementwise.cu``):
-RMSNorm, RoPE, SwiGLU, fused softmax cross-entropy, embedding, flat AdamW / SGD."""
+RMSNorm, LayerNorm, RoPE, SwiGLU, bias + GELU, fused softmax cross-entropy, embedding, flat
+AdamW / SGD."""
 
 from __future__ import annotations
 
@@ -23,6 +24,10 @@ def _get():
             lib.bcom_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, ci, ci, cf, vp]
             lib.bcom_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, vp]
             lib.bcom_rope.argtypes = [vp, vp, vp, ll, ci, ci, ll, ci, ci, vp]
+            lib.bcom_layernorm_fwd.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, cf, vp]
+            lib.bcom_layernorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, vp]
+            lib.bcom_bias_gelu_fwd.argtypes = [vp, vp, vp, ll, ci, vp]
+            lib.bcom_bias_gelu_bwd.argtypes = [vp, vp, vp, vp, vp, ll, ci, vp]
             lib.bcom_swiglu_fwd.argtypes = [vp, vp, ll, ci, vp]
             lib.bcom_swiglu_bwd.argtypes = [vp, vp, vp, ll, ci, vp]
             lib.bcom_cross_entropy.argtypes = [vp, vp, vp, vp, ci, ci, ll, vp]
@@ -130,6 +135,102 @@ class RopeQKFunction(torch.autograd.Function):
 
 def rope_qk_(qkv, cos, sin, heads: int, head_dim: int, seq: int):
     return RopeQKFunction.apply(qkv, cos, sin, heads, head_dim, seq)
+
+
+# ----------------------------------------------------------------------------------
+def _grad_target(param: torch.Tensor, n: int, device):
+    """fp32 buffer a parameter gradient is accumulated into: the flat ``main_grad`` view when
+    the parameter has one (then autograd gets ``None``), else a fresh zero vector."""
+    main = getattr(param, "main_grad", None)
+    if main is not None:
+        return main, True
+    return torch.zeros(n, dtype=torch.float32, device=device), False
+
+
+class LayerNormFunction(torch.autograd.Function):
+    """LayerNorm over the last dimension (bf16, H <= 1024, H % 8 == 0)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        lib = _need()
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        check(lib.bcom_layernorm_fwd(ptr(x2), ptr(weight), ptr(bias), ptr(y), ptr(mean),
+                                     ptr(rstd), rows, H, float(eps), stream_ptr(x.device)),
+              "layernorm_fwd")
+        ctx.save_for_backward(x2, weight, bias, mean, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _need()
+        x2, weight, bias, mean, rstd = ctx.saved_tensors
+        H = x2.shape[1]
+        dy2 = dy.reshape(-1, H)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        dw, w_main = _grad_target(weight, H, dy.device)
+        db, b_main = _grad_target(bias, H, dy.device)
+        check(lib.bcom_layernorm_bwd(ptr(dy2), ptr(x2), ptr(weight), ptr(mean), ptr(rstd),
+                                     ptr(dx), ptr(dw), ptr(db), x2.shape[0], H,
+                                     stream_ptr(dy.device)), "layernorm_bwd")
+        return (dx.view(ctx.shape), None if w_main else dw.to(weight.dtype),
+                None if b_main else db.to(bias.dtype), None)
+
+
+def layernorm_supported(x: torch.Tensor) -> bool:
+    H = x.shape[-1]
+    return x.is_cuda and x.dtype == torch.bfloat16 and H % 8 == 0 and H <= 1024
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5
+              ) -> torch.Tensor:
+    return LayerNormFunction.apply(x, weight, bias, eps)
+
+
+class BiasGeluFunction(torch.autograd.Function):
+    """``gelu(x + bias)`` with the tanh approximation; the backward pass recomputes the
+    activation from ``x`` and ``bias`` and accumulates the bias gradient in fp32."""
+
+    @staticmethod
+    def forward(ctx, x, bias):
+        lib = _need()
+        C = x.shape[-1]
+        x2 = x.reshape(-1, C)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = torch.empty_like(x2)
+        check(lib.bcom_bias_gelu_fwd(ptr(x2), ptr(bias), ptr(y), x2.shape[0], C,
+                                     stream_ptr(x.device)), "bias_gelu_fwd")
+        ctx.save_for_backward(x2, bias)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _need()
+        x2, bias = ctx.saved_tensors
+        C = x2.shape[1]
+        dy2 = dy.reshape(-1, C)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        db, b_main = _grad_target(bias, C, dy.device)
+        check(lib.bcom_bias_gelu_bwd(ptr(dy2), ptr(x2), ptr(bias), ptr(dx), ptr(db),
+                                     x2.shape[0], C, stream_ptr(dy.device)), "bias_gelu_bwd")
+        return dx.view(ctx.shape), None if b_main else db.to(bias.dtype)
+
+
+def bias_gelu(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    return BiasGeluFunction.apply(x, bias)
 
 
 # ----------------------------------------------------------------------------------

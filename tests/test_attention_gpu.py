@@ -18,10 +18,11 @@ def _ref(qkv, B, S, nh, hd):
     return o.transpose(1, 2).reshape(B * S, H)
 
 
+@pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("B,S,nh", [(1, 128, 1), (2, 256, 2), (1, 512, 4), (1, 2048, 2)])
-def test_attention_forward_backward(B, S, nh):
-    assert A.available()
-    hd, H = 128, nh * 128
+def test_attention_forward_backward(B, S, nh, hd):
+    assert A.available() and A.supported(S, hd)
+    H = nh * hd
     g = torch.Generator(device="cuda").manual_seed(S + nh)
     qkv = (torch.randn(B * S, 3 * H, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
     d_out = (torch.randn(B * S, H, device="cuda", generator=g) * 0.5).to(torch.bfloat16)

@@ -1,4 +1,5 @@
-"""Trainer kernels (RMSNorm, RoPE, SwiGLU, cross-entropy, embedding, AdamW, SGD) against
+"""Trainer kernels (RMSNorm, LayerNorm, RoPE, SwiGLU, bias + GELU, cross-entropy, embedding,
+AdamW, SGD) against
 plain PyTorch fp32 references of the same ops."""
 
 import pytest
@@ -45,6 +46,54 @@ def _rope_ref(t, cos, sin):
     half = t.shape[-1] // 2
     a, b = t[..., :half], t[..., half:]
     return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+
+
+@pytest.mark.parametrize("rows,H", [(64, 256), (1000, 1024), (37, 768), (5, 8)])
+def test_layernorm_fwd_bwd(rows, H):
+    x = (_bf(rows, H, seed=1).float() * 2 + 0.5).to(torch.bfloat16).requires_grad_()
+    w = (1 + 0.1 * _bf(H, seed=2).float()).to(torch.bfloat16).requires_grad_()
+    b = (0.1 * _bf(H, seed=4).float()).to(torch.bfloat16).requires_grad_()
+    dy = _bf(rows, H, seed=3)
+    assert K.layernorm_supported(x)
+    y = K.layernorm(x, w, b, 1e-5)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.layer_norm(xr, (H,), wr, br, 1e-5)
+    yr.backward(dy.float())
+    _close(y, yr, atol=3e-2)
+    _close(x.grad, xr.grad, atol=4e-2)
+    tol = 0.02 * rows ** 0.5 + 0.05
+    assert torch.allclose(w.grad.float(), wr.grad, rtol=3e-2, atol=tol)
+    assert torch.allclose(b.grad.float(), br.grad, rtol=3e-2, atol=tol)
+    # fp32 main_grad accumulation: gradients land in the flat buffers, autograd sees None
+    w2, b2 = w.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    w2.main_grad = torch.ones(H, device="cuda")
+    b2.main_grad = torch.zeros(H, device="cuda")
+    K.layernorm(x.detach(), w2, b2, 1e-5).backward(dy)
+    assert w2.grad is None and b2.grad is None
+    assert torch.allclose(w2.main_grad - 1, wr.grad, rtol=1e-2, atol=tol)
+    assert torch.allclose(b2.main_grad, br.grad, rtol=1e-2, atol=tol)
+    assert not K.layernorm_supported(torch.empty(2, 2048, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("rows,C", [(64, 256), (777, 4096), (3, 8)])
+def test_bias_gelu_fwd_bwd(rows, C):
+    x = (_bf(rows, C, seed=5).float() * 2).to(torch.bfloat16).requires_grad_()
+    b = _bf(C, seed=6).requires_grad_()
+    dy = _bf(rows, C, seed=7)
+    y = K.bias_gelu(x, b)
+    y.backward(dy)
+    xr, br = x.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    yr = torch.nn.functional.gelu(xr + br, approximate="tanh")
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    assert torch.allclose(b.grad.float(), br.grad, rtol=3e-2, atol=0.03 * rows ** 0.5 + 0.05)
+    b2 = b.detach().clone().requires_grad_()
+    b2.main_grad = torch.zeros(C, device="cuda")
+    K.bias_gelu(x.detach(), b2).backward(dy)
+    assert b2.grad is None
+    assert torch.allclose(b2.main_grad, br.grad, rtol=1e-2, atol=0.03 * rows ** 0.5 + 0.05)
 
 
 def test_rope_fwd_bwd():
