@@ -139,14 +139,15 @@ def attention(args):
     from bitscom_b200.ops import attention as A
 
     _, tflops, tag = _peaks()
-    B, S, nh, hd = args.batch, args.seq, args.heads, 128
+    B, S, nh, hd = args.batch, args.seq, args.heads, args.head_dim
     H = nh * hd
     qkv = (torch.randn(B * S, 3 * H, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
     d_out = (torch.randn(B * S, H, device="cuda") * 0.5).to(torch.bfloat16)
     for _ in range(args.warmup):
         A.attention(qkv, B, S, nh, hd).backward(d_out)
-    outs = []
-    ms_f = _timed(lambda i: outs.append(A.attention(qkv, B, S, nh, hd)), args.iters)
+    ms_f = _timed(lambda i: A.attention(qkv, B, S, nh, hd), args.iters)
+    # the backward pass consumes one forward graph per call: build them outside the timing
+    outs = [A.attention(qkv, B, S, nh, hd) for _ in range(3 * args.iters)]
     ms_b = _timed(lambda i: outs[i].backward(d_out), args.iters)
     A.check_status()
     flops = 4.0 * B * nh * S * S * hd / 2
@@ -155,6 +156,7 @@ def attention(args):
     ms_ref = _timed(lambda i: torch.nn.functional.scaled_dot_product_attention(
         q, k, v, is_causal=True), args.iters)
     print(json.dumps({"case": "attention_tcgen05", "batch": B, "seq": S, "heads": nh,
+                      "head_dim": hd,
                       "fwd_ms": ms_f, "fwd_tflops": flops / ms_f / 1e9,
                       "fwd_frac_bf16_peak": flops / ms_f / 1e9 / tflops,
                       "bwd_ms": ms_b, "bwd_tflops": 2.5 * flops / ms_b / 1e9,
@@ -188,6 +190,25 @@ def elementwise(args):
     rows.append(("swiglu_fwd", ms_f, 3 * T * F * 2))
     ms = _timed(lambda i: K.swiglu(gu).backward(dh), args.iters) - ms_f
     rows.append(("swiglu_bwd", ms, 5 * T * F * 2))
+    # GPT-2 medium shapes: LayerNorm over 1024, bias + GELU over 4096
+    xl, wl, bl = bf(T, 1024).requires_grad_(), bf(1024).requires_grad_(), bf(1024).requires_grad_()
+    wl.main_grad, bl.main_grad = torch.zeros(1024, device="cuda"), torch.zeros(1024, device="cuda")
+    dyl = bf(T, 1024)
+    for _ in range(args.warmup):
+        K.layernorm(xl, wl, bl).backward(dyl)
+    ms_f = _timed(lambda i: K.layernorm(xl, wl, bl), args.iters)
+    rows.append(("layernorm_fwd", ms_f, 2 * T * 1024 * 2))
+    ms = _timed(lambda i: K.layernorm(xl, wl, bl).backward(dyl), args.iters) - ms_f
+    rows.append(("layernorm_bwd", ms, 3 * T * 1024 * 2))
+    xg, bg = bf(T, 4096).requires_grad_(), bf(4096).requires_grad_()
+    bg.main_grad = torch.zeros(4096, device="cuda")
+    dyg = bf(T, 4096)
+    for _ in range(args.warmup):
+        K.bias_gelu(xg, bg).backward(dyg)
+    ms_f = _timed(lambda i: K.bias_gelu(xg, bg), args.iters)
+    rows.append(("bias_gelu_fwd", ms_f, 2 * T * 4096 * 2))
+    ms = _timed(lambda i: K.bias_gelu(xg, bg).backward(dyg), args.iters) - ms_f
+    rows.append(("bias_gelu_bwd", ms, 3 * T * 4096 * 2))
     logits = bf(T, V)
     tgt = torch.randint(1, V, (T,), device="cuda")
     for _ in range(args.warmup):
@@ -211,6 +232,7 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--elems", type=int, default=1 << 25)
     ap.add_argument("--bits", type=int, default=4)

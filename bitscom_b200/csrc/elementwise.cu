@@ -104,52 +104,78 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
 
 // dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw += sum_rows dy * x * rstd (fp32)
 // Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dw partial in registers
-// (thread t owns columns t*8 + k*blockDim*8), adding it to dw once at the end.
+// (thread t owns columns t*8 + k*blockDim*8), adding it to dw once at the end.  A row is read
+// once: x and dy stay in registers (as packed bf16) across the reduction, the next row's loads
+// are issued before the reduction of the current one, and the reduction costs one barrier
+// (warp partials in a double-buffered scratch, every thread adds them up itself).
 template <int MAX_ITERS>
 __global__ void __launch_bounds__(512)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                    const bf16* __restrict__ w, const float* __restrict__ rstd,
                    bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
-  __shared__ float scratch[33];
-  float acc[MAX_ITERS][8];
+  __shared__ float partial[2][16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  float acc[MAX_ITERS][8], fw[MAX_ITERS][8];
+  Bf8 cx[MAX_ITERS], cg[MAX_ITERS], nx[MAX_ITERS], ng[MAX_ITERS];
 #pragma unroll
-  for (int k = 0; k < MAX_ITERS; ++k)
+  for (int k = 0; k < MAX_ITERS; ++k) {
+    const int c = (threadIdx.x + k * blockDim.x) * 8;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[k][i] = 0.0f;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const bf16* xr = x + (size_t)row * H;
-    const bf16* gr = dy + (size_t)row * H;
+    for (int i = 0; i < 8; ++i) acc[k][i] = fw[k][i] = 0.0f;
+    if (c < H) load8(w + c, fw[k]);
+  }
+  auto fetch = [&](int row, Bf8 (&bx)[MAX_ITERS], Bf8 (&bg)[MAX_ITERS]) {
+#pragma unroll
+    for (int k = 0; k < MAX_ITERS; ++k) {
+      const int c = (threadIdx.x + k * blockDim.x) * 8;
+      if (c < H) {
+        bx[k] = *reinterpret_cast<const Bf8*>(x + (size_t)row * H + c);
+        bg[k] = *reinterpret_cast<const Bf8*>(dy + (size_t)row * H + c);
+      }
+    }
+  };
+  int row = blockIdx.x;
+  if (row < rows) fetch(row, cx, cg);
+  int parity = 0;
+  for (; row < rows; row += gridDim.x, parity ^= 1) {
+    const int next = row + gridDim.x;
+    if (next < rows) fetch(next, nx, ng);
     const float rs = rstd[row];
     float dot = 0.0f;
 #pragma unroll
     for (int k = 0; k < MAX_ITERS; ++k) {
       const int c = (threadIdx.x + k * blockDim.x) * 8;
       if (c < H) {
-        float fx[8], fg[8], fw[8];
-        load8(xr + c, fx);
-        load8(gr + c, fg);
-        load8(w + c, fw);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          dot += fg[i] * fw[i] * fx[i];
-          acc[k][i] += fg[i] * fx[i] * rs;
+          const float fx = __bfloat162float(cx[k].v[i]), fg = __bfloat162float(cg[k].v[i]);
+          dot += fg * fw[k][i] * fx;
+          acc[k][i] += fg * fx * rs;
         }
       }
     }
-    dot = block_sum(dot, scratch);
-    const float coef = dot * rs * rs * rs / (float)H;
+    dot = warp_sum(dot);
+    if (lane == 0) partial[parity][warp] = dot;
+    __syncthreads();  // the other buffer is free again: its readers passed the previous barrier
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) total += i < nwarps ? partial[parity][i] : 0.0f;
+    const float coef = total * rs * rs * rs / (float)H;
     bf16* dr = dx + (size_t)row * H;
 #pragma unroll
     for (int k = 0; k < MAX_ITERS; ++k) {
       const int c = (threadIdx.x + k * blockDim.x) * 8;
       if (c < H) {
-        float fx[8], fg[8], fw[8];
-        load8(xr + c, fx);
-        load8(gr + c, fg);
-        load8(w + c, fw);
+        float o[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) fx[i] = fg[i] * fw[i] * rs - fx[i] * coef;
-        store8(dr + c, fx);
+        for (int i = 0; i < 8; ++i) {
+          const float fx = __bfloat162float(cx[k].v[i]), fg = __bfloat162float(cg[k].v[i]);
+          o[i] = fg * fw[k][i] * rs - fx * coef;
+        }
+        store8(dr + c, o);
+        cx[k] = nx[k];
+        cg[k] = ng[k];
       }
     }
   }

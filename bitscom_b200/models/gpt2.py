@@ -45,9 +45,12 @@ class GPT2Config:
 
 
 class GPT2(torch.nn.Module):
-    def __init__(self, cfg: GPT2Config, device="cuda", seed: int = 0, pad_to: int = 256):
+    def __init__(self, cfg: GPT2Config, device="cuda", seed: int = 0, pad_to: int = 256,
+                 fused_ops: bool = True):
         super().__init__()
         self.cfg = cfg
+        # False: LayerNorm, GELU and attention from torch (the library baseline for A/B runs)
+        self.fused_ops = fused_ops
         D, V = cfg.d_model, cfg.padded_vocab
         shapes: Dict[str, Tuple[int, ...]] = {"wte": (V, D), "wpe": (cfg.seq, D)}
         for i in range(cfg.n_layer):
@@ -92,9 +95,11 @@ class GPT2(torch.nn.Module):
         D, nh = cfg.d_model, cfg.n_head
         x = K.embedding(ids.reshape(-1), self._w("wte")) + self._w("wpe")[:S].repeat(B, 1)
         hd = D // nh
-        fused_attn = A.available() and A.supported(S, hd)
-        ln = K.layernorm if K.layernorm_supported(x) else (
+        fused_attn = self.fused_ops and A.available() and A.supported(S, hd)
+        ln = K.layernorm if self.fused_ops and K.layernorm_supported(x) else (
             lambda t, w, b: F.layer_norm(t, (D,), w, b))
+        gelu = K.bias_gelu if self.fused_ops else (
+            lambda t, b: F.gelu(t + b, approximate="tanh"))
         for i in range(cfg.n_layer):
             h = ln(x, self._w(f"h{i}.ln1_w"), self._w(f"h{i}.ln1_b"))
             qkv = G.linear(h, self._w(f"h{i}.wqkv")) + self._w(f"h{i}.bqkv")
@@ -107,7 +112,7 @@ class GPT2(torch.nn.Module):
                 a = a.transpose(1, 2).reshape(B * S, D)
             x = x + G.linear(a, self._w(f"h{i}.wo")) + self._w(f"h{i}.bo")
             h = ln(x, self._w(f"h{i}.ln2_w"), self._w(f"h{i}.ln2_b"))
-            h = K.bias_gelu(G.linear(h, self._w(f"h{i}.wfc")), self._w(f"h{i}.bfc"))
+            h = gelu(G.linear(h, self._w(f"h{i}.wfc")), self._w(f"h{i}.bfc"))
             x = x + G.linear(h, self._w(f"h{i}.wproj")) + self._w(f"h{i}.bproj")
         x = ln(x, self._w("lnf_w"), self._w("lnf_b"))
         logits = G.linear(x, self._w("wte"))

@@ -42,6 +42,26 @@ def stream_ptr(device: Optional[torch.device] = None) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def on_device(device: torch.device):
+    """Context that makes ``device`` current for a native launch.  When it already is (one
+    process per GPU, the normal case) this is a no-op object: the full ``torch.cuda.device``
+    guard costs several microseconds per call, which is visible for small kernels."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
 def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 

@@ -94,7 +94,7 @@ def blockwise_quantize_pack(x: torch.Tensor, bitwidth: int, block_size: int,
     n = x.numel()
     packed = torch.empty(packed_nbytes(n, bitwidth), dtype=torch.uint8, device=x.device)
     scales = torch.empty(-(-n // block_size), dtype=torch.float16, device=x.device)
-    with torch.cuda.device(x.device):
+    with _native.on_device(x.device):
         check(lib.bcom_blockwise_quantize_pack(
             ptr(x), DTYPE_CODE[x.dtype], n, bitwidth, block_size, int(bool(stochastic)),
             _key(sr_seed, stochastic, sr_stream), int(sr_offset) & 0xFFFFFFFF,
@@ -115,7 +115,7 @@ def blockwise_unpack_dequantize(packed: torch.Tensor, scales: torch.Tensor, bitw
             f"scales length {scales.numel()} does not match expected blocks "
             f"{-(-numel // block_size)}")
     out = torch.empty(numel, dtype=dtype, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _native.on_device(packed.device):
         check(lib.bcom_blockwise_unpack_dequantize(
             ptr(packed), ptr(scales), bitwidth, numel, block_size, ptr(out),
             DTYPE_CODE[dtype], stream_ptr(packed.device)), "blockwise_unpack_dequantize")
@@ -130,7 +130,7 @@ def quantize_per_tensor(x: torch.Tensor, bitwidth: int, stochastic: bool = False
     flat = x.detach().contiguous().view(-1)
     q = torch.empty(flat.numel(), dtype=torch.int16, device=x.device)
     scratch = torch.empty(2, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _native.on_device(x.device):
         check(lib.bcom_quantize_per_tensor(
             ptr(flat), DTYPE_CODE[flat.dtype], flat.numel(), bitwidth, int(bool(stochastic)),
             _key(sr_seed, stochastic, 2), int(sr_offset) & 0xFFFFFFFF,
@@ -143,7 +143,7 @@ def dequantize_per_tensor(q: torch.Tensor, scale: float) -> torch.Tensor:
     lib = _get()
     flat = q.contiguous().view(-1)
     out = torch.empty(flat.numel(), dtype=torch.float32, device=q.device)
-    with torch.cuda.device(q.device):
+    with _native.on_device(q.device):
         check(lib.bcom_dequantize_per_tensor(ptr(flat), flat.numel(), float(scale), ptr(out),
                                              stream_ptr(q.device)), "dequantize_per_tensor")
     return out.view(q.shape)
@@ -153,7 +153,7 @@ def pack(q: torch.Tensor, bitwidth: int) -> torch.Tensor:
     lib = _get()
     flat = q.contiguous().view(-1)
     out = torch.empty(packed_nbytes(flat.numel(), bitwidth), dtype=torch.uint8, device=q.device)
-    with torch.cuda.device(q.device):
+    with _native.on_device(q.device):
         check(lib.bcom_pack(ptr(flat), flat.numel(), bitwidth, ptr(out), stream_ptr(q.device)),
               "pack")
     return out
@@ -165,7 +165,7 @@ def unpack(packed: torch.Tensor, bitwidth: int, numel: int) -> torch.Tensor:
     if packed.numel() < packed_nbytes(numel, bitwidth):
         raise ValueError("packed buffer is smaller than numel codes")
     out = torch.empty(numel, dtype=torch.int16, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _native.on_device(packed.device):
         check(lib.bcom_unpack(ptr(packed), numel, bitwidth, ptr(out),
                               stream_ptr(packed.device)), "unpack")
     return out

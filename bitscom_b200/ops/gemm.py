@@ -73,7 +73,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
     if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16,
                                                                       torch.float32):
         raise ValueError("bad output tensor")
-    with torch.cuda.device(a.device):
+    with _native.on_device(a.device):
         check(lib.bcom_gemm_bf16(
             ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
             int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32),

@@ -55,6 +55,9 @@ def main(argv=None):
     ap.add_argument("--param-bits", type=int, default=8)
     ap.add_argument("--mode", default="lowbit", choices=["lowbit", "nccl"])
     ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
+    ap.add_argument("--torch-ops", action="store_true",
+                    help="LayerNorm, GELU and attention from torch instead of this library's "
+                         "kernels (A/B baseline)")
     ap.add_argument("--out", default="gpurun_out/gpt2_sharded.jsonl")
     args = ap.parse_args(argv)
 
@@ -66,7 +69,7 @@ def main(argv=None):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     cfg = GPT2Config.medium() if args.model == "medium" else GPT2Config.tiny()
-    model = GPT2(cfg, dev, seed=0, pad_to=256 * max(world, 1))
+    model = GPT2(cfg, dev, seed=0, pad_to=256 * max(world, 1), fused_ops=not args.torch_ops)
     flat = model.flat
     if args.mode == "lowbit" and world > 1:
         ggrp = LowBitGroup(bitwidth=args.grad_bits, block_size=256, error_feedback=True)
@@ -107,7 +110,7 @@ def main(argv=None):
     if rank == 0:
         tokens = world * args.micro_batch * cfg.seq
         row = {"workload": "gpt2_medium_sharded" if args.model == "medium" else "gpt2_tiny",
-               "mode": args.mode, "world": world, "grad_bits": args.grad_bits,
+               "mode": args.mode, "world": world, "fused_ops": not args.torch_ops, "grad_bits": args.grad_bits,
                "param_bits": args.param_bits, "ms_per_step": float(ms.item()),
                "tokens_per_s": tokens / float(ms.item()) * 1e3,
                "loss_first": float(first.item()), "loss_last": float(last.item())}
