@@ -708,8 +708,7 @@ int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int se
   using namespace attn;
   if (!shape_ok(batch, seq, heads, head_dim)) return 1001;
   if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return 1002;
-  (void)cudaFree(nullptr);
-  (void)cudaGetLastError();
+  tc::bind_context_once();
   cudaStream_t st = (cudaStream_t)stream;
   return head_dim == 128 ? launch_fwd<128>(qkv, out, lse2, batch, seq, heads, scale, st)
                          : launch_fwd<64>(qkv, out, lse2, batch, seq, heads, scale, st);
@@ -724,8 +723,7 @@ int bcom_attention_bwd(const void* qkv, const void* out, const void* d_out, cons
   using namespace attn;
   if (!shape_ok(batch, seq, heads, head_dim)) return 1001;
   if (((uintptr_t)qkv & 15) || ((uintptr_t)d_out & 15) || ((uintptr_t)dqkv & 15)) return 1002;
-  (void)cudaFree(nullptr);
-  (void)cudaGetLastError();
+  tc::bind_context_once();
   cudaStream_t st = (cudaStream_t)stream;
   return head_dim == 128
              ? launch_bwd<128>(qkv, out, d_out, lse2, dqkv, (float*)dq_acc, (float*)delta, batch,

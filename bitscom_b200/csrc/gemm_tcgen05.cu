@@ -405,7 +405,7 @@ int bcom_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   CUtensorMap tmA, tmB;
   // the tensor-map encoder is a driver call: make sure this thread (it may be an autograd
   // worker) has the device's primary context bound
-  (void)cudaFree(nullptr);
+  tc::bind_context_once();
   if (a_mn_major ? make_map(&tmA, A, K, M, lda, 64, BK) : make_map(&tmA, A, M, K, lda, BK, BM))
     return 1003;
   if (b_mn_major ? make_map(&tmB, B, K, N, ldb, 64, BK) : make_map(&tmB, B, N, K, ldb, BK, BN))

@@ -190,4 +190,20 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// Host side.  Driver calls such as the tensor-map encoder need the device's primary context
+// bound to the calling thread, which an autograd worker thread may not have yet: a no-op
+// runtime call binds it.  Done once per (thread, device), so that later calls issue nothing
+// that stream capture would object to.
+inline void bind_context_once() {
+  static thread_local int bound_device = -1;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  if (dev != bound_device) {
+    (void)cudaFree(nullptr);
+    (void)cudaGetLastError();
+    bound_device = dev;
+  }
+}
+
+
 }  // namespace tc

@@ -55,6 +55,8 @@ def main(argv=None):
     ap.add_argument("--param-bits", type=int, default=8)
     ap.add_argument("--mode", default="lowbit", choices=["lowbit", "nccl"])
     ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="capture forward + backward into one CUDA graph (launch-bound model)")
     ap.add_argument("--torch-ops", action="store_true",
                     help="LayerNorm, GELU and attention from torch instead of this library's "
                          "kernels (A/B baseline)")
@@ -81,14 +83,27 @@ def main(argv=None):
         opt = K.FlatAdamW(flat.master, flat.grads, flat.params, lr=3e-4)
     g = torch.Generator().manual_seed(5 + rank)
 
-    def step():
-        ids = torch.randint(0, cfg.vocab_size, (args.micro_batch, cfg.seq), generator=g)
-        ids = ids.pin_memory().to(dev, non_blocking=True)
+    def fwd_bwd(ids):
         loss = model(ids, targets=ids)
         loss.backward()
         model.collect_autograd_grads()
-        opt.step()
         return loss.detach()
+
+    compute = fwd_bwd
+    if args.cuda_graph:
+        # forward + backward of the fixed-shape step as one graph launch; the sharded
+        # optimizer and its collectives stay eager
+        from ..utils.graphs import GraphedStep
+
+        example = torch.zeros(args.micro_batch, cfg.seq, dtype=torch.int64, device=dev)
+        compute = GraphedStep(fwd_bwd, [example], reset=lambda: flat.grads.zero_())
+
+    def step():
+        ids = torch.randint(0, cfg.vocab_size, (args.micro_batch, cfg.seq), generator=g)
+        ids = ids.pin_memory().to(dev, non_blocking=True)
+        loss = compute(ids)
+        opt.step()
+        return loss.clone() if args.cuda_graph else loss
 
     for _ in range(args.warmup):
         step()
@@ -110,7 +125,8 @@ def main(argv=None):
     if rank == 0:
         tokens = world * args.micro_batch * cfg.seq
         row = {"workload": "gpt2_medium_sharded" if args.model == "medium" else "gpt2_tiny",
-               "mode": args.mode, "world": world, "fused_ops": not args.torch_ops, "grad_bits": args.grad_bits,
+               "mode": args.mode, "world": world, "fused_ops": not args.torch_ops,
+               "cuda_graph": bool(args.cuda_graph), "grad_bits": args.grad_bits,
                "param_bits": args.param_bits, "ms_per_step": float(ms.item()),
                "tokens_per_s": tokens / float(ms.item()) * 1e3,
                "loss_first": float(first.item()), "loss_last": float(last.item())}
