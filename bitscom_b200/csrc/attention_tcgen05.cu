@@ -284,6 +284,321 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 12
 }
 
 // ---------------------------------------------------------------------------
+// forward, software-pipelined variant
+// ---------------------------------------------------------------------------
+// Same tiles and math as attention_fwd_kernel, but the tensor pipe and the softmax no
+// longer take turns:
+//   * warp 4 is the issuer (one thread drives TMA and tcgen05.mma), warps 0-3 do the softmax
+//     (thread t <-> query row t <-> TMEM lane t) and never wait for a copy;
+//   * S is double-buffered in TMEM, so S_{j+1} = Q K_{j+1}^T is computed while the softmax of
+//     block j runs; K and V are double-buffered in shared memory and fetched two blocks ahead;
+//   * O stays in TMEM and P V accumulates into it (no per-block read-back); a warp rescales
+//     its 32 rows of O (tcgen05.ld / st) only in blocks where one of them raised its running
+//     maximum, which after the first few blocks of a row is rare.
+// Order on the tensor pipe: QK_0, QK_1, PV_0, QK_2, PV_1, QK_3, ...
+// mbarriers: bar_k[b] / bar_v[b] copy of block j landed (b = j & 1, phase j >> 1);
+// bar_s[b] S_j ready; bar_p (128 arrivals) P_j written, S_j consumed, O rescaled;
+// bar_o PV_j done (phase j).  No barrier can complete twice between two waits of the same
+// waiter: QK_{j+2} and PV_j are issued only after bar_p of block j.
+constexpr int kPipeThreads = 160;
+
+struct PipeShared {
+  uint64_t bar_q, bar_k[2], bar_v[2], bar_s[2], bar_p, bar_o;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+template <int HD> struct FwdPipe {
+  static constexpr int Q_BYTES = BQ * HD * 2;
+  static constexpr int K_BYTES = BKF * HD * 2;
+  static constexpr int DATA = Q_BYTES + 4 * K_BYTES + FWD_P_BYTES;  // 112 KiB at head_dim 128
+  // no slack for manual alignment (two CTAs of 112 KiB + 1 KiB reserved each just fit one
+  // SM): the kernel checks that the dynamic window is 1024-byte aligned and gives up if not
+  static constexpr int SMEM = DATA + 128;
+  static constexpr int TMEM_COLS = 256;  // S0 (64) + S1 (64) + O (HD)
+};
+
+// 2^x as one MUFU instruction (arguments here are <= 0; tiny results flush to zero)
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// every lane waits; the verdict is made uniform so that the warp stays converged for the
+// warp-collective tcgen05.ld / st that follow
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
+  const bool ok = tc::mbar_wait(bar, parity, kBudgetNs);
+  return __all_sync(0xffffffffu, ok);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kPipeThreads, 2)
+attention_fwd_pipelined_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 128}
+                               const __grid_constant__ CUtensorMap tm_kv,   // box {64, 64}
+                               const FwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr int Q_BYTES = FwdPipe<HD>::Q_BYTES, K_BYTES = FwdPipe<HD>::K_BYTES;
+  uint8_t* sQ = smem;
+  uint8_t* sK0 = sQ + Q_BYTES;
+  uint8_t* sV0 = sK0 + 2 * K_BYTES;
+  uint8_t* sP = sV0 + 2 * K_BYTES;
+  PipeShared* sh = reinterpret_cast<PipeShared*>(sP + FWD_P_BYTES);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if ((tc::smem_u32(smem) & 1023u) != 0u) {  // same answer in every thread of the CTA
+    if (tid == 0) record_fail(20);
+    return;
+  }
+  const int qblocks = p.seq / BQ;
+  const int qb = qblocks - 1 - (int)(blockIdx.x % qblocks);  // heavy query blocks first
+  const int bh = blockIdx.x / qblocks;
+  const int h = bh % p.heads, b = bh / p.heads;
+  const int H = p.heads * HD;
+  const int row0 = b * p.seq + qb * BQ;
+  const int q_col = h * HD, k_col = H + h * HD, v_col = 2 * H + h * HD;
+  const int n = (qb * BQ + BQ) / BKF;  // causal: keys 0 .. q0 + 127
+
+  if (tid == 0) {
+    tc::mbar_init(&sh->bar_q, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&sh->bar_k[i], 1);
+      tc::mbar_init(&sh->bar_v[i], 1);
+      tc::mbar_init(&sh->bar_s[i], 1);
+    }
+    tc::mbar_init(&sh->bar_p, 128);
+    tc::mbar_init(&sh->bar_o, 1);
+    sh->abort = 0;
+    tc::fence_mbar_init();
+  }
+  if (warp == 4) tc::tmem_alloc(&sh->tmem_base, FwdPipe<HD>::TMEM_COLS);
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem = sh->tmem_base;
+  const uint32_t tO = tmem + 128;
+
+  if (warp == 4) {
+    // ------------------------------- issuer -------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc::make_idesc_bf16(BQ, BKF, false, false);
+      constexpr uint32_t idesc_o = tc::make_idesc_bf16(BQ, HD, false, true);
+      const uint32_t aQ = tc::smem_u32(sQ), aK0 = tc::smem_u32(sK0), aV0 = tc::smem_u32(sV0),
+                     aP = tc::smem_u32(sP);
+      bool ok = true;
+      auto wait = [&](uint64_t* bar, uint32_t parity, unsigned code) {
+        if (ok && !tc::mbar_wait(bar, parity, kBudgetNs)) {
+          ok = false;
+          sh->abort = 1;
+          record_fail(code);
+        }
+      };
+      auto load_k = [&](int j) {
+        uint64_t* bar = &sh->bar_k[j & 1];
+        tc::mbar_expect_tx(bar, K_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tc::tma_load_2d(sK0 + (j & 1) * K_BYTES + c * BKF * 128, &tm_kv, bar, k_col + 64 * c,
+                          b * p.seq + j * BKF);
+      };
+      auto load_v = [&](int j) {
+        uint64_t* bar = &sh->bar_v[j & 1];
+        tc::mbar_expect_tx(bar, K_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tc::tma_load_2d(sV0 + (j & 1) * K_BYTES + c * BKF * 128, &tm_kv, bar, v_col + 64 * c,
+                          b * p.seq + j * BKF);
+      };
+      auto issue_qk = [&](int j) {
+        const uint32_t aK = aK0 + (j & 1) * K_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          tc::umma_bf16(tmem + (j & 1) * 64, desc_kmajor(aQ, BQ, ks), desc_kmajor(aK, BKF, ks),
+                        idesc_s, ks != 0);
+        tc::umma_commit(&sh->bar_s[j & 1]);
+      };
+      auto issue_pv = [&](int j) {
+        const uint32_t aV = aV0 + (j & 1) * K_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BKF / 16; ++ks)
+          tc::umma_bf16(tO, desc_kmajor(aP, BQ, ks), desc_mnmajor(aV, BKF, ks), idesc_o,
+                        (j != 0) || (ks != 0));
+        tc::umma_commit(&sh->bar_o);
+      };
+
+      tc::mbar_expect_tx(&sh->bar_q, Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c)
+        tc::tma_load_2d(sQ + c * BQ * 128, &tm_q, &sh->bar_q, q_col + 64 * c, row0);
+      load_k(0);
+      load_v(0);
+      if (n > 1) {
+        load_k(1);
+        load_v(1);
+      }
+      wait(&sh->bar_q, 0, 21);
+      wait(&sh->bar_k[0], 0, 22);
+      if (ok) {
+        tc::tc_fence_after_sync();
+        issue_qk(0);
+      }
+      if (n > 1) {
+        wait(&sh->bar_k[1], 0, 22);
+        if (ok) {
+          tc::tc_fence_after_sync();
+          issue_qk(1);
+        }
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        const uint32_t par2 = (uint32_t)(j >> 1) & 1u;
+        if (j + 2 < n) {  // K buffer j & 1 is free once QK_j has completed
+          wait(&sh->bar_s[j & 1], par2, 23);
+          if (ok) load_k(j + 2);
+        }
+        if (j >= 1 && j + 1 < n) {  // V buffer (j + 1) & 1 is free once PV_{j-1} has completed
+          wait(&sh->bar_o, (uint32_t)(j - 1) & 1u, 24);
+          if (ok) load_v(j + 1);
+        }
+        wait(&sh->bar_p, (uint32_t)j & 1u, 25);  // P_j written, S_j consumed, O rescaled
+        wait(&sh->bar_v[j & 1], par2, 26);
+        if (!ok) break;
+        tc::tc_fence_after_sync();
+        issue_pv(j);
+        if (j + 2 < n) {
+          wait(&sh->bar_k[j & 1], (uint32_t)((j + 2) >> 1) & 1u, 22);
+          if (!ok) break;
+          tc::tc_fence_after_sync();
+          issue_qk(j + 2);
+        }
+      }
+      // every MMA issued must have finished before TMEM is handed back
+      if (ok && n > 0) wait(&sh->bar_o, (uint32_t)(n - 1) & 1u, 27);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- softmax warps ------------------------------------
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const int q_idx = qb * BQ + tid;  // position of this thread's query inside the sequence
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      if (!warp_wait(&sh->bar_s[j & 1], (uint32_t)(j >> 1) & 1u)) {
+        ok = false;
+        if (lane == 0) { sh->abort = 1; record_fail(28); }
+        break;
+      }
+      tc::tc_fence_after_sync();
+      const uint32_t tS = tmem + (j & 1) * 64;
+      float s[BKF];  // raw scores (unscaled), then probabilities
+      {
+        uint32_t r[BKF];
+        tc::tmem_ld_32x32(tS + lane_addr, reinterpret_cast<uint32_t(&)[32]>(r[0]));
+        tc::tmem_ld_32x32(tS + lane_addr + 32, reinterpret_cast<uint32_t(&)[32]>(r[32]));
+        tc::tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < BKF; ++i) s[i] = __uint_as_float(r[i]);
+      }
+      const int k0 = j * BKF;
+      if (k0 + BKF - 1 > qb * BQ) {  // block touches the diagonal
+#pragma unroll
+        for (int i = 0; i < BKF; ++i)
+          if (k0 + i > q_idx) s[i] = -INFINITY;
+      }
+      // the softmax scale is positive, so the maximum can be taken on the raw scores; four
+      // independent chains instead of one 64-deep one (this loop is latency bound)
+      float mx[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+      for (int i = 4; i < BKF; i += 4) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], s[i + q]);
+      }
+      const float m_blk =
+          fmaxf(m_run, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
+      const float alpha = ex2_fast(m_run - m_blk);  // first block: 2^(-inf) = 0
+      float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int i = 0; i < BKF; i += 4) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          s[i + q] = ex2_fast(fmaf(s[i + q], p.scale_log2, -m_blk));
+          sm[q] += s[i + q];
+        }
+      }
+      l_run = l_run * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
+      m_run = m_blk;
+      if (j > 0) {
+        // PV_{j-1} done: the P buffer may be overwritten and O is at rest
+        if (!warp_wait(&sh->bar_o, (uint32_t)(j - 1) & 1u)) {
+          ok = false;
+          if (lane == 0) { sh->abort = 1; record_fail(29); }
+          break;
+        }
+        tc::tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tc::tmem_ld_32x32(tO + lane_addr + c * 32, r);
+            tc::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tc::tmem_st_32x32(tO + lane_addr + c * 32, r);
+          }
+          tc::tmem_wait_st();
+        }
+      }
+#pragma unroll
+      for (int c8 = 0; c8 < BKF / 8; ++c8) {
+        uint4 v;
+        v.x = pack_bf16(s[c8 * 8 + 0], s[c8 * 8 + 1]);
+        v.y = pack_bf16(s[c8 * 8 + 2], s[c8 * 8 + 3]);
+        v.z = pack_bf16(s[c8 * 8 + 4], s[c8 * 8 + 5]);
+        v.w = pack_bf16(s[c8 * 8 + 6], s[c8 * 8 + 7]);
+        *reinterpret_cast<uint4*>(sP + swz(tid, c8)) = v;
+      }
+      tc::fence_proxy_async();       // generic-proxy smem writes -> visible to the MMA
+      tc::tc_fence_before_sync();    // orders the TMEM reads / writes above before the arrival
+      tc::mbar_arrive(&sh->bar_p);
+      if (__any_sync(0xffffffffu, sh->abort != 0)) {
+        ok = false;
+        break;
+      }
+    }
+    // ---- epilogue: O / l -> out ----
+    if (ok && n > 0 && warp_wait(&sh->bar_o, (uint32_t)(n - 1) & 1u)) {
+      tc::tc_fence_after_sync();
+      const float inv = 1.0f / l_run;
+      __nv_bfloat16* dst = p.out + (size_t)(row0 + tid) * H + q_col;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(tO + lane_addr + c * 32, r);
+        tc::tmem_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[u * 8 + 0]) * inv, __uint_as_float(r[u * 8 + 1]) * inv);
+          v.y = pack_bf16(__uint_as_float(r[u * 8 + 2]) * inv, __uint_as_float(r[u * 8 + 3]) * inv);
+          v.z = pack_bf16(__uint_as_float(r[u * 8 + 4]) * inv, __uint_as_float(r[u * 8 + 5]) * inv);
+          v.w = pack_bf16(__uint_as_float(r[u * 8 + 6]) * inv, __uint_as_float(r[u * 8 + 7]) * inv);
+          reinterpret_cast<uint4*>(dst + c * 32)[u] = v;
+        }
+      }
+      p.lse2[((size_t)b * p.heads + h) * p.seq + q_idx] = m_run + log2f(l_run);
+    } else if (ok && lane == 0) {
+      sh->abort = 1;
+      record_fail(30);
+    }
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tmem, FwdPipe<HD>::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------
 struct BwdParams {
@@ -653,6 +968,40 @@ static int launch_fwd(const void* qkv, void* out, void* lse2, int batch, int seq
   return (int)cudaGetLastError();
 }
 
+static int g_fwd_variant = 1;  // 0: attention_fwd_kernel, 1: attention_fwd_pipelined_kernel
+
+template <int HD>
+static int launch_fwd_pipelined(const void* qkv, void* out, void* lse2, int batch, int seq,
+                                int heads, float scale, cudaStream_t st) {
+  const long long tokens = (long long)batch * seq;
+  const int W = 3 * heads * HD;
+  CUtensorMap tm_q, tm_kv;
+  if (make_map(&tm_q, qkv, tokens, W, 64, BQ)) return 1003;
+  if (make_map(&tm_kv, qkv, tokens, W, 64, BKF)) return 1004;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute((const void*)attention_fwd_pipelined_kernel<HD>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    FwdPipe<HD>::SMEM);
+    if (attr_err == cudaSuccess)  // two CTAs of 112 KiB need the largest shared-memory carve-out
+      attr_err = cudaFuncSetAttribute((const void*)attention_fwd_pipelined_kernel<HD>,
+                                      cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      cudaSharedmemCarveoutMaxShared);
+  });
+  if (attr_err != cudaSuccess) return 1005;
+  FwdParams p;
+  p.out = (__nv_bfloat16*)out;
+  p.lse2 = (float*)lse2;
+  p.batch = batch;
+  p.seq = seq;
+  p.heads = heads;
+  p.scale_log2 = scale * kLog2e;
+  const int grid = batch * heads * (seq / BQ);
+  attention_fwd_pipelined_kernel<HD><<<grid, kPipeThreads, FwdPipe<HD>::SMEM, st>>>(tm_q, tm_kv, p);
+  return (int)cudaGetLastError();
+}
+
 template <int HD>
 static int launch_bwd(const void* qkv, const void* out, const void* d_out, const void* lse2,
                       void* dqkv, float* dq_acc, float* delta, int batch, int seq, int heads,
@@ -710,8 +1059,20 @@ int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int se
   if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return 1002;
   tc::bind_context_once();
   cudaStream_t st = (cudaStream_t)stream;
+  if (g_fwd_variant == 1)
+    return head_dim == 128
+               ? launch_fwd_pipelined<128>(qkv, out, lse2, batch, seq, heads, scale, st)
+               : launch_fwd_pipelined<64>(qkv, out, lse2, batch, seq, heads, scale, st);
   return head_dim == 128 ? launch_fwd<128>(qkv, out, lse2, batch, seq, heads, scale, st)
                          : launch_fwd<64>(qkv, out, lse2, batch, seq, heads, scale, st);
+}
+
+// 0 selects the forward kernel whose MMA and softmax take turns, 1 the software-pipelined one
+// (issuer warp, double-buffered S in TMEM, O accumulated in TMEM).  Returns the previous value.
+int bcom_attention_set_fwd_variant(int variant) {
+  const int old = attn::g_fwd_variant;
+  if (variant == 0 || variant == 1) attn::g_fwd_variant = variant;
+  return old;
 }
 
 // d_out: [batch*seq, heads*head_dim]; dqkv (written): [batch*seq, 3*heads*head_dim];

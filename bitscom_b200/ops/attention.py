@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Dict, Tuple
 
 import torch
@@ -15,6 +16,9 @@ from ._native import NativeError, check, ptr, stream_ptr
 
 _lib = None
 _scratch: Dict[Tuple, torch.Tensor] = {}
+# forward kernels: "simple" alternates MMA and softmax inside a CTA; "pipelined" has an issuer
+# warp, double-buffered scores in TMEM and the output accumulated in TMEM
+_FWD_VARIANTS = {"simple": 0, "pipelined": 1}
 
 
 def _get():
@@ -26,6 +30,10 @@ def _get():
             lib.bcom_attention_fwd.argtypes = [vp, vp, vp, ci, ci, ci, ci, cf, vp]
             lib.bcom_attention_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, cf, vp]
             lib.bcom_attention_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
+            lib.bcom_attention_set_fwd_variant.argtypes = [ci]
+            variant = os.environ.get("BITSCOM_ATTN_FWD", "").strip().lower()
+            if variant in _FWD_VARIANTS:
+                lib.bcom_attention_set_fwd_variant(_FWD_VARIANTS[variant])
         else:
             lib = None
         _lib = lib if lib is not None else False
@@ -34,6 +42,18 @@ def _get():
 
 def available() -> bool:
     return _native.cuda_present() and _get() is not None
+
+
+def set_forward_variant(name: str) -> str:
+    """Select the forward kernel ("simple" or "pipelined", also ``BITSCOM_ATTN_FWD``); returns
+    the name that was active before."""
+    if name not in _FWD_VARIANTS:
+        raise ValueError(f"unknown attention forward variant {name!r}")
+    lib = _get()
+    if lib is None:
+        raise NativeError("attention kernel needs the bcom_llama library and a GPU")
+    old = lib.bcom_attention_set_fwd_variant(_FWD_VARIANTS[name])
+    return "pipelined" if old == 1 else "simple"
 
 
 def supported(seq: int, head_dim: int) -> bool:
