@@ -141,6 +141,7 @@ def attention(args):
     _, tflops, tag = _peaks()
     B, S, nh, hd = args.batch, args.seq, args.heads, args.head_dim
     A.set_forward_variant(args.fwd_variant)
+    A.set_backward_dq_variant(args.bwd_dq)
     H = nh * hd
     qkv = (torch.randn(B * S, 3 * H, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
     d_out = (torch.randn(B * S, H, device="cuda") * 0.5).to(torch.bfloat16)
@@ -157,7 +158,7 @@ def attention(args):
     ms_ref = _timed(lambda i: torch.nn.functional.scaled_dot_product_attention(
         q, k, v, is_causal=True), args.iters)
     print(json.dumps({"case": "attention_tcgen05", "batch": B, "seq": S, "heads": nh,
-                      "head_dim": hd, "fwd_variant": args.fwd_variant,
+                      "head_dim": hd, "fwd_variant": args.fwd_variant, "bwd_dq": args.bwd_dq,
                       "fwd_ms": ms_f, "fwd_tflops": flops / ms_f / 1e9,
                       "fwd_frac_bf16_peak": flops / ms_f / 1e9 / tflops,
                       "bwd_ms": ms_b, "bwd_tflops": 2.5 * flops / ms_b / 1e9,
@@ -235,6 +236,7 @@ def main(argv=None):
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
     ap.add_argument("--fwd-variant", default="pipelined", choices=["simple", "pipelined"])
+    ap.add_argument("--bwd-dq", default="tma", choices=["atomic", "tma"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--elems", type=int, default=1 << 25)
     ap.add_argument("--bits", type=int, default=4)

@@ -625,10 +625,16 @@ template <int HD> struct Bwd {
   static constexpr int SMEM = 4 * TILE + 2 * TILE_SQ + 1024 + sizeof(BwdShared) + 64;
 };
 
-template <int HD>
+// TMA_DQ: how a dQ tile reaches the fp32 accumulator.  false: float4 atomics straight from
+// registers.  true: the tile is staged in shared memory (in the P^T / dS^T buffers, which are
+// idle at that point; 128-byte swizzled so that the row-per-thread stores do not collide)
+// and added to global memory by TMA reductions of [128 rows x 32 floats] boxes, which the L2
+// performs at full-line granularity while the next block's MMAs run.
+template <int HD, bool TMA_DQ>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 128} over qkv
                      const __grid_constant__ CUtensorMap tm_do,    // box {64, 128} over dO
+                     const __grid_constant__ CUtensorMap tm_dq,    // fp32, box {32, 128} (TMA_DQ)
                      const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -725,8 +731,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
         tc::umma_bf16(tDP, desc_kmajor(aV, 128, ks), desc_kmajor(aDO, 128, ks), idesc_kk,
                       ks != 0);
       tc::umma_commit(&sh->bar_1);
+      // the previous block's dQ reductions must have read their staging tile (the P^T / dS^T
+      // buffers) before anybody overwrites it below
+      if constexpr (TMA_DQ) tc::bulk_wait_group_read0();
     }
-    __syncthreads();  // lse / delta visible
+    __syncthreads();  // lse / delta visible; staging tile free
     if (!tc::mbar_wait(&sh->bar_1, par, kBudgetNs)) { sh->abort = 1; record_fail(13); }
     tc::tc_fence_after_sync();
 
@@ -793,7 +802,21 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
     if (tid == 0 && qi + 1 < nq) load_q(qi + 1);  // Q and dO tiles are free again
 
     // ---- dQ rows (thread t <-> query row t) into the fp32 buffer ----
-    {
+    if constexpr (TMA_DQ) {
+      // sub-tile c holds columns [32c, 32c + 32) of the 128 rows: 128 bytes per row, swizzled
+#pragma unroll 1
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(tDQ + lane_addr + c * 32, r);
+        tc::tmem_wait_ld();
+        uint8_t* tile = sPT + c * (128 * 128);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(tile + swz(row, u)) =
+              make_uint4(r[u * 4], r[u * 4 + 1], r[u * 4 + 2], r[u * 4 + 3]);
+      }
+      tc::fence_proxy_async();  // generic-proxy stores -> visible to the TMA engine
+    } else {
       float* dst = p.dq_acc + (size_t)(b * p.seq + qpos0 + row) * H + q_col;
 #pragma unroll 1
       for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
@@ -809,7 +832,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
     }
     tc::tc_fence_before_sync();
     __syncthreads();  // everybody has read dQ before the next S^T overwrites its columns
+    if constexpr (TMA_DQ) {
+      if (tid == 0 && !sh->abort) {
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c)
+          tc::tma_reduce_add_2d(&tm_dq, sPT + c * (128 * 128), q_col + 32 * c,
+                                b * p.seq + qpos0);
+        tc::bulk_commit_group();
+      }
+    }
     if (sh->abort) break;
+  }
+  if constexpr (TMA_DQ) {
+    if (tid == 0) tc::bulk_wait_group0();  // the reductions are performed before the CTA exits
   }
 
   // ---- dK, dV rows (thread t <-> key row t) ----
@@ -940,6 +975,25 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
   return (int)r;
 }
 
+// fp32 [rows, cols] map with 128-byte swizzle: boxes of 32 floats (one swizzle row) x box_rows
+static int make_map_f32(CUtensorMap* map, const void* ptr, long long rows, long long cols,
+                        int box_cols, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box,
+         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "bitscom_b200: fp32 tensor map failed (%d): ptr=%p rows=%lld cols=%lld\n",
+            (int)r, ptr, rows, cols);
+  return (int)r;
+}
+
 // ---- launchers, one instantiation per head dim ------------------------------------
 template <int HD>
 static int launch_fwd(const void* qkv, void* out, void* lse2, int batch, int seq, int heads,
@@ -968,6 +1022,7 @@ static int launch_fwd(const void* qkv, void* out, void* lse2, int batch, int seq
   return (int)cudaGetLastError();
 }
 
+static int g_bwd_dq_variant = 1;  // 0: float4 atomics, 1: TMA reduce-add from shared memory
 static int g_fwd_variant = 1;  // 0: attention_fwd_kernel, 1: attention_fwd_pipelined_kernel
 
 template <int HD>
@@ -1002,22 +1057,37 @@ static int launch_fwd_pipelined(const void* qkv, void* out, void* lse2, int batc
   return (int)cudaGetLastError();
 }
 
+template <int HD, bool TMA_DQ>
+static int launch_bwd_kernel(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do,
+                             const CUtensorMap& tm_dq, const BwdParams& p, int grid,
+                             cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel<HD, TMA_DQ>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd<HD>::SMEM);
+  });
+  if (attr_err != cudaSuccess) return 1005;
+  attention_bwd_kernel<HD, TMA_DQ><<<grid, kBwdThreads, Bwd<HD>::SMEM, st>>>(tm_qkv, tm_do, tm_dq,
+                                                                           p);
+  return 0;
+}
+
 template <int HD>
 static int launch_bwd(const void* qkv, const void* out, const void* d_out, const void* lse2,
                       void* dqkv, float* dq_acc, float* delta, int batch, int seq, int heads,
                       float scale, cudaStream_t st) {
   const long long tokens = (long long)batch * seq;
   const int H = heads * HD;
-  CUtensorMap tm_qkv, tm_do;
+  CUtensorMap tm_qkv, tm_do, tm_dq;
   if (make_map(&tm_qkv, qkv, tokens, 3 * H, 64, 128)) return 1003;
   if (make_map(&tm_do, d_out, tokens, H, 64, 128)) return 1004;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel<HD>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd<HD>::SMEM);
-  });
-  if (attr_err != cudaSuccess) return 1005;
+  const bool tma_dq = g_bwd_dq_variant == 1;
+  if (tma_dq) {
+    if (((uintptr_t)dq_acc & 15) || make_map_f32(&tm_dq, dq_acc, tokens, H, 32, 128)) return 1007;
+  } else {
+    tm_dq = tm_do;  // unused by the kernel
+  }
   {
     const long long warps = tokens * heads;
     const int grid = (int)((warps * 32 + 255) / 256);
@@ -1036,7 +1106,9 @@ static int launch_bwd(const void* qkv, const void* out, const void* d_out, const
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   const int grid = batch * heads * (seq / BKB);
-  attention_bwd_kernel<HD><<<grid, kBwdThreads, Bwd<HD>::SMEM, st>>>(tm_qkv, tm_do, p);
+  const int rc = tma_dq ? launch_bwd_kernel<HD, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
+                        : launch_bwd_kernel<HD, false>(tm_qkv, tm_do, tm_dq, p, grid, st);
+  if (rc) return rc;
   attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
   return (int)cudaGetLastError();
 }
@@ -1048,6 +1120,14 @@ static bool shape_ok(int batch, int seq, int heads, int head_dim) {
 }  // namespace attn
 
 extern "C" {
+
+// 0: dQ tiles are added to the fp32 accumulator with float4 atomics; 1: with TMA reductions
+// from a shared-memory staging tile.  Returns the previous value.
+int bcom_attention_set_bwd_dq_variant(int variant) {
+  const int old = attn::g_bwd_dq_variant;
+  if (variant == 0 || variant == 1) attn::g_bwd_dq_variant = variant;
+  return old;
+}
 
 // qkv: [batch*seq, 3*heads*head_dim] bf16 (q | k | v, RoPE already applied); out: [batch*seq,
 // heads*head_dim] bf16; lse2: [batch, heads, seq] fp32.  head_dim is 64 or 128 and seq a

@@ -19,6 +19,9 @@ _scratch: Dict[Tuple, torch.Tensor] = {}
 # forward kernels: "simple" alternates MMA and softmax inside a CTA; "pipelined" has an issuer
 # warp, double-buffered scores in TMEM and the output accumulated in TMEM
 _FWD_VARIANTS = {"simple": 0, "pipelined": 1}
+# how the backward kernel adds a dQ tile to the fp32 accumulator: float4 atomics from
+# registers, or TMA reductions from a shared-memory staging tile
+_BWD_DQ_VARIANTS = {"atomic": 0, "tma": 1}
 
 
 def _get():
@@ -31,6 +34,10 @@ def _get():
             lib.bcom_attention_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, cf, vp]
             lib.bcom_attention_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
             lib.bcom_attention_set_fwd_variant.argtypes = [ci]
+            lib.bcom_attention_set_bwd_dq_variant.argtypes = [ci]
+            dq = os.environ.get("BITSCOM_ATTN_BWD_DQ", "").strip().lower()
+            if dq in _BWD_DQ_VARIANTS:
+                lib.bcom_attention_set_bwd_dq_variant(_BWD_DQ_VARIANTS[dq])
             variant = os.environ.get("BITSCOM_ATTN_FWD", "").strip().lower()
             if variant in _FWD_VARIANTS:
                 lib.bcom_attention_set_fwd_variant(_FWD_VARIANTS[variant])
@@ -54,6 +61,18 @@ def set_forward_variant(name: str) -> str:
         raise NativeError("attention kernel needs the bcom_llama library and a GPU")
     old = lib.bcom_attention_set_fwd_variant(_FWD_VARIANTS[name])
     return "pipelined" if old == 1 else "simple"
+
+
+def set_backward_dq_variant(name: str) -> str:
+    """Select how dQ tiles are accumulated ("atomic" or "tma", also ``BITSCOM_ATTN_BWD_DQ``);
+    returns the name that was active before."""
+    if name not in _BWD_DQ_VARIANTS:
+        raise ValueError(f"unknown attention backward dQ variant {name!r}")
+    lib = _get()
+    if lib is None:
+        raise NativeError("attention kernel needs the bcom_llama library and a GPU")
+    old = lib.bcom_attention_set_bwd_dq_variant(_BWD_DQ_VARIANTS[name])
+    return "tma" if old == 1 else "atomic"
 
 
 def supported(seq: int, head_dim: int) -> bool:

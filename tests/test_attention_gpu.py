@@ -76,6 +76,34 @@ def test_forward_variants_match_reference(B, S, nh, hd, variant):
     assert e < 3e-2 * max(1.0, xr.grad.abs().max().item()), f"grad max err {e}"
 
 
+@pytest.mark.parametrize("dq", ["tma", "atomic"])
+@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("B,S,nh", [(1, 128, 1), (2, 384, 2), (1, 1024, 3)])
+def test_backward_dq_variants_match_reference(B, S, nh, hd, dq):
+    """dQ accumulated by TMA reductions from a swizzled staging tile, and by float4 atomics,
+    against fp32 autograd; two calls in a row (the accumulator must be left zeroed)."""
+    H = nh * hd
+    g = torch.Generator(device="cuda").manual_seed(7 * S + nh + hd)
+    qkv = (torch.randn(B * S, 3 * H, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
+    d_out = (torch.randn(B * S, H, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    xr = qkv.float().requires_grad_()
+    _ref(xr, B, S, nh, hd).backward(d_out.float())
+    before = A.set_backward_dq_variant(dq)
+    try:
+        for _ in range(2):
+            x = qkv.clone().requires_grad_()
+            A.attention(x, B, S, nh, hd).backward(d_out)
+            torch.cuda.synchronize()
+            A.check_status()
+            for name, lo in (("dq", 0), ("dk", H), ("dv", 2 * H)):
+                got, want = x.grad[:, lo:lo + H].float(), xr.grad[:, lo:lo + H]
+                e = (got - want).abs().max().item()
+                tol = 3e-2 * max(1.0, want.abs().max().item())
+                assert e < tol, f"{name} max err {e} (tol {tol})"
+    finally:
+        A.set_backward_dq_variant(before)
+
+
 def test_attention_second_call_reuses_zeroed_scratch():
     B, S, nh, hd = 1, 256, 2, 128
     H = nh * hd
