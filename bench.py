@@ -167,7 +167,10 @@ def run_ours(args):
     value = tokens * args.steps / (ms_dev / 1e3)
     e2e_value = tokens * args.steps / (ms_e2e / 1e3)
     c = trainer.cfg
-    h2d = c.micro_batches * c.micro_batch_size * c.seq_length * 8
+    # whole-job bytes per step: every rank copies its replica's token ids from pinned host
+    # memory (first stage: inputs, last stage: targets); every last-stage rank reads its loss
+    h2d = c.micro_batches * c.micro_batch_size * c.seq_length * 8 * max(world, 1)
+    d2h = 4 * trainer.dp
     launches = estimate_launches(trainer, args.steps)
     base = _baseline_value()
     out = {
@@ -189,7 +192,7 @@ def run_ours(args):
                    "l2": "per-step working set (>100 GB weights+activations) exceeds the "
                          "126 MB L2; no flush needed"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 if trainer.model.is_last else 0,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "loss": loss_e2e},
         "gpu_launches": launches,
         "clocks": clocks,

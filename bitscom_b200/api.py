@@ -491,6 +491,17 @@ class LowBitGroup:
             state = self._ef_states[key] = ErrorFeedbackState()
         return state
 
+    def residual_norms(self) -> Dict[Hashable, Tuple[float, float]]:
+        """L2 norms of the stage-1 and stage-2 error-feedback residuals per bucket key (0.0
+        where a stage is not in use).  A residual norm that keeps growing means the codec is
+        too coarse for the gradients it is fed; the call synchronises the device."""
+        out = {}
+        for key, st in self._ef_states.items():
+            n1 = float(st.stage1.float().norm().item()) if st.stage1 is not None else 0.0
+            n2 = float(st.stage2.float().norm().item()) if st.stage2 is not None else 0.0
+            out[key] = (n1, n2)
+        return out
+
     def state_dict(self) -> dict:
         """Residuals and the stochastic-rounding call counter, for exact resume."""
         return {
@@ -695,6 +706,12 @@ class LowBitGroup:
         if flat.numel() == 0:
             return flat
         with _timing.span("lowbit_allreduce_host_engine"):
+            world = dist.get_world_size(group)
+            shard = -(-int(flat.numel()) // world)
+            wire = (shard * self.bitwidth + 7) // 8 + 2 * -(-shard // self.block_size)
+            _timing.add("host_engine_calls")
+            _timing.add("host_engine_payload_bytes", flat.numel() * flat.element_size())
+            _timing.add("host_engine_wire_bytes", 2 * (world - 1) * wire)
             return _FlatLowBitAllReduce(self, flat, group, ef=ef).start().finish()
 
     def _lowbit_allreduce_via_alltoall(self, tensor: torch.Tensor) -> None:

@@ -17,7 +17,9 @@
 #include <thread>
 #include <vector>
 
-#if defined(__GNUC__) && defined(__x86_64__)
+// (BCOM_NO_CLONES: the load-time resolver of cloned functions runs before ThreadSanitizer's
+// runtime is up, so sanitizer builds switch the clones off)
+#if defined(__GNUC__) && defined(__x86_64__) && !defined(BCOM_NO_CLONES)
 #define BCOM_CLONES __attribute__((target_clones("avx2", "default")))
 #else
 #define BCOM_CLONES
@@ -366,7 +368,7 @@ int bcom_cpu_blockwise_quantize_pack_mt(const float* x, long long n, int bits, i
   fan_out(nblocks, 8, threads, min_blocks, [=](long long b0, long long b1) {
     const long long e0 = b0 * block, e1 = b1 * block < n ? b1 * block : n;
     const long long p0 = packed_nbytes(e0, bits), p1 = packed_nbytes(e1, bits);
-    std::memset(packed + p0, 0, (size_t)(p1 - p0));
+    if (p1 > p0) std::memset(packed + p0, 0, (size_t)(p1 - p0));  // n == 0: packed may be null
     quantize_range(x, n, bits, block, stochastic != 0, key, idx_offset, b0, b1, packed, scales);
   });
   return 0;

@@ -268,6 +268,14 @@ class FusedLowBitComm:
             check(rc, "bcom_collective")
         self.launches += 1
         _timing.add("fused_launches")
+        # traffic counters: payload = the tensor as the caller sees it; wire = packed codes +
+        # fp16 block scales this rank stores into its peers' memory over NVLink
+        elem = {0: 4, 1: 2, 2: 2}[int(args.dtype)]
+        shard_wire = (int(args.S) * int(args.bits) + 7) // 8 + 2 * -(-int(args.S) // int(args.block))
+        peers = self.world - 1
+        phases = {MODE_ALL_REDUCE: 2, MODE_REDUCE_SCATTER: 1, MODE_ALL_GATHER: 1}[int(args.mode)]
+        _timing.add("fused_payload_bytes", int(args.n) * elem)
+        _timing.add("fused_wire_bytes", phases * peers * shard_wire)
         if not async_op:
             return None
         done = torch.cuda.Event()

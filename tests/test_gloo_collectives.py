@@ -156,3 +156,32 @@ def _bucket_sync_worker(rank, world):
 
 def test_grad_bucket_sync_matches_model_with_per_bucket_residuals():
     run_ranks(_bucket_sync_worker, 2)
+
+
+def _counters_worker(rank, world):
+    from bitscom_b200.utils import timing
+
+    timing.reset_counters()
+    group = LowBitGroup(bitwidth=4, error_feedback=True, stage2_error_feedback=True)
+    n = 10_000
+    for it in range(3):
+        t = torch.randn(n, generator=torch.Generator().manual_seed(100 * it + rank))
+        group.all_reduce(t, ef_key="bucket0")
+    c = timing.counters()
+    shard = -(-n // world)
+    wire = (shard * 4 + 7) // 8 + 2 * -(-shard // 256)
+    assert c["host_engine_calls"] == 3
+    assert c["host_engine_payload_bytes"] == 3 * n * 4
+    assert c["host_engine_wire_bytes"] == 3 * 2 * (world - 1) * wire
+    norms = group.residual_norms()
+    assert set(norms) == {"bucket0"}
+    n1, n2 = norms["bucket0"]
+    # 4-bit residuals of unit-variance data: non-zero, and well below the data norm
+    assert 0 < n1 < 0.3 * (n ** 0.5) and 0 < n2 < 0.3 * (shard ** 0.5) * world
+    plain = LowBitGroup(bitwidth=4)
+    plain.all_reduce(torch.randn(64))
+    assert plain.residual_norms() == {}
+
+
+def test_traffic_counters_and_residual_norms():
+    run_ranks(_counters_worker, 2)
