@@ -39,7 +39,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--path", default="python", choices=["python", "backend"])
-    ap.add_argument("--out", default="gpurun_out/reference_allreduce.jsonl")
+    ap.add_argument("--out", default="bench_outputs/reference_allreduce.jsonl")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", 0))

@@ -95,7 +95,7 @@ class ClockSampler:
 
 
 def _baseline_value():
-    """BASELINE.md publishes no Llama-7B tokens/s for the reference."""
+    """The reference publishes no Llama-7B tokens/s figure, so there is nothing to divide by."""
     return None
 
 

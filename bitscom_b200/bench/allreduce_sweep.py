@@ -67,7 +67,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-ef", action="store_true")
     ap.add_argument("--nearest", action="store_true")
-    ap.add_argument("--out", default="gpurun_out/allreduce_sweep.jsonl")
+    ap.add_argument("--out", default="bench_outputs/allreduce_sweep.jsonl")
     args = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", 0))

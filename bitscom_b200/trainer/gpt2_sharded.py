@@ -60,7 +60,7 @@ def main(argv=None):
     ap.add_argument("--torch-ops", action="store_true",
                     help="LayerNorm, GELU and attention from torch instead of this library's "
                          "kernels (A/B baseline)")
-    ap.add_argument("--out", default="gpurun_out/gpt2_sharded.jsonl")
+    ap.add_argument("--out", default="bench_outputs/gpt2_sharded.jsonl")
     args = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", 0))

@@ -34,7 +34,7 @@ def main(argv=None):
     ap.add_argument("--mode", default="lowbit", choices=["lowbit", "nccl"])
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--no-error-feedback", action="store_true")
-    ap.add_argument("--out", default="gpurun_out/resnet18_ddp.jsonl")
+    ap.add_argument("--out", default="bench_outputs/resnet18_ddp.jsonl")
     args = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", 0))

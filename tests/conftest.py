@@ -10,7 +10,17 @@ if ROOT not in sys.path:
 # DETAIL mode wraps custom backends in a wrapper group that needs sequence numbers.
 os.environ["TORCH_DISTRIBUTED_DEBUG"] = "OFF"
 
-REFERENCE_PYTHON = os.environ.get("BITSCOM_REFERENCE_PYTHON", "/root/reference/python")
+# where the reference's python/ folder is looked for: an explicit override, a checkout next to
+# this repository, or the copy installed for the benchmark's reference arm
+_REFERENCE_CANDIDATES = [
+    os.environ.get("BITSCOM_REFERENCE_PYTHON"),
+    os.path.join(os.path.dirname(ROOT), "reference", "python"),
+    os.path.join(ROOT, "baseline", "_ref"),
+]
+REFERENCE_PYTHON = next(
+    (c for c in _REFERENCE_CANDIDATES
+     if c and os.path.exists(os.path.join(c, "bitscom", "quantization.py"))),
+    _REFERENCE_CANDIDATES[1])
 
 
 def pytest_configure(config):
