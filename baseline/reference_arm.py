@@ -59,7 +59,10 @@ def _run(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: if one rank fails, the others report instead of waiting
+        from datetime import timedelta
+
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=240))
 
     seq, micro_batches = 2048, 4
     cfg = LlamaConfig(vocab_size=32000, hidden_size=4096, intermediate_size=11008,
