@@ -318,6 +318,14 @@ class ProcessGroupLowBit : public c10d::Backend {
   int64_t fused_launches() const { return launches_; }
   const LowBitOptions& options() const { return options_; }
 
+  // Orderly teardown of the inner NCCL group (its communicators and helper threads), for
+  // callers that keep the process alive after destroy_process_group(): torch shuts down
+  // ProcessGroupNCCL instances it knows about, but not one that lives inside another backend,
+  // whose teardown would otherwise be left to the destructor.
+  void shutdown() {
+    if (nccl_) nccl_->shutdown();
+  }
+
  private:
   struct Residual {
     at::Tensor stage1, stage2;
@@ -531,7 +539,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            })
       .def("residual_state", &ProcessGroupLowBit::residual_state)
       .def("clear_residuals", &ProcessGroupLowBit::clear_residuals)
-      .def("fused_launches", &ProcessGroupLowBit::fused_launches);
+      .def("fused_launches", &ProcessGroupLowBit::fused_launches)
+      .def("shutdown", &ProcessGroupLowBit::shutdown,
+           py::call_guard<py::gil_scoped_release>());
 
   m.def("create_backend", &create_backend, py::arg("store"), py::arg("rank"), py::arg("size"),
         py::arg("timeout") = std::chrono::milliseconds(600000), py::arg("bitwidth") = 4,
