@@ -50,6 +50,7 @@ class TrainerConfig:
     dp_sync: str = "pipeline_a"   # "pipeline_a" | "flat" | "dense"
     local_size: int = 1           # ranks per local group of pipeline-A
     overlap: bool = True
+    simulate_quantization: bool = False   # reference flag: quantize round trip before dense ops
     lr: float = 1e-4
     weight_decay: float = 0.01
     seed: int = 0
@@ -107,6 +108,7 @@ class LlamaTrainer:
             self.lowbit = LowBitGroup(
                 bitwidth=cfg.bitwidth, process_group=self.dp_group,
                 block_size=cfg.block_size, stochastic_rounding=cfg.stochastic_rounding,
+                simulate_quantization=cfg.simulate_quantization,
                 error_feedback=cfg.error_feedback,
                 stage2_error_feedback=cfg.stage2_error_feedback, sr_seed=cfg.seed + 17)
             local_group = inter_group = None
@@ -270,10 +272,21 @@ def main(argv=None):
     ap.add_argument("--bitwidth", type=int, default=4)
     ap.add_argument("--backend", default="lowbit", choices=["lowbit", "nccl"])
     ap.add_argument("--stochastic_rounding", action="store_true")
+    ap.add_argument("--simulate_quantization", action="store_true")
     ap.add_argument("--no_error_feedback", action="store_true")
     ap.add_argument("--dp_sync", default="pipeline_a", choices=["pipeline_a", "flat", "dense"])
     ap.add_argument("--local_size", type=int, default=1)
     ap.add_argument("--max_steps", type=int, default=10)
+    ap.add_argument("--epochs", type=int, default=1)
+    ap.add_argument("--dataset", default="synthetic",
+                    help="'synthetic', a text file (one document per line) or a token file "
+                         "(.bin/.u16/.i32/.i64/.npy); nothing is downloaded")
+    ap.add_argument("--dataset_config", default=None,
+                    help="accepted for command-line compatibility with the reference; unused")
+    ap.add_argument("--tokenizer", default="bytes",
+                    help="'bytes', a SentencePiece .model file or a local tokenizer directory")
+    ap.add_argument("--use_auth_token", action="store_true",
+                    help="accepted for compatibility; there is no download to authorise")
     ap.add_argument("--lr", type=float, default=1e-4)
     ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
     ap.add_argument("--output_dir", default=None, help="write a checkpoint here at the end")
@@ -289,14 +302,30 @@ def main(argv=None):
         stochastic_rounding=args.stochastic_rounding,
         error_feedback=not args.no_error_feedback,
         dp_sync="dense" if args.backend == "nccl" else args.dp_sync,
-        local_size=args.local_size, lr=args.lr)
+        local_size=args.local_size, lr=args.lr,
+        simulate_quantization=args.simulate_quantization)
     trainer = LlamaTrainer(mcfg, tcfg)
-    for step in range(args.max_steps):
-        t0 = time.perf_counter()
-        loss = trainer.train_step(trainer.synthetic_batch(step))
-        if loss is not None:
-            print(json.dumps({"step": step, "loss": float(loss.item()),
-                              "step_s": time.perf_counter() - t0}), flush=True)
+    from ..data import build_loader
+
+    # every pipeline stage of a replica reads the same batches (first stage: inputs, last
+    # stage: targets), so the sampler is keyed by the data-parallel rank only
+    loader = build_loader(args.dataset, args.tokenizer, seq_length=tcfg.seq_length,
+                          vocab_size=mcfg.vocab_size, micro_batches=tcfg.micro_batches,
+                          micro_batch_size=tcfg.micro_batch_size, dp_size=trainer.dp,
+                          dp_rank=trainer.dp_rank, seed=tcfg.seed)
+    step = 0
+    for epoch in range(args.epochs):
+        loader.set_epoch(epoch)
+        for batch in loader:
+            if step >= args.max_steps:
+                break
+            t0 = time.perf_counter()
+            loss = trainer.train_step(batch)
+            loader.mark_consumed()
+            if loss is not None:
+                print(json.dumps({"step": step, "epoch": epoch, "loss": float(loss.item()),
+                                  "step_s": time.perf_counter() - t0}), flush=True)
+            step += 1
     if args.output_dir:
         from ..utils.checkpoint import save_checkpoint
 
