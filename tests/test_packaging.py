@@ -30,3 +30,25 @@ def test_compile_commands_cover_all_sources():
     files = {os.path.basename(f) for f in json.loads(out.stdout.strip().splitlines()[-1])}
     want = {s for spec in _build.LIBRARIES.values() for s in spec["sources"]} | {"backend.cc"}
     assert want <= files
+
+
+def test_c_host_example_links_against_the_cpu_codec(tmp_path):
+    """The C API is callable from a plain C program (examples/cpu_codec_example.c)."""
+    import shutil
+
+    import pytest
+
+    from bitscom_b200.ops import cpu_codec
+
+    cc = shutil.which("cc") or shutil.which("gcc")
+    if cc is None or not cpu_codec.available():
+        pytest.skip("needs a C compiler and the CPU codec library")
+    libdir = os.path.dirname(_build.lib_path("bcom_cpu"))
+    exe = str(tmp_path / "example")
+    build = subprocess.run([cc, os.path.join(ROOT, "examples", "cpu_codec_example.c"),
+                            f"-L{libdir}", "-lbcom_cpu", "-lm", f"-Wl,-rpath,{libdir}", "-o", exe],
+                           capture_output=True, text=True, timeout=120)
+    assert build.returncode == 0, build.stderr[-2000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "packed bytes" in run.stdout
