@@ -235,7 +235,8 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
-    ap.add_argument("--fwd-variant", default="pipelined", choices=["simple", "pipelined"])
+    ap.add_argument("--fwd-variant", default="pipelined",
+                    choices=["simple", "pipelined", "pipelined8"])
     ap.add_argument("--bwd-dq", default="tma", choices=["atomic", "tma"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--elems", type=int, default=1 << 25)
