@@ -34,7 +34,7 @@ import torch.distributed as dist
 from .quantization import (
     DEFAULT_BLOCK_SIZE,
     SUPPORTED_BITWIDTHS,
-    _HAS_CUDA_KERNELS,
+    _HAS_CUDA_KERNELS,  # noqa: F401  (re-exported: callers of the reference patch it here)
     CompressedTensor,
     compress_tensor,
     decompress_tensor,

@@ -23,7 +23,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _native
-from ..ops._native import DTYPE_CODE, NativeError, check, ptr
+from ..ops._native import DTYPE_CODE, NativeError, check
 from ..quantization import sr_key
 from ..utils import timing as _timing
 

@@ -17,10 +17,7 @@ training on top of both is new here.
 
 from __future__ import annotations
 
-from typing import Optional
-
 import torch
-import torch.distributed as dist
 
 from ..ops import nn as K
 from .flat import FlatParameters
