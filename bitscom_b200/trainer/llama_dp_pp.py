@@ -222,6 +222,18 @@ class LlamaTrainer:
             return torch.stack(losses).sum()
         return None
 
+    def check_kernels(self) -> None:
+        """Raise if a GEMM or attention kernel gave up on one of its bounded waits since the
+        last check (it then returned early and its output is not valid).  Synchronises the
+        device, so call it where the step is synchronised anyway."""
+        from ..ops import attention as A
+        from ..ops import gemm as G
+
+        if G.available():
+            G.check_status()
+        if A.available():
+            A.check_status()
+
     # -- checkpoint -----------------------------------------------------------------------
     def state_dict(self) -> dict:
         sd = {"step": self.step_count, "opt": self.opt.state_dict(),
@@ -325,6 +337,8 @@ def main(argv=None):
             if loss is not None:
                 print(json.dumps({"step": step, "epoch": epoch, "loss": float(loss.item()),
                                   "step_s": time.perf_counter() - t0}), flush=True)
+            if step % 50 == 0:
+                trainer.check_kernels()
             step += 1
     if args.output_dir:
         from ..utils.checkpoint import save_checkpoint
