@@ -114,7 +114,16 @@ class LinearFunction(torch.autograd.Function):
             # dW[out, in] = dy^T x: both operands stored [K=T, *]
             main = getattr(weight, "main_grad", None)
             if main is not None:
-                gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=main, accumulate=True)
+                from ..parallel.deferred import DeferredWork
+
+                queue = DeferredWork.active()
+                if queue is not None:
+                    # pipeline parallelism: the input gradient goes out first, this GEMM runs
+                    # while it is on the wire
+                    queue.add(lambda: gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=main,
+                                           accumulate=True))
+                else:
+                    gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=main, accumulate=True)
                 dw = None
             else:
                 dw = gemm(dy2, x2, a_mn_major=True, b_mn_major=True)

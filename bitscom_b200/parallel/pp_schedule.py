@@ -16,10 +16,13 @@ neighbouring stages from blocking each other.
 
 from __future__ import annotations
 
+import contextlib
 from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
+
+from .deferred import DeferredWork
 
 Action = Tuple[str, int]  # ("F" | "B", micro-batch index)
 
@@ -98,13 +101,19 @@ class PipelineRunner:
 
     def __init__(self, stage: int, stages: int, group, prev_rank: Optional[int],
                  next_rank: Optional[int], act_shape: Tuple[int, ...],
-                 dtype: torch.dtype = torch.bfloat16, device="cuda"):
+                 dtype: torch.dtype = torch.bfloat16, device="cuda", defer_wgrad: bool = False):
+        # defer_wgrad: backward steps (except the step's last one, whose gradients feed the
+        # data-parallel bucket hooks as they appear) queue their weight-gradient GEMMs and run
+        # them after the input gradient has been handed to the transport
+        self.defer_wgrad = defer_wgrad
         self.stage, self.stages, self.group = stage, stages, group
         self.prev_rank, self.next_rank = prev_rank, next_rank
         self.act_shape, self.dtype, self.device = tuple(act_shape), dtype, device
         self.is_first, self.is_last = stage == 0, stage == stages - 1
 
-    def _exchange(self, comm: Comm, to_next=None, to_prev=None):
+    def _exchange(self, comm: Comm, to_next=None, to_prev=None, between=None):
+        """Issue the step's sends / receives; ``between`` runs after they have been issued and
+        before they are waited for (work that overlaps the transfer)."""
         ops, got_prev, got_next = [], None, None
         if comm.send_prev:
             ops.append(dist.P2POp(dist.isend, to_prev, self.prev_rank, self.group))
@@ -116,9 +125,11 @@ class PipelineRunner:
         if comm.recv_next:
             got_next = torch.empty(self.act_shape, dtype=self.dtype, device=self.device)
             ops.append(dist.P2POp(dist.irecv, got_next, self.next_rank, self.group))
-        if ops:
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()  # stream-ordered wait; the host does not block
+        reqs = dist.batch_isend_irecv(ops) if ops else []
+        if between is not None:
+            between()
+        for req in reqs:
+            req.wait()  # stream-ordered wait; the host does not block
         return got_prev, got_next
 
     def run(self, microbatches: int, forward_fn: Callable, on_last_backward: Optional[
@@ -130,7 +141,11 @@ class PipelineRunner:
         outputs: dict = {}
         losses: List[torch.Tensor] = []
         next_input = next_grad = None
+        flush = None  # weight-gradient work queued by the current backward step
         for pos, (kind, mb, comm) in enumerate(plan):
+            if flush is not None:  # the previous step had nothing to send: run its queue now
+                flush()
+                flush = None
             to_next = to_prev = None
             if kind == "F":
                 x = None
@@ -148,17 +163,24 @@ class PipelineRunner:
                 out = outputs.pop(mb)
                 if pos == last_b and on_last_backward is not None:
                     on_last_backward()
-                if self.is_last:
-                    out.backward()
-                else:
-                    torch.autograd.backward(out, grad_tensors=next_grad)
-                    next_grad = None
+                deferred = DeferredWork() if (self.defer_wgrad and pos != last_b) else None
+                with deferred if deferred is not None else contextlib.nullcontext():
+                    if self.is_last:
+                        out.backward()
+                    else:
+                        torch.autograd.backward(out, grad_tensors=next_grad)
+                        next_grad = None
                 if not self.is_first:
                     to_prev = inputs.pop(mb).grad
+                if deferred is not None:
+                    flush = deferred.flush
             if comm.any():
-                got_prev, got_next = self._exchange(comm, to_next, to_prev)
+                got_prev, got_next = self._exchange(comm, to_next, to_prev, between=flush)
+                flush = None
                 if comm.recv_prev:
                     next_input = got_prev
                 if comm.recv_next:
                     next_grad = got_next
+        if flush is not None:
+            flush()
         return losses

@@ -51,6 +51,7 @@ class TrainerConfig:
     local_size: int = 1           # ranks per local group of pipeline-A
     overlap: bool = True
     simulate_quantization: bool = False   # reference flag: quantize round trip before dense ops
+    defer_wgrad: bool = False  # pipeline stages send input gradients before weight-gradient GEMMs
     lr: float = 1e-4
     weight_decay: float = 0.01
     seed: int = 0
@@ -101,7 +102,7 @@ class LlamaTrainer:
             prev_rank=self.rank - 1 if self.pp_rank > 0 else None,
             next_rank=self.rank + 1 if self.pp_rank < self.pp - 1 else None,
             act_shape=(cfg.micro_batch_size * cfg.seq_length, model_cfg.hidden_size),
-            device=self.device) if self.pp > 1 else None
+            device=self.device, defer_wgrad=cfg.defer_wgrad) if self.pp > 1 else None
 
         self.sync: Optional[GradBucketSync] = None
         if self.dp > 1:
@@ -288,6 +289,9 @@ def main(argv=None):
     ap.add_argument("--no_error_feedback", action="store_true")
     ap.add_argument("--dp_sync", default="pipeline_a", choices=["pipeline_a", "flat", "dense"])
     ap.add_argument("--local_size", type=int, default=1)
+    ap.add_argument("--defer_wgrad", action="store_true",
+                    help="pipeline stages run weight-gradient GEMMs after sending the input "
+                         "gradient (shrinks the 1F1B bubble)")
     ap.add_argument("--max_steps", type=int, default=10)
     ap.add_argument("--epochs", type=int, default=1)
     ap.add_argument("--dataset", default="synthetic",
@@ -315,7 +319,7 @@ def main(argv=None):
         error_feedback=not args.no_error_feedback,
         dp_sync="dense" if args.backend == "nccl" else args.dp_sync,
         local_size=args.local_size, lr=args.lr,
-        simulate_quantization=args.simulate_quantization)
+        simulate_quantization=args.simulate_quantization, defer_wgrad=args.defer_wgrad)
     trainer = LlamaTrainer(mcfg, tcfg)
     from ..data import build_loader
 

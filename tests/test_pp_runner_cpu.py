@@ -6,6 +6,7 @@ import pytest
 import torch
 import torch.distributed as dist
 
+from bitscom_b200.parallel.deferred import DeferredWork
 from bitscom_b200.parallel.pp_schedule import PipelineRunner
 
 from _dist import run_ranks
@@ -73,3 +74,111 @@ def _worker(rank, world, microbatches):
 @pytest.mark.parametrize("stages,microbatches", [(2, 4), (3, 5), (4, 4), (2, 1)])
 def test_1f1b_runner_matches_unsplit_model(stages, microbatches):
     run_ranks(_worker, stages, microbatches)
+
+
+class _DeferringLinear(torch.autograd.Function):
+    """A linear layer whose weight gradient goes to ``weight.main_grad`` and is queued when a
+    ``DeferredWork`` context is active: the CPU twin of ``ops.gemm.LinearFunction``."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return x @ weight.t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        queue = DeferredWork.active()
+        work = lambda: weight.main_grad.add_(dy.t() @ x)  # noqa: E731
+        if queue is not None:
+            queue.add(work)
+            _LOG.append("queued")
+        else:
+            work()
+            _LOG.append("now")
+        return dy @ weight, None
+
+
+_LOG = []
+
+
+def _deferral_worker(rank, world, microbatches, defer):
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(50 + rank)
+    weights = [torch.nn.Parameter(torch.randn(WIDTH, WIDTH, generator=g) * 0.3) for _ in range(2)]
+    for w in weights:
+        w.main_grad = torch.zeros_like(w)
+    runner = PipelineRunner(rank, world, dist.group.WORLD, rank - 1 if rank > 0 else None,
+                            rank + 1 if rank < world - 1 else None, (MB_ROWS, WIDTH),
+                            dtype=torch.float32, device="cpu", defer_wgrad=defer)
+    sent_before_flush = []
+    real_exchange = runner._exchange
+
+    def spy(comm, to_next=None, to_prev=None, between=None):
+        def wrapped():
+            sent_before_flush.append(to_prev is not None)
+            between()
+        return real_exchange(comm, to_next, to_prev, between=wrapped if between else None)
+
+    runner._exchange = spy
+
+    def forward_fn(mb, x):
+        inp, tgt = _micro_batch(mb)
+        h = inp if rank == 0 else x
+        for w in weights:
+            h = torch.tanh(_DeferringLinear.apply(h, w))
+        return torch.nn.functional.mse_loss(h, tgt) / microbatches if rank == world - 1 else h
+
+    runner.run(microbatches, forward_fn)
+    grads = torch.stack([w.main_grad for w in weights])
+    everyone = [torch.empty_like(grads) for _ in range(world)]
+    dist.all_gather(everyone, grads)
+    # reference: the same stack of layers, unsplit, plain autograd
+    ws = []
+    for r in range(world):
+        gr = torch.Generator().manual_seed(50 + r)
+        ws += [(torch.randn(WIDTH, WIDTH, generator=gr) * 0.3).requires_grad_() for _ in range(2)]
+    for mb in range(microbatches):
+        inp, tgt = _micro_batch(mb)
+        h = inp
+        for w in ws:
+            h = torch.tanh(h @ w.t())
+        (torch.nn.functional.mse_loss(h, tgt) / microbatches).backward()
+    want = torch.stack([w.grad for w in ws]).view(world, 2, WIDTH, WIDTH)
+    for r in range(world):
+        assert torch.allclose(everyone[r], want[r], atol=1e-5), r
+    if defer:
+        # every backward step but the last one queued its two weight gradients
+        assert _LOG.count("queued") == 2 * (microbatches - 1) and _LOG.count("now") == 2
+        if rank > 0:  # ... and ran them only after the input gradient was handed over
+            assert sent_before_flush and all(sent_before_flush)
+    else:
+        assert _LOG.count("queued") == 0
+
+
+@pytest.mark.parametrize("defer", [True, False])
+@pytest.mark.parametrize("stages,microbatches", [(2, 4), (3, 5)])
+def test_deferred_weight_gradients_match_and_follow_the_send(stages, microbatches, defer):
+    run_ranks(_deferral_worker, stages, microbatches, defer)
+
+
+def test_deferred_work_context_rules():
+    q = DeferredWork()
+    ran = []
+    with q:
+        assert DeferredWork.active() is q
+        q.add(lambda: ran.append(1))
+        q.add(lambda: ran.append(2))
+        with pytest.raises(RuntimeError):
+            with DeferredWork():
+                pass
+    assert DeferredWork.active() is None and ran == [] and len(q) == 2
+    q.flush()
+    assert ran == [1, 2] and len(q) == 0 and q.flushes == 1
+    q.flush()
+    assert q.flushes == 1
+    with pytest.raises(ValueError):
+        with q:
+            q.add(lambda: ran.append(3))
+            raise ValueError("step failed")
+    assert len(q) == 0 and ran == [1, 2]      # a failed step drops its queue
