@@ -48,6 +48,25 @@ def _load_cuda_codec():
 _CUDA = _load_cuda_codec()
 _HAS_CUDA_KERNELS = _CUDA is not None
 
+_CPU_NATIVE = None  # False once loading has failed
+
+
+def _cpu_codec():
+    """The C++ CPU codec (bit-equal to the torch-op path below, several times faster), or
+    ``None`` when it cannot be built / loaded or ``BITSCOM_CPU_CODEC=0`` asks for torch ops."""
+    global _CPU_NATIVE
+    if _CPU_NATIVE is None:
+        try:
+            import os
+
+            from .ops import cpu_codec as _c
+
+            _CPU_NATIVE = _c if (os.environ.get("BITSCOM_CPU_CODEC", "1") != "0"
+                                 and _c.available()) else False
+        except Exception:  # pragma: no cover - depends on the toolchain
+            _CPU_NATIVE = False
+    return _CPU_NATIVE or None
+
 
 def validate_bitwidth(bitwidth: int) -> None:
     if bitwidth not in SUPPORTED_BITWIDTHS:
@@ -295,6 +314,17 @@ def quantize_pack_tensor_blockwise(
             sr_stream)
         return packed, scales, int(tensor.numel())
 
+    native = _cpu_codec() if tensor.device.type == "cpu" else None
+    if native is not None:
+        seed = sr_seed
+        if stochastic_rounding and seed is None:
+            # unseeded: a fresh stream per call, drawn from torch's generator so that
+            # torch.manual_seed still makes a run repeatable
+            seed = int(torch.randint(0, 2 ** 31 - 1, (1,)).item())
+        packed, scales = native.blockwise_quantize_pack(
+            tensor, bitwidth, block_size, stochastic_rounding, seed, sr_offset, sr_stream)
+        return packed, scales, int(tensor.numel())
+
     q, scales = quantize_tensor_blockwise(
         tensor, bitwidth, block_size=block_size,
         stochastic_rounding=stochastic_rounding,
@@ -323,6 +353,17 @@ def unpack_dequantize_tensor_blockwise(
     if scales.is_cuda and _cuda_blockwise_ok(packed, bitwidth, block_size, dtype):
         out = _CUDA.blockwise_unpack_dequantize(
             packed, scales, bitwidth, int(numel), block_size, dtype)
+        if shape is not None:
+            out = out.view(*shape)
+        return out.to(device=device, dtype=dtype)
+
+    native = _cpu_codec() if (packed.device.type == "cpu" and scales.device.type == "cpu"
+                              and packed.dtype == torch.uint8
+                              and scales.dtype == torch.float16) else None
+    if native is not None:
+        if scales.numel() != -(-int(numel) // block_size):
+            raise ValueError("scales length does not match numel and block_size")
+        out = native.blockwise_unpack_dequantize(packed, scales, bitwidth, int(numel), block_size)
         if shape is not None:
             out = out.view(*shape)
         return out.to(device=device, dtype=dtype)
