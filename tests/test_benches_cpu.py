@@ -164,3 +164,29 @@ def test_quantize_curve_host_columns(tmp_path):
     rows = QC.main(["--min-pow2", "10", "--max-pow2", "10", "--max-iters", "3", "--warmup", "1",
                     "--device", "cpu"])
     assert "gpu_ms" not in rows[0] and rows[0]["cpu_melems_per_s"] > 0
+
+
+# ------------------------------------------------------------------------- examples
+def _run_example(name, port):
+    env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           os.path.join(ROOT, "examples", name)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    return out.stdout
+
+
+def test_quickstart_example_keeps_the_accumulated_error_small():
+    out = _run_example("allreduce_quickstart.py", 29661)
+    line = next(l for l in out.splitlines() if "relative error" in l)
+    words = line.split()
+    with_ef, without = float(words[words.index("feedback") + 1]), float(words[-1])
+    assert with_ef < 0.6 * without and without < 0.5
+
+
+def test_ddp_hook_example_trains():
+    out = _run_example("ddp_comm_hook.py", 29662)
+    line = next(l for l in out.splitlines() if l.startswith("loss "))
+    first, last = (float(v) for v in line[5:].split(" -> "))
+    assert last < 0.6 * first
