@@ -10,6 +10,7 @@ from typing import Optional
 
 import torch
 
+from ..parallel.deferred import DeferredWork
 from . import _native
 from ._native import NativeError, check, ptr, stream_ptr
 
@@ -114,8 +115,6 @@ class LinearFunction(torch.autograd.Function):
             # dW[out, in] = dy^T x: both operands stored [K=T, *]
             main = getattr(weight, "main_grad", None)
             if main is not None:
-                from ..parallel.deferred import DeferredWork
-
                 queue = DeferredWork.active()
                 if queue is not None:
                     # pipeline parallelism: the input gradient goes out first, this GEMM runs
