@@ -55,6 +55,7 @@ struct RankParams {
   int mode;
   unsigned int key1, key2;
   float post_scale;
+  unsigned char* mc;    // NVLink multicast mapping of the symmetric blocks, or null
 };
 
 // ---------------------------------------------------------------------------
@@ -67,6 +68,14 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   unsigned long long v;
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
+}
+// one store that NVSwitch replicates into every rank's copy of the multicast-mapped block
+__device__ __forceinline__ void multimem_st_b32(void* mc_addr, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_st_b64(void* mc_addr, uint32_t lo, uint32_t hi) {
+  const unsigned long long v = ((unsigned long long)hi << 32) | lo;
+  asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(mc_addr), "l"(v) : "memory");
 }
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
@@ -212,7 +221,9 @@ __device__ __forceinline__ void push_group(unsigned char* slot, size_t scale_off
 // ---------------------------------------------------------------------------
 // the collective, as seen by one rank whose CTAs are numbered cta in [0, ncta)
 // ---------------------------------------------------------------------------
-template <typename T, int BITS, bool SR, bool ALIGNED>
+// MC: the packed groups of the all-gather half go out as multimem stores through p.mc (built
+// for 4- and 8-bit codes, whose groups are whole 32- / 64-bit words); scales stay on peer stores.
+template <typename T, int BITS, bool SR, bool ALIGNED, bool MC = false>
 __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   const int tid = threadIdx.x;
   const long long nthreads = (long long)ncta * blockDim.x;
@@ -343,11 +354,25 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
         quant8<BITS, SR>(acc, sf, p.key2, idx2, q);
       }
       const Packed8<BITS> pk = pack8<BITS>(q);
-      for (int k = 0; k < W; ++k) {
-        const int t = (p.rank + k) % W;
-        unsigned char* slot = p.peer[t] + BCOM_CONTROL_BYTES + p.region_bytes +
-                              (size_t)p.rank * p.slot_stride;
-        push_group<BITS>(slot, p.scale_off, g, lanes, llog, pk, sh);
+      if constexpr (MC) {
+        static_assert(BITS == 4 || BITS == 8, "multimem path: whole-word groups only");
+        const size_t slot_off = BCOM_CONTROL_BYTES + p.region_bytes + (size_t)p.rank * p.slot_stride;
+        unsigned char* dst = p.mc + slot_off + (size_t)g * BITS;
+        if constexpr (BITS == 4) multimem_st_b32(dst, pk.w[0]);
+        else multimem_st_b64(dst, pk.w[0], pk.w[1]);
+        if ((g & (lanes - 1)) == 0) {
+          for (int k = 0; k < W; ++k) {
+            const int t = (p.rank + k) % W;
+            reinterpret_cast<__half*>(p.peer[t] + slot_off + p.scale_off)[g >> llog] = sh;
+          }
+        }
+      } else {
+        for (int k = 0; k < W; ++k) {
+          const int t = (p.rank + k) % W;
+          unsigned char* slot = p.peer[t] + BCOM_CONTROL_BYTES + p.region_bytes +
+                                (size_t)p.rank * p.slot_stride;
+          push_group<BITS>(slot, p.scale_off, g, lanes, llog, pk, sh);
+        }
       }
     }
   }
@@ -386,6 +411,13 @@ template <typename T, int BITS, bool SR, bool ALIGNED>
 __global__ void __launch_bounds__(kCollThreads, 2)
 lowbit_collective_kernel(const RankParams p) {
   run_rank<T, BITS, SR, ALIGNED>(p, blockIdx.x, gridDim.x);
+}
+
+// the same kernel with the all-gather half on NVLink multicast stores (aligned buckets only)
+template <typename T, int BITS, bool SR>
+__global__ void __launch_bounds__(kCollThreads, 2)
+lowbit_collective_mc_kernel(const RankParams p) {
+  run_rank<T, BITS, SR, true, true>(p, blockIdx.x, gridDim.x);
 }
 
 // Same-device emulation of `world` ranks in ONE cooperative launch: CTA groups play the
@@ -442,6 +474,26 @@ static bool pick_kernel(int dtype, int bits, bool sr, bool aligned, RealKernel* 
     case 0: return pick_bits<float>(bits, sr, aligned, real, emu);
     case 1: return pick_bits<__half>(bits, sr, aligned, real, emu);
     case 2: return pick_bits<__nv_bfloat16>(bits, sr, aligned, real, emu);
+    default: return false;
+  }
+}
+
+template <typename T>
+static bool pick_mc_bits(int bits, bool sr, RealKernel* real) {
+  if (bits == 4) *real = sr ? lowbit_collective_mc_kernel<T, 4, true>
+                            : lowbit_collective_mc_kernel<T, 4, false>;
+  else if (bits == 8) *real = sr ? lowbit_collective_mc_kernel<T, 8, true>
+                                 : lowbit_collective_mc_kernel<T, 8, false>;
+  else return false;
+  return true;
+}
+
+// multicast variant of the kernel for this setting, if there is one
+static bool pick_mc_kernel(int dtype, int bits, bool sr, RealKernel* real) {
+  switch (dtype) {
+    case 0: return pick_mc_bits<float>(bits, sr, real);
+    case 1: return pick_mc_bits<__half>(bits, sr, real);
+    case 2: return pick_mc_bits<__nv_bfloat16>(bits, sr, real);
     default: return false;
   }
 }
@@ -521,6 +573,7 @@ static void fill_params(const BcomComm* c, const BcomCollArgs& a, long long c0, 
   p->key1 = a.key1;
   p->key2 = a.key2;
   p->post_scale = a.post_scale;
+  p->mc = c->mc;
 }
 
 static int ctas_for(const BcomComm* c, const BcomCollArgs& a, long long L, int resident_per_sm) {
@@ -573,6 +626,11 @@ int bcom_collective(BcomComm* c, const BcomCollArgs* args, void* stream) {
   EmuKernel unused;
   if (!pick_kernel(a.dtype, a.bits, a.stochastic != 0, is_aligned(a), &kernel, &unused))
     return (int)cudaErrorNotSupported;
+  // with a multicast mapping, the modes that have an all-gather half use the multimem kernel
+  if (c->mc != nullptr && is_aligned(a) && a.mode != BCOM_MODE_REDUCE_SCATTER) {
+    RealKernel mc_kernel;
+    if (pick_mc_kernel(a.dtype, a.bits, a.stochastic != 0, &mc_kernel)) kernel = mc_kernel;
+  }
   int resident = 0;
   cudaError_t err = resident_ctas((const void*)kernel, &resident);
   if (err != cudaSuccess) return (int)err;

@@ -1,5 +1,6 @@
 // Host side of the symmetric-memory communicator: allocation, CUDA IPC mapping of the
 // peers' blocks, status record, reset.  See symm.h for the layout and the protocol.
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -43,9 +44,55 @@ int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out) {
     return (int)err;
   }
   c->peer[rank] = c->local;
+  c->owns_local = true;
   *out = c;
   return 0;
 }
+
+size_t bcom_comm_block_bytes(size_t region_bytes) {
+  return BCOM_CONTROL_BYTES + 2 * bcom_align_up(region_bytes, 4096);
+}
+
+int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* const* bases,
+                              void* mc_base, BcomComm** out) {
+  if (!out || !bases || world < 1 || world > BCOM_MAX_WORLD || rank < 0 || rank >= world)
+    return (int)cudaErrorInvalidValue;
+  for (int p = 0; p < world; ++p)
+    if (!bases[p] || ((uintptr_t)bases[p] & 255)) return (int)cudaErrorInvalidValue;
+  if ((uintptr_t)mc_base & 255) return (int)cudaErrorInvalidValue;
+  BcomComm* c = new (std::nothrow) BcomComm();
+  if (!c) return (int)cudaErrorMemoryAllocation;
+  std::memset(c, 0, sizeof(*c));
+  c->rank = rank;
+  c->world = world;
+  c->region_bytes = bcom_align_up(region_bytes, 4096);
+  c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes;
+  c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
+  c->local = (unsigned char*)bases[rank];
+  c->mc = (unsigned char*)mc_base;
+  c->owns_local = false;
+  for (int p = 0; p < world; ++p) c->peer[p] = (unsigned char*)bases[p];
+  cudaError_t err = cudaGetDevice(&c->device);
+  if (err == cudaSuccess)
+    err = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
+  if (err == cudaSuccess) err = cudaMemset(c->local, 0, BCOM_CONTROL_BYTES);
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
+  if (err == cudaSuccess)
+    err = cudaHostAlloc((void**)&c->status_host, 8 * sizeof(unsigned int), cudaHostAllocMapped);
+  if (err == cudaSuccess) {
+    std::memset(c->status_host, 0, 8 * sizeof(unsigned int));
+    err = cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0);
+  }
+  if (err != cudaSuccess) {
+    if (c->status_host) cudaFreeHost(c->status_host);
+    delete c;
+    return (int)err;
+  }
+  *out = c;
+  return 0;
+}
+
+void* bcom_comm_multicast_base(BcomComm* c) { return c ? c->mc : nullptr; }
 
 int bcom_comm_destroy(BcomComm* c) {
   if (!c) return 0;
@@ -53,7 +100,7 @@ int bcom_comm_destroy(BcomComm* c) {
   cudaDeviceSynchronize();
   for (int p = 0; p < c->world; ++p)
     if (c->opened[p] && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
-  if (c->local) cudaFree(c->local);
+  if (c->local && c->owns_local) cudaFree(c->local);
   if (c->status_host) cudaFreeHost(c->status_host);
   delete c;
   return 0;

@@ -62,6 +62,18 @@ typedef struct {
 } BcomCollArgs;
 
 int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out);
+// Adopt blocks that somebody else allocated and mapped (for example torch symmetric memory):
+// bases[p] is rank p's block as mapped into this process (bases[rank] the local one), each
+// bcom_comm_block_bytes(region_bytes) long; mc_base is the NVLink multicast mapping of the
+// same blocks (a store through it lands in every rank's block) or NULL.  The caller keeps
+// ownership of the memory, and all ranks must pass a barrier between this call (which zeroes
+// the local control page) and the first collective.  With a multicast mapping the 4- and
+// 8-bit all-gather half sends each packed group with one multimem store instead of one store
+// per peer.
+int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* const* bases,
+                              void* mc_base, BcomComm** out);
+size_t bcom_comm_block_bytes(size_t region_bytes);
+void* bcom_comm_multicast_base(BcomComm* comm);
 int bcom_comm_destroy(BcomComm* comm);
 // 64-byte CUDA IPC handle of this rank's block
 int bcom_comm_ipc_handle(BcomComm* comm, void* handle_out);

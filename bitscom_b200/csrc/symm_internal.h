@@ -12,6 +12,8 @@ struct BcomComm {
   size_t region_bytes;      // bytes of each of the two data regions
   size_t total_bytes;
   unsigned char* local;     // this rank's block
+  unsigned char* mc;        // NVLink multicast mapping of the block (all ranks), or null
+  bool owns_local;          // the block was allocated by bcom_comm_create (else: adopted)
   unsigned char* peer[BCOM_MAX_WORLD];
   bool opened[BCOM_MAX_WORLD];  // peer mapping came from cudaIpcOpenMemHandle
   unsigned int* status_host;    // pinned, mapped

@@ -59,6 +59,12 @@ def _get():
         if lib is not None:
             vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
             lib.bcom_comm_create.argtypes = [ci, ci, ctypes.c_size_t, ctypes.POINTER(vp)]
+            lib.bcom_comm_create_external.argtypes = [ci, ci, ctypes.c_size_t,
+                                                      ctypes.POINTER(vp), vp, ctypes.POINTER(vp)]
+            lib.bcom_comm_block_bytes.argtypes = [ctypes.c_size_t]
+            lib.bcom_comm_block_bytes.restype = ctypes.c_size_t
+            lib.bcom_comm_multicast_base.argtypes = [vp]
+            lib.bcom_comm_multicast_base.restype = vp
             lib.bcom_comm_destroy.argtypes = [vp]
             lib.bcom_comm_ipc_handle.argtypes = [vp, vp]
             lib.bcom_comm_open_peers.argtypes = [vp, vp]
@@ -86,6 +92,10 @@ def _get():
 
 def available() -> bool:
     return _native.cuda_present() and _get() is not None
+
+
+def _flag(name: str) -> bool:
+    return os.environ.get(name, "0").strip().lower() in ("1", "true", "yes", "on")
 
 
 def default_region_bytes() -> int:
@@ -131,15 +141,26 @@ def _args(inp, out, res1, res2, n, S, dtype, bits, block, mode, stochastic, seed
 class _NativeComm:
     """Owner of one ``BcomComm*``."""
 
-    def __init__(self, rank: int, world: int, region_bytes: int, device: torch.device):
+    def __init__(self, rank: int, world: int, region_bytes: int, device: torch.device,
+                 external_bases: Optional[List[int]] = None, multicast_base: int = 0):
+        """``external_bases``: adopt blocks mapped by somebody else (one address per rank)
+        instead of allocating one and exchanging CUDA IPC handles; ``multicast_base``: the
+        NVLink multicast mapping of those blocks (0 = none)."""
         self.lib = _get()
         if self.lib is None:
             raise NativeError("fused collectives need the bcom_comm library and a GPU")
         self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.external = external_bases is not None
         handle = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            check(self.lib.bcom_comm_create(rank, world, region_bytes, ctypes.byref(handle)),
-                  "bcom_comm_create")
+            if self.external:
+                bases = (ctypes.c_void_p * world)(*[int(b) for b in external_bases])
+                check(self.lib.bcom_comm_create_external(
+                    rank, world, region_bytes, bases, ctypes.c_void_p(int(multicast_base)),
+                    ctypes.byref(handle)), "bcom_comm_create_external")
+            else:
+                check(self.lib.bcom_comm_create(rank, world, region_bytes,
+                                                ctypes.byref(handle)), "bcom_comm_create")
         self.handle = handle
         # live view of the pinned status record: word 0 != 0 means a kernel gave up
         self._status_view = (ctypes.c_uint * 8).from_address(
@@ -200,11 +221,15 @@ class FusedLowBitComm:
         dist.all_gather_object(hosts, socket.gethostname(), group=group)
         if len(set(hosts)) != 1:
             raise FusedUnavailable("fused collectives need all ranks on one NVSwitch domain")
-        self.native = _NativeComm(self.rank, self.world,
-                                  region_bytes or default_region_bytes(), self.device)
-        handles: List[Optional[bytes]] = [None] * self.world
-        dist.all_gather_object(handles, self.native.ipc_handle(), group=group)
-        self.native.open_peers(handles)
+        region = region_bytes or default_region_bytes()
+        self.multicast = False
+        self._symm = None  # keeps torch's symmetric allocation alive
+        self.native = self._try_multicast_comm(region) if _flag("BITSCOM_NVLS") else None
+        if self.native is None:
+            self.native = _NativeComm(self.rank, self.world, region, self.device)
+            handles: List[Optional[bytes]] = [None] * self.world
+            dist.all_gather_object(handles, self.native.ipc_handle(), group=group)
+            self.native.open_peers(handles)
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle,
                                                  timeout_ms or default_timeout_ms())
         self.side_stream = torch.cuda.Stream(device=self.device)
@@ -213,6 +238,37 @@ class FusedLowBitComm:
         # every rank has mapped every peer before anybody launches
         dist.barrier(group=group, device_ids=[self.device.index]
                      if dist.get_backend(group) == "nccl" else None)
+
+    def _try_multicast_comm(self, region_bytes: int) -> Optional[_NativeComm]:
+        """Blocks allocated through torch symmetric memory, which also maps them through an
+        NVLink multicast object when the fabric supports it: the all-gather half of the 4- and
+        8-bit collectives then sends each packed group with ONE multimem store that NVSwitch
+        replicates, instead of one store per peer.  Opt-in (``BITSCOM_NVLS=1``): a rank that dies
+        while its memory is bound to a multicast object can fault its peers, so failure tests
+        and fault-tolerant jobs should stay on the plain peer-store path.  Returns ``None``,
+        on every rank alike, when any rank could not set it up."""
+        lib = _get()
+        comm, hdl, buf = None, None, None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            nbytes = int(lib.bcom_comm_block_bytes(region_bytes))
+            buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            hdl = symm_mem.rendezvous(buf, group=self.group)
+            mc = int(hdl.multicast_ptr) if getattr(hdl, "has_multicast_support", False) else 0
+            bases = [int(p) for p in hdl.buffer_ptrs]
+            ok = mc != 0 and len(bases) == self.world
+        except Exception:  # symmetric memory not available for this group / device
+            ok = False
+        votes: List[Optional[bool]] = [None] * self.world
+        dist.all_gather_object(votes, bool(ok), group=self.group)
+        if not all(votes):
+            return None
+        comm = _NativeComm(self.rank, self.world, region_bytes, self.device,
+                           external_bases=bases, multicast_base=mc)
+        self._symm = (buf, hdl)
+        self.multicast = True
+        return comm
 
     @classmethod
     def for_group(cls, group, device) -> "FusedLowBitComm":
