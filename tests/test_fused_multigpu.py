@@ -1,5 +1,7 @@
 """Fused collectives across real GPUs (one process per GPU, NCCL for the plumbing)."""
 
+import os
+
 import pytest
 import torch
 import torch.distributed as dist
@@ -43,6 +45,8 @@ def _worker(rank, world, n, bits, dtype, iters):
     comm = group._fused_comms[id(group.pg)]
     assert comm.launches == iters
     comm.check_status()
+    if os.environ.get("BITSCOM_NVLS", "0") == "1" and os.environ.get("BITSCOM_REQUIRE_NVLS"):
+        assert comm.multicast, "the NVLS path was asked for but not set up"
     # stream-ordered variant with fused post-scale
     y = _input(rank, n, 99, dtype).cuda()
     side = torch.cuda.Stream()
@@ -75,3 +79,37 @@ def test_all_gpus_all_reduce_bit_exact():
     if n_gpus < 4:
         pytest.skip("needs 4 or more GPUs")
     run_ranks(_worker, n_gpus, 1 << 17, 4, torch.float32, 2, backend="nccl", timeout=600)
+
+
+@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
+                    reason="the NVLS (multimem) path has not been run on GPUs yet; "
+                           "set BITSCOM_EXPERIMENTAL=1 to try it")
+@pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
+                                          (8, torch.bfloat16, 300032)])
+def test_two_gpu_all_reduce_bit_exact_over_nvls(bits, dtype, n, monkeypatch):
+    """The same bit-exact check with the all-gather half on multimem stores (the children
+    inherit the environment).  Not for failure tests: a rank that dies while its memory is
+    bound to a multicast object can fault its peers."""
+    _need(2)
+    monkeypatch.setenv("BITSCOM_NVLS", "1")
+    monkeypatch.setenv("BITSCOM_REQUIRE_NVLS", "1")
+    run_ranks(_worker8 if bits == 8 else _worker, 2, n, bits, dtype, 3, backend="nccl")
+
+
+def _worker8(rank, world, n, bits, dtype, iters):
+    """8-bit goes through the communicator directly (LowBitGroup all-reduces 8-bit densely)."""
+    from bitscom_b200.api import ErrorFeedbackState
+    from bitscom_b200.parallel.fused import FusedLowBitComm
+
+    torch.set_num_threads(1)
+    comm = FusedLowBitComm.for_group(dist.group.WORLD, torch.device("cuda", rank))
+    assert comm.multicast or not os.environ.get("BITSCOM_REQUIRE_NVLS")
+    state, ef = SimState(), ErrorFeedbackState()
+    for it in range(iters):
+        everyone = [_input(r, n, it, dtype) for r in range(world)]
+        want = simulate_all_reduce(everyone, bits, 256, state=state, stage2=True)[rank]
+        x = everyone[rank].cuda()
+        comm.all_reduce(x, bitwidth=bits, block_size=256, ef=ef, stage2=True)
+        torch.cuda.synchronize()
+        assert torch.equal(x.cpu(), want), f"rank {rank} iter {it}"
+    comm.check_status()
