@@ -517,6 +517,27 @@ class LowBitGroup:
             st.load_state_dict(v)
             self._ef_states[k] = st
 
+    def check_agreement(self, tensor: torch.Tensor) -> None:
+        """Collective debugging aid: raises ``RuntimeError`` on every rank unless all ranks
+        hold bit-identical copies of ``tensor``.  A low-bit all-reduce must leave the same bits
+        everywhere (every rank dequantizes the same packed shards); a difference means a shard
+        was damaged in transit or the ranks ran with different options.  Costs one pass over
+        the tensor and an all-gather of two integers."""
+        flat = tensor.detach().contiguous().view(-1)
+        words = flat.view({1: torch.uint8, 2: torch.int16, 4: torch.int32,
+                           8: torch.int64}[flat.element_size()]).to(torch.int64)
+        weights = (torch.arange(words.numel(), device=words.device, dtype=torch.int64)
+                   % 65521) + 1
+        digest = torch.stack([words.sum(), (words * weights).sum(),
+                              torch.tensor(words.numel(), device=words.device)])
+        everyone = [torch.empty_like(digest) for _ in range(self.world_size)]
+        dist.all_gather(everyone, digest, group=self.pg)
+        mine = everyone[0]
+        bad = [r for r, d in enumerate(everyone) if not torch.equal(d, mine)]
+        if bad:
+            raise RuntimeError(f"ranks disagree on the tensor's bits: ranks {bad} differ from "
+                               "rank 0")
+
     def check_consistency(self) -> None:
         """Collective: every rank of the group must have been built with the same codec
         options, otherwise packed shards of different sizes would meet on the wire.

@@ -104,3 +104,59 @@ def _async_error_surfaces_at_wait(rank, world):
 def test_async_work_reports_peer_failure_at_wait():
     out = _spawn(_async_error_surfaces_at_wait, 2, timeout_s=4)
     assert out[0].startswith("error: "), out
+
+
+# ---------------------------------------------------------------------------------------
+# a fake transport: the collectives the host engine uses are wrapped on ONE rank so that a
+# shard arrives late or damaged
+# ---------------------------------------------------------------------------------------
+def _with_fake_transport(rank, world, mode):
+    from bitscom_b200 import LowBitGroup
+
+    real_a2a, real_gather = dist.all_to_all_single, dist.all_gather
+    calls = {"n": 0}
+
+    def fake_a2a(output, input, *args, **kwargs):
+        if mode == "delay":
+            time.sleep(0.5)                       # a slow link: later, but intact
+        return real_a2a(output, input, *args, **kwargs)
+
+    def fake_gather(tensor_list, tensor, *args, **kwargs):
+        # the gather half carries the reduced, re-quantized shards: damage on this path makes
+        # one rank dequantize different bits than the others
+        work = real_gather(tensor_list, tensor, *args, **kwargs)
+        calls["n"] += 1
+        if mode == "corrupt" and calls["n"] == 1 and tensor.dtype == torch.uint8:
+            if work is not None:
+                work.wait()
+            tensor_list[1].view(-1)[5] ^= 0x7F    # one damaged byte of packed codes
+        return work
+
+    if rank == 0:
+        dist.all_to_all_single, dist.all_gather = fake_a2a, fake_gather
+    group = LowBitGroup(bitwidth=4)
+    x = torch.randn(8192, generator=torch.Generator().manual_seed(3 + rank))
+    group.all_reduce(x)
+    try:
+        group.check_agreement(x)
+    except RuntimeError as exc:
+        return "disagree: " + str(exc)[:40]
+    return "agree"
+
+
+def _delay(rank, world):
+    return _with_fake_transport(rank, world, "delay")
+
+
+def _corrupt(rank, world):
+    return _with_fake_transport(rank, world, "corrupt")
+
+
+def test_delayed_shard_is_only_late():
+    out = _spawn(_delay, 2, timeout_s=20)
+    assert out == {0: "agree", 1: "agree"}, out
+
+
+def test_damaged_shard_is_caught_by_the_agreement_check():
+    out = _spawn(_corrupt, 2, timeout_s=20)
+    assert all(v.startswith("disagree: ranks disagree") for v in out.values()), out
