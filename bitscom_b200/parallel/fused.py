@@ -138,6 +138,17 @@ def _args(inp, out, res1, res2, n, S, dtype, bits, block, mode, stochastic, seed
         post_scale=float(post_scale), max_ctas=int(max_ctas), reserved=0)
 
 
+def traffic_bytes(args: CollArgs, world: int):
+    """(payload, wire) bytes of one collective on one rank: payload is the tensor as the
+    caller sees it, wire the packed codes and fp16 block scales this rank stores into its
+    peers' memory over NVLink (both halves for an all-reduce, one for the other modes)."""
+    elem = {0: 4, 1: 2, 2: 2}[int(args.dtype)]
+    shard = int(args.S)
+    shard_wire = (shard * int(args.bits) + 7) // 8 + 2 * -(-shard // int(args.block))
+    phases = 2 if int(args.mode) == MODE_ALL_REDUCE else 1
+    return int(args.n) * elem, phases * (world - 1) * shard_wire
+
+
 class _NativeComm:
     """Owner of one ``BcomComm*``."""
 
@@ -324,14 +335,9 @@ class FusedLowBitComm:
             check(rc, "bcom_collective")
         self.launches += 1
         _timing.add("fused_launches")
-        # traffic counters: payload = the tensor as the caller sees it; wire = packed codes +
-        # fp16 block scales this rank stores into its peers' memory over NVLink
-        elem = {0: 4, 1: 2, 2: 2}[int(args.dtype)]
-        shard_wire = (int(args.S) * int(args.bits) + 7) // 8 + 2 * -(-int(args.S) // int(args.block))
-        peers = self.world - 1
-        phases = {MODE_ALL_REDUCE: 2, MODE_REDUCE_SCATTER: 1, MODE_ALL_GATHER: 1}[int(args.mode)]
-        _timing.add("fused_payload_bytes", int(args.n) * elem)
-        _timing.add("fused_wire_bytes", phases * peers * shard_wire)
+        payload, wire = traffic_bytes(args, self.world)
+        _timing.add("fused_payload_bytes", payload)
+        _timing.add("fused_wire_bytes", wire)
         if not async_op:
             return None
         done = torch.cuda.Event()
