@@ -185,3 +185,53 @@ def _counters_worker(rank, world):
 
 def test_traffic_counters_and_residual_norms():
     run_ranks(_counters_worker, 2)
+
+
+# The reference's distributed all-reduce test walks five deterministic input patterns
+# (tests/test_lowbit_allreduce_reference.py:24-60,167-194: linspace / random / alternating /
+# small_range / sparse_spikes at 4, 2 and 1 bit, sizes 1031 / 4099 / 2048 / 512 / 777) and
+# compares with a CPU simulation to 1e-4.  Here the result must equal the model bit for bit.
+_PATTERNS = [("linspace", 4, 1031), ("random", 2, 4099), ("alternating", 1, 2048),
+             ("small_range", 4, 512), ("sparse_spikes", 2, 777)]
+
+
+def _pattern(name, rank, numel):
+    if name == "linspace":
+        return torch.linspace(-1.0, 1.0, numel) * (rank + 1)
+    if name == "random":
+        return torch.randn(numel, generator=torch.Generator().manual_seed(17 + rank))
+    if name == "alternating":
+        sign = torch.where(torch.arange(numel) % 2 == 0, 1.0, -1.0)
+        return sign * (0.5 + 0.25 * rank)
+    if name == "small_range":
+        return torch.linspace(-1e-4, 1e-4, numel) + 1e-5 * rank
+    x = torch.zeros(numel)
+    x[:: 97 + rank] = 10.0 * (rank + 1)
+    x[1::211] = -3.0
+    return x
+
+
+def _pattern_worker(rank, world):
+    for name, bits, numel in _PATTERNS:
+        everyone = [_pattern(name, r, numel) for r in range(world)]
+        want = simulate_all_reduce(everyone, bits, 256)[rank]
+        mine = everyone[rank].clone()
+        LowBitGroup(bitwidth=bits).all_reduce(mine)
+        assert torch.equal(mine, want), name
+        assert torch.isfinite(mine).all()
+    # stochastic rounding: two unseeded runs differ, stay finite, and all ranks agree
+    base = _pattern("random", rank, 4099)
+    runs = []
+    for _ in range(2):
+        t = base.clone()
+        g = LowBitGroup(bitwidth=4, stochastic_rounding=True)
+        g.all_reduce(t)
+        g.check_agreement(t)
+        runs.append(t)
+    assert torch.isfinite(runs[0]).all() and not torch.equal(runs[0], runs[1])
+    dense = torch.stack([_pattern("random", r, 4099) for r in range(world)]).sum(0)
+    assert (runs[0] - dense).abs().max() < 3.0
+
+
+def test_reference_input_patterns_match_the_model():
+    run_ranks(_pattern_worker, 2)
