@@ -190,3 +190,29 @@ def test_ddp_hook_example_trains():
     line = next(l for l in out.splitlines() if l.startswith("loss "))
     first, last = (float(v) for v in line[5:].split(" -> "))
     assert last < 0.6 * first
+
+
+def test_roofline_report_table():
+    from bitscom_b200.bench import roofline_report as RR
+
+    lines = [
+        json.dumps({"case": "gemm_tcgen05", "M": 4096, "N": 4096, "K": 4096, "ms": 0.11,
+                    "tflops": 1250.0, "frac_bf16_peak": 0.76, "peaks": "of measured"}),
+        json.dumps({"case": "attention_tcgen05", "batch": 2, "seq": 2048, "heads": 32,
+                    "head_dim": 128, "fwd_variant": "pipelined", "bwd_dq": "tma",
+                    "fwd_ms": 0.137, "fwd_tflops": 503.0, "fwd_frac_bf16_peak": 0.30,
+                    "bwd_ms": 0.673, "bwd_tflops": 255.0, "bwd_frac_bf16_peak": 0.15,
+                    "peaks": "of measured"}),
+        json.dumps({"case": "elementwise", "tokens": 8192, "peaks": "of fallback", "kernels": [
+            {"name": "adamw_flat", "ms": 1.5, "gbs": 6071.0, "frac_hbm": 0.93}]}),
+        json.dumps({"bytes": 1 << 30, "dtype": "fp32", "world": 8, "bits": 4, "lowbit_ms": 1.317,
+                    "lowbit_fp32eq_gbs": 815.0, "roofline_frac": 0.59, "peaks": "measured"}),
+        "not json", json.dumps({"something": "else"}),
+    ]
+    rows = RR.collect(lines)
+    assert [r["kernel"] for r in rows] == [
+        "gemm_tcgen05", "attention_tcgen05 fwd (pipelined)", "attention_tcgen05 bwd (dQ tma)",
+        "adamw_flat", "low-bit all-reduce 4-bit"]
+    table = RR.to_markdown(rows)
+    assert "| gemm_tcgen05 | 4096 x 4096 x 4096 | 0.110 ms | 1250 TFLOP/s | 0.76 |" in table
+    assert "8 GPUs, 1024 MB fp32" in table and "HBM copy, of fallback" in table
