@@ -52,3 +52,18 @@ def test_c_host_example_links_against_the_cpu_codec(tmp_path):
     run = subprocess.run([exe], capture_output=True, text=True, timeout=60)
     assert run.returncode == 0, run.stdout + run.stderr
     assert "packed bytes" in run.stdout
+
+
+def test_info_command_reports_libraries():
+    out = subprocess.run([sys.executable, "-m", "bitscom_b200", "info"], cwd=ROOT,
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    import json
+
+    rep = json.loads(out.stdout)
+    assert rep["package"] == bitscom_b200.__version__
+    assert set(rep["libraries"]) == set(_build.available_libraries())
+    assert rep["libraries"]["bcom_cpu"]["loads"] is True
+    bad = subprocess.run([sys.executable, "-m", "bitscom_b200", "bogus"], cwd=ROOT,
+                         capture_output=True, text=True, timeout=120)
+    assert bad.returncode == 2
