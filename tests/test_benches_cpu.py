@@ -17,7 +17,20 @@ from bitscom_b200.bench import trace_stable_window as TW
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port(hint):
+    """A port nobody listens on right now (``hint`` is only used if the probe fails)."""
+    import socket
+
+    try:
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+            s.bind(("127.0.0.1", 0))
+            return s.getsockname()[1]
+    except OSError:
+        return hint
+
+
 def _torchrun(module, args, port, nproc=2, timeout=600):
+    port = _free_port(port)
     env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", str(nproc),
            "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", module] + args
@@ -168,6 +181,7 @@ def test_quantize_curve_host_columns(tmp_path):
 
 # ------------------------------------------------------------------------- examples
 def _run_example(name, port):
+    port = _free_port(port)
     env = dict(os.environ, OMP_NUM_THREADS="1", PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
