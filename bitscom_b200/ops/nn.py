@@ -356,7 +356,27 @@ class FlatAdamW:
         self.exp_avg_sq = torch.zeros_like(master)
         self.step_count = 0
 
+    def _step_host(self, grad_scale: float, zero_grad: bool) -> None:
+        """The kernel's arithmetic in torch ops, for buffers that live on the CPU (CPU ranks
+        exercise the sharded optimizer's collectives with it)."""
+        b1, b2 = self.betas
+        g = self.grad * grad_scale
+        self.exp_avg.mul_(b1).add_(g, alpha=1.0 - b1)
+        self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1.0 - b2)
+        mhat = self.exp_avg / (1.0 - b1 ** self.step_count)
+        vhat = self.exp_avg_sq / (1.0 - b2 ** self.step_count)
+        self.master.mul_(1.0 - self.lr * self.weight_decay)
+        self.master.addcdiv_(mhat, vhat.sqrt_().add_(self.eps), value=-self.lr)
+        if zero_grad:
+            self.grad.zero_()
+        if self.params_bf16 is not None:
+            self.params_bf16.copy_(self.master)
+
     def step(self, grad_scale: float = 1.0, zero_grad: bool = True) -> None:
+        if not self.master.is_cuda:
+            self.step_count += 1
+            self._step_host(grad_scale, zero_grad)
+            return
         lib = _need()
         self.step_count += 1
         check(lib.bcom_adamw(ptr(self.master), ptr(self.params_bf16), ptr(self.grad),
