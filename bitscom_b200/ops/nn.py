@@ -409,6 +409,13 @@ class FlatSGD:
         self.buf = torch.zeros_like(param)
 
     def step(self, grad_scale: float = 1.0, zero_grad: bool = True) -> None:
+        if not self.param.is_cuda:  # the kernel's arithmetic in torch ops, for CPU buffers
+            g = self.grad * grad_scale + self.weight_decay * self.param
+            self.buf.mul_(self.momentum).add_(g)
+            self.param.add_(self.buf, alpha=-self.lr)
+            if zero_grad:
+                self.grad.zero_()
+            return
         lib = _need()
         check(lib.bcom_sgd_momentum(ptr(self.param), ptr(self.grad), ptr(self.buf),
                                     self.param.numel(), float(self.lr), float(self.momentum),

@@ -69,3 +69,21 @@ def _zero_worker(rank, world):
 
 def test_sharded_adamw_tracks_dense_adamw_on_cpu_ranks():
     run_ranks(_zero_worker, 2)
+
+
+def test_flat_sgd_host_path_matches_torch():
+    from bitscom_b200.ops.nn import FlatSGD
+
+    torch.manual_seed(0)
+    param = torch.randn(512)
+    ref = torch.nn.Parameter(param.clone())
+    grad = torch.zeros(512)
+    opt = FlatSGD(param, grad, lr=0.1, momentum=0.9, weight_decay=1e-3)
+    tref = torch.optim.SGD([ref], lr=0.1, momentum=0.9, weight_decay=1e-3)
+    for step in range(4):
+        g = torch.randn(512, generator=torch.Generator().manual_seed(step))
+        grad.copy_(g * 4.0)
+        opt.step(grad_scale=0.25)
+        ref.grad = g.clone()
+        tref.step()
+        assert torch.allclose(param, ref.detach(), atol=1e-6) and grad.eq(0).all()
