@@ -12,8 +12,10 @@ on a side stream under backward.  ``--mode nccl`` is the dense baseline.
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
+import time
 
 import torch
 import torch.distributed as dist
@@ -35,17 +37,24 @@ def main(argv=None):
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--no-error-feedback", action="store_true")
     ap.add_argument("--out", default="bench_outputs/resnet18_ddp.jsonl")
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu",
+                    help="'cpu' runs the same program on CPU ranks over gloo (plumbing check)")
     args = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", 0))
     local = int(os.environ.get("LOCAL_RANK", rank))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    cuda = args.device == "cuda"
+    if cuda:
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
     torch.manual_seed(0)
     model = ResNet18().to(dev).to(memory_format=torch.channels_last)
-    ddp = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb)
+    ddp = DDP(model, device_ids=[local] if cuda else None, bucket_cap_mb=args.bucket_mb)
     if args.mode == "lowbit" and world > 1:
         group = LowBitGroup(bitwidth=args.bitwidth, block_size=256,
                             error_feedback=not args.no_error_feedback)
@@ -58,7 +67,7 @@ def main(argv=None):
 
     def step():
         opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
+        with torch.autocast("cuda", dtype=torch.bfloat16) if cuda else contextlib.nullcontext():
             loss = F.cross_entropy(ddp(x), y)
         loss.backward()
         opt.step()
@@ -66,24 +75,32 @@ def main(argv=None):
 
     for _ in range(args.warmup):
         step()
-    torch.cuda.synchronize()
+    if cuda:
+        torch.cuda.synchronize()
     dist.barrier()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
+    if cuda:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+    t0 = time.perf_counter()
     first = last = None
     for i in range(args.steps):
         loss = step()
         if i == 0:
             first = loss.detach()
         last = loss.detach()
-    e.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([s.elapsed_time(e) / args.steps], device=dev)
+    if cuda:
+        e.record()
+        torch.cuda.synchronize()
+        elapsed_ms = s.elapsed_time(e)
+    else:
+        elapsed_ms = (time.perf_counter() - t0) * 1e3
+    ms = torch.tensor([elapsed_ms / args.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
         row = {"workload": "resnet18_cifar_ddp", "mode": args.mode, "world": world,
                "bitwidth": args.bitwidth if args.mode == "lowbit" else 32,
-               "batch_per_gpu": args.batch, "ms_per_step": float(ms.item()),
+               "device": args.device, "batch_per_gpu": args.batch,
+               "ms_per_step": float(ms.item()),
                "samples_per_s": world * args.batch / float(ms.item()) * 1e3,
                "loss_first": float(first.item()), "loss_last": float(last.item())}
         print(json.dumps(row), flush=True)

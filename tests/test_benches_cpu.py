@@ -230,3 +230,16 @@ def test_roofline_report_table():
     table = RR.to_markdown(rows)
     assert "| gemm_tcgen05 | 4096 x 4096 x 4096 | 0.110 ms | 1250 TFLOP/s | 0.76 |" in table
     assert "8 GPUs, 1024 MB fp32" in table and "HBM copy, of fallback" in table
+
+
+def test_resnet18_ddp_trainer_on_cpu_ranks(tmp_path):
+    """Config-3 program end to end on CPU ranks: torch DDP buckets through the low-bit
+    communication hook (2-bit + error feedback), loss reported, output row written."""
+    out = str(tmp_path / "resnet.jsonl")
+    recs = _torchrun("bitscom_b200.trainer.resnet18_ddp",
+                     ["--device", "cpu", "--steps", "3", "--warmup", "1", "--batch", "8",
+                      "--bucket-mb", "4", "--out", out], port=29663, timeout=900)
+    row = recs[-1]
+    assert row["workload"] == "resnet18_cifar_ddp" and row["world"] == 2 and row["bitwidth"] == 2
+    assert row["loss_last"] == row["loss_last"] and row["samples_per_s"] > 0
+    assert os.path.exists(out)
