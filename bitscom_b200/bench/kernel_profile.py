@@ -237,7 +237,7 @@ def main(argv=None):
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
     ap.add_argument("--fwd-variant", default="pipelined",
                     choices=["simple", "pipelined", "pipelined8"])
-    ap.add_argument("--bwd-dq", default="tma", choices=["atomic", "tma"])
+    ap.add_argument("--bwd-dq", default="tma", choices=["atomic", "tma", "tma_early"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--elems", type=int, default=1 << 25)
     ap.add_argument("--bits", type=int, default=4)

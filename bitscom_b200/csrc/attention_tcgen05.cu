@@ -961,6 +961,7 @@ struct BwdParams {
 
 struct BwdShared {
   uint64_t bar_kv, bar_q, bar_1, bar_2;
+  uint64_t bar_2a;  // EARLY: dV and dK have read Q and dO (dQ may still be running)
   uint32_t tmem_base;
   volatile int abort;
   float lse[BQ];
@@ -978,7 +979,12 @@ template <int HD> struct Bwd {
 // idle at that point; 128-byte swizzled so that the row-per-thread stores do not collide)
 // and added to global memory by TMA reductions of [128 rows x 32 floats] boxes, which the L2
 // performs at full-line granularity while the next block's MMAs run.
-template <int HD, bool TMA_DQ>
+// EARLY (with TMA_DQ): two latencies of the query-block loop are taken off its critical path.
+// dV / dK are committed on a barrier of their own, so the next block's Q and dO tiles are
+// requested as soon as those two products have read the current ones, under the dQ product
+// and its drain; and the next block's log-sum-exp / delta rows are fetched into registers
+// during the current block instead of at the top of the next one.
+template <int HD, bool TMA_DQ, bool EARLY = false>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 128} over qkv
                      const __grid_constant__ CUtensorMap tm_do,    // box {64, 128} over dO
@@ -1015,6 +1021,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
     tc::mbar_init(&sh->bar_q, 1);
     tc::mbar_init(&sh->bar_1, 1);
     tc::mbar_init(&sh->bar_2, 1);
+    tc::mbar_init(&sh->bar_2a, 1);
     sh->abort = 0;
     tc::fence_mbar_init();
   }
@@ -1056,11 +1063,31 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
 
   if (!tc::mbar_wait(&sh->bar_kv, 0, kBudgetNs)) { sh->abort = 1; record_fail(11); }
 
+  // EARLY: row statistics of the NEXT query block, fetched one block ahead
+  float lse_next = 0.0f, delta_next = 0.0f;
+  if constexpr (EARLY) {
+    if (tid < BQ) {
+      const size_t base = ((size_t)b * p.heads + h) * p.seq + (size_t)kb * BQ;
+      lse_next = p.lse2[base + tid];
+      delta_next = p.delta[base + tid];
+    }
+  }
+
   for (int qi = 0; qi < nq; ++qi) {
     const uint32_t par = (uint32_t)qi & 1u;
     const int qpos0 = (kb + qi) * BQ;  // first query position of this block
     // row statistics of the 128 queries of this block
-    {
+    if constexpr (EARLY) {
+      if (tid < BQ) {
+        sh->lse[tid] = lse_next;
+        sh->delta[tid] = delta_next;
+        if (qi + 1 < nq) {  // issue the next block's loads now, consume them a block later
+          const size_t base = ((size_t)b * p.heads + h) * p.seq + qpos0 + BQ;
+          lse_next = p.lse2[base + tid];
+          delta_next = p.delta[base + tid];
+        }
+      }
+    } else {
       const size_t base = ((size_t)b * p.heads + h) * p.seq + qpos0;
       if (tid < BQ) {
         sh->lse[tid] = p.lse2[base + tid];
@@ -1139,15 +1166,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
       for (int ks = 0; ks < BQ / 16; ++ks)
         tc::umma_bf16(tDK, desc_kmajor(aDS, 128, ks), desc_mnmajor(aQ, 128, ks), idesc_kn,
                       acc | (ks != 0));
+      if constexpr (EARLY) tc::umma_commit(&sh->bar_2a);  // dV, dK issued: Q / dO readers
 #pragma unroll
       for (int ks = 0; ks < BKB / 16; ++ks)
         tc::umma_bf16(tDQ, desc_mnmajor(aDS, 128, ks), desc_mnmajor(aK, 128, ks), idesc_nn,
                       ks != 0);
       tc::umma_commit(&sh->bar_2);
+      if constexpr (EARLY) {
+        // Q and dO are free once dV and dK are done; dQ (reads dS^T and K) may still run
+        if (!tc::mbar_wait(&sh->bar_2a, par, kBudgetNs)) { sh->abort = 1; record_fail(15); }
+        if (!sh->abort && qi + 1 < nq) load_q(qi + 1);
+      }
     }
     if (!tc::mbar_wait(&sh->bar_2, par, kBudgetNs)) { sh->abort = 1; record_fail(14); }
     tc::tc_fence_after_sync();
-    if (tid == 0 && qi + 1 < nq) load_q(qi + 1);  // Q and dO tiles are free again
+    if constexpr (!EARLY) {
+      if (tid == 0 && qi + 1 < nq) load_q(qi + 1);  // Q and dO tiles are free again
+    }
 
     // ---- dQ rows (thread t <-> query row t) into the fp32 buffer ----
     if constexpr (TMA_DQ) {
@@ -1370,7 +1405,8 @@ static int launch_fwd(const void* qkv, void* out, void* lse2, int batch, int seq
   return (int)cudaGetLastError();
 }
 
-static int g_bwd_dq_variant = 1;  // 0: float4 atomics, 1: TMA reduce-add from shared memory
+// 0: float4 atomics, 1: TMA reduce-add from shared memory, 2: 1 + early loads of the next block
+static int g_bwd_dq_variant = 1;
 // 0: attention_fwd_kernel, 1: attention_fwd_pipelined_kernel, 2: attention_fwd_pipelined8_kernel
 static int g_fwd_variant = 1;
 
@@ -1439,19 +1475,19 @@ static int launch_fwd_pipelined8(const void* qkv, void* out, void* lse2, int bat
   return (int)cudaGetLastError();
 }
 
-template <int HD, bool TMA_DQ>
+template <int HD, bool TMA_DQ, bool EARLY = false>
 static int launch_bwd_kernel(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do,
                              const CUtensorMap& tm_dq, const BwdParams& p, int grid,
                              cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel<HD, TMA_DQ>,
+    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel<HD, TMA_DQ, EARLY>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd<HD>::SMEM);
   });
   if (attr_err != cudaSuccess) return 1005;
-  attention_bwd_kernel<HD, TMA_DQ><<<grid, kBwdThreads, Bwd<HD>::SMEM, st>>>(tm_qkv, tm_do, tm_dq,
-                                                                           p);
+  attention_bwd_kernel<HD, TMA_DQ, EARLY><<<grid, kBwdThreads, Bwd<HD>::SMEM, st>>>(
+      tm_qkv, tm_do, tm_dq, p);
   return 0;
 }
 
@@ -1464,7 +1500,7 @@ static int launch_bwd(const void* qkv, const void* out, const void* d_out, const
   CUtensorMap tm_qkv, tm_do, tm_dq;
   if (make_map(&tm_qkv, qkv, tokens, 3 * H, 64, 128)) return 1003;
   if (make_map(&tm_do, d_out, tokens, H, 64, 128)) return 1004;
-  const bool tma_dq = g_bwd_dq_variant == 1;
+  const bool tma_dq = g_bwd_dq_variant >= 1;
   if (tma_dq) {
     if (((uintptr_t)dq_acc & 15) || make_map_f32(&tm_dq, dq_acc, tokens, H, 32, 128)) return 1007;
   } else {
@@ -1488,8 +1524,10 @@ static int launch_bwd(const void* qkv, const void* out, const void* d_out, const
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   const int grid = batch * heads * (seq / BKB);
-  const int rc = tma_dq ? launch_bwd_kernel<HD, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
-                        : launch_bwd_kernel<HD, false>(tm_qkv, tm_do, tm_dq, p, grid, st);
+  const int rc = g_bwd_dq_variant == 2
+                     ? launch_bwd_kernel<HD, true, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
+                 : tma_dq ? launch_bwd_kernel<HD, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
+                          : launch_bwd_kernel<HD, false>(tm_qkv, tm_do, tm_dq, p, grid, st);
   if (rc) return rc;
   attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
   return (int)cudaGetLastError();
@@ -1504,10 +1542,11 @@ static bool shape_ok(int batch, int seq, int heads, int head_dim) {
 extern "C" {
 
 // 0: dQ tiles are added to the fp32 accumulator with float4 atomics; 1: with TMA reductions
-// from a shared-memory staging tile.  Returns the previous value.
+// from a shared-memory staging tile; 2: as 1, with the next query block's loads issued early.
+// Returns the previous value.
 int bcom_attention_set_bwd_dq_variant(int variant) {
   const int old = attn::g_bwd_dq_variant;
-  if (variant == 0 || variant == 1) attn::g_bwd_dq_variant = variant;
+  if (variant >= 0 && variant <= 2) attn::g_bwd_dq_variant = variant;
   return old;
 }
 

@@ -22,7 +22,7 @@ _scratch: Dict[Tuple, torch.Tensor] = {}
 _FWD_VARIANTS = {"simple": 0, "pipelined": 1, "pipelined8": 2}
 # how the backward kernel adds a dQ tile to the fp32 accumulator: float4 atomics from
 # registers, or TMA reductions from a shared-memory staging tile
-_BWD_DQ_VARIANTS = {"atomic": 0, "tma": 1}
+_BWD_DQ_VARIANTS = {"atomic": 0, "tma": 1, "tma_early": 2}
 
 
 def _get():
@@ -65,7 +65,8 @@ def set_forward_variant(name: str) -> str:
 
 
 def set_backward_dq_variant(name: str) -> str:
-    """Select how dQ tiles are accumulated ("atomic" or "tma", also ``BITSCOM_ATTN_BWD_DQ``);
+    """Select how dQ tiles are accumulated ("atomic", "tma", or "tma_early": "tma" with the
+    next query block's loads issued under the dQ product; also ``BITSCOM_ATTN_BWD_DQ``);
     returns the name that was active before."""
     if name not in _BWD_DQ_VARIANTS:
         raise ValueError(f"unknown attention backward dQ variant {name!r}")
@@ -73,7 +74,7 @@ def set_backward_dq_variant(name: str) -> str:
     if lib is None:
         raise NativeError("attention kernel needs the bcom_llama library and a GPU")
     old = lib.bcom_attention_set_bwd_dq_variant(_BWD_DQ_VARIANTS[name])
-    return "tma" if old == 1 else "atomic"
+    return {0: "atomic", 1: "tma", 2: "tma_early"}[old]
 
 
 def supported(seq: int, head_dim: int) -> bool:

@@ -133,6 +133,16 @@ def test_experimental_forward_variant_pipelined8(B, S, nh, hd):
     assert e < 3e-2 * max(1.0, xr.grad.abs().max().item())
 
 
+@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
+                    reason="kernel variants that have not been run on a GPU yet; "
+                           "set BITSCOM_EXPERIMENTAL=1 to try them")
+@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("B,S,nh", [(1, 128, 1), (2, 384, 2), (1, 1024, 3)])
+def test_experimental_backward_variant_tma_early(B, S, nh, hd):
+    """The backward kernel that requests the next Q / dO tiles and row statistics early."""
+    test_backward_dq_variants_match_reference(B, S, nh, hd, "tma_early")
+
+
 def test_attention_second_call_reuses_zeroed_scratch():
     B, S, nh, hd = 1, 256, 2, 128
     H = nh * hd
