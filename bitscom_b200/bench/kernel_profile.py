@@ -103,6 +103,7 @@ def gemm(args):
     from bitscom_b200.ops import gemm as G
 
     _, tflops, tag = _peaks()
+    G.set_variant(args.gemm_variant)
     M, N, K = args.m, args.n, args.k
     copies = max(1, min(8, (256 << 20) // max(1, (M * K + N * K) * 2)))
     As = [(torch.randn(M, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
@@ -125,12 +126,13 @@ def gemm(args):
     G.check_status()
     if args.wgrad:
         tf = 2 * M * N * K / ms / 1e9
-        print(json.dumps({"case": "gemm_tcgen05_wgrad_fp32_accumulate", "M": M, "N": N, "K": K,
-                          "ms": ms, "tflops": tf, "frac_bf16_peak": tf / tflops, "peaks": tag}))
+        print(json.dumps({"case": "gemm_tcgen05_wgrad_fp32_accumulate",
+                          "variant": args.gemm_variant, "M": M, "N": N, "K": K, "ms": ms, "tflops": tf, "frac_bf16_peak": tf / tflops, "peaks": tag}))
         return
     ms_ref = _timed(lambda i: torch.matmul(As[i % copies], Bs[i % copies].t()), args.iters)
     tf = 2 * M * N * K / ms / 1e9
-    print(json.dumps({"case": "gemm_tcgen05", "M": M, "N": N, "K": K, "ms": ms, "tflops": tf,
+    print(json.dumps({"case": "gemm_tcgen05", "variant": args.gemm_variant, "M": M, "N": N,
+                      "K": K, "ms": ms, "tflops": tf,
                       "frac_bf16_peak": tf / tflops, "torch_matmul_ms": ms_ref,
                       "torch_tflops": 2 * M * N * K / ms_ref / 1e9, "peaks": tag}))
 
@@ -250,6 +252,7 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--wgrad", action="store_true")
+    ap.add_argument("--gemm-variant", default="1cta", choices=["1cta", "2cta"])
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)

@@ -6,6 +6,7 @@ reference trainer's model is plain ``nn.Linear``
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -15,6 +16,9 @@ from . import _native
 from ._native import NativeError, check, ptr, stream_ptr
 
 _lib = None
+_lib2 = None      # the CTA-pair kernel's library, loaded when that variant is first selected
+_variant = None   # "1cta" | "2cta"; None until the first call reads BITSCOM_GEMM
+_VARIANTS = ("1cta", "2cta")
 
 
 def _get():
@@ -30,19 +34,69 @@ def _get():
     return _lib or None
 
 
+def _get2():
+    """The CTA-pair kernel (``csrc/gemm_tcgen05_2cta.cu``), or ``None`` when its library is
+    not part of this installation."""
+    global _lib2
+    if _lib2 is None:
+        try:
+            lib = _native.load("bcom_gemm2")
+        except Exception:  # sources and binary both absent
+            lib = None
+        if lib is not None:
+            vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+            lib.bcom_gemm2_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ll, ll, ll, ci, ci, ci, ci,
+                                            ci, vp]
+            lib.bcom_gemm2_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
+        _lib2 = lib if lib is not None else False
+    return _lib2 or None
+
+
 def available() -> bool:
     return _native.cuda_present() and _get() is not None
 
 
-_STATUS = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "accumulator hand-off"}
+def variant() -> str:
+    """The kernel that ``gemm`` launches: "1cta" (default) or "2cta" (CTA pairs, 256x256 tiles,
+    ``tcgen05.mma.cta_group::2``).  Initialised from ``BITSCOM_GEMM``."""
+    global _variant
+    if _variant is None:
+        want = os.environ.get("BITSCOM_GEMM", "1cta").strip().lower()
+        _variant = "1cta"
+        if want == "2cta":
+            set_variant("2cta")
+        elif want != "1cta":
+            raise ValueError(f"BITSCOM_GEMM={want!r}: expected one of {_VARIANTS}")
+    return _variant
+
+
+def set_variant(name: str) -> str:
+    """Select the GEMM kernel; returns the name that was active before.  Raises
+    ``NativeError`` if the CTA-pair library is not available."""
+    global _variant
+    if name not in _VARIANTS:
+        raise ValueError(f"unknown GEMM variant {name!r}")
+    old = _variant or "1cta"
+    if name == "2cta" and _get2() is None:
+        raise NativeError("the CTA-pair GEMM needs the bcom_gemm2 library and a GPU")
+    _variant = name
+    return old
+
+
+_STATUS = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "accumulator hand-off",
+           5: "MMA issuer (peer CTA's stage)", 6: "stage forwarder"}
 
 
 def check_status(clear: bool = True) -> None:
     """Raise if a GEMM kernel gave up on one of its bounded waits (synchronises)."""
     out = (ctypes.c_uint * 4)()
     check(_get().bcom_gemm_status(ctypes.byref(out), int(clear)), "bcom_gemm_status")
+    which = "tcgen05 GEMM"
+    if not out[0] and _lib2:
+        check(_lib2.bcom_gemm2_status(ctypes.byref(out), int(clear)), "bcom_gemm2_status")
+        which = "tcgen05 CTA-pair GEMM"
     if out[0]:
-        raise NativeError(f"tcgen05 GEMM timed out in the {_STATUS.get(out[0], out[0])} "
+        raise NativeError(f"{which} timed out in the {_STATUS.get(out[0], out[0])} "
                           f"(cta {out[1]}, thread {out[2]})")
 
 
@@ -74,8 +128,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
     if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16,
                                                                       torch.float32):
         raise ValueError("bad output tensor")
+    launch = lib.bcom_gemm_bf16 if variant() == "1cta" else _get2().bcom_gemm2_bf16
     with _native.on_device(a.device):
-        check(lib.bcom_gemm_bf16(
+        check(launch(
             ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
             int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32),
             int(accumulate), int(max_ctas), stream_ptr(a.device)), "bcom_gemm_bf16")

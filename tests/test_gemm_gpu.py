@@ -1,5 +1,7 @@
 """tcgen05 GEMM against a plain fp32 matmul of the same bf16 inputs."""
 
+import os
+
 import pytest
 import torch
 
@@ -110,6 +112,40 @@ def test_linear_autograd_matches_torch():
     _check(w2.main_grad, 2 * wr.grad, 1024)
     assert w2.grad is None
     G.check_status()
+
+
+@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
+                    reason="kernel variants that have not been run on a GPU yet; "
+                           "set BITSCOM_EXPERIMENTAL=1 to try them")
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 256), (512, 256, 1024),
+                                   (200, 264, 136), (1024, 1024, 4096), (77, 8, 40),
+                                   (4096, 4096, 512)])
+def test_experimental_cta_pair_gemm(a_mn, b_mn, M, N, K):
+    """The CTA-pair kernel (256x256 tiles, tcgen05 cta_group::2) against fp32 matmul, bf16 and
+    accumulating fp32 outputs; exact on small integers, so a swapped half tile cannot hide in
+    the tolerance."""
+    a = _mk(K, M, 1) if a_mn else _mk(M, K, 1)
+    b = _mk(K, N, 2) if b_mn else _mk(N, K, 2)
+    if (a.shape[1] % 8) or (b.shape[1] % 8):
+        pytest.skip("row stride must stay 16-byte aligned")
+    ai = torch.randint(-3, 4, a.shape, device="cuda").to(torch.bfloat16)
+    bi = torch.randint(-3, 4, b.shape, device="cuda").to(torch.bfloat16)
+    before = G.set_variant("2cta")
+    try:
+        out = G.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn)
+        acc = G.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out_dtype=torch.float32)
+        G.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=acc, accumulate=True)
+        exact = G.gemm(ai, bi, a_mn_major=a_mn, b_mn_major=b_mn, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        G.check_status()
+    finally:
+        G.set_variant(before)
+    ref = _ref(a, b, a_mn, b_mn)
+    _check(out, ref, K)
+    _check(acc, 2 * ref, K)
+    assert torch.equal(exact, _ref(ai, bi, a_mn, b_mn))
 
 
 @pytest.mark.performance
