@@ -121,13 +121,22 @@ class ErrorFeedbackState:
     def __init__(self):
         self.stage1: Optional[torch.Tensor] = None
         self.stage2: Optional[torch.Tensor] = None
+        self.carry_over = False  # set by LowBitGroup.rebind: the world size is about to change
 
     def ensure(self, plan: ShardPlan, device, stage2: bool):
         if self.stage1 is None or self.stage1.numel() != plan.padded \
                 or self.stage1.device != torch.device(device):
-            self.stage1 = torch.zeros(plan.padded, dtype=torch.float32, device=device)
+            fresh = torch.zeros(plan.padded, dtype=torch.float32, device=device)
+            if self.carry_over and self.stage1 is not None \
+                    and self.stage1.device == fresh.device:
+                # same bucket, new shard plan: the stage-1 residual is per element of this
+                # rank's own gradient and stays valid (the padding's residual is zero)
+                n = min(plan.numel, int(self.stage1.numel()))
+                fresh[:n] = self.stage1[:n]
+            self.stage1 = fresh
             self.stage2 = None
-        if stage2 and self.stage2 is None:
+        self.carry_over = False
+        if stage2 and (self.stage2 is None or self.stage2.numel() != plan.shard_len):
             self.stage2 = torch.zeros(plan.shard_len, dtype=torch.float32, device=device)
 
     def state_dict(self):
@@ -516,6 +525,25 @@ class LowBitGroup:
             st = ErrorFeedbackState()
             st.load_state_dict(v)
             self._ef_states[k] = st
+
+    def rebind(self, process_group=None) -> None:
+        """Point this group at another process group, typically the one built among the
+        survivors after a rank was lost (``utils.health.shrink_process_group``).  Stage-1
+        residuals are kept (they belong to this rank's own gradient elements) and re-laid
+        out for the new shard plan on first use; stage-2 residuals belong to shards whose
+        owners have changed and are dropped; fused communicators of the old group are
+        released.  Call it between steps, on every surviving rank."""
+        self.pg = process_group or dist.distributed_c10d._get_default_group()
+        if any(self._fused_comms.values()):
+            from .parallel.fused import FusedLowBitComm
+
+            # communicators are cached per process-group object; the old group's symmetric
+            # blocks map memory of peers that may be gone
+            FusedLowBitComm.drop_cache()
+        self._fused_comms = {}
+        for st in self._ef_states.values():
+            st.carry_over = True
+            st.stage2 = None
 
     def check_agreement(self, tensor: torch.Tensor) -> None:
         """Collective debugging aid: raises ``RuntimeError`` on every rank unless all ranks

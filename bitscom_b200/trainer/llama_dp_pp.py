@@ -276,6 +276,26 @@ def _default_attention() -> str:
         return "sdpa"
 
 
+def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
+    step = 0
+    for epoch in range(args.epochs):
+        loader.set_epoch(epoch)
+        for batch in loader:
+            if step >= args.max_steps:
+                break
+            if monitor is not None:
+                monitor.check()
+            t0 = time.perf_counter()
+            loss = trainer.train_step(batch)
+            loader.mark_consumed()
+            if loss is not None:
+                print(json.dumps({"step": step, "epoch": epoch, "loss": float(loss.item()),
+                                  "step_s": time.perf_counter() - t0}), flush=True)
+            if step % 50 == 0:
+                trainer.check_kernels()
+            step += 1
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--pp_size", type=int, default=1)
@@ -306,6 +326,11 @@ def main(argv=None):
     ap.add_argument("--lr", type=float, default=1e-4)
     ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
     ap.add_argument("--output_dir", default=None, help="write a checkpoint here at the end")
+    ap.add_argument("--health_check", action="store_true",
+                    help="heartbeats through the rendezvous store: a rank that leaves, fails "
+                         "or falls silent is noticed on the host before the next step; the "
+                         "survivors write a checkpoint (with --output_dir) and stop")
+    ap.add_argument("--health_timeout", type=float, default=30.0)
     args = ap.parse_args(argv)
 
     mcfg = LlamaConfig.llama7b() if args.model == "llama7b" else LlamaConfig.tiny()
@@ -329,29 +354,42 @@ def main(argv=None):
                           vocab_size=mcfg.vocab_size, micro_batches=tcfg.micro_batches,
                           micro_batch_size=tcfg.micro_batch_size, dp_size=trainer.dp,
                           dp_rank=trainer.dp_rank, seed=tcfg.seed)
-    step = 0
-    for epoch in range(args.epochs):
-        loader.set_epoch(epoch)
-        for batch in loader:
-            if step >= args.max_steps:
-                break
-            t0 = time.perf_counter()
-            loss = trainer.train_step(batch)
-            loader.mark_consumed()
-            if loss is not None:
-                print(json.dumps({"step": step, "epoch": epoch, "loss": float(loss.item()),
-                                  "step_s": time.perf_counter() - t0}), flush=True)
-            if step % 50 == 0:
-                trainer.check_kernels()
-            step += 1
+    monitor = None
+    if args.health_check and dist.is_initialized() and dist.get_world_size() > 1:
+        from ..utils.health import HealthMonitor
+
+        monitor = HealthMonitor(dist.distributed_c10d._get_default_store(), trainer.rank,
+                                dist.get_world_size(), interval_s=1.0,
+                                timeout_s=args.health_timeout)
+    try:
+        _train_loop(args, trainer, loader, tcfg, monitor)
+    except Exception as exc:
+        from ..utils.health import PeerLostError
+
+        if not isinstance(exc, PeerLostError):
+            if monitor is not None:
+                monitor.report_failure(exc)
+            raise
+        # between steps, nothing of this rank in flight: keep what has been learnt and stop
+        # without another collective (the peer would never answer)
+        print(json.dumps({"stopped": str(exc), "step": trainer.step_count}), flush=True)
+        if args.output_dir:
+            from ..utils.checkpoint import save_checkpoint
+
+            save_checkpoint(args.output_dir, trainer.state_dict(), trainer.rank)
+        monitor.close()
+        return 3
     if args.output_dir:
         from ..utils.checkpoint import save_checkpoint
 
         save_checkpoint(args.output_dir, trainer.state_dict(), trainer.rank)
     if dist.is_initialized():
         dist.barrier()
+        if monitor is not None:
+            monitor.leave()  # after the barrier: nobody is still stepping
         dist.destroy_process_group()
+    return 0
 
 
 if __name__ == "__main__":
-    main()
+    raise SystemExit(main())
