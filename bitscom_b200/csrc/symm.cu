@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "symm_internal.h"
 
@@ -12,6 +13,16 @@
     cudaError_t e__ = (expr);                  \
     if (e__ != cudaSuccess) return (int)e__;   \
   } while (0)
+
+// canary pattern in the unused tail of the control page and in the guard page behind the regions
+static cudaError_t write_canaries(BcomComm* c) {
+  cudaError_t err = cudaMemset(c->local + BCOM_CTL_CANARY, BCOM_CANARY_BYTE,
+                               BCOM_CONTROL_BYTES - BCOM_CTL_CANARY);
+  if (err == cudaSuccess)
+    err = cudaMemset(c->local + BCOM_CONTROL_BYTES + 2 * c->region_bytes, BCOM_CANARY_BYTE,
+                     BCOM_GUARD_BYTES);
+  return err;
+}
 
 extern "C" {
 
@@ -24,13 +35,14 @@ int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out) {
   c->rank = rank;
   c->world = world;
   c->region_bytes = bcom_align_up(region_bytes, 4096);
-  c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes;
+  c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes + BCOM_GUARD_BYTES;
   c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
   cudaError_t err = cudaGetDevice(&c->device);
   if (err == cudaSuccess)
     err = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
   if (err == cudaSuccess) err = cudaMalloc((void**)&c->local, c->total_bytes);
   if (err == cudaSuccess) err = cudaMemset(c->local, 0, BCOM_CONTROL_BYTES);
+  if (err == cudaSuccess) err = write_canaries(c);
   if (err == cudaSuccess)
     err = cudaHostAlloc((void**)&c->status_host, 8 * sizeof(unsigned int), cudaHostAllocMapped);
   if (err == cudaSuccess) {
@@ -50,7 +62,7 @@ int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out) {
 }
 
 size_t bcom_comm_block_bytes(size_t region_bytes) {
-  return BCOM_CONTROL_BYTES + 2 * bcom_align_up(region_bytes, 4096);
+  return BCOM_CONTROL_BYTES + 2 * bcom_align_up(region_bytes, 4096) + BCOM_GUARD_BYTES;
 }
 
 int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* const* bases,
@@ -66,7 +78,7 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
   c->rank = rank;
   c->world = world;
   c->region_bytes = bcom_align_up(region_bytes, 4096);
-  c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes;
+  c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes + BCOM_GUARD_BYTES;
   c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
   c->local = (unsigned char*)bases[rank];
   c->mc = (unsigned char*)mc_base;
@@ -76,6 +88,7 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
   if (err == cudaSuccess)
     err = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
   if (err == cudaSuccess) err = cudaMemset(c->local, 0, BCOM_CONTROL_BYTES);
+  if (err == cudaSuccess) err = write_canaries(c);
   if (err == cudaSuccess) err = cudaDeviceSynchronize();
   if (err == cudaSuccess)
     err = cudaHostAlloc((void**)&c->status_host, 8 * sizeof(unsigned int), cudaHostAllocMapped);
@@ -103,6 +116,32 @@ int bcom_comm_destroy(BcomComm* c) {
   if (c->local && c->owns_local) cudaFree(c->local);
   if (c->status_host) cudaFreeHost(c->status_host);
   delete c;
+  return 0;
+}
+
+int bcom_comm_check_canaries(BcomComm* c, long long* first_bad) {
+  if (!c || !first_bad) return (int)cudaErrorInvalidValue;
+  *first_bad = -1;
+  int before = -1;
+  BCOM_TRY(cudaGetDevice(&before));
+  if (before != c->device) BCOM_TRY(cudaSetDevice(c->device));
+  const size_t head = BCOM_CONTROL_BYTES - BCOM_CTL_CANARY;
+  const size_t tail_off = BCOM_CONTROL_BYTES + 2 * c->region_bytes;
+  std::vector<unsigned char> host(head + BCOM_GUARD_BYTES);
+  cudaError_t err = cudaDeviceSynchronize();
+  if (err == cudaSuccess)
+    err = cudaMemcpy(host.data(), c->local + BCOM_CTL_CANARY, head, cudaMemcpyDeviceToHost);
+  if (err == cudaSuccess)
+    err = cudaMemcpy(host.data() + head, c->local + tail_off, BCOM_GUARD_BYTES,
+                     cudaMemcpyDeviceToHost);
+  if (before != c->device) (void)cudaSetDevice(before);
+  if (err != cudaSuccess) return (int)err;
+  for (size_t i = 0; i < host.size(); ++i) {
+    if (host[i] != BCOM_CANARY_BYTE) {
+      *first_bad = (long long)(i < head ? BCOM_CTL_CANARY + i : tail_off + (i - head));
+      break;
+    }
+  }
   return 0;
 }
 

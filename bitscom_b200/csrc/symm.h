@@ -3,8 +3,10 @@
 // One communicator per (process group, device).  Every rank allocates one block of
 // device memory with the same layout
 //
-//     [ control 4 KiB | receive region | gather region ]
+//     [ control 4 KiB | receive region | gather region | guard 4 KiB ]
 //
+// (the unused tail of the control page and the guard page hold a fixed byte pattern that no
+// kernel may touch; bcom_comm_check_canaries verifies it, see below)
 // and maps every peer's block (CUDA IPC between processes of one NVSwitch domain).
 // The fused kernel pushes packed shards into the *destination's* regions with plain
 // peer stores, so a consumer only ever reads its own HBM; cross-GPU ordering uses
@@ -20,6 +22,8 @@
 
 #define BCOM_MAX_WORLD 16
 #define BCOM_CONTROL_BYTES 4096
+#define BCOM_GUARD_BYTES 4096
+#define BCOM_CANARY_BYTE 0xA5
 #define BCOM_IPC_HANDLE_BYTES 64
 
 #ifdef __cplusplus
@@ -75,6 +79,12 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
 size_t bcom_comm_block_bytes(size_t region_bytes);
 void* bcom_comm_multicast_base(BcomComm* comm);
 int bcom_comm_destroy(BcomComm* comm);
+// Debugging aid for tests: synchronises the device and checks the canary bytes around this
+// rank's regions (control-page tail in front of the receive region, guard page behind the
+// gather region).  A store that missed its slot, from this rank's kernels or from a peer's
+// pushes, shows up here.  Returns 0 and *first_bad = -1 when intact; otherwise 0 with the
+// byte offset (inside the block) of the first damaged byte; a CUDA error code on failure.
+int bcom_comm_check_canaries(BcomComm* comm, long long* first_bad);
 // 64-byte CUDA IPC handle of this rank's block
 int bcom_comm_ipc_handle(BcomComm* comm, void* handle_out);
 // handles: world * 64 bytes, in rank order (own entry ignored)

@@ -28,5 +28,6 @@ struct BcomComm {
 #define BCOM_CTL_FLAG2 128    // u64[BCOM_MAX_WORLD]: peer p finished pushing phase-2 data
 #define BCOM_CTL_ARRIVE1 256  // u32: CTAs of this rank that finished phase 1
 #define BCOM_CTL_ARRIVE2 264  // u32: CTAs of this rank that finished phase 2
+#define BCOM_CTL_CANARY 512   // from here to the end of the page: canary bytes
 
 static inline size_t bcom_align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }

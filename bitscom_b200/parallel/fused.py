@@ -66,6 +66,7 @@ def _get():
             lib.bcom_comm_multicast_base.argtypes = [vp]
             lib.bcom_comm_multicast_base.restype = vp
             lib.bcom_comm_destroy.argtypes = [vp]
+            lib.bcom_comm_check_canaries.argtypes = [vp, ctypes.POINTER(ll)]
             lib.bcom_comm_ipc_handle.argtypes = [vp, vp]
             lib.bcom_comm_open_peers.argtypes = [vp, vp]
             lib.bcom_comm_set_peer.argtypes = [vp, ci, vp]
@@ -201,6 +202,17 @@ class _NativeComm:
                 self.handle, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)),
                 "bcom_comm_reset")
 
+    def check_canaries(self) -> None:
+        """Debugging aid (synchronises the device): raise if a store landed outside the
+        regions of this rank's block, in the guard bytes in front of or behind them."""
+        bad = ctypes.c_longlong(-1)
+        check(self.lib.bcom_comm_check_canaries(self.handle, ctypes.byref(bad)),
+              "bcom_comm_check_canaries")
+        if bad.value >= 0:
+            raise FusedCollectiveError(
+                f"rank {self.rank}: guard bytes of the symmetric block were overwritten at "
+                f"offset {bad.value}")
+
     def close(self) -> None:
         if self.handle:
             self.lib.bcom_comm_destroy(self.handle)
@@ -313,6 +325,10 @@ class FusedLowBitComm:
     def set_timeout_ms(self, ms: float) -> None:
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle, float(ms))
 
+    def check_canaries(self) -> None:
+        """Debugging aid for tests: see ``_NativeComm.check_canaries``."""
+        self.native.check_canaries()
+
     # -- launch -------------------------------------------------------------------------
     def _launch(self, args: CollArgs, async_op: bool, keep):
         from ..api import _CudaEventWork
@@ -422,6 +438,10 @@ class EmulatedWorld:
 
     def status(self) -> List[List[int]]:
         return [c.status() for c in self.comms]
+
+    def check_canaries(self) -> None:
+        for c in self.comms:
+            c.check_canaries()
 
     def reset(self):
         for c in self.comms:

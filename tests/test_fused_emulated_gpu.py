@@ -29,8 +29,12 @@ def make_world():
 
     yield make
     torch.cuda.synchronize()
-    for w in worlds:
-        w.close()
+    try:
+        for w in worlds:
+            w.check_canaries()  # no store landed outside the regions of any rank's block
+    finally:
+        for w in worlds:
+            w.close()
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])

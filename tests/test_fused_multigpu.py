@@ -45,6 +45,8 @@ def _worker(rank, world, n, bits, dtype, iters):
     comm = group._fused_comms[id(group.pg)]
     assert comm.launches == iters
     comm.check_status()
+    torch.distributed.barrier()  # every peer's pushes have landed
+    comm.check_canaries()
     if os.environ.get("BITSCOM_NVLS", "0") == "1" and os.environ.get("BITSCOM_REQUIRE_NVLS"):
         assert comm.multicast, "the NVLS path was asked for but not set up"
     # stream-ordered variant with fused post-scale
@@ -113,3 +115,5 @@ def _worker8(rank, world, n, bits, dtype, iters):
         torch.cuda.synchronize()
         assert torch.equal(x.cpu(), want), f"rank {rank} iter {it}"
     comm.check_status()
+    torch.distributed.barrier()  # every peer's pushes have landed
+    comm.check_canaries()
