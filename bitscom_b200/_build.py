@@ -35,11 +35,13 @@ LIBRARIES: Dict[str, dict] = {
                   "deps": ["codec.cuh", "symm.h"], "flags": []},
     "bcom_cpu": {"sources": ["cpu_codec.cc"], "deps": [], "flags": [], "host_only": True},
     "bcom_llama": {"sources": ["gemm_tcgen05.cu", "attention_tcgen05.cu", "elementwise.cu"],
-                   "deps": ["tc_common.cuh", "gemm_epilogue.cuh", "no_alloc.h"], "flags": []},
+                   "deps": ["tc_common.cuh", "gemm_epilogue.cuh", "gemm_schedule.cuh", "no_alloc.h"],
+                   "flags": []},
     # CTA-pair GEMM (opt-in variant): a library of its own, so that it can be left out of a
     # deployment without touching the default kernels
     "bcom_gemm2": {"sources": ["gemm_tcgen05_2cta.cu"],
-                   "deps": ["tc_common.cuh", "gemm_epilogue.cuh"], "flags": []},
+                   "deps": ["tc_common.cuh", "gemm_epilogue.cuh", "gemm_schedule.cuh"],
+                   "flags": []},
 }
 
 _lock = threading.Lock()

@@ -104,6 +104,8 @@ def gemm(args):
 
     _, tflops, tag = _peaks()
     G.set_variant(args.gemm_variant)
+    if args.split_tail:
+        G.set_split_tail(True)
     M, N, K = args.m, args.n, args.k
     copies = max(1, min(8, (256 << 20) // max(1, (M * K + N * K) * 2)))
     As = [(torch.randn(M, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
@@ -253,6 +255,8 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--wgrad", action="store_true")
     ap.add_argument("--gemm-variant", default="1cta", choices=["1cta", "2cta"])
+    ap.add_argument("--split-tail", action="store_true",
+                    help="one-CTA GEMM: half tiles for a sparsely filled last wave")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)

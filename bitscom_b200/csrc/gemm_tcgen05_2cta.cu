@@ -29,6 +29,7 @@
 #include <mutex>
 
 #include "gemm_epilogue.cuh"
+#include "gemm_schedule.cuh"
 #include "tc_common.cuh"
 
 namespace gemm2 {
@@ -171,13 +172,7 @@ __device__ __forceinline__ void fail(Shared* sh, unsigned int code) {
 }
 
 __device__ __forceinline__ void tile_coords(const Params& p, int t, int* tm, int* tn) {
-  const int per_group = GROUP_M * p.tiles_n;
-  const int group = t / per_group;
-  const int first_m = group * GROUP_M;
-  const int gsz = min(GROUP_M, p.tiles_m - first_m);
-  const int r = t - group * per_group;
-  *tm = first_m + r % gsz;
-  *tn = r / gsz;
+  gemm_sched::tile_coords<GROUP_M>(p.tiles_m, p.tiles_n, t, tm, tn);
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>

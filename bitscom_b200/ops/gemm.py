@@ -30,6 +30,9 @@ def _get():
             lib.bcom_gemm_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ll, ll, ll, ci, ci, ci, ci,
                                            ci, vp]
             lib.bcom_gemm_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
+            lib.bcom_gemm_set_split_tail.argtypes = [ci]
+            if os.environ.get("BITSCOM_GEMM_SPLIT_TAIL", "0") == "1":
+                lib.bcom_gemm_set_split_tail(1)
         _lib = lib if lib is not None else False
     return _lib or None
 
@@ -81,6 +84,17 @@ def set_variant(name: str) -> str:
         raise NativeError("the CTA-pair GEMM needs the bcom_gemm2 library and a GPU")
     _variant = name
     return old
+
+
+def set_split_tail(on: bool) -> bool:
+    """One-CTA kernel only: when the last wave of 128x256 tiles fills at most half of the grid
+    (512 tiles on 148 SMs: every 4096 x 4096 output), process its tiles as 128x128 halves on
+    twice as many CTAs.  Off by default (also ``BITSCOM_GEMM_SPLIT_TAIL=1``); returns the
+    previous setting."""
+    lib = _get()
+    if lib is None:
+        raise NativeError("tcgen05 GEMM needs the bcom_llama library and a GPU")
+    return bool(lib.bcom_gemm_set_split_tail(int(bool(on))))
 
 
 _STATUS = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "accumulator hand-off",
