@@ -136,10 +136,34 @@ class HealthMonitor:
         if gone:
             raise PeerLostError(gone)
 
-    def leave(self) -> None:
-        """Orderly exit between steps: peers learn of it at their next poll."""
+    def leave(self, wait_release_s: float = 0.0) -> bool:
+        """Orderly exit between steps: peers learn of it at their next poll.
+
+        With ``wait_release_s`` > 0 the call then waits (at most that long) until every peer
+        that is still alive has called ``release([this rank])``, i.e. has let go of whatever
+        it had mapped from this rank (symmetric-memory blocks of the fused collectives), so
+        that this process can free that memory and exit without pulling it away under a
+        peer.  Returns whether all of them did."""
         self.store.set(f"left/{self.rank}", "1")
+        ok = True
+        if wait_release_s > 0:
+            deadline = time.monotonic() + wait_release_s
+            waiting = [p for p in self.peers() if p not in self.lost()]
+            while waiting and time.monotonic() < deadline:
+                waiting = [p for p in waiting
+                           if not self.store.check([f"released/{p}/{self.rank}"])
+                           and p not in self.lost()]
+                if waiting:
+                    time.sleep(min(0.05, self.interval_s))
+            ok = not waiting
         self.close()
+        return ok
+
+    def release(self, ranks: Iterable[int]) -> None:
+        """Tell ranks that have left that this rank no longer holds anything of theirs (call it
+        after ``LowBitGroup.rebind`` has dropped the old communicators)."""
+        for r in ranks:
+            self.store.set(f"released/{self.rank}/{int(r)}", "1")
 
     def report_failure(self, exc: BaseException) -> None:
         self.store.set(f"failed/{self.rank}", f"{type(exc).__name__}: {exc}"[:500])

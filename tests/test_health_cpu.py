@@ -81,6 +81,27 @@ def test_leave_and_reported_failure_are_seen_at_the_next_poll_and_are_final():
     assert 2 in a.lost()
 
 
+def test_leaver_waits_until_its_peers_have_released_its_memory():
+    import threading
+
+    a, b, c = _monitors(3, interval_s=0.05, timeout_s=60.0)
+    for m in (a, b, c):
+        m.beat()
+    assert c.leave(wait_release_s=0.3) is False  # nobody released yet: gives up after 0.3 s
+    done = {}
+    t = threading.Thread(target=lambda: done.setdefault("ok", c.leave(wait_release_s=10.0)))
+    t.start()
+    time.sleep(0.1)
+    a.poll()
+    assert a.lost() == {2: "left"}
+    a.release([2])
+    time.sleep(0.2)
+    assert "ok" not in done  # rank 1 still holds a mapping
+    b.release([2])
+    t.join(timeout=10)
+    assert done.get("ok") is True
+
+
 def test_guard_does_not_publish_news_about_other_ranks():
     a, b = _monitors(2, interval_s=0.1, timeout_s=60.0)
     with pytest.raises(PeerLostError):
