@@ -1,6 +1,5 @@
 """tcgen05 causal attention (forward + backward) against fp32 SDPA on the same inputs."""
 
-import math
 import os
 
 import pytest

@@ -7,7 +7,6 @@ import tempfile
 import time
 from datetime import timedelta
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp

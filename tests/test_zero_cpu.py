@@ -4,7 +4,6 @@ result tracks a dense AdamW on the averaged gradient closely, and every rank end
 with bit-identical parameters."""
 
 import torch
-import torch.distributed as dist
 
 from bitscom_b200 import LowBitGroup
 from bitscom_b200.ops.nn import FlatAdamW
