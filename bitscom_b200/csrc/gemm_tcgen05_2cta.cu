@@ -250,6 +250,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
+      // Producer tail: the stage-release arrivals come from the leader's commits and land in
+      // this CTA's shared memory asynchronously; wait until the last fill of every stage has
+      // been released, so that none of them can arrive after this CTA has left.
+      for (int i = 0; i < STAGES && !sh->abort; ++i) {
+        if (!tc::mbar_wait(&sh->empty[stage], phase ^ 1u, kWaitBudgetNs)) {
+          fail(sh, kProducerTimeout);
+          break;
+        }
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
     }
   } else if (warp == 1) {
     if (lane == 0 && leader) {

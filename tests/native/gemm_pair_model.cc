@@ -106,6 +106,7 @@ struct Pair {
   std::atomic<int> acc_kb[2];                   // k-blocks accumulated into the buffer
   std::atomic<int> acc_readers[2];              // epilogue warps (of both CTAs) draining it
   std::atomic<int> tiles_stored{0};
+  std::atomic<int> tail_done[2];                // the CTA's producer has seen every release
   Work tensor, copy[2];
 
   Pair(int t, int k) : tiles(t), num_kb(k) {
@@ -121,6 +122,7 @@ struct Pair {
 #endif
       acc_tag[b] = -1; acc_kb[b] = 0; acc_readers[b] = 0;
     }
+    tail_done[0] = tail_done[1] = 0;
   }
 
   void producer(int c) {
@@ -140,6 +142,12 @@ struct Pair {
         nap(rng, 10);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+    // producer tail: every stage's last fill has been released before this CTA may leave
+    for (int i = 0; i < STAGES; ++i) {
+      if (!empty[c][stage].wait(phase ^ 1u)) die("producer tail: stage never released", id);
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    }
+    tail_done[c] = 1;
   }
 
   void forwarder() {
@@ -177,6 +185,7 @@ struct Pair {
           --stage_readers[s];
         });
         tensor.push([this, s] {  // commit -> empty[stage] in the CTAs of the mask
+          if (tail_done[0] || tail_done[1]) fail("a stage release arrived after its CTA left", s);
           empty[0][s].arrive();
 #if BUG != 3
           empty[1][s].arrive();
