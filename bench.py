@@ -114,7 +114,8 @@ def run_ours(args):
     seq = 2048 if args.model == "llama7b" else 256
     tcfg = TrainerConfig(pp_size=pp, micro_batches=args.micro_batches or 4 * pp,
                          micro_batch_size=args.micro_batch_size, seq_length=seq, bitwidth=4,
-                         error_feedback=True, dp_sync=args.dp_sync, local_size=args.local_size)
+                         error_feedback=True, dp_sync=args.dp_sync, local_size=args.local_size,
+                         defer_wgrad=args.defer_wgrad)
     trainer = LlamaTrainer(mcfg, tcfg)
     rank, dev = trainer.rank, trainer.device
 
@@ -185,7 +186,8 @@ def run_ours(args):
                    if args.model == "llama7b" else "tiny",
                    "global_batch": trainer.dp * c.micro_batches * c.micro_batch_size,
                    "seq_len": c.seq_length, "parallelism": f"dp{trainer.dp}xpp{trainer.pp}",
-                   "micro_batches": c.micro_batches, "schedule": "1F1B",
+                   "micro_batches": c.micro_batches,
+                   "schedule": "1F1B" + (" + deferred weight gradients" if c.defer_wgrad else ""),
                    "grad_sync": f"{c.dp_sync} 4-bit block 256 + error feedback"
                    if trainer.dp > 1 else "none (dp=1)",
                    "attention": mcfg.attention, "optimizer": "AdamW fp32 master",
@@ -239,6 +241,9 @@ def main():
     ap.add_argument("--attention", default=None, choices=[None, "tcgen05", "sdpa"])
     ap.add_argument("--dp-sync", default="pipeline_a", choices=["pipeline_a", "flat", "dense"])
     ap.add_argument("--local-size", type=int, default=1)
+    ap.add_argument("--defer-wgrad", action="store_true",
+                    help="pipeline stages send the input gradient before running the "
+                         "weight-gradient GEMMs (off by default)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
