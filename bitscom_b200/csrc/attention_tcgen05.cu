@@ -1321,60 +1321,16 @@ attention_dq_finish_kernel(float* __restrict__ dq_acc, __nv_bfloat16* __restrict
 // ---------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
-            cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  });
-  return fn;
-}
-
+// dense 2-D bf16 matrix [rows, cols]
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
                     int box_cols, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -1;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    fprintf(stderr, "bitscom_b200: attention tensor map failed (%d): ptr=%p rows=%lld cols=%lld\n",
-            (int)r, ptr, rows, cols);
-  return (int)r;
+  return tc::make_tensor_map_2d(map, ptr, 2, rows, cols, cols, box_cols, box_rows);
 }
 
 // fp32 [rows, cols] map with 128-byte swizzle: boxes of 32 floats (one swizzle row) x box_rows
 static int make_map_f32(CUtensorMap* map, const void* ptr, long long rows, long long cols,
                         int box_cols, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -1;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box,
-         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    fprintf(stderr, "bitscom_b200: fp32 tensor map failed (%d): ptr=%p rows=%lld cols=%lld\n",
-            (int)r, ptr, rows, cols);
-  return (int)r;
+  return tc::make_tensor_map_2d(map, ptr, 4, rows, cols, cols, box_cols, box_rows);
 }
 
 // ---- launchers, one instantiation per head dim ------------------------------------

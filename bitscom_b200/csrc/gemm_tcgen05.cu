@@ -255,45 +255,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
-            cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  });
-  return fn;
-}
-
 // 2-D bf16 row-major matrix [rows, cols] with leading dimension ld (elements).
-// Returns the driver's result code (0 = ok, -1 = entry point missing).
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
                     long long ld, int box_cols, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -1;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult r =
-      fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    fprintf(stderr,
-            "bitscom_b200: cuTensorMapEncodeTiled failed (%d): ptr=%p rows=%lld cols=%lld "
-            "ld=%lld box=%dx%d\n",
-            (int)r, ptr, rows, cols, ld, box_cols, box_rows);
-  return (int)r;
+  return tc::make_tensor_map_2d(map, ptr, 2, rows, cols, ld, box_cols, box_rows);
 }
 
 typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const Params);

@@ -17,6 +17,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdio>
+#include <mutex>
+
 namespace tc {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -232,7 +235,55 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
-// Host side.  Driver calls such as the tensor-map encoder need the device's primary context
+// Host side.  cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link
+// against libcuda); nullptr when the driver does not offer it.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+// Tensor map of a 2-D row-major matrix [rows, cols] of bf16 (elem_bytes 2) or fp32 (4)
+// elements with leading dimension `ld` (elements), 128-byte swizzle, boxes of
+// box_cols x box_rows elements, out-of-range elements read as zero.  Returns the driver's
+// result code (0 = ok, -1 = entry point missing) and reports a failure on stderr.
+inline int make_tensor_map_2d(CUtensorMap* map, const void* ptr, int elem_bytes, long long rows,
+                              long long cols, long long ld, int box_cols, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const bool half = elem_bytes == 2;
+  const CUresult r = fn(
+      map, half ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+      const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B,
+      half ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr,
+            "bitscom_b200: cuTensorMapEncodeTiled failed (%d): ptr=%p elem=%d rows=%lld "
+            "cols=%lld ld=%lld box=%dx%d\n",
+            (int)r, ptr, elem_bytes, rows, cols, ld, box_cols, box_rows);
+  return (int)r;
+}
+
+// Driver calls such as the tensor-map encoder need the device's primary context
 // bound to the calling thread, which an autograd worker thread may not have yet: a no-op
 // runtime call binds it.  Done once per (thread, device), so that later calls issue nothing
 // that stream capture would object to.
