@@ -124,11 +124,14 @@ class ErrorFeedbackState:
         self.carry_over = False  # set by LowBitGroup.rebind: the world size is about to change
 
     def ensure(self, plan: ShardPlan, device, stage2: bool):
-        if self.stage1 is None or self.stage1.numel() != plan.padded \
-                or self.stage1.device != torch.device(device):
+        if self.stage1 is not None and self.stage1.device != torch.device(device):
+            # residuals restored from a checkpoint that was loaded on another device
+            self.stage1 = self.stage1.to(device)
+            if self.stage2 is not None:
+                self.stage2 = self.stage2.to(device)
+        if self.stage1 is None or self.stage1.numel() != plan.padded:
             fresh = torch.zeros(plan.padded, dtype=torch.float32, device=device)
-            if self.carry_over and self.stage1 is not None \
-                    and self.stage1.device == fresh.device:
+            if self.carry_over and self.stage1 is not None:
                 # same bucket, new shard plan: the stage-1 residual is per element of this
                 # rank's own gradient and stays valid (the padding's residual is zero)
                 n = min(plan.numel, int(self.stage1.numel()))
