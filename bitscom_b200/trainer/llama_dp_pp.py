@@ -278,11 +278,16 @@ def _default_attention() -> str:
 
 def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
     step = 0
+    resumed = trainer.step_count  # > 0 after --resume: those batches have been trained on
     for epoch in range(args.epochs):
         loader.set_epoch(epoch)
         for batch in loader:
             if step >= args.max_steps:
                 break
+            if step < resumed:
+                loader.mark_consumed()
+                step += 1
+                continue
             if monitor is not None:
                 monitor.check()
             t0 = time.perf_counter()
@@ -294,6 +299,10 @@ def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
             if step % 50 == 0:
                 trainer.check_kernels()
             step += 1
+            if args.output_dir and args.save_every and step % args.save_every == 0:
+                from ..utils.checkpoint import save_checkpoint
+
+                save_checkpoint(args.output_dir, trainer.state_dict(), trainer.rank)
 
 
 def main(argv=None):
@@ -326,6 +335,11 @@ def main(argv=None):
     ap.add_argument("--lr", type=float, default=1e-4)
     ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
     ap.add_argument("--output_dir", default=None, help="write a checkpoint here at the end")
+    ap.add_argument("--save_every", type=int, default=0,
+                    help="also write the checkpoint every N steps (0 = only at the end)")
+    ap.add_argument("--resume", default=None,
+                    help="continue from the per-rank checkpoint files in this directory "
+                         "(same parallel layout as the run that wrote them)")
     ap.add_argument("--health_check", action="store_true",
                     help="heartbeats through the rendezvous store: a rank that leaves, fails "
                          "or falls silent is noticed on the host before the next step; the "
@@ -354,13 +368,23 @@ def main(argv=None):
                           vocab_size=mcfg.vocab_size, micro_batches=tcfg.micro_batches,
                           micro_batch_size=tcfg.micro_batch_size, dp_size=trainer.dp,
                           dp_rank=trainer.dp_rank, seed=tcfg.seed)
+    if args.resume:
+        from ..utils.checkpoint import checkpoint_path, load_checkpoint
+
+        if os.path.exists(checkpoint_path(args.resume, trainer.rank)):
+            trainer.load_state_dict(load_checkpoint(args.resume, trainer.rank))
     monitor = None
     if args.health_check and dist.is_initialized() and dist.get_world_size() > 1:
+        from ..launch import agent_store
         from ..utils.health import HealthMonitor
 
-        monitor = HealthMonitor(dist.distributed_c10d._get_default_store(), trainer.rank,
-                                dist.get_world_size(), interval_s=1.0,
-                                timeout_s=args.health_timeout)
+        # the launcher's store outlives every rank; without a launcher the rendezvous store
+        # (hosted by rank 0) has to do
+        store = agent_store() or dist.distributed_c10d._get_default_store()
+        generation = os.environ.get("BITSCOM_RESTART_COUNT", "0")
+        monitor = HealthMonitor(store, trainer.rank, dist.get_world_size(), interval_s=1.0,
+                                timeout_s=args.health_timeout,
+                                prefix=f"bitscom/health/gen{generation}")
     try:
         _train_loop(args, trainer, loader, tcfg, monitor)
     except Exception as exc:
