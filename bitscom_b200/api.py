@@ -406,6 +406,7 @@ class LowBitGroup:
         self._sr_calls = 0
         self._ef_states: Dict[Hashable, ErrorFeedbackState] = {}
         self._fused_comms: Dict[int, object] = {}
+        self.health = None  # optional utils.health.HealthMonitor, see attach_health
 
     # -- backend progress / scheduled handles (reference api.py:363-391) -----------
     def _backend_attr(self, name: str):
@@ -529,6 +530,18 @@ class LowBitGroup:
             st.load_state_dict(v)
             self._ef_states[k] = st
 
+    def attach_health(self, monitor) -> None:
+        """Consult ``monitor`` (a ``utils.health.HealthMonitor``) before every collective of
+        this group: a peer that has left, failed or fallen silent then raises
+        ``PeerLostError`` on the host, before anything is launched that would wait for it on
+        the device.  The check reads state the monitor's thread keeps current; it costs no
+        store round trip.  ``None`` detaches."""
+        self.health = monitor
+
+    def _precheck(self) -> None:
+        if self.health is not None:
+            self.health.check()
+
     def rebind(self, process_group=None) -> None:
         """Point this group at another process group, typically the one built among the
         survivors after a rank was lost (``utils.health.shrink_process_group``).  Stage-1
@@ -627,6 +640,7 @@ class LowBitGroup:
         ``simulate_quantization`` is set).  Returns ``None`` when synchronous, a
         Work-like object with ``wait()`` otherwise.
         """
+        self._precheck()
         if self._comm_debug_enabled():
             self._comm_debug(
                 f"all_reduce entry numel={int(tensor.numel())} dtype={tensor.dtype} "
@@ -693,6 +707,7 @@ class LowBitGroup:
         """Enqueue the whole all-reduce on ``stream`` and return an event-backed handle
         (``wait`` / ``block_current_stream`` / ``is_completed``); ``post_scale`` is
         applied to the result on the same stream (reference ``api.py:577-629``)."""
+        self._precheck()
         pg = group or self.pg
         lowbit = op == dist.ReduceOp.SUM and self._should_use_lowbit_path_for_group(op, pg)
 
@@ -883,6 +898,7 @@ class LowBitGroup:
         first half of the all-reduce (quantize, exchange, ordered fp32 sum)."""
         from .parallel.sharded import lowbit_reduce_scatter
 
+        self._precheck()
         return lowbit_reduce_scatter(self, output, input, ef_key=ef_key, async_op=async_op)
 
     def all_gather_lowbit(self, output: torch.Tensor, input: torch.Tensor, *,
@@ -891,6 +907,7 @@ class LowBitGroup:
         half of the all-reduce (quantize own shard, gather, dequantize)."""
         from .parallel.sharded import lowbit_all_gather
 
+        self._precheck()
         return lowbit_all_gather(self, output, input, ef_key=ef_key, async_op=async_op)
 
     # -- compress / decompress ----------------------------------------------------------

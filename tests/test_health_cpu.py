@@ -102,6 +102,41 @@ def test_leaver_waits_until_its_peers_have_released_its_memory():
     assert done.get("ok") is True
 
 
+def test_attached_monitor_stops_a_collective_before_it_is_launched(monkeypatch):
+    """``LowBitGroup.attach_health``: with a lost peer every collective entry point raises on
+    the host and nothing reaches the process group."""
+    import bitscom_b200.api as api
+
+    calls = []
+    monkeypatch.setattr(api.dist, "get_world_size", lambda group=None: 2)
+    monkeypatch.setattr(api.dist, "get_rank", lambda group=None: 0)
+    class Done:
+        def wait(self):
+            return True
+
+    monkeypatch.setattr(api.dist, "all_reduce",
+                        lambda *a, **k: (calls.append("all_reduce"), Done())[1])
+    group = api.LowBitGroup(bitwidth=8, process_group=object())
+    a, b = _monitors(2, interval_s=0.1, timeout_s=60.0)
+    a.beat(), b.beat()
+    a.poll()
+    group.attach_health(a)
+    group.all_reduce(torch.ones(8))          # healthy: goes through (8 bit = dense path)
+    assert calls == ["all_reduce"]
+    b.leave()
+    a.poll()
+    for call in (lambda: group.all_reduce(torch.ones(8)),
+                 lambda: group.all_reduce_stream(torch.ones(8), stream=None),
+                 lambda: group.reduce_scatter_lowbit(torch.ones(4), torch.ones(8)),
+                 lambda: group.all_gather_lowbit(torch.ones(8), torch.ones(4))):
+        with pytest.raises(PeerLostError):
+            call()
+    assert calls == ["all_reduce"]
+    group.attach_health(None)
+    group.all_reduce(torch.ones(8))
+    assert calls == ["all_reduce", "all_reduce"]
+
+
 def test_guard_does_not_publish_news_about_other_ranks():
     a, b = _monitors(2, interval_s=0.1, timeout_s=60.0)
     with pytest.raises(PeerLostError):
