@@ -385,6 +385,8 @@ def main(argv=None):
         monitor = HealthMonitor(store, trainer.rank, dist.get_world_size(), interval_s=1.0,
                                 timeout_s=args.health_timeout,
                                 prefix=f"bitscom/health/gen{generation}")
+        if getattr(trainer, "lowbit", None) is not None:
+            trainer.lowbit.attach_health(monitor)  # also before every gradient bucket
     try:
         _train_loop(args, trainer, loader, tcfg, monitor)
     except Exception as exc:

@@ -61,6 +61,7 @@ def main(argv=None) -> int:
                                 torch.nn.Linear(64, 1)).to(dev)
     params = list(model.parameters())
     group = bitscom.LowBitGroup(bitwidth=4, error_feedback=True)
+    group.attach_health(monitor)  # checked again right before every collective
     teacher = torch.randn(32, 1, generator=torch.Generator().manual_seed(7)).to(dev)
 
     # -- resume ------------------------------------------------------------------------------
