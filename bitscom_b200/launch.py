@@ -164,6 +164,11 @@ def main(argv=None) -> int:
     command = args.command[1:] if args.command[:1] == ["--"] else args.command
     if not command:
         ap.error("no command given")
+
+    def on_term(signum, frame):  # unwind through run()'s finally, which stops the children
+        raise SystemExit(128 + signum)
+
+    signal.signal(signal.SIGTERM, on_term)
     return run(command, args.nproc, min_nproc=args.min_nproc, max_restarts=args.max_restarts,
                shrink=args.shrink, grace_s=args.grace)
 
