@@ -17,6 +17,8 @@ training on top of both is new here.
 
 from __future__ import annotations
 
+from typing import List
+
 import torch
 
 from ..ops import nn as K
@@ -65,3 +67,39 @@ class ShardedAdamW:
     def load_state_dict(self, sd):
         self.opt.load_state_dict(sd["opt"])
         self.master_shard.copy_(sd["master_shard"])
+
+
+def reshard_state(states: List[dict], new_world: int, numel: int) -> List[dict]:
+    """Re-partition the optimizer state of a sharded run for another world size.
+
+    ``states`` are the ``ShardedAdamW.state_dict()`` of every rank of the old run, in rank
+    order (for example read back from the per-rank checkpoint files after a restart with
+    fewer ranks); ``numel`` is the unpadded number of parameters.  Returns one state dict per
+    rank of the new run.  The flat buffer of a run is padded to ``world * 256`` elements, so
+    the padded lengths of the two runs may differ: padding holds zero parameters with zero
+    moments and is cut or added at the end."""
+    if not states:
+        raise ValueError("no states given")
+    steps = {int(s["opt"]["step"]) for s in states}
+    if len(steps) != 1:
+        raise ValueError(f"the ranks' states are from different steps: {sorted(steps)}")
+    unit = new_world * 256
+    padded = -(-int(numel) // unit) * unit
+    step = steps.pop()
+    out: List[dict] = [{"opt": {"step": step}} for _ in range(new_world)]
+
+    def repartition(pick):
+        full = torch.cat([pick(s).reshape(-1).to(torch.float32).cpu() for s in states])
+        if full.numel() < numel:
+            raise ValueError("the states hold fewer elements than numel")
+        full = full[:numel]
+        if padded > numel:
+            full = torch.cat([full, torch.zeros(padded - numel)])
+        return list(full.view(new_world, padded // new_world).unbind(0))
+
+    for name in ("exp_avg", "exp_avg_sq", "master"):
+        for r, piece in enumerate(repartition(lambda s, name=name: s["opt"][name])):
+            out[r]["opt"][name] = piece.clone()
+    for r in range(new_world):
+        out[r]["master_shard"] = out[r]["opt"]["master"].clone()
+    return out

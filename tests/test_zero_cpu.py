@@ -86,3 +86,54 @@ def test_flat_sgd_host_path_matches_torch():
         ref.grad = g.clone()
         tref.step()
         assert torch.allclose(param, ref.detach(), atol=1e-6) and grad.eq(0).all()
+
+
+def test_reshard_state_moves_optimizer_state_between_world_sizes():
+    """State of a 4-rank run re-partitioned for 3 ranks (padding changes: 4 x 256 vs 3 x 256)
+    and for 1 rank; the single-rank optimizer then steps exactly like a dense AdamW that was
+    given the same full state."""
+    from bitscom_b200.parallel.zero import reshard_state
+
+    numel = 1500
+    g = torch.Generator().manual_seed(3)
+    old_world, old_padded = 4, 2048
+    full = {k: torch.zeros(old_padded) for k in ("master", "exp_avg", "exp_avg_sq")}
+    full["master"][:numel] = torch.randn(numel, generator=g)
+    full["exp_avg"][:numel] = torch.randn(numel, generator=g) * 1e-2
+    full["exp_avg_sq"][:numel] = torch.rand(numel, generator=g) * 1e-3
+    shard = old_padded // old_world
+    states = [{"opt": dict({k: v[r * shard:(r + 1) * shard].clone() for k, v in full.items()},
+                           step=7),
+               "master_shard": full["master"][r * shard:(r + 1) * shard].clone()}
+              for r in range(old_world)]
+
+    three = reshard_state(states, 3, numel)
+    assert [s["opt"]["master"].numel() for s in three] == [512, 512, 512]   # 1536 = 2 * 768
+    for k in ("master", "exp_avg", "exp_avg_sq"):
+        joined = torch.cat([s["opt"][k] for s in three])
+        assert torch.equal(joined[:numel], full[k][:numel]) and joined[numel:].eq(0).all()
+    assert all(s["opt"]["step"] == 7 for s in three)
+
+    one = reshard_state(states, 1, numel)[0]
+    flat = FlatParameters({"w": (numel,)}, "cpu", pad_to=256)
+    class Solo:  # world 1: the group is never asked to talk
+        world_size, rank = 1, 0
+
+    opt = ShardedAdamW(flat, Solo(), lr=1e-2)
+    opt.load_state_dict(one)
+    ref_master, ref_grad = full["master"][:1536].clone(), torch.zeros(1536)
+    ref = FlatAdamW(ref_master, ref_grad, None, lr=1e-2)
+    ref.load_state_dict({"step": 7, "exp_avg": full["exp_avg"][:1536],
+                         "exp_avg_sq": full["exp_avg_sq"][:1536], "master": ref_master.clone()})
+    grad = torch.randn(1536, generator=g) * 1e-2
+    flat.grads.copy_(grad)
+    ref_grad.copy_(grad)
+    opt.step()
+    ref.step()
+    assert torch.equal(opt.master_shard, ref_master)
+
+    import pytest
+
+    states[2]["opt"]["step"] = 8
+    with pytest.raises(ValueError):
+        reshard_state(states, 2, numel)
