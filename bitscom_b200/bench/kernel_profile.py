@@ -173,6 +173,9 @@ def attention(args):
 def elementwise(args):
     from bitscom_b200.ops import nn as K
 
+    if args.rmsnorm_bwd_rows != 1:
+        K.set_rmsnorm_bwd_rows(args.rmsnorm_bwd_rows)
+
     hbm, _, tag = _peaks()
     T, H, F, V = args.tokens, 4096, 11008, 32000
     rows = []
@@ -255,6 +258,7 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--wgrad", action="store_true")
     ap.add_argument("--gemm-variant", default="1cta", choices=["1cta", "2cta"])
+    ap.add_argument("--rmsnorm-bwd-rows", type=int, default=1, choices=[1, 4])
     ap.add_argument("--split-tail", action="store_true",
                     help="one-CTA GEMM: half tiles for a sparsely filled last wave")
     ap.add_argument("--iters", type=int, default=5)

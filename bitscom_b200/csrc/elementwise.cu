@@ -189,6 +189,87 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   }
 }
 
+// Variant of the kernel above for H <= 512 * 8 (one 8-element pack per thread): ROWS rows per
+// CTA barrier instead of one.  The thread-to-column mapping (and with it the weight gradient
+// in registers) stays; what changes is that the loads of ROWS rows are in flight at once and
+// that the ROWS dot products share one barrier.  Off by default (bcom_rmsnorm_bwd_set_rows).
+template <int ROWS>
+__global__ void __launch_bounds__(512)
+rmsnorm_bwd_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                        const bf16* __restrict__ w, const float* __restrict__ rstd,
+                        bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
+  __shared__ float partial[2][ROWS][16];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int c = threadIdx.x * 8;
+  const bool live = c < H;
+  float acc[8], fw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = fw[i] = 0.0f;
+  if (live) load8(w + c, fw);
+  Bf8 cx[ROWS], cg[ROWS], nx[ROWS], ng[ROWS];
+  auto fetch = [&](int row0, Bf8 (&bx)[ROWS], Bf8 (&bg)[ROWS]) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int row = row0 + r;
+      if (live && row < rows) {
+        bx[r] = *reinterpret_cast<const Bf8*>(x + (size_t)row * H + c);
+        bg[r] = *reinterpret_cast<const Bf8*>(dy + (size_t)row * H + c);
+      }
+    }
+  };
+  // CTA b owns the row groups b, b + gridDim.x, ... of ROWS consecutive rows each
+  int row0 = blockIdx.x * ROWS;
+  if (row0 < rows) fetch(row0, cx, cg);
+  int parity = 0;
+  for (; row0 < rows; row0 += gridDim.x * ROWS, parity ^= 1) {
+    const int next0 = row0 + gridDim.x * ROWS;
+    if (next0 < rows) fetch(next0, nx, ng);
+    float rs[ROWS], dot[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const bool ok = row0 + r < rows;
+      rs[r] = ok ? rstd[row0 + r] : 0.0f;
+      dot[r] = 0.0f;
+      if (live && ok) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float fx = __bfloat162float(cx[r].v[i]), fg = __bfloat162float(cg[r].v[i]);
+          dot[r] += fg * fw[i] * fx;
+          acc[i] += fg * fx * rs[r];
+        }
+      }
+      dot[r] = warp_sum(dot[r]);
+      if (lane == 0) partial[parity][r][warp] = dot[r];
+    }
+    __syncthreads();  // the other buffer is free again: its readers passed the previous barrier
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      if (row0 + r < rows) {
+        float total = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) total += i < nwarps ? partial[parity][r][i] : 0.0f;
+        const float coef = total * rs[r] * rs[r] * rs[r] / (float)H;
+        if (live) {
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float fx = __bfloat162float(cx[r].v[i]), fg = __bfloat162float(cg[r].v[i]);
+            o[i] = fg * fw[i] * rs[r] - fx * coef;
+          }
+          store8(dx + (size_t)(row0 + r) * H + c, o);
+        }
+      }
+      cx[r] = nx[r];
+      cg[r] = ng[r];
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) atomicAdd(dw + c + i, acc[i]);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // LayerNorm (GPT-2): y = (x - mean) * rstd * w + b.  One warp per row, the row held in
 // registers between the statistics and the output (one read of x).  H <= 32 * 8 * MAX_ITERS
@@ -633,6 +714,15 @@ int bcom_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int rows
   return (int)cudaGetLastError();
 }
 
+// 1: one row per CTA barrier (default); 4: four rows per barrier for H <= 4096 (off by default)
+static int g_rmsnorm_bwd_rows = 1;
+
+int bcom_rmsnorm_bwd_set_rows(int rows_per_barrier) {
+  const int old = g_rmsnorm_bwd_rows;
+  if (rows_per_barrier == 1 || rows_per_barrier == 4) g_rmsnorm_bwd_rows = rows_per_barrier;
+  return old;
+}
+
 int bcom_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
                      void* dw_fp32, int rows, int H, void* stream) {
   if (rows <= 0) return 0;
@@ -641,6 +731,14 @@ int bcom_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* r
   const int grid = rows < 148 * 2 ? rows : 148 * 2;
   const int iters = (H / 8 + 511) / 512;
   cudaStream_t st = (cudaStream_t)stream;
+  if (g_rmsnorm_bwd_rows == 4 && iters <= 1) {
+    const int groups = (rows + 3) / 4;
+    const int g4 = groups < 148 ? groups : 148;  // 128 registers x 512 threads: one CTA per SM
+    rmsnorm_bwd_rows_kernel<4><<<g4, 512, 0, st>>>((const bf16*)dy, (const bf16*)x,
+                                                   (const bf16*)w, (const float*)rstd, (bf16*)dx,
+                                                   (float*)dw_fp32, rows, H);
+    return (int)cudaGetLastError();
+  }
   if (iters <= 1)
     rmsnorm_bwd_kernel<1><<<grid, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
                                                 (const float*)rstd, (bf16*)dx, (float*)dw_fp32,

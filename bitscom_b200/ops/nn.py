@@ -5,6 +5,7 @@ AdamW / SGD."""
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -23,6 +24,9 @@ def _get():
             vp, ll, ci, cf = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
             lib.bcom_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, ci, ci, cf, vp]
             lib.bcom_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, vp]
+            lib.bcom_rmsnorm_bwd_set_rows.argtypes = [ci]
+            if os.environ.get("BITSCOM_RMSNORM_BWD_ROWS", "1") == "4":
+                lib.bcom_rmsnorm_bwd_set_rows(4)
             lib.bcom_rope.argtypes = [vp, vp, vp, ll, ci, ci, ll, ci, ci, vp]
             lib.bcom_layernorm_fwd.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, cf, vp]
             lib.bcom_layernorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, vp]
@@ -81,6 +85,14 @@ class RMSNormFunction(torch.autograd.Function):
         check(lib.bcom_rmsnorm_bwd(ptr(dy2), ptr(x2), ptr(weight), ptr(rstd), ptr(dx), ptr(dw),
                                    x2.shape[0], H, stream_ptr(dy.device)), "rmsnorm_bwd")
         return dx.view(ctx.shape), (None if main is not None else dw.to(weight.dtype)), None
+
+
+def set_rmsnorm_bwd_rows(rows_per_barrier: int) -> int:
+    """RMSNorm backward: rows processed per CTA barrier, 1 (default) or 4 (more loads in flight;
+    hidden sizes up to 4096; also ``BITSCOM_RMSNORM_BWD_ROWS=4``).  Returns the previous value."""
+    if rows_per_barrier not in (1, 4):
+        raise ValueError("rows_per_barrier must be 1 or 4")
+    return int(_need().bcom_rmsnorm_bwd_set_rows(int(rows_per_barrier)))
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:

@@ -2,6 +2,8 @@
 AdamW, SGD) against
 plain PyTorch fp32 references of the same ops."""
 
+import os
+
 import pytest
 import torch
 
@@ -40,6 +42,31 @@ def test_rmsnorm_fwd_bwd(rows, H):
     K.rmsnorm(x.detach(), w2, 1e-5).backward(dy)
     assert w2.grad is None
     assert torch.allclose(w2.main_grad, wr.grad, rtol=2e-2, atol=0.01 * rows ** 0.5 + 0.02)
+
+
+@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
+                    reason="kernel variants that have not been run on a GPU yet; "
+                           "set BITSCOM_EXPERIMENTAL=1 to try them")
+@pytest.mark.parametrize("rows,H", [(64, 256), (1000, 4096), (37, 1024), (5, 8), (4097, 4096),
+                                    (3, 4096), (8192, 4096)])
+def test_experimental_rmsnorm_bwd_four_rows_per_barrier(rows, H):
+    """The variant that handles four rows per CTA barrier gives the same gradients as the
+    default kernel (same formula per element; dw differs by summation order)."""
+    x, dy = _bf(rows, H, seed=1), _bf(rows, H, seed=3)
+    w = (1 + 0.1 * _bf(H, seed=2).float()).to(torch.bfloat16)
+    grads = {}
+    for variant in (1, 4):
+        before = K.set_rmsnorm_bwd_rows(variant)
+        try:
+            xv, wv = x.clone().requires_grad_(), w.clone().requires_grad_()
+            K.rmsnorm(xv, wv, 1e-5).backward(dy)
+            torch.cuda.synchronize()
+            grads[variant] = (xv.grad.clone(), wv.grad.float().clone())
+        finally:
+            K.set_rmsnorm_bwd_rows(before)
+    # the compiler may contract multiply-adds differently in the two kernels: one bf16 ulp
+    assert torch.allclose(grads[1][0].float(), grads[4][0].float(), rtol=1e-2, atol=1e-3)
+    assert torch.allclose(grads[1][1], grads[4][1], rtol=2e-2, atol=0.01 * rows ** 0.5 + 0.02)
 
 
 def _rope_ref(t, cos, sin):
