@@ -1,43 +1,38 @@
 """bitscom_b200: Blackwell-native low-bit collectives for PyTorch.
 
-Drop-in for the public API of Squirrel7ang/bitscom (``python/bitscom/__init__.py:19-51``):
+The package keeps the public names of Squirrel7ang/bitscom (``python/bitscom/__init__.py:19-51``)
+so that ``import bitscom_b200 as bitscom`` is enough to switch:
 
-    import bitscom_b200 as bitscom
-    bitscom.init(bitwidth=4)
+    bitscom.init(bitwidth=4)                                   # registers the backend
     torch.distributed.init_process_group(backend="lowbit")
-    group = bitscom.LowBitGroup(bitwidth=4)
-    group.all_reduce(tensor)
+    bitscom.LowBitGroup(bitwidth=4).all_reduce(tensor)
+
+What goes beyond the reference (error feedback on every path, seeded stochastic rounding, the
+fused kernels, sharded collectives, failure handling) hangs off ``LowBitGroup`` and the
+``parallel`` / ``utils`` subpackages.
 """
 
 from typing import Optional
 
-from .quantization import DEFAULT_BLOCK_SIZE, SUPPORTED_BITWIDTHS
-from .lowbit_backend import is_extension_available, register_lowbit_backend
+from . import quantization as _q
 from .api import LowBitGroup
-
-__all__ = [
-    "register_lowbit_backend",
-    "is_extension_available",
-    "LowBitGroup",
-    "SUPPORTED_BITWIDTHS",
-    "init",
-]
+from .lowbit_backend import is_extension_available, register_lowbit_backend
 
 __version__ = "0.1.0"
+SUPPORTED_BITWIDTHS = _q.SUPPORTED_BITWIDTHS
+DEFAULT_BLOCK_SIZE = _q.DEFAULT_BLOCK_SIZE
+
+__all__ = ("init", "register_lowbit_backend", "is_extension_available", "LowBitGroup",
+           "SUPPORTED_BITWIDTHS")
 
 
-def init(
-    bitwidth: int = 4,
-    error_feedback: bool = False,
-    error_feedback_mode: Optional[str] = None,
-    block_size: int = DEFAULT_BLOCK_SIZE,
-    stage2_error_feedback: Optional[bool] = None,
-):
-    """Register the ``lowbit`` backend; call before ``init_process_group``."""
-    register_lowbit_backend(
-        bitwidth=bitwidth,
-        error_feedback=error_feedback,
-        error_feedback_mode=error_feedback_mode,
-        block_size=block_size,
-        stage2_error_feedback=stage2_error_feedback,
-    )
+def init(bitwidth: int = 4, error_feedback: bool = False,
+         error_feedback_mode: Optional[str] = None, block_size: int = DEFAULT_BLOCK_SIZE,
+         stage2_error_feedback: Optional[bool] = None) -> None:
+    """Register the ``lowbit`` torch.distributed backend with these codec options (one option
+    set per process; a second call with other options raises).  Call it before
+    ``torch.distributed.init_process_group(backend="lowbit")``."""
+    options = dict(bitwidth=bitwidth, error_feedback=error_feedback,
+                   error_feedback_mode=error_feedback_mode, block_size=block_size,
+                   stage2_error_feedback=stage2_error_feedback)
+    register_lowbit_backend(**options)
