@@ -114,6 +114,24 @@ def check_status(clear: bool = True) -> None:
                           f"(cta {out[1]}, thread {out[2]})")
 
 
+def _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
+    """The kernel's contract for tensors that live on the CPU (fp32 accumulation, result
+    rounded once): CPU ranks run the trainers' plumbing with it."""
+    A = a.float().t() if a_mn_major else a.float()
+    B = b.float() if b_mn_major else b.float().t()
+    if A.shape[1] != B.shape[0]:
+        raise ValueError(f"reduction dimensions differ: {A.shape[1]} vs {B.shape[0]}")
+    c = A @ B
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs an output tensor")
+        return c.to(out_dtype)
+    if out.shape != c.shape:
+        raise ValueError("bad output tensor")
+    out.copy_(out.float() + c if accumulate else c)
+    return out
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
          b_mn_major: bool = False, out: Optional[torch.Tensor] = None,
          out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
@@ -124,6 +142,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
     ``b``: ``[N, K]`` (K-major) or, with ``b_mn_major``, stored ``[K, N]``.
     Operands are 2-D with unit stride in the last dimension; row strides are free.
     """
+    if not a.is_cuda:
+        return _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate)
     lib = _get()
     if lib is None:
         raise NativeError("tcgen05 GEMM needs the bcom_llama library and a GPU")

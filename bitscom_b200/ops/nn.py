@@ -287,12 +287,26 @@ class CrossEntropyFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits, targets, ignore_index, loss_scale):
-        lib = _need()
         V = logits.shape[-1]
         l2 = logits.view(-1, V)
         t = targets.reshape(-1).to(torch.int64).contiguous()
         valid = (t != ignore_index).sum().clamp_(min=1).to(torch.float32)
         scale = (loss_scale / valid).reshape(1).contiguous()
+        if not logits.is_cuda:  # the kernel's arithmetic in torch ops, for CPU ranks
+            keep = t != ignore_index
+            z = l2.float()
+            lse = torch.logsumexp(z, dim=-1)
+            safe = t.clamp(min=0, max=V - 1)
+            per_row = torch.where(keep, lse - z.gather(1, safe[:, None])[:, 0],
+                                  torch.zeros_like(lse))
+            d = torch.softmax(z, dim=-1)
+            d[torch.arange(d.shape[0]), safe] -= 1.0
+            d.mul_(keep[:, None].to(d.dtype) * scale[0])
+            l2.copy_(d)
+            ctx.save_for_backward(logits)
+            ctx.mark_non_differentiable(valid)
+            return per_row.sum() * scale[0], valid
+        lib = _need()
         per_row = torch.empty(l2.shape[0], dtype=torch.float32, device=logits.device)
         check(lib.bcom_cross_entropy(ptr(l2), ptr(t), ptr(per_row), ptr(scale), l2.shape[0], V,
                                      int(ignore_index), stream_ptr(logits.device)),
@@ -318,9 +332,12 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int
 class EmbeddingFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ids, table):
-        lib = _need()
         flat = ids.reshape(-1).to(torch.int64).contiguous()
         H = table.shape[1]
+        if not table.is_cuda:  # CPU ranks
+            ctx.save_for_backward(flat, table)
+            return table.detach().index_select(0, flat).view(*ids.shape, H)
+        lib = _need()
         out = torch.empty(flat.numel(), H, dtype=table.dtype, device=table.device)
         check(lib.bcom_embedding_fwd(ptr(flat), ptr(table), ptr(out), flat.numel(), H,
                                      table.shape[0], stream_ptr(table.device)), "embedding_fwd")
@@ -329,7 +346,6 @@ class EmbeddingFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        lib = _need()
         flat, table = ctx.saved_tensors
         H = table.shape[1]
         d = dout.reshape(-1, H)
@@ -338,6 +354,10 @@ class EmbeddingFunction(torch.autograd.Function):
         main = getattr(table, "main_grad", None)
         dt = main if main is not None else torch.zeros(table.shape, dtype=torch.float32,
                                                         device=table.device)
+        if not table.is_cuda:  # CPU ranks
+            dt.index_add_(0, flat, d.float())
+            return None, (None if main is not None else dt.to(table.dtype))
+        lib = _need()
         check(lib.bcom_embedding_bwd(ptr(flat), ptr(d), ptr(dt), flat.numel(), H, table.shape[0],
                                      stream_ptr(table.device)), "embedding_bwd")
         return None, (None if main is not None else dt.to(table.dtype))

@@ -16,6 +16,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import time
 
 import torch
 import torch.distributed as dist
@@ -61,15 +62,27 @@ def main(argv=None):
                     help="LayerNorm, GELU and attention from torch instead of this library's "
                          "kernels (A/B baseline)")
     ap.add_argument("--out", default="bench_outputs/gpt2_sharded.jsonl")
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu",
+                    choices=["cuda", "cpu"],
+                    help="'cpu' runs the same program on CPU ranks over gloo with torch ops "
+                         "(plumbing check of the sharded optimizer and its collectives)")
     args = ap.parse_args(argv)
+    cuda = args.device == "cuda"
+    if not cuda:
+        args.torch_ops, args.cuda_graph = True, False
 
     rank = int(os.environ.get("RANK", 0))
     local = int(os.environ.get("LOCAL_RANK", rank))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    if cuda:
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev = torch.device("cpu")
+        if world > 1:
+            dist.init_process_group("gloo")
     cfg = GPT2Config.medium() if args.model == "medium" else GPT2Config.tiny()
     model = GPT2(cfg, dev, seed=0, pad_to=256 * max(world, 1), fused_ops=not args.torch_ops)
     flat = model.flat
@@ -100,32 +113,41 @@ def main(argv=None):
 
     def step():
         ids = torch.randint(0, cfg.vocab_size, (args.micro_batch, cfg.seq), generator=g)
-        ids = ids.pin_memory().to(dev, non_blocking=True)
+        if cuda:
+            ids = ids.pin_memory().to(dev, non_blocking=True)
         loss = compute(ids)
         opt.step()
         return loss.clone() if args.cuda_graph else loss
 
     for _ in range(args.warmup):
         step()
-    torch.cuda.synchronize()
+    if cuda:
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
+    if cuda:
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+    t0 = time.perf_counter()
     first = last = None
     for i in range(args.steps):
         last = step()
         if i == 0:
             first = last
-    e.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([s.elapsed_time(e) / args.steps], device=dev)
+    if cuda:
+        e.record()
+        torch.cuda.synchronize()
+        elapsed_ms = s.elapsed_time(e)
+    else:
+        elapsed_ms = (time.perf_counter() - t0) * 1e3
+    ms = torch.tensor([elapsed_ms / args.steps], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
         tokens = world * args.micro_batch * cfg.seq
         row = {"workload": "gpt2_medium_sharded" if args.model == "medium" else "gpt2_tiny",
-               "mode": args.mode, "world": world, "fused_ops": not args.torch_ops,
+               "mode": args.mode, "world": world, "device": args.device,
+               "fused_ops": not args.torch_ops,
                "cuda_graph": bool(args.cuda_graph), "grad_bits": args.grad_bits,
                "param_bits": args.param_bits, "ms_per_step": float(ms.item()),
                "tokens_per_s": tokens / float(ms.item()) * 1e3,
