@@ -58,11 +58,18 @@ def _need():
 class RMSNormFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, eps):
-        lib = _need()
         H = x.shape[-1]
         x2 = x.reshape(-1, H)
         if not x2.is_contiguous():
             x2 = x2.contiguous()
+        if not x.is_cuda:  # the kernel's arithmetic in torch ops, for CPU ranks
+            xf = x2.float()
+            rstd = torch.rsqrt(xf.pow(2).mean(-1) + eps)
+            y = (xf * rstd[:, None] * weight.float()).to(x.dtype)
+            ctx.save_for_backward(x2, weight, rstd)
+            ctx.shape = x.shape
+            return y.view(x.shape)
+        lib = _need()
         y = torch.empty_like(x2)
         rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
         check(lib.bcom_rmsnorm_fwd(ptr(x2), ptr(weight), ptr(y), ptr(rstd), x2.shape[0], H,
@@ -73,15 +80,22 @@ class RMSNormFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        lib = _need()
         x2, weight, rstd = ctx.saved_tensors
         H = x2.shape[1]
         dy2 = dy.reshape(-1, H)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
-        dx = torch.empty_like(x2)
         main = getattr(weight, "main_grad", None)
         dw = main if main is not None else torch.zeros(H, dtype=torch.float32, device=dy.device)
+        if not dy.is_cuda:  # CPU ranks
+            xf, gf, rs = x2.float(), dy2.float(), rstd[:, None]
+            gw = gf * weight.float()
+            coef = (gw * xf).sum(-1, keepdim=True) * rs.pow(3) / H
+            dxh = (gw * rs - xf * coef).to(x2.dtype)
+            dw.add_((gf * xf * rs).sum(0))
+            return dxh.view(ctx.shape), (None if main is not None else dw.to(weight.dtype)), None
+        lib = _need()
+        dx = torch.empty_like(x2)
         check(lib.bcom_rmsnorm_bwd(ptr(dy2), ptr(x2), ptr(weight), ptr(rstd), ptr(dx), ptr(dw),
                                    x2.shape[0], H, stream_ptr(dy.device)), "rmsnorm_bwd")
         return dx.view(ctx.shape), (None if main is not None else dw.to(weight.dtype)), None
@@ -110,6 +124,15 @@ def rope_tables(seq: int, head_dim: int, theta: float = 10000.0, device="cuda"
 
 def _rope_inplace(x2: torch.Tensor, col0: int, heads: int, head_dim: int, cos, sin, seq: int,
                   backward: bool):
+    if not x2.is_cuda:  # CPU ranks: rotate-half on every head of this third, in place
+        half = head_dim // 2
+        t = x2[:, col0:col0 + heads * head_dim].reshape(-1, seq, heads, head_dim).float()
+        c = cos[:seq, None, :].float()
+        s = sin[:seq, None, :].float() * (-1.0 if backward else 1.0)
+        a, b = t[..., :half], t[..., half:]
+        rot = torch.cat([a * c - b * s, b * c + a * s], -1)
+        x2[:, col0:col0 + heads * head_dim] = rot.reshape(x2.shape[0], -1).to(x2.dtype)
+        return
     lib = _need()
     view = x2[:, col0:]
     check(lib.bcom_rope(ptr(view), ptr(cos), ptr(sin), x2.shape[0], heads, head_dim,
@@ -249,11 +272,16 @@ def bias_gelu(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
 class SwiGLUFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gate_up):
-        lib = _need()
         F = gate_up.shape[-1] // 2
         gu = gate_up.reshape(-1, 2 * F)
         if not gu.is_contiguous():
             gu = gu.contiguous()
+        if not gate_up.is_cuda:  # CPU ranks
+            g, u = gu[:, :F].float(), gu[:, F:].float()
+            ctx.save_for_backward(gu)
+            ctx.shape = gate_up.shape
+            return (g * torch.sigmoid(g) * u).to(gu.dtype).view(*gate_up.shape[:-1], F)
+        lib = _need()
         h = torch.empty(gu.shape[0], F, dtype=gu.dtype, device=gu.device)
         check(lib.bcom_swiglu_fwd(ptr(gu), ptr(h), gu.shape[0], F, stream_ptr(gu.device)),
               "swiglu_fwd")
@@ -263,12 +291,18 @@ class SwiGLUFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dh):
-        lib = _need()
         (gu,) = ctx.saved_tensors
         F = gu.shape[1] // 2
         d = dh.reshape(-1, F)
         if not d.is_contiguous():
             d = d.contiguous()
+        if not dh.is_cuda:  # CPU ranks
+            g, u, df = gu[:, :F].float(), gu[:, F:].float(), d.float()
+            sg = torch.sigmoid(g)
+            silu = g * sg
+            dgu = torch.cat([df * u * (sg + silu * (1.0 - sg)), df * silu], 1).to(gu.dtype)
+            return dgu.view(ctx.shape)
+        lib = _need()
         dgu = torch.empty_like(gu)
         check(lib.bcom_swiglu_bwd(ptr(gu), ptr(d), ptr(dgu), gu.shape[0], F,
                                   stream_ptr(gu.device)), "swiglu_bwd")

@@ -52,33 +52,41 @@ class TrainerConfig:
     overlap: bool = True
     simulate_quantization: bool = False   # reference flag: quantize round trip before dense ops
     defer_wgrad: bool = False  # pipeline stages send input gradients before weight-gradient GEMMs
+    device: str = "cuda"       # "cpu": CPU ranks over gloo with the ops' host paths (plumbing)
     lr: float = 1e-4
     weight_decay: float = 0.01
     seed: int = 0
 
 
-def _init_distributed() -> Tuple[int, int, int]:
+def _init_distributed(device: str = "cuda") -> Tuple[int, int, int]:
+    cuda = device == "cuda"
     if "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1:
         rank = int(os.environ["RANK"])
         local = int(os.environ.get("LOCAL_RANK", rank))
-        torch.cuda.set_device(local)
+        if cuda:
+            torch.cuda.set_device(local)
         if not dist.is_initialized():
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            if cuda:
+                dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            else:
+                dist.init_process_group("gloo")
         return rank, dist.get_world_size(), local
-    torch.cuda.set_device(0)
+    if cuda:
+        torch.cuda.set_device(0)
     return 0, 1, 0
 
 
 class LlamaTrainer:
     def __init__(self, model_cfg: LlamaConfig, cfg: TrainerConfig):
         self.cfg, self.model_cfg = cfg, model_cfg
-        self.rank, self.world, self.local = _init_distributed()
+        self.rank, self.world, self.local = _init_distributed(cfg.device)
         if self.world % cfg.pp_size:
             raise RuntimeError(f"world_size {self.world} must be divisible by pp_size "
                                f"{cfg.pp_size}")
         self.pp, self.dp = cfg.pp_size, self.world // cfg.pp_size
         self.pp_rank, self.dp_rank = self.rank % self.pp, self.rank // self.pp
-        self.device = torch.device("cuda", self.local)
+        self.device = torch.device("cuda", self.local) if cfg.device == "cuda" \
+            else torch.device("cpu")
 
         # groups: every rank creates all of them in the same order
         self.pp_group = self.dp_group = None
@@ -181,7 +189,7 @@ class LlamaTrainer:
         g = torch.Generator().manual_seed(1000003 * (step + 1) + self.dp_rank)
         ids = torch.randint(1, self.model_cfg.vocab_size,
                             (c.micro_batches, c.micro_batch_size, c.seq_length), generator=g)
-        return ids.pin_memory() if pinned else ids
+        return ids.pin_memory() if pinned and self.device.type == "cuda" else ids
 
     # -- one optimizer step ---------------------------------------------------------------
     def train_step(self, ids_host_or_dev: torch.Tensor) -> Optional[torch.Tensor]:
@@ -279,6 +287,13 @@ def _default_attention() -> str:
 def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
     step = 0
     resumed = trainer.step_count  # > 0 after --resume: those batches have been trained on
+    # BITSCOM_INJECT_EXIT="rank:step[:generation]": the named rank exits before that step (a
+    # failure made on the host, for recovery tests; generation = the launcher's restart count)
+    inject = None
+    generation = int(os.environ.get("BITSCOM_RESTART_COUNT", "0"))
+    if os.environ.get("BITSCOM_INJECT_EXIT"):
+        parts = [int(v) for v in os.environ["BITSCOM_INJECT_EXIT"].split(":")]
+        inject = (parts[0], parts[1], parts[2] if len(parts) > 2 else 0)
     for epoch in range(args.epochs):
         loader.set_epoch(epoch)
         for batch in loader:
@@ -290,6 +305,8 @@ def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
                 continue
             if monitor is not None:
                 monitor.check()
+            if inject and (trainer.rank, step, generation) == inject:
+                os._exit(17)  # host-side fault injection: this rank is simply gone
             t0 = time.perf_counter()
             loss = trainer.train_step(batch)
             loader.mark_consumed()
@@ -340,6 +357,10 @@ def main(argv=None):
     ap.add_argument("--resume", default=None,
                     help="continue from the per-rank checkpoint files in this directory "
                          "(same parallel layout as the run that wrote them)")
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu",
+                    choices=["cuda", "cpu"],
+                    help="'cpu' runs the same program on CPU ranks over gloo with the ops' host "
+                         "paths (plumbing check; use --model tiny)")
     ap.add_argument("--health_check", action="store_true",
                     help="heartbeats through the rendezvous store: a rank that leaves, fails "
                          "or falls silent is noticed on the host before the next step; the "
@@ -348,7 +369,7 @@ def main(argv=None):
     args = ap.parse_args(argv)
 
     mcfg = LlamaConfig.llama7b() if args.model == "llama7b" else LlamaConfig.tiny()
-    mcfg.attention = _default_attention()
+    mcfg.attention = _default_attention() if args.device == "cuda" else "sdpa"
     if args.model == "tiny":
         args.seq_length = min(args.seq_length, mcfg.max_seq)
     tcfg = TrainerConfig(
@@ -358,7 +379,8 @@ def main(argv=None):
         error_feedback=not args.no_error_feedback,
         dp_sync="dense" if args.backend == "nccl" else args.dp_sync,
         local_size=args.local_size, lr=args.lr,
-        simulate_quantization=args.simulate_quantization, defer_wgrad=args.defer_wgrad)
+        simulate_quantization=args.simulate_quantization, defer_wgrad=args.defer_wgrad,
+        device=args.device)
     trainer = LlamaTrainer(mcfg, tcfg)
     from ..data import build_loader
 
@@ -392,19 +414,29 @@ def main(argv=None):
     except Exception as exc:
         from ..utils.health import PeerLostError
 
-        if not isinstance(exc, PeerLostError):
+        between_steps = isinstance(exc, PeerLostError)
+        lost = exc.ranks if between_steps else {}
+        if monitor is not None and not between_steps:
+            # a collective that has lost its peer fails by itself (connection reset, process
+            # group timeout); give the monitor a moment to say whether that is what happened
+            deadline = time.monotonic() + args.health_timeout + 2.0
+            while not lost and time.monotonic() < deadline:
+                lost = monitor.lost()
+                time.sleep(0.1)
+        if not lost:
             if monitor is not None:
                 monitor.report_failure(exc)
             raise
-        # between steps, nothing of this rank in flight: keep what has been learnt and stop
-        # without another collective (the peer would never answer)
-        print(json.dumps({"stopped": str(exc), "step": trainer.step_count}), flush=True)
-        if args.output_dir:
+        print(json.dumps({"stopped": str(PeerLostError(lost)), "step": trainer.step_count,
+                          "between_steps": between_steps}), flush=True)
+        if args.output_dir and between_steps:
+            # nothing of this rank in flight: keep what has been learnt.  (After a failure in
+            # the middle of a step the last periodic checkpoint stays the one to resume from.)
             from ..utils.checkpoint import save_checkpoint
 
             save_checkpoint(args.output_dir, trainer.state_dict(), trainer.rank)
         monitor.close()
-        return 3
+        os._exit(3)  # no teardown collectives: the peer would never answer
     if args.output_dir:
         from ..utils.checkpoint import save_checkpoint
 

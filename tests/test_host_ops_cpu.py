@@ -78,6 +78,47 @@ def test_host_embedding_forward_and_scatter_add():
     assert t2.grad is None and torch.equal(t2.main_grad, want)
 
 
+def test_host_rmsnorm_swiglu_rope_match_fp32_autograd():
+    x = _bf(6, 32, seed=11).requires_grad_()
+    w = (1 + 0.1 * _bf(32, seed=12).float()).to(torch.bfloat16).requires_grad_()
+    dy = _bf(6, 32, seed=13)
+    K.rmsnorm(x, w, 1e-5).backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr).backward(dy.float())
+    assert torch.allclose(x.grad.float(), xr.grad, atol=2e-2)
+    assert torch.allclose(w.grad.float(), wr.grad, atol=3e-2)
+
+    gu = _bf(5, 16, seed=14).float().mul(2).to(torch.bfloat16).requires_grad_()
+    dh = _bf(5, 8, seed=15)
+    K.swiglu(gu).backward(dh)
+    gr = gu.detach().float().requires_grad_()
+    (F.silu(gr[:, :8]) * gr[:, 8:]).backward(dh.float())
+    assert torch.allclose(gu.grad.float(), gr.grad, atol=2e-2)
+
+    B, S, nh, hd = 2, 8, 2, 8
+    W = nh * hd
+    cos, sin = K.rope_tables(S, hd, 1e4, "cpu")
+    q = _bf(B * S, 3 * W, seed=16)
+
+    def rotate(t):
+        t = t.view(B, S, nh, hd).float()
+        a, b = t[..., :hd // 2], t[..., hd // 2:]
+        c, s_ = cos[None, :, None, :], sin[None, :, None, :]
+        return torch.cat([a * c - b * s_, b * c + a * s_], -1).reshape(B * S, W)
+
+    def reference(t):
+        return torch.cat([rotate(t[:, :W]), rotate(t[:, W:2 * W]), t[:, 2 * W:].float()], 1)
+
+    q0 = q.clone().requires_grad_()
+    out = K.rope_qk_(q0 * 1.0, cos, sin, nh, hd, S)
+    assert torch.allclose(out.float(), reference(q), atol=2e-2)
+    g = _bf(B * S, 3 * W, seed=17)
+    out.backward(g)
+    qr = q.float().requires_grad_()
+    reference(qr).backward(g.float())
+    assert torch.allclose(q0.grad.float(), qr.grad, atol=2e-2)
+
+
 def _free_port() -> int:
     import socket
 

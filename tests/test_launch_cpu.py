@@ -69,3 +69,30 @@ def test_restarts_are_bounded(tmp_path):
     assert run.returncode == 1
     events = [r["launch"] for r in _rows(run.stderr) if "launch" in r]
     assert events == ["generation started", "generation failed"]
+
+
+def test_llama_trainer_recovers_under_the_launcher(tmp_path):
+    """The headline trainer itself (tiny model, CPU ranks): rank 1 disappears before step 3
+    (host-side injection), rank 0's collective fails, the heartbeat monitor names the lost
+    peer, rank 0 stops with exit code 3, the launcher restarts both ranks, and they resume from
+    the periodic checkpoints at step 3 and finish step 5."""
+    ckpt = str(tmp_path / "ckpt")
+    env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1",
+               BITSCOM_INJECT_EXIT="1:3")
+    cmd = [sys.executable, "-m", "bitscom_b200.launch", "--nproc", "2", "--max-restarts", "1",
+           "--grace", "30", "--", sys.executable, "-m", "bitscom_b200.trainer.llama_dp_pp",
+           "--device", "cpu", "--model", "tiny", "--seq_length", "64", "--micro_batches", "2",
+           "--batch_size", "2", "--max_steps", "6", "--lr", "1e-3", "--health_check",
+           "--health_timeout", "3", "--output_dir", ckpt, "--resume", ckpt, "--save_every", "1"]
+    run = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, (run.stdout[-2000:], run.stderr[-3000:])
+    rows = _rows(run.stdout)
+    steps = sorted(r["step"] for r in rows if "step_s" in r)
+    assert steps == [0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 5, 5]      # each step once per rank, no repeats
+    stopped = [r for r in rows if "stopped" in r]
+    assert len(stopped) == 1 and stopped[0]["step"] == 3 and "rank 1" in stopped[0]["stopped"]
+    events = [r for r in _rows(run.stderr) if "launch" in r]
+    failed = [r for r in events if r["launch"] == "generation failed"]
+    assert len(failed) == 1 and failed[0]["exit_codes"] == {"0": 3, "1": 17}
+    assert failed[0]["lost"] == [1]
+    assert events[-1]["launch"] == "finished" and events[-1]["generation"] == 1
