@@ -12,7 +12,7 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(pp: int, sync: str, steps: int) -> None:
+def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False) -> None:
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
@@ -22,7 +22,8 @@ def _worker(pp: int, sync: str, steps: int) -> None:
     mcfg = LlamaConfig.tiny(max_seq=64)
     mcfg.attention = "sdpa"
     tcfg = TrainerConfig(pp_size=pp, micro_batches=4, micro_batch_size=2, seq_length=64,
-                         bitwidth=4, error_feedback=True, dp_sync=sync, lr=1e-2, device="cpu")
+                         bitwidth=4, error_feedback=True, dp_sync=sync, lr=1e-2, device="cpu",
+                         defer_wgrad=defer_wgrad)
     trainer = LlamaTrainer(mcfg, tcfg)
     losses = []
     for _ in range(steps):
@@ -43,12 +44,12 @@ def _free_port() -> int:
         return sock.getsockname()[1]
 
 
-def _run(nproc: int, pp: int, sync: str, steps: int = 6):
+def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = False):
     env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1")
     run = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", str(nproc),
          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-         os.path.abspath(__file__), str(pp), sync, str(steps)],
+         os.path.abspath(__file__), str(pp), sync, str(steps), str(int(defer_wgrad))],
         cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert run.returncode == 0, run.stderr[-3000:]
     rows = [json.loads(line) for line in run.stdout.splitlines() if line.startswith("{")]
@@ -81,5 +82,21 @@ def test_dp2_pp2_trains_with_lowbit_pipeline_a_sync():
         assert abs(lo["losses"][-1] - de["losses"][-1]) < 0.3, (lo["losses"], de["losses"])
 
 
+def test_flat_lowbit_sync_without_pipeline_stages():
+    """dp2 x pp1 with the flat low-bit all-reduce per bucket (no hierarchy, no pipeline)."""
+    rows = _run(2, 1, "flat")
+    assert [r["dp_rank"] for r in rows] == [0, 1]
+    assert all(r["losses"][-1] < r["losses"][0] - 0.5 for r in rows)
+
+
+def test_deferred_weight_gradients_change_nothing_but_the_order_of_work():
+    """With ``defer_wgrad`` a stage sends the input gradient before it runs the queued
+    weight-gradient GEMMs; every gradient is still accumulated in micro-batch order, so the
+    loss curve is the same to the last bit."""
+    plain = _run(4, 2, "dense", steps=4)
+    deferred = _run(4, 2, "dense", steps=4, defer_wgrad=True)
+    assert [r["losses"] for r in plain] == [r["losses"] for r in deferred]
+
+
 if __name__ == "__main__":
-    _worker(int(sys.argv[1]), sys.argv[2], int(sys.argv[3]))
+    _worker(int(sys.argv[1]), sys.argv[2], int(sys.argv[3]), bool(int(sys.argv[4])))
