@@ -82,6 +82,32 @@ def test_dp2_pp2_trains_with_lowbit_pipeline_a_sync():
         assert abs(lo["losses"][-1] - de["losses"][-1]) < 0.3, (lo["losses"], de["losses"])
 
 
+def _cli(tmp_path, port_tag, *extra):
+    env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1")
+    run = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", "2",
+         "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+         "-m", "bitscom_b200.trainer.llama_dp_pp", "--device", "cpu", "--model", "tiny",
+         "--seq_length", "64", "--micro_batches", "2", "--batch_size", "2", "--lr", "1e-3",
+         *extra], cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stderr[-3000:]
+    text = run.stdout.replace("}{", "}\n{")   # two ranks may print on one line
+    rows = [json.loads(line) for line in text.splitlines() if line.startswith('{"step"')]
+    return sorted((r["step"], r["loss"]) for r in rows)
+
+
+def test_trainer_cli_resumes_on_the_same_trajectory(tmp_path):
+    """Six steps in one go against three steps, a checkpoint (weights, optimizer, residuals of
+    the low-bit gradient sync, step counter) and three more steps from it: the same losses to
+    the last bit, and the resumed run does not repeat or skip a batch."""
+    ckpt = str(tmp_path / "ckpt")
+    whole = _cli(tmp_path, 0, "--max_steps", "6")
+    first = _cli(tmp_path, 1, "--max_steps", "3", "--output_dir", ckpt)
+    second = _cli(tmp_path, 2, "--max_steps", "6", "--resume", ckpt)
+    assert [s for s, _ in whole] == [0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 5, 5]
+    assert first + second == whole
+
+
 def test_flat_lowbit_sync_without_pipeline_stages():
     """dp2 x pp1 with the flat low-bit all-reduce per bucket (no hierarchy, no pipeline)."""
     rows = _run(2, 1, "flat")
