@@ -22,6 +22,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 import time
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
@@ -53,13 +54,21 @@ class TrainerConfig:
     simulate_quantization: bool = False   # reference flag: quantize round trip before dense ops
     defer_wgrad: bool = False  # pipeline stages send input gradients before weight-gradient GEMMs
     device: str = "cuda"       # "cpu": CPU ranks over gloo with the ops' host paths (plumbing)
+    pg_timeout_s: Optional[float] = None  # process-group timeout (None: torch's default)
     lr: float = 1e-4
     weight_decay: float = 0.01
     seed: int = 0
 
 
-def _init_distributed(device: str = "cuda") -> Tuple[int, int, int]:
+def _init_distributed(device: str = "cuda", timeout_s: Optional[float] = None
+                      ) -> Tuple[int, int, int]:
     cuda = device == "cuda"
+    extra = {}
+    if timeout_s:
+        import datetime
+
+        # a collective whose peer is gone then fails after this long instead of the default
+        extra["timeout"] = datetime.timedelta(seconds=float(timeout_s))
     if "RANK" in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1:
         rank = int(os.environ["RANK"])
         local = int(os.environ.get("LOCAL_RANK", rank))
@@ -67,9 +76,9 @@ def _init_distributed(device: str = "cuda") -> Tuple[int, int, int]:
             torch.cuda.set_device(local)
         if not dist.is_initialized():
             if cuda:
-                dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+                dist.init_process_group("nccl", device_id=torch.device("cuda", local), **extra)
             else:
-                dist.init_process_group("gloo")
+                dist.init_process_group("gloo", **extra)
         return rank, dist.get_world_size(), local
     if cuda:
         torch.cuda.set_device(0)
@@ -79,7 +88,7 @@ def _init_distributed(device: str = "cuda") -> Tuple[int, int, int]:
 class LlamaTrainer:
     def __init__(self, model_cfg: LlamaConfig, cfg: TrainerConfig):
         self.cfg, self.model_cfg = cfg, model_cfg
-        self.rank, self.world, self.local = _init_distributed(cfg.device)
+        self.rank, self.world, self.local = _init_distributed(cfg.device, cfg.pg_timeout_s)
         if self.world % cfg.pp_size:
             raise RuntimeError(f"world_size {self.world} must be divisible by pp_size "
                                f"{cfg.pp_size}")
@@ -311,8 +320,11 @@ def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
             loss = trainer.train_step(batch)
             loader.mark_consumed()
             if loss is not None:
-                print(json.dumps({"step": step, "epoch": epoch, "loss": float(loss.item()),
-                                  "step_s": time.perf_counter() - t0}), flush=True)
+                # one write per line: several ranks share the launcher's pipe
+                sys.stdout.write(json.dumps({"step": step, "epoch": epoch,
+                                             "loss": float(loss.item()),
+                                             "step_s": time.perf_counter() - t0}) + "\n")
+                sys.stdout.flush()
             if step % 50 == 0:
                 trainer.check_kernels()
             step += 1
@@ -366,6 +378,9 @@ def main(argv=None):
                          "or falls silent is noticed on the host before the next step; the "
                          "survivors write a checkpoint (with --output_dir) and stop")
     ap.add_argument("--health_timeout", type=float, default=30.0)
+    ap.add_argument("--pg_timeout", type=float, default=None,
+                    help="seconds after which a collective without its peer gives up "
+                         "(default: torch's process-group default)")
     args = ap.parse_args(argv)
 
     mcfg = LlamaConfig.llama7b() if args.model == "llama7b" else LlamaConfig.tiny()
@@ -380,7 +395,7 @@ def main(argv=None):
         dp_sync="dense" if args.backend == "nccl" else args.dp_sync,
         local_size=args.local_size, lr=args.lr,
         simulate_quantization=args.simulate_quantization, defer_wgrad=args.defer_wgrad,
-        device=args.device)
+        device=args.device, pg_timeout_s=args.pg_timeout)
     trainer = LlamaTrainer(mcfg, tcfg)
     from ..data import build_loader
 

@@ -16,6 +16,7 @@ import json
 import os
 import sys
 import time
+from datetime import timedelta
 
 import torch
 import torch.distributed as dist
@@ -37,6 +38,8 @@ def main(argv=None) -> int:
     ap.add_argument("--fail-rank", type=int, default=-1)
     ap.add_argument("--fail-step", type=int, default=-1)
     ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
+    ap.add_argument("--pg-timeout", type=float, default=10.0,
+                    help="seconds after which a collective without its peer gives up")
     args = ap.parse_args(argv)
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -44,10 +47,11 @@ def main(argv=None) -> int:
     if args.device == "cuda":
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         dev = torch.device("cuda", torch.cuda.current_device())
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=args.pg_timeout))
     else:
         dev = torch.device("cpu")
-        dist.init_process_group("gloo")
+        # a short timeout: a collective whose peer is gone must fail, not wait for half an hour
+        dist.init_process_group("gloo", timeout=timedelta(seconds=args.pg_timeout))
 
     store = agent_store()
     monitor = None

@@ -22,7 +22,7 @@ def _launch(tmp_path, launcher_args, worker_args, timeout=600):
 
 def _rows(text):
     out = []
-    for line in text.splitlines():
+    for line in text.replace("}{", "}\n{").splitlines():   # ranks share one pipe
         line = line.strip()
         if line.startswith("{"):
             try:
@@ -43,7 +43,7 @@ def test_job_without_failures_runs_one_generation(tmp_path):
 
 def test_lost_rank_leads_to_a_smaller_generation_that_resumes(tmp_path):
     run = _launch(tmp_path, ["--nproc", "3", "--min-nproc", "2", "--shrink", "--max-restarts",
-                             "2", "--grace", "20"],
+                             "2", "--grace", "40"],
                   ["--steps", "10", "--fail-rank", "2", "--fail-step", "4"])
     assert run.returncode == 0, (run.stdout[-2000:], run.stderr[-3000:])
     rows = _rows(run.stdout)
@@ -64,7 +64,7 @@ def test_restarts_are_bounded(tmp_path):
     # the failing rank is rank 1 of a two-rank job that may not shrink: generation 1 succeeds
     # only because the example fails in generation 0 alone; with no restarts allowed the
     # launcher gives up
-    run = _launch(tmp_path, ["--nproc", "2", "--max-restarts", "0", "--grace", "20"],
+    run = _launch(tmp_path, ["--nproc", "2", "--max-restarts", "0", "--grace", "40"],
                   ["--steps", "6", "--fail-rank", "1", "--fail-step", "2"])
     assert run.returncode == 1
     events = [r["launch"] for r in _rows(run.stderr) if "launch" in r]
@@ -80,7 +80,8 @@ def test_llama_trainer_recovers_under_the_launcher(tmp_path):
     env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1",
                BITSCOM_INJECT_EXIT="1:3")
     cmd = [sys.executable, "-m", "bitscom_b200.launch", "--nproc", "2", "--max-restarts", "1",
-           "--grace", "30", "--", sys.executable, "-m", "bitscom_b200.trainer.llama_dp_pp",
+           "--grace", "40", "--", sys.executable, "-m", "bitscom_b200.trainer.llama_dp_pp",
+           "--pg_timeout", "10",
            "--device", "cpu", "--model", "tiny", "--seq_length", "64", "--micro_batches", "2",
            "--batch_size", "2", "--max_steps", "6", "--lr", "1e-3", "--health_check",
            "--health_timeout", "3", "--output_dir", ckpt, "--resume", ckpt, "--save_every", "1"]
