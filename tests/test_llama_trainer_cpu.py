@@ -31,8 +31,10 @@ def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False) -> None:
         if loss is not None:
             losses.append(float(loss))
     if losses:
-        print(json.dumps({"rank": trainer.rank, "dp_rank": trainer.dp_rank, "dp": trainer.dp,
-                          "pp": trainer.pp, "losses": losses}), flush=True)
+        sys.stdout.write(json.dumps({"rank": trainer.rank, "dp_rank": trainer.dp_rank,
+                                     "dp": trainer.dp, "pp": trainer.pp,
+                                     "losses": losses}) + "\n")   # one write: a shared pipe
+        sys.stdout.flush()
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
@@ -52,7 +54,8 @@ def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = Fal
          os.path.abspath(__file__), str(pp), sync, str(steps), str(int(defer_wgrad))],
         cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert run.returncode == 0, run.stderr[-3000:]
-    rows = [json.loads(line) for line in run.stdout.splitlines() if line.startswith("{")]
+    text = run.stdout.replace("}{", "}\n{")
+    rows = [json.loads(line) for line in text.splitlines() if line.startswith("{")]
     return sorted(rows, key=lambda r: r["rank"])
 
 
