@@ -3,6 +3,7 @@ model, through the ops' host paths: own 1F1B schedule across two stages, buckete
 gradient sync through pipeline-A across two replicas, flat AdamW.  Run as a script this file is
 the per-rank worker."""
 
+import functools
 import json
 import os
 import socket
@@ -46,6 +47,7 @@ def _free_port() -> int:
         return sock.getsockname()[1]
 
 
+@functools.lru_cache(maxsize=None)   # the runs are deterministic: tests share them
 def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = False):
     env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1")
     run = subprocess.run(
@@ -122,8 +124,8 @@ def test_deferred_weight_gradients_change_nothing_but_the_order_of_work():
     """With ``defer_wgrad`` a stage sends the input gradient before it runs the queued
     weight-gradient GEMMs; every gradient is still accumulated in micro-batch order, so the
     loss curve is the same to the last bit."""
-    plain = _run(4, 2, "dense", steps=4)
-    deferred = _run(4, 2, "dense", steps=4, defer_wgrad=True)
+    plain = _run(4, 2, "dense")
+    deferred = _run(4, 2, "dense", defer_wgrad=True)
     assert [r["losses"] for r in plain] == [r["losses"] for r in deferred]
 
 
