@@ -15,6 +15,7 @@ holds the embedding on the first stage and the final norm + LM head on the last.
 
 from __future__ import annotations
 
+import zlib
 from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
 
@@ -115,12 +116,16 @@ class LlamaStage(torch.nn.Module):
         self._rope: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None
 
     def reset_parameters(self, seed: int = 0) -> None:
-        gen = torch.Generator(device=self.flat.params.device).manual_seed(seed + self.stage)
+        """Every tensor draws from a stream keyed by (seed, its name), so a parameter has the
+        same initial value whichever pipeline stage owns it: a model split over stages starts
+        from the same weights as the unsplit one."""
+        gen = torch.Generator(device=self.flat.params.device)
         with torch.no_grad():
             for name, view in self.flat.named_views():
                 if "norm" in name:
                     view.fill_(1.0)
                 else:
+                    gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (1 << 62))
                     view.copy_(torch.randn(view.shape, device=view.device, generator=gen,
                                            dtype=torch.float32) * self.cfg.init_std)
         self.flat.sync_master_from_params()

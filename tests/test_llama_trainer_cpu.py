@@ -13,14 +13,15 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False) -> None:
+def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False,
+            untied: bool = False) -> None:
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
     from bitscom_b200.models.llama import LlamaConfig
     from bitscom_b200.trainer.llama_dp_pp import LlamaTrainer, TrainerConfig
 
-    mcfg = LlamaConfig.tiny(max_seq=64)
+    mcfg = LlamaConfig.tiny(max_seq=64, num_layers=4, tie_embeddings=not untied)
     mcfg.attention = "sdpa"
     tcfg = TrainerConfig(pp_size=pp, micro_batches=4, micro_batch_size=2, seq_length=64,
                          bitwidth=4, error_feedback=True, dp_sync=sync, lr=1e-2, device="cpu",
@@ -48,12 +49,14 @@ def _free_port() -> int:
 
 
 @functools.lru_cache(maxsize=None)   # the runs are deterministic: tests share them
-def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = False):
+def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = False,
+         untied: bool = False):
     env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1")
     run = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", str(nproc),
          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-         os.path.abspath(__file__), str(pp), sync, str(steps), str(int(defer_wgrad))],
+         os.path.abspath(__file__), str(pp), sync, str(steps), str(int(defer_wgrad)),
+         str(int(untied))],
         cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert run.returncode == 0, run.stderr[-3000:]
     text = run.stdout.replace("}{", "}\n{")
@@ -61,11 +64,26 @@ def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = Fal
     return sorted(rows, key=lambda r: r["rank"])
 
 
+def test_pipeline_split_computes_what_the_unsplit_model_computes():
+    """With an output head of its own (so that both variants are the same network) a model cut
+    into two or four pipeline stages follows the unsplit model's loss curve exactly: stages
+    exchange the bf16 activations and gradients the unsplit model passes between its layers,
+    every parameter starts from the same value whichever stage owns it, and every gradient is
+    accumulated in micro-batch order."""
+    whole = _run(1, 1, "dense", untied=True)
+    two = _run(2, 2, "dense", untied=True)
+    four = _run(4, 4, "dense", untied=True)
+    assert len(whole) == len(two) == len(four) == 1
+    assert whole[0]["losses"][-1] < whole[0]["losses"][0] - 0.5
+    assert two[0]["losses"] == whole[0]["losses"]
+    assert four[0]["losses"] == whole[0]["losses"]
+
+
 def test_dp2_pp2_behaves_like_dp2_pp1_with_dense_gradient_sync():
     """Two pipeline stages against the unsplit model, two replicas each.  The two are not the
     same network (a split model has an output head of its own on the last stage where the
-    unsplit one ties it to the embedding, and stages draw their weights from their own random
-    streams), so the curves are compared loosely: same start, both fall, similar end."""
+    unsplit one ties it to the embedding), so the curves are compared loosely: same start, both
+    fall, similar end."""
     split = [r for r in _run(4, 2, "dense") if r["dp_rank"] == 0]
     whole = [r for r in _run(2, 1, "dense") if r["dp_rank"] == 0]
     assert len(split) == 1 and split[0]["pp"] == 2 and split[0]["dp"] == 2
@@ -130,4 +148,5 @@ def test_deferred_weight_gradients_change_nothing_but_the_order_of_work():
 
 
 if __name__ == "__main__":
-    _worker(int(sys.argv[1]), sys.argv[2], int(sys.argv[3]), bool(int(sys.argv[4])))
+    _worker(int(sys.argv[1]), sys.argv[2], int(sys.argv[3]), bool(int(sys.argv[4])),
+            bool(int(sys.argv[5])))
