@@ -137,6 +137,7 @@ def test_trainer_cli_resumes_on_the_same_trajectory(tmp_path):
     ckpt = str(tmp_path / "ckpt")
     whole = _cli(tmp_path, 0, "--max_steps", "6")
     first = _cli(tmp_path, 1, "--max_steps", "3", "--output_dir", ckpt)
+    _CLI_CACHE[("--max_steps", "3")] = first   # the same run without the checkpoint at its end
     second = _cli(tmp_path, 2, "--max_steps", "6", "--resume", ckpt)
     assert [s for s, _ in whole] == [0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 5, 5]
     assert first + second == whole
