@@ -30,6 +30,7 @@ class FlatParameters:
                 n *= s
             self.offsets[name] = (cursor, n, tuple(shape))
             cursor += -(-n // ALIGN) * ALIGN
+        self.used = cursor  # elements before the padding to ``pad_to`` (the same for every pad_to)
         self.numel = -(-cursor // pad_to) * pad_to
         self.params = torch.zeros(self.numel, dtype=dtype, device=device)
         self.grads = torch.zeros(self.numel, dtype=torch.float32, device=device)

@@ -62,6 +62,13 @@ def main(argv=None):
                     help="LayerNorm, GELU and attention from torch instead of this library's "
                          "kernels (A/B baseline)")
     ap.add_argument("--out", default="bench_outputs/gpt2_sharded.jsonl")
+    ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--output_dir", default=None,
+                    help="write per-rank checkpoints (optimizer shard, step) here at the end")
+    ap.add_argument("--resume", default=None,
+                    help="continue from the checkpoints in this directory; the run that wrote "
+                         "them may have had another number of ranks (lowbit mode: the sharded "
+                         "optimizer state is re-partitioned)")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu",
                     choices=["cuda", "cpu"],
                     help="'cpu' runs the same program on CPU ranks over gloo with torch ops "
@@ -89,12 +96,27 @@ def main(argv=None):
     if args.mode == "lowbit" and world > 1:
         ggrp = LowBitGroup(bitwidth=args.grad_bits, block_size=256, error_feedback=True)
         pgrp = LowBitGroup(bitwidth=args.param_bits, block_size=256, error_feedback=True)
-        opt = ShardedAdamW(flat, ggrp, lr=3e-4, param_bits_group=pgrp)
+        opt = ShardedAdamW(flat, ggrp, lr=args.lr, param_bits_group=pgrp)
     elif world > 1:
-        opt = DenseShardedAdamW(flat, world, rank, 3e-4)
+        opt = DenseShardedAdamW(flat, world, rank, args.lr)
     else:
-        opt = K.FlatAdamW(flat.master, flat.grads, flat.params, lr=3e-4)
-    g = torch.Generator().manual_seed(5 + rank)
+        opt = K.FlatAdamW(flat.master, flat.grads, flat.params, lr=args.lr)
+    done = 0
+    if args.resume:
+        done = _resume(args.resume, opt, flat, rank, world)
+    g = torch.Generator().manual_seed(5 + rank + 1000 * done)
+
+    def master_sum():
+        """Sum of the fp32 master weights over all shards (float64): a fingerprint of the
+        optimizer's weights that does not depend on how they are partitioned."""
+        if not isinstance(opt, ShardedAdamW):
+            return None
+        t = opt.master_shard.double().sum().reshape(1)
+        if world > 1:
+            dist.all_reduce(t)
+        return float(t.item())
+
+    fingerprint_start = master_sum()
 
     def fwd_bwd(ids):
         loss = model(ids, targets=ids)
@@ -143,6 +165,7 @@ def main(argv=None):
     ms = torch.tensor([elapsed_ms / args.steps], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    fingerprint_end = master_sum()
     if rank == 0:
         tokens = world * args.micro_batch * cfg.seq
         row = {"workload": "gpt2_medium_sharded" if args.model == "medium" else "gpt2_tiny",
@@ -151,15 +174,47 @@ def main(argv=None):
                "cuda_graph": bool(args.cuda_graph), "grad_bits": args.grad_bits,
                "param_bits": args.param_bits, "ms_per_step": float(ms.item()),
                "tokens_per_s": tokens / float(ms.item()) * 1e3,
-               "loss_first": float(first.item()), "loss_last": float(last.item())}
+               "loss_first": float(first.item()), "loss_last": float(last.item()),
+               "steps_done_before": done, "master_sum_start": fingerprint_start,
+               "master_sum_end": fingerprint_end}
         print(json.dumps(row), flush=True)
         if args.out:
             os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
             with open(args.out, "a") as f:
                 f.write(json.dumps(row) + "\n")
+    if args.output_dir and isinstance(opt, ShardedAdamW):
+        from ..utils.checkpoint import save_checkpoint
+
+        save_checkpoint(args.output_dir, {"step": done + args.warmup + args.steps,
+                                          "world": world, "used": flat.used,
+                                          "zero": opt.state_dict()}, rank)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _resume(directory: str, opt, flat, rank: int, world: int) -> int:
+    """Load the sharded optimizer state written by a run of ``old_world`` ranks (any number)
+    and rebuild the bf16 parameters from the fp32 master shards.  Returns the steps done."""
+    from ..parallel.zero import reshard_state
+    from ..utils.checkpoint import load_checkpoint
+
+    if not isinstance(opt, ShardedAdamW):
+        raise SystemExit("--resume needs the sharded optimizer (lowbit mode, 2 or more ranks)")
+    head = load_checkpoint(directory, 0)
+    old_world = int(head["world"])
+    if old_world == world:
+        mine = load_checkpoint(directory, rank)["zero"]
+    else:
+        states = [head["zero"]] + [load_checkpoint(directory, r)["zero"]
+                                   for r in range(1, old_world)]
+        mine = reshard_state(states, world, int(head["used"]))[rank]
+    opt.load_state_dict(mine)
+    # every rank needs the whole bf16 model: gather the master shards densely, once
+    full = torch.empty(flat.numel, dtype=torch.float32, device=flat.params.device)
+    dist.all_gather_into_tensor(full, opt.master_shard)
+    flat.params.copy_(full)
+    return int(head["step"])
 
 
 if __name__ == "__main__":

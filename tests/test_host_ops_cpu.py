@@ -150,3 +150,31 @@ def test_gpt2_sharded_trainer_on_two_cpu_ranks(tmp_path):
         assert row["device"] == "cpu" and row["world"] == 2 and not row["fused_ops"]
         assert row["loss_last"] < row["loss_first"]
     assert abs(low["loss_last"] - dense["loss_last"]) < 0.05
+
+
+def _gpt2(nproc, tmp_path, *extra):
+    env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1")
+    out = tmp_path / "rows.jsonl"
+    run = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", str(nproc),
+         "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+         "-m", "bitscom_b200.trainer.gpt2_sharded", "--device", "cpu", "--model", "tiny",
+         "--micro-batch", "2", "--warmup", "0", "--out", str(out), *extra],
+        cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert run.returncode == 0, run.stderr[-3000:]
+    return json.loads(out.read_text().strip().splitlines()[-1])
+
+
+def test_sharded_run_resumes_on_another_number_of_ranks(tmp_path):
+    """Four ranks train and checkpoint their optimizer shards; two ranks (and then three, whose
+    padding differs) pick the state up: the fp32 master weights they start from are the ones
+    the four-rank run ended with, and the step counter carries over."""
+    ckpt = str(tmp_path / "ckpt")
+    four = _gpt2(4, tmp_path, "--steps", "3", "--output_dir", ckpt)
+    assert four["steps_done_before"] == 0
+    assert abs(four["master_sum_end"] - four["master_sum_start"]) > 1e-6   # it did train
+    for world in (2, 3):
+        again = _gpt2(world, tmp_path, "--steps", "1", "--resume", ckpt)
+        assert again["world"] == world and again["steps_done_before"] == 3
+        assert abs(again["master_sum_start"] - four["master_sum_end"]) < 1e-9 * max(
+            1.0, abs(four["master_sum_end"]))
