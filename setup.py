@@ -116,5 +116,7 @@ setup(
     packages=find_packages(include=["bitscom_b200", "bitscom_b200.*"]),
     package_data={"bitscom_b200": ["csrc/*", "lib/*.so"]},
     python_requires=">=3.10",
+    entry_points={"console_scripts": ["bitscom-launch=bitscom_b200.launch:main",
+                                      "bitscom-info=bitscom_b200.__main__:main"]},
     cmdclass={"build_ext": BuildNative, "build_py": BuildPyWithNative},
 )
