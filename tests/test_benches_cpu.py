@@ -206,6 +206,14 @@ def test_ddp_hook_example_trains():
     assert last < 0.6 * first
 
 
+def test_sharded_optimizer_example_trains():
+    out = _run_example("sharded_optimizer.py", 29663)
+    assert "each of 2 ranks keeps 2304 of 4608 fp32 master weights" in out
+    line = next(l for l in out.splitlines() if l.startswith("loss "))
+    first, last = (float(v) for v in line[5:].split(" -> "))
+    assert last < 0.2 * first
+
+
 def test_roofline_report_table():
     from bitscom_b200.bench import roofline_report as RR
 
