@@ -539,8 +539,9 @@ class LowBitGroup:
         self.health = monitor
 
     def _precheck(self) -> None:
-        if self.health is not None:
-            self.health.check()
+        monitor = getattr(self, "health", None)
+        if monitor is not None:
+            monitor.check()
 
     def rebind(self, process_group=None) -> None:
         """Point this group at another process group, typically the one built among the
