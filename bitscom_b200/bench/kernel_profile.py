@@ -129,7 +129,8 @@ def gemm(args):
     if args.wgrad:
         tf = 2 * M * N * K / ms / 1e9
         print(json.dumps({"case": "gemm_tcgen05_wgrad_fp32_accumulate",
-                          "variant": args.gemm_variant, "M": M, "N": N, "K": K, "ms": ms, "tflops": tf, "frac_bf16_peak": tf / tflops, "peaks": tag}))
+                          "variant": args.gemm_variant, "M": M, "N": N, "K": K, "ms": ms,
+                          "tflops": tf, "frac_bf16_peak": tf / tflops, "peaks": tag}))
         return
     ms_ref = _timed(lambda i: torch.matmul(As[i % copies], Bs[i % copies].t()), args.iters)
     tf = 2 * M * N * K / ms / 1e9
