@@ -119,7 +119,8 @@ class LlamaTrainer:
             prev_rank=self.rank - 1 if self.pp_rank > 0 else None,
             next_rank=self.rank + 1 if self.pp_rank < self.pp - 1 else None,
             act_shape=(cfg.micro_batch_size * cfg.seq_length, model_cfg.hidden_size),
-            device=self.device, defer_wgrad=cfg.defer_wgrad) if self.pp > 1 else None
+            device=self.device, defer_wgrad=cfg.defer_wgrad,
+            defer_last=cfg.defer_wgrad) if self.pp > 1 else None
 
         self.sync: Optional[GradBucketSync] = None
         if self.dp > 1:
@@ -213,8 +214,13 @@ class LlamaTrainer:
         last_mb = c.micro_batches - 1
 
         def forward_fn(mb: int, x: Optional[torch.Tensor]):
+            # with deferred weight gradients the last backward's GEMMs run after its input
+            # gradient has been sent (the deferral that shortens the pipeline's drain), so the
+            # per-layer bucket launches, which need finished gradients, give way to one sync
+            # after the step
             model.on_layer_backward = self._layer_done if (
-                mb == last_mb and self.sync is not None and c.overlap) else None
+                mb == last_mb and self.sync is not None and c.overlap
+                and not (c.defer_wgrad and self.runner is not None)) else None
             if not model.is_first:
                 model.set_shape(c.micro_batch_size, c.seq_length)
             inp = ids[mb] if model.is_first else x

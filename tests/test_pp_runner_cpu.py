@@ -103,6 +103,7 @@ _LOG = []
 
 
 def _deferral_worker(rank, world, microbatches, defer):
+    defer, defer_last = bool(defer), defer == "all"
     torch.set_num_threads(1)
     g = torch.Generator().manual_seed(50 + rank)
     weights = [torch.nn.Parameter(torch.randn(WIDTH, WIDTH, generator=g) * 0.3) for _ in range(2)]
@@ -110,7 +111,8 @@ def _deferral_worker(rank, world, microbatches, defer):
         w.main_grad = torch.zeros_like(w)
     runner = PipelineRunner(rank, world, dist.group.WORLD, rank - 1 if rank > 0 else None,
                             rank + 1 if rank < world - 1 else None, (MB_ROWS, WIDTH),
-                            dtype=torch.float32, device="cpu", defer_wgrad=defer)
+                            dtype=torch.float32, device="cpu", defer_wgrad=defer,
+                            defer_last=defer_last)
     sent_before_flush = []
     real_exchange = runner._exchange
 
@@ -148,15 +150,19 @@ def _deferral_worker(rank, world, microbatches, defer):
     for r in range(world):
         assert torch.allclose(everyone[r], want[r], atol=1e-5), r
     if defer:
-        # every backward step but the last one queued its two weight gradients
-        assert _LOG.count("queued") == 2 * (microbatches - 1) and _LOG.count("now") == 2
+        # every backward step but the last one queued its two weight gradients; with
+        # defer_last the last one did too
+        if defer_last:
+            assert _LOG.count("queued") == 2 * microbatches and _LOG.count("now") == 0
+        else:
+            assert _LOG.count("queued") == 2 * (microbatches - 1) and _LOG.count("now") == 2
         if rank > 0:  # ... and ran them only after the input gradient was handed over
             assert sent_before_flush and all(sent_before_flush)
     else:
         assert _LOG.count("queued") == 0
 
 
-@pytest.mark.parametrize("defer", [True, False])
+@pytest.mark.parametrize("defer", [True, False, "all"])
 @pytest.mark.parametrize("stages,microbatches", [(2, 4), (3, 5)])
 def test_deferred_weight_gradients_match_and_follow_the_send(stages, microbatches, defer):
     run_ranks(_deferral_worker, stages, microbatches, defer)

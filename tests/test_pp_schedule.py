@@ -83,3 +83,22 @@ def test_p2p_plan_is_deadlock_free_and_ordered(stages, mbs):
         assert got_fwd[s] == list(range(mbs))       # activations arrive in order
     for s in range(stages - 1):
         assert got_bwd[s] == list(range(mbs))       # gradients arrive in order
+
+
+def test_timeline_simulation_matches_the_bubble_formula_and_shows_what_deferral_buys():
+    """Plain 1F1B idles (P - 1) forward + backward slots; deferring weight gradients shortens
+    the step only when the step's last backward is deferred too (the drain runs through it)."""
+    from bitscom_b200.parallel.pp_schedule import simulate_timeline
+
+    for stages, mbs in [(1, 4), (2, 8), (4, 8), (4, 16), (8, 32)]:
+        plain = simulate_timeline(stages, mbs)
+        assert abs(plain["efficiency"] - mbs / (mbs + stages - 1)) < 1e-12
+        partly = simulate_timeline(stages, mbs, defer_wgrad=True)
+        fully = simulate_timeline(stages, mbs, defer_wgrad=True, defer_last=True)
+        assert partly["step_time"] == plain["step_time"]
+        if stages > 1:
+            assert fully["step_time"] == plain["step_time"] - (stages - 1) * 1.0
+        assert fully["ideal_time"] == plain["ideal_time"]
+    uneven = simulate_timeline(2, 8, t_forward=1.0, t_input_grad=1.4, t_weight_grad=0.6,
+                               defer_wgrad=True, defer_last=True, t_send=0.05)
+    assert 0.9 < uneven["efficiency"] < 1.0
