@@ -162,8 +162,8 @@ def _deferral_worker(rank, world, microbatches, defer):
         assert _LOG.count("queued") == 0
 
 
-@pytest.mark.parametrize("defer", [True, False, "all"])
-@pytest.mark.parametrize("stages,microbatches", [(2, 4), (3, 5)])
+@pytest.mark.parametrize("stages,microbatches,defer", [(2, 4, True), (2, 4, False),
+                                                       (3, 5, "all"), (3, 5, True)])
 def test_deferred_weight_gradients_match_and_follow_the_send(stages, microbatches, defer):
     run_ranks(_deferral_worker, stages, microbatches, defer)
 
