@@ -1,5 +1,7 @@
 """Tiny Llama stage on the hand-written kernels against a plain fp32 PyTorch model."""
 
+import os
+
 import pytest
 import torch
 
@@ -67,6 +69,27 @@ def test_tiny_llama_loss_and_grads(attention):
     opt.step()
     loss2 = model(ids, targets=ids)
     assert loss2.item() < loss.item()
+
+
+@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
+                    reason="consistency check of the ops' host paths against the kernels; "
+                           "set BITSCOM_EXPERIMENTAL=1 to run it")
+def test_host_paths_follow_the_kernels():
+    """The same tiny model (same seed, hence the same weights) on the GPU through the kernels
+    and on the CPU through the ops' host paths: loss and flat gradient agree to bf16 accuracy."""
+    cfg = LlamaConfig.tiny(attention="sdpa", hidden_size=256, num_heads=2, max_seq=128)
+    ids = torch.randint(1, cfg.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5))
+    results = {}
+    for device in ("cuda", "cpu"):
+        model = LlamaStage(cfg, device=device, seed=3)
+        loss = model(ids.to(device), targets=ids.to(device))
+        loss.backward()
+        results[device] = (float(loss), model.flat.grads.detach().float().cpu().clone(),
+                           model.flat.params.detach().float().cpu().clone())
+    assert torch.equal(results["cuda"][2], results["cpu"][2])      # same initial weights
+    assert abs(results["cuda"][0] - results["cpu"][0]) < 0.02
+    g_gpu, g_cpu = results["cuda"][1], results["cpu"][1]
+    assert (g_gpu - g_cpu).norm() < 0.05 * g_cpu.norm()
 
 
 def test_trainer_cli_trains_on_a_text_file(tmp_path, capsys):
