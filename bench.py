@@ -16,8 +16,13 @@ with CUDA events (max over ranks):
   * `value`: inputs already on the device, loss read once at the end;
   * `e2e`: every step copies its token ids from pinned host memory and reads the loss
     back to the host.
+At N >= 2 the line also carries an `allreduce` block: the fused low-bit all-reduce against
+NCCL bf16 / fp32 on 64 MB and 1 GB buckets over all N GPUs, with a bit-exact check against the
+golden model (bitscom_b200/bench/allreduce_block.py), measured before the model is built.
 `--impl reference` runs the reference's library from baseline/_ref (see
-baseline/reference_arm.py) or prints why it cannot.
+baseline/reference_arm.py) or prints why it cannot.  `--impl torch` runs this repo's model code
+with torch.matmul (cuBLAS) and SDPA in place of the tcgen05 GEMM and attention kernels: the
+library bar the hand-written kernels are measured against.
 """
 
 from __future__ import annotations
@@ -35,68 +40,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.proc = None
-        self.lines = []
-        self.thread = None
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu), "-lms", "200"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except Exception:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
-        self.thread.start()
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-                power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
-                "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
-
-
-def _baseline_value():
-    """The reference publishes no Llama-7B tokens/s figure, so there is nothing to divide by."""
-    return None
+from bitscom_b200.utils.clocks import ClockSampler  # noqa: E402
 
 
 def run_ours(args):
@@ -118,9 +62,21 @@ def run_ours(args):
                          micro_batch_size=args.micro_batch_size, seq_length=seq, bitwidth=4,
                          error_feedback=True, dp_sync=args.dp_sync, local_size=args.local_size,
                          defer_wgrad=args.defer_wgrad, device=args.device)
+    if args.impl == "torch":
+        from bitscom_b200.ops import gemm as G
+
+        G.use_library_gemm(True)
+        mcfg.attention = "sdpa"
+
+    # the collective half of the metric, over all N GPUs, before the model takes the memory
+    allreduce = None
+    if world > 1 and cuda and args.impl == "ours" and not args.no_allreduce_block:
+        allreduce = allreduce_block(args)
+
     trainer = LlamaTrainer(mcfg, tcfg)
     rank, dev = trainer.rank, trainer.device
 
+    from bitscom_b200.ops import _native
     from bitscom_b200.utils import timing
 
     def barrier():
@@ -166,8 +122,11 @@ def run_ours(args):
     sampler = ClockSampler(trainer.local)
     if rank == 0:
         sampler.start()
+    launches_before = _native.launch_count()
     ms_dev, loss_dev = timed(args.steps, False, args.warmup)
-    launches = trainer.opt.step_count  # placeholder, replaced below
+    # kernels of this library launched by THIS rank inside the device-timed region, counted
+    # where the native launch functions are called (ops/_native.py)
+    launches = _native.launch_count() - launches_before
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e, loss_e2e = timed(args.steps, True, args.warmup + args.steps)
     trainer.check_kernels()  # a kernel that gave up on a bounded wait must not yield a number
@@ -180,24 +139,23 @@ def run_ours(args):
     # memory (first stage: inputs, last stage: targets); every last-stage rank reads its loss
     h2d = c.micro_batches * c.micro_batch_size * c.seq_length * 8 * max(world, 1)
     d2h = 4 * trainer.dp
-    launches = estimate_launches(trainer, args.steps) if cuda else 0
-    base = _baseline_value()
     out = {
         "metric": "llama7b_dp_pp_train_tokens_per_s" if args.model == "llama7b"
         else "tiny_llama_train_tokens_per_s",
         "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": (value / base) if base else None,
+        "scaling": "weak", "vs_baseline": None,  # the reference publishes no tokens/s figure
         "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
-        "impl": "bitscom_b200", "device": args.device,
+        "impl": "bitscom_b200" if args.impl == "ours"
+        else "torch (this repo's model code on torch.matmul / cuBLAS and SDPA)",
+        "device": args.device,
         "config": {"model": "llama-7b (32L, 4096h, 32 heads, ffn 11008, vocab 32000)"
                    if args.model == "llama7b" else "tiny",
                    "global_batch": trainer.dp * c.micro_batches * c.micro_batch_size,
                    "seq_len": c.seq_length, "parallelism": f"dp{trainer.dp}xpp{trainer.pp}",
                    "micro_batches": c.micro_batches,
                    "schedule": "1F1B" + (" + deferred weight gradients" if c.defer_wgrad else ""),
-                   "grad_sync": f"{c.dp_sync} 4-bit block 256 + error feedback"
-                   if trainer.dp > 1 else "none (dp=1)",
+                   "grad_sync": trainer.grad_sync_description(),
                    "attention": mcfg.attention, "optimizer": "AdamW fp32 master",
                    "l2": ("per-step working set (>100 GB weights+activations) exceeds the "
                           "126 MB L2; no flush needed") if args.model == "llama7b"
@@ -206,35 +164,46 @@ def run_ours(args):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "loss": loss_e2e},
         "gpu_launches": launches,
+        "gpu_launches_note": "own kernels launched by rank 0 in the device-timed region",
         "clocks": clocks,
         "loss": loss_dev,
     }
+    if allreduce is not None:
+        out["allreduce"] = allreduce
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier()
+        import bitscom_b200
+
+        bitscom_b200.shutdown()  # release symmetric blocks in order, before the group goes
         dist.destroy_process_group()
 
 
-def estimate_launches(trainer, steps: int) -> int:
-    """Own-kernel launches per timed region, counted from the model structure: per layer
-    and micro-batch 4 forward GEMMs + 8 backward GEMMs, 2+2 RMSNorm, 2+2 RoPE, 1+1 SwiGLU,
-    attention forward/backward (own kernel only), plus embedding / head / loss / AdamW and
-    the fused collective launches counted by the communicator."""
-    m = trainer.model
-    layers = m.layer_range[1] - m.layer_range[0]
-    own_attn = 2 if trainer.model_cfg.attention == "tcgen05" else 0
-    per_layer = 12 + 4 + 4 + 2 + own_attn
-    per_mb = layers * per_layer
-    if m.is_first:
-        per_mb += 2
-    if m.is_last:
-        per_mb += 2 + 3 + 1
-    total = steps * (trainer.cfg.micro_batches * per_mb + 1)
-    from bitscom_b200.utils import timing
+def allreduce_block(args) -> dict:
+    """Fused low-bit all-reduce vs NCCL bf16 / fp32 over all ranks of the job (see
+    bitscom_b200/bench/allreduce_block.py); returns the record on every rank."""
+    import torch
+    import torch.distributed as dist
 
-    total += int(timing.counters().get("fused_launches", 0))
-    return total
+    from bitscom_b200.bench import allreduce_block as AB
+    from bitscom_b200.parallel.fused import FusedLowBitComm
+    from bitscom_b200.trainer.llama_dp_pp import _init_distributed
+
+    rank, world, local = _init_distributed("cuda")
+    comm = FusedLowBitComm.for_group(dist.group.WORLD, torch.device("cuda", local))
+    exact = AB.bit_exact_check(comm, world, rank)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    rows = AB.measure(comm, sizes_mb=args.allreduce_mb, iters=10, warmup=3)
+    clocks = sampler.stop() if rank == 0 else None
+    comm.close()  # collective: the symmetric blocks go before the model is built
+    torch.cuda.empty_cache()
+    return {"setting": "4-bit, block 256, stochastic rounding, error feedback + stage 2",
+            "world": world, "bit_exact_vs_golden_model": exact, "rows": rows, "clocks": clocks,
+            "timing": "CUDA events, 10 calls after 3 warm-ups on rotating buffers (> L2 in "
+                      "total), max over ranks"}
 
 
 def main():
@@ -242,7 +211,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
     ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
     ap.add_argument("--pp", type=int, default=0)
     ap.add_argument("--micro-batches", type=int, default=0)
@@ -253,6 +222,9 @@ def main():
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="'cpu' (with --model tiny) runs the same program on CPU ranks: a check "
                          "of this script's output contract, not a benchmark")
+    ap.add_argument("--allreduce-mb", type=float, nargs="+", default=[64, 1024],
+                    help="bucket sizes (MB) of the all-reduce block reported at N >= 2")
+    ap.add_argument("--no-allreduce-block", action="store_true")
     ap.add_argument("--defer-wgrad", action="store_true",
                     help="pipeline stages send the input gradient before running the "
                          "weight-gradient GEMMs (off by default)")

@@ -40,6 +40,7 @@ from .quantization import (
     decompress_tensor,
     quantize_pack_tensor_blockwise,
     roundtrip_tensor,
+    stage1_stream,
     unpack_dequantize_tensor_blockwise,
 )
 from .utils import timing as _timing
@@ -190,12 +191,13 @@ class _FlatLowBitAllReduce:
             flat = flat.to(torch.float32) + self.ef.stage1
         S = plan.shard_len
         packed_out, scales_out = [], []
+        stream1 = stage1_stream(dist.get_rank(self.group))
         for j in range(self.world):
             shard = flat[j * S:(j + 1) * S]
             p, s, _ = quantize_pack_tensor_blockwise(
                 shard, o.bitwidth, block_size=o.block_size,
                 stochastic_rounding=o.stochastic_rounding,
-                sr_seed=self._seed, sr_offset=j * S, sr_stream=0)
+                sr_seed=self._seed, sr_offset=j * S, sr_stream=stream1)
             packed_out.append(p)
             scales_out.append(s)
             if self.ef is not None:
@@ -562,6 +564,25 @@ class LowBitGroup:
             st.carry_over = True
             st.stage2 = None
 
+    def check_status(self) -> None:
+        """Raise ``FusedCollectiveError`` if a fused kernel launched through this group has
+        given up on a bounded wait (a peer never arrived): the tensors of that collective
+        hold partial results.  Reads the communicators' host-mapped status records; no device
+        synchronisation, so a kernel still running is not waited for."""
+        for comm in self._fused_comms.values():
+            if comm and comm.native.handle is not None:
+                comm.check_status()
+
+    def close(self) -> None:
+        """Collective: release the fused communicators this group has used (see
+        ``FusedLowBitComm.close``).  Every rank of the group calls it, between steps, before
+        ``destroy_process_group``; the group falls back to creating a fresh communicator if it
+        is used again.  ``bitscom_b200.shutdown()`` does this for every group at once."""
+        comms = [c for c in self._fused_comms.values() if c]
+        self._fused_comms = {}
+        for comm in comms:
+            comm.close()
+
     def check_agreement(self, tensor: torch.Tensor) -> None:
         """Collective debugging aid: raises ``RuntimeError`` on every rank unless all ranks
         hold bit-identical copies of ``tensor``.  A low-bit all-reduce must leave the same bits
@@ -604,6 +625,8 @@ class LowBitGroup:
                 raise RuntimeError("fused=True needs CUDA tensors")
             return None
         comm = self._fused_comms.get(id(group))
+        if comm and comm.native.handle is None:
+            comm = None  # closed (``close`` / ``bitscom_b200.shutdown``): build a fresh one
         if comm is None:
             from .parallel.fused import FusedLowBitComm, FusedUnavailable
 
@@ -667,9 +690,12 @@ class LowBitGroup:
 
         if self._should_use_pipeline_a(op, local_group, inter_group):
             self._comm_debug("path=hierarchical_lowbit_pipeline_a")
+            # ef_key only when given: callers' stand-ins for this method keep the reference's
+            # signature
+            extra = {} if ef_key is None else {"ef_key": ef_key}
             self._hierarchical_lowbit_allreduce_pipeline_a(
                 tensor, local_group=local_group, inter_group=inter_group,
-                chunk_size=chunk_size, local_quantize=local_quantize)
+                chunk_size=chunk_size, local_quantize=local_quantize, **extra)
             # pipeline-A runs its ordered local/inter/finalize phases to completion
             return _ImmediateWork() if async_op else None
 
@@ -852,11 +878,12 @@ class LowBitGroup:
     # -- hierarchical pipeline-A -------------------------------------------------------
     def _hierarchical_lowbit_allreduce_pipeline_a(self, tensor: torch.Tensor, *, local_group,
                                                   inter_group, chunk_size: Optional[int],
-                                                  local_quantize: bool) -> None:
+                                                  local_quantize: bool,
+                                                  ef_key: Optional[Hashable] = None) -> None:
         from .parallel.pipeline_a import run_pipeline_a
 
         run_pipeline_a(self, tensor, local_group=local_group, inter_group=inter_group,
-                       chunk_size=chunk_size, local_quantize=local_quantize)
+                       chunk_size=chunk_size, local_quantize=local_quantize, ef_key=ef_key)
 
     # -- passthrough collectives (reference api.py:1460-1505) ---------------------------
     def _maybe_simulate(self, tensor: torch.Tensor) -> torch.Tensor:

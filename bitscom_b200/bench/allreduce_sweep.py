@@ -132,6 +132,9 @@ def main(argv=None):
             for r in rows:
                 f.write(json.dumps(r) + "\n")
     dist.barrier()
+    import bitscom_b200
+
+    bitscom_b200.shutdown()  # release symmetric blocks in order, before the group goes
     dist.destroy_process_group()
 
 

@@ -159,6 +159,9 @@ def main(argv=None):
                     w.writerow(["step", "rel_error", "lowbit_ms", "baseline_ms"])
                     w.writerows(rows)
     dist.barrier()
+    import bitscom_b200
+
+    bitscom_b200.shutdown()  # release symmetric blocks in order, before the group goes
     dist.destroy_process_group()
     return results
 

@@ -416,6 +416,9 @@ def main(argv=None):
     if rank == 0:
         summarize(args.out_dir, args.bitwidth)
     dist.barrier()
+    import bitscom_b200
+
+    bitscom_b200.shutdown()  # release symmetric blocks in order, before the group goes
     dist.destroy_process_group()
 
 

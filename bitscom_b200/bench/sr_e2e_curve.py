@@ -129,6 +129,9 @@ def main(argv=None):
                 for i in range(args.steps):
                     w.writerow([i + 1] + [curves[k][i] for k in curves])
     dist.barrier()
+    import bitscom_b200
+
+    bitscom_b200.shutdown()  # release symmetric blocks in order, before the group goes
     dist.destroy_process_group()
 
 

@@ -76,14 +76,37 @@ static int dtype_code(at::ScalarType t) {
   }
 }
 
+// The communicator as the backend and its Work objects share it: a Work may outlive the
+// backend's close(), after which `comm` is null and there is no status left to read.
+struct CommSlot {
+  std::mutex mu;
+  BcomComm* comm = nullptr;
+};
+
+// Raises if a fused kernel of this communicator gave up on one of its bounded waits.  Reads
+// the host-mapped status record only: no device synchronisation.
+static void raise_if_gave_up(const std::shared_ptr<CommSlot>& slot) {
+  if (!slot) return;
+  unsigned int st[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  {
+    std::lock_guard<std::mutex> lock(slot->mu);
+    if (!slot->comm) return;
+    bcom_comm_status(slot->comm, st);
+  }
+  TORCH_CHECK(st[0] == 0, "lowbit fused collective gave up waiting: code ", st[0], ", rank ",
+              st[3], " waited on peer ", st[2],
+              "; the tensors of that collective are not valid");
+}
+
 // ---------------------------------------------------------------------------
 // Work: a CUDA event on the communication stream
 // ---------------------------------------------------------------------------
 class WorkLowBit : public c10d::Work {
  public:
-  WorkLowBit(int rank, c10d::OpType op, std::vector<at::Tensor> outputs, BcomComm* comm,
-             c10::DeviceIndex device)
-      : c10d::Work(rank, op), outputs_(std::move(outputs)), comm_(comm), device_(device) {
+  WorkLowBit(int rank, c10d::OpType op, std::vector<at::Tensor> outputs,
+             std::shared_ptr<CommSlot> comm, c10::DeviceIndex device)
+      : c10d::Work(rank, op), outputs_(std::move(outputs)), comm_(std::move(comm)),
+        device_(device) {
     future_ = c10::make_intrusive<at::ivalue::Future>(
         c10::ListType::create(c10::TensorType::get()),
         std::vector<c10::Device>{c10::Device(c10::kCUDA, device)});
@@ -102,9 +125,13 @@ class WorkLowBit : public c10d::Work {
   }
   bool isSuccess() const override { return true; }
 
-  // stream-ordered: the caller's current stream waits for the result, the host does not
+  // Stream-ordered: the caller's current stream waits for the result, the host does not.  A
+  // kernel that has ALREADY given up (this collective's, if it ran to its time limit before
+  // the call, or an earlier one's) raises here; one that gives up later is reported by the
+  // next collective, isCompleted() or synchronize().
   bool wait(std::chrono::milliseconds /*timeout*/ = kNoTimeout) override {
     done_.block(c10::cuda::getCurrentCUDAStream(device_));
+    check_status();
     return true;
   }
   void synchronize() override {
@@ -123,15 +150,9 @@ class WorkLowBit : public c10d::Work {
   std::vector<at::Tensor> result() override { return outputs_; }
 
  private:
-  void check_status() {
-    if (!comm_) return;
-    unsigned int st[8];
-    bcom_comm_status(comm_, st);
-    TORCH_CHECK(st[0] == 0, "lowbit fused collective gave up waiting: code ", st[0], ", rank ",
-                st[3], " waited on peer ", st[2]);
-  }
+  void check_status() { raise_if_gave_up(comm_); }
   std::vector<at::Tensor> outputs_;
-  BcomComm* comm_;
+  std::shared_ptr<CommSlot> comm_;
   c10::DeviceIndex device_;
   at::cuda::CUDAEvent done_;
   c10::intrusive_ptr<at::ivalue::Future> future_;
@@ -167,8 +188,18 @@ class ProcessGroupLowBit : public c10d::Backend {
     nccl_ = c10::make_intrusive<c10d::ProcessGroupNCCL>(store_, rank, size, nccl_opts);
   }
 
+  // The destructor of the inner ProcessGroupNCCL joins its watchdog and heartbeat threads, and
+  // those may need the GIL to finish (dropping the last reference of a tensor that has a
+  // Python object, the stuck-GIL probe).  pybind runs this destructor with the GIL held, so
+  // it is released for the teardown: torch binds its own ProcessGroupNCCL with a holder that
+  // does the same.  Joining those threads with the GIL held can deadlock the process.
   ~ProcessGroupLowBit() override {
-    if (comm_) bcom_comm_destroy(comm_);
+    if (Py_IsInitialized() && PyGILState_Check()) {
+      pybind11::gil_scoped_release nogil;
+      teardown(/*handshake_ms=*/2000);
+    } else {
+      teardown(/*handshake_ms=*/2000);
+    }
   }
 
   const std::string getBackendName() const override { return "lowbit"; }
@@ -192,7 +223,7 @@ class ProcessGroupLowBit : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> allreduce(std::vector<at::Tensor>& tensors,
                                            const c10d::AllreduceOptions& opts) override {
     if (tensors.size() != 1 || !use_lowbit_allreduce(tensors[0], opts))
-      return nccl_->allreduce(tensors, opts);
+      return nccl().allreduce(tensors, opts);
     return lowbit_collective(tensors[0], tensors[0], BCOM_MODE_ALL_REDUCE,
                              c10d::OpType::ALLREDUCE);
   }
@@ -202,7 +233,7 @@ class ProcessGroupLowBit : public c10d::Backend {
     const bool lowbit = options_.bitwidth < 16 && opts.reduceOp == c10d::ReduceOp::SUM &&
                         getSize() > 1 && fused_ok(input) && fused_ok(output) &&
                         input.scalar_type() == output.scalar_type();
-    if (!lowbit) return nccl_->_reduce_scatter_base(output, input, opts);
+    if (!lowbit) return nccl()._reduce_scatter_base(output, input, opts);
     TORCH_CHECK(input.numel() == output.numel() * getSize(),
                 "reduce_scatter: input must hold world * output elements");
     return lowbit_collective(input, output, BCOM_MODE_REDUCE_SCATTER,
@@ -216,7 +247,7 @@ class ProcessGroupLowBit : public c10d::Backend {
     const bool lowbit = outputs.size() == 1 && options_.bitwidth < 16 &&
                         opts.reduceOp == c10d::ReduceOp::SUM && getSize() > 1 &&
                         fused_ok(outputs[0]);
-    if (!lowbit) return nccl_->reduce_scatter(outputs, inputs, opts);
+    if (!lowbit) return nccl().reduce_scatter(outputs, inputs, opts);
     auto& shards = inputs[0];
     TORCH_CHECK((int)shards.size() == getSize(), "reduce_scatter: need one input per rank");
     for (auto& s : shards)
@@ -240,39 +271,39 @@ class ProcessGroupLowBit : public c10d::Backend {
   // ---- passthroughs -------------------------------------------------------------------
   c10::intrusive_ptr<c10d::Work> broadcast(std::vector<at::Tensor>& t,
                                            const c10d::BroadcastOptions& o) override {
-    return nccl_->broadcast(t, o);
+    return nccl().broadcast(t, o);
   }
   c10::intrusive_ptr<c10d::Work> reduce(std::vector<at::Tensor>& t,
                                         const c10d::ReduceOptions& o) override {
-    return nccl_->reduce(t, o);
+    return nccl().reduce(t, o);
   }
   c10::intrusive_ptr<c10d::Work> allgather(std::vector<std::vector<at::Tensor>>& out,
                                            std::vector<at::Tensor>& in,
                                            const c10d::AllgatherOptions& o) override {
-    return nccl_->allgather(out, in, o);
+    return nccl().allgather(out, in, o);
   }
   c10::intrusive_ptr<c10d::Work> _allgather_base(at::Tensor& out, at::Tensor& in,
                                                  const c10d::AllgatherOptions& o) override {
-    return nccl_->_allgather_base(out, in, o);
+    return nccl()._allgather_base(out, in, o);
   }
   c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& out, at::Tensor& in,
                                                std::vector<int64_t>& os, std::vector<int64_t>& is,
                                                const c10d::AllToAllOptions& o) override {
-    return nccl_->alltoall_base(out, in, os, is, o);
+    return nccl().alltoall_base(out, in, os, is, o);
   }
   c10::intrusive_ptr<c10d::Work> alltoall(std::vector<at::Tensor>& out,
                                           std::vector<at::Tensor>& in,
                                           const c10d::AllToAllOptions& o) override {
-    return nccl_->alltoall(out, in, o);
+    return nccl().alltoall(out, in, o);
   }
   c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& t, int dst, int tag) override {
-    return nccl_->send(t, dst, tag);
+    return nccl().send(t, dst, tag);
   }
   c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& t, int src, int tag) override {
-    return nccl_->recv(t, src, tag);
+    return nccl().recv(t, src, tag);
   }
   c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& o) override {
-    return nccl_->barrier(o);
+    return nccl().barrier(o);
   }
   void setSequenceNumberForGroup() override {}
   uint64_t getSequenceNumberForGroup() override { return seq_; }
@@ -318,19 +349,85 @@ class ProcessGroupLowBit : public c10d::Backend {
   int64_t fused_launches() const { return launches_; }
   const LowBitOptions& options() const { return options_; }
 
-  // Orderly teardown of the inner NCCL group (its communicators and helper threads), for
-  // callers that keep the process alive after destroy_process_group(): torch shuts down
-  // ProcessGroupNCCL instances it knows about, but not one that lives inside another backend,
-  // whose teardown would otherwise be left to the destructor.
-  void shutdown() {
-    if (nccl_) nccl_->shutdown();
-  }
+  // Orderly, collective teardown: every rank calls it after its last collective and before
+  // destroy_process_group().  Releases the symmetric block with a handshake through the store
+  // (wait for own kernels -> all ranks -> unmap peers -> all ranks -> free), then shuts down the
+  // inner NCCL group (its communicators and helper threads): torch shuts down the
+  // ProcessGroupNCCL instances it knows about, but not one that lives inside another backend.
+  // Idempotent; the destructor does the same with a short handshake limit if it was not called.
+  void shutdown() { teardown((int64_t)options_.timeout.count()); }
+
+  // Releases the symmetric block only (the NCCL passthroughs keep working).
+  void close_symmetric() { close_symmetric_impl((int64_t)options_.timeout.count()); }
 
  private:
   struct Residual {
     at::Tensor stage1, stage2;
   };
   using Key = std::tuple<int64_t, int64_t, int>;
+
+  // All ranks reach `key` (counted through the store) or `limit_ms` passes; false on the limit.
+  bool store_barrier(const std::string& key, int64_t limit_ms) {
+    try {
+      store_->add(key, 1);
+      const auto deadline =
+          std::chrono::steady_clock::now() + std::chrono::milliseconds(limit_ms);
+      while (store_->add(key, 0) < getSize()) {
+        if (std::chrono::steady_clock::now() >= deadline) return false;
+        std::this_thread::sleep_for(std::chrono::milliseconds(1));
+      }
+      return true;
+    } catch (...) {  // the store is gone (its host left): treat as "peers not reachable"
+      return false;
+    }
+  }
+
+  void close_symmetric_impl(int64_t limit_ms) {
+    std::lock_guard<std::mutex> lock(mu_);
+    if (!comm_) return;
+    inflight_.clear();
+    const std::string prefix =
+        "bitscom_b200/symm/close" + std::to_string(comm_generation_) + "/";
+    c10::cuda::CUDAGuard guard(device_);
+    cudaDeviceSynchronize();  // own kernels done: nothing of this rank stores into a peer
+    bool everyone = store_barrier(prefix + "quiet", limit_ms);
+    bcom_comm_close_peers(comm_);
+    everyone = everyone && store_barrier(prefix + "unmapped", limit_ms);
+    BcomComm* dead = nullptr;
+    {
+      std::lock_guard<std::mutex> slot_lock(slot_->mu);
+      dead = slot_->comm;
+      slot_->comm = nullptr;
+    }
+    comm_ = nullptr;
+    // A peer that did not answer may still map this block: freeing it then is undefined, so
+    // the block is left to the driver's process teardown instead.
+    if (everyone) bcom_comm_destroy(dead);
+    comm_stream_.reset();
+    ++comm_generation_;
+  }
+
+  void teardown(int64_t handshake_ms) {
+    close_symmetric_impl(handshake_ms);
+    c10::intrusive_ptr<c10d::ProcessGroupNCCL> nccl;
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      nccl = std::move(nccl_);
+      nccl_ = nullptr;
+    }
+    if (nccl) {
+      try {
+        nccl->shutdown();
+      } catch (...) {
+      }
+      nccl.reset();  // joins the helper threads; the caller has released the GIL
+    }
+  }
+
+  c10d::ProcessGroupNCCL& nccl() const {
+    TORCH_CHECK(nccl_, "lowbit backend: used after shutdown()");
+    return *nccl_;
+  }
 
   void ensure_comm(c10::DeviceIndex device) {
     if (comm_) {
@@ -341,9 +438,13 @@ class ProcessGroupLowBit : public c10d::Backend {
     device_ = device;
     TORCH_CHECK(bcom_comm_create(getRank(), getSize(), (size_t)options_.region_bytes, &comm_) == 0,
                 "lowbit backend: could not allocate the symmetric block");
+    {
+      std::lock_guard<std::mutex> slot_lock(slot_->mu);
+      slot_->comm = comm_;
+    }
     std::vector<uint8_t> mine(BCOM_IPC_HANDLE_BYTES);
     TORCH_CHECK(bcom_comm_ipc_handle(comm_, mine.data()) == 0, "cudaIpcGetMemHandle failed");
-    const std::string prefix = "bitscom_b200/symm/";
+    const std::string prefix = "bitscom_b200/symm/gen" + std::to_string(comm_generation_) + "/";
     store_->set(prefix + std::to_string(getRank()), mine);
     std::vector<uint8_t> all((size_t)getSize() * BCOM_IPC_HANDLE_BYTES);
     for (int r = 0; r < getSize(); ++r) {
@@ -383,6 +484,7 @@ class ProcessGroupLowBit : public c10d::Backend {
     const auto device = in.device().index();
     std::lock_guard<std::mutex> lock(mu_);
     ensure_comm(device);
+    raise_if_gave_up(slot_);  // an earlier kernel that gave up left partial results behind
     c10::cuda::CUDAGuard guard(device);
     const int W = getSize();
     BcomCollArgs a{};
@@ -412,7 +514,7 @@ class ProcessGroupLowBit : public c10d::Backend {
     }
     if (a.n == 0) {
       auto work = c10::make_intrusive<WorkLowBit>(getRank(), op, std::vector<at::Tensor>{out},
-                                                  comm_, device);
+                                                  slot_, device);
       work->mark_enqueued(c10::cuda::getCurrentCUDAStream(device));
       return work;
     }
@@ -421,7 +523,7 @@ class ProcessGroupLowBit : public c10d::Backend {
     ready.record(c10::cuda::getCurrentCUDAStream(device));
     ready.block(*comm_stream_);
     auto work = c10::make_intrusive<WorkLowBit>(getRank(), op, std::vector<at::Tensor>{out},
-                                                comm_, device);
+                                                slot_, device);
     {
       c10::cuda::CUDAStreamGuard sguard(*comm_stream_);
       const int rc = bcom_collective(comm_, &a, (void*)comm_stream_->stream());
@@ -445,6 +547,8 @@ class ProcessGroupLowBit : public c10d::Backend {
   EFMode ef_mode_ = EFMode::kNone;
   c10::intrusive_ptr<c10d::ProcessGroupNCCL> nccl_;
   BcomComm* comm_ = nullptr;
+  std::shared_ptr<CommSlot> slot_ = std::make_shared<CommSlot>();
+  int comm_generation_ = 0;  // symmetric blocks created so far (store keys are per generation)
   c10::DeviceIndex device_ = -1;
   std::unique_ptr<c10::cuda::CUDAStream> comm_stream_;
   std::map<Key, Residual> residuals_;
@@ -541,6 +645,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("clear_residuals", &ProcessGroupLowBit::clear_residuals)
       .def("fused_launches", &ProcessGroupLowBit::fused_launches)
       .def("shutdown", &ProcessGroupLowBit::shutdown,
+           py::call_guard<py::gil_scoped_release>())
+      .def("close_symmetric", &ProcessGroupLowBit::close_symmetric,
            py::call_guard<py::gil_scoped_release>());
 
   m.def("create_backend", &create_backend, py::arg("store"), py::arg("rank"), py::arg("size"),

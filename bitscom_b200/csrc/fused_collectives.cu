@@ -543,6 +543,8 @@ static int validate(const BcomComm* c, const BcomCollArgs& a) {
   if (!c || a.n < 0 || a.S <= 0 || !block_ok(a.block)) return (int)cudaErrorInvalidValue;
   if (a.n > (long long)c->world * a.S) return (int)cudaErrorInvalidValue;
   if (a.mode < 0 || a.mode > 2) return (int)cudaErrorInvalidValue;
+  for (int r = 0; r < c->world; ++r)  // a peer was unmapped (bcom_comm_close_peers) or never wired
+    if (!c->peer[r]) return (int)cudaErrorInvalidResourceHandle;
   return 0;
 }
 

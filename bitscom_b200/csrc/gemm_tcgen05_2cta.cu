@@ -10,12 +10,13 @@
 //   * one thread of the even CTA (the leader) issues tcgen05.mma.cta_group::2 with M = 256,
 //     N = 256, K = 16: the tensor cores of both SMs run it, each on its own 128 rows of A and
 //     on both halves of B, and each accumulates its 128 x 256 slice in its own tensor memory;
-//   * tcgen05.commit with a CTA mask releases a ring stage, and publishes a finished
-//     accumulator, in both CTAs at once;
-//   * TMA loads are plain per-CTA loads (no cluster multicast) that complete on the loading
-//     CTA's own mbarrier; one thread of the odd CTA forwards "my stage is full" to the leader
-//     with a remote mbarrier arrive, and the epilogue warps of the odd CTA hand their
-//     accumulator buffer back the same way.
+//   * two tcgen05.commit per event, one on each CTA's barrier (the peer's is addressed through
+//     mapa), release a ring stage and publish a finished accumulator in both CTAs;
+//   * TMA loads are per-CTA loads in the cta_group::2 form: each CTA loads its own half of the
+//     operands into its own shared memory, and both halves complete on the LEADER's "stage
+//     full" barrier (the leader expects the bytes of both), so the MMA issuer waits on one
+//     barrier per stage; the epilogue warps of the odd CTA hand their accumulator buffer back
+//     with a remote mbarrier arrive.  Every load is an ordinary load of one CTA.
 //
 // Every wait is bounded; on expiry the kernel records a code, all roles of both CTAs drain
 // (each through its own bounded waits), tensor memory is released and the kernel returns.
@@ -50,29 +51,31 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256;
-constexpr uint16_t kBothCtas = 3;
 
 enum Status : unsigned int {
-  kOk = 0, kProducerTimeout = 1, kMmaTimeout = 2, kEpilogueTimeout = 3, kAccumTimeout = 4,
-  kPeerStageTimeout = 5, kForwardTimeout = 6
+  kOk = 0, kProducerTimeout = 1, kMmaTimeout = 2, kEpilogueTimeout = 3, kAccumTimeout = 4
 };
 
 __device__ unsigned int g_status[4];
+// Optional per-pair cycle counters of the MMA issuer {waiting for operands, waiting for a free
+// accumulator, whole loop, k-blocks}: written when a buffer has been registered
+// (bcom_gemm2_set_profile), for finding out which hand-off a slow shape is waiting on.
+__device__ unsigned long long* g_profile;
 
 struct Params {
   void* C;
   long long ldc;
   int M, N, K;
   int tiles_m, tiles_n;
+  int flags;  // experiment switches of the MMA issuer loop (bcom_gemm2_set_flags)
 };
 
 // Identical layout, at identical shared-memory offsets, in both CTAs of a pair: the MMA and the
 // commit address the peer's operands and barriers by the leader's offsets.
 struct Shared {
-  uint64_t full[STAGES];       // this CTA's TMA loads of the stage have landed
-  uint64_t peer_full[STAGES];  // leader only: the odd CTA's loads of the stage have landed
-  uint64_t empty[STAGES];      // the pair's MMAs have read the stage (commit to both CTAs)
-  uint64_t acc_full[2];        // accumulator buffer complete (commit to both CTAs)
+  uint64_t full[STAGES];       // leader only: both CTAs' TMA loads of the stage have landed
+  uint64_t empty[STAGES];      // the pair's MMAs have read the stage (one commit per CTA)
+  uint64_t acc_full[2];        // accumulator buffer complete (one commit per CTA)
   uint64_t acc_empty[2];       // leader only: all 8 epilogue warps of the pair drained it
   uint32_t tmem_base;
   volatile int abort;
@@ -153,13 +156,28 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// The barrier at this shared-memory offset in every CTA of `cta_mask` receives one arrival
+// The barrier at shared::cluster address `bar` (this CTA's or the peer's) receives one arrival
 // once all tcgen05 operations issued so far by this thread have completed.
-__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+__device__ __forceinline__ void umma_commit_to(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+// Both CTAs of the pair: the barrier at this offset here, and the one at the same offset in the
+// peer (`peer_bar` = map_to_cta(bar, 1)).
+__device__ __forceinline__ void umma_commit_both(uint64_t* bar, uint32_t peer_bar) {
+  umma_commit_to(tc::smem_u32(bar));
+  umma_commit_to(peer_bar);
+}
+// 2-D tiled load of the CTA-pair form: the data lands in THIS CTA's shared memory, the bytes
+// are counted on the barrier at shared::cluster address `bar`, which may be the peer's.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
+                                                 uint32_t bar, int c0, int c1) {
   asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
-      " [%0], %1;" ::"r"(tc::smem_u32(bar)),
-      "h"(cta_mask)
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(tc::smem_u32(smem_dst)), "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
 
@@ -196,7 +214,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       tc::mbar_init(&sh->full[s], 1);
-      tc::mbar_init(&sh->peer_full[s], 1);
       tc::mbar_init(&sh->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -231,21 +248,25 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           }
           uint8_t* sA = smem + stage * STAGE_BYTES;
           uint8_t* sB = sA + A_BYTES;
-          tc::mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
+          // the leader's barrier counts the bytes of both CTAs; the odd CTA's bytes may land
+          // before this expect (the count goes negative for a moment), which is fine: the
+          // phase cannot complete before the leader's own arrival below
+          if (leader) tc::mbar_expect_tx(&sh->full[stage], 2 * STAGE_BYTES);
+          const uint32_t bar = map_to_cta(&sh->full[stage], 0);
           const int k0 = kb * BK;
           if constexpr (A_MN) {
 #pragma unroll
             for (int c = 0; c < BM_CTA / 64; ++c)
-              tc::tma_load_2d(sA + c * CHUNK_BYTES, &tmA, &sh->full[stage], m0 + c * 64, k0);
+              tma_load_2d_pair(sA + c * CHUNK_BYTES, &tmA, bar, m0 + c * 64, k0);
           } else {
-            tc::tma_load_2d(sA, &tmA, &sh->full[stage], k0, m0);
+            tma_load_2d_pair(sA, &tmA, bar, k0, m0);
           }
           if constexpr (B_MN) {
 #pragma unroll
             for (int c = 0; c < BN_CTA / 64; ++c)
-              tc::tma_load_2d(sB + c * CHUNK_BYTES, &tmB, &sh->full[stage], n0 + c * 64, k0);
+              tma_load_2d_pair(sB + c * CHUNK_BYTES, &tmB, bar, n0 + c * 64, k0);
           } else {
-            tc::tma_load_2d(sB, &tmB, &sh->full[stage], k0, n0);
+            tma_load_2d_pair(sB, &tmB, bar, k0, n0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -268,28 +289,32 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       int iter = 0;
+      unsigned long long* const prof = g_profile;
+      long long t_full = 0, t_acc = 0, n_kb = 0;
+      const long long t_begin = prof ? clock64() : 0;
       for (int t = pair; t < total_tiles && !sh->abort; t += num_pairs, ++iter) {
         const int buf = iter & 1;
         const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+        long long c0 = prof ? clock64() : 0;
         if (!mbar_wait_cluster(&sh->acc_empty[buf], acc_phase ^ 1u, kWaitBudgetNs)) {
           fail(sh, kAccumTimeout);
           break;
         }
+        if (prof) t_acc += clock64() - c0;
         tc::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!tc::mbar_wait(&sh->full[stage], phase, kWaitBudgetNs)) {
+          if (prof) c0 = clock64();
+          // the odd CTA's bytes arrive from the other SM: cluster-scope acquire
+          if (!((p.flags & 2) ? tc::mbar_wait(&sh->full[stage], phase, kWaitBudgetNs)
+                              : mbar_wait_cluster(&sh->full[stage], phase, kWaitBudgetNs))) {
             fail(sh, kMmaTimeout);
             ok = false;
             break;
           }
-          if (!mbar_wait_cluster(&sh->peer_full[stage], phase, kWaitBudgetNs)) {
-            fail(sh, kPeerStageTimeout);
-            ok = false;
-            break;
-          }
-          tc::tc_fence_after_sync();
+          if (prof) { t_full += clock64() - c0; ++n_kb; }
+          if (!(p.flags & 1)) tc::tc_fence_after_sync();
           const uint32_t a_addr = tc::smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
@@ -302,28 +327,18 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                 : tc::make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
             umma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit_pair(&sh->empty[stage], kBothCtas);  // both CTAs may refill the stage
+          // both CTAs may refill the stage
+          umma_commit_both(&sh->empty[stage], map_to_cta(&sh->empty[stage], 1));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit_pair(&sh->acc_full[buf], kBothCtas);
+        umma_commit_both(&sh->acc_full[buf], map_to_cta(&sh->acc_full[buf], 1));
       }
-    } else if (lane == 0) {
-      // ------------------------------ stage forwarder (odd CTA) ----------------
-      // tells the leader, stage by stage, that this CTA's operands have landed
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = pair; t < total_tiles && ok && !sh->abort; t += num_pairs) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!tc::mbar_wait(&sh->full[stage], phase, kWaitBudgetNs)) {
-            fail(sh, kForwardTimeout);
-            ok = false;
-            break;
-          }
-          mbar_arrive_cluster(map_to_cta(&sh->peer_full[stage], 0));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        }
+      if (prof) {
+        prof[4 * pair + 0] = (unsigned long long)t_full;
+        prof[4 * pair + 1] = (unsigned long long)t_acc;
+        prof[4 * pair + 2] = (unsigned long long)(clock64() - t_begin);
+        prof[4 * pair + 3] = (unsigned long long)n_kb;
       }
     }
   } else {
@@ -389,9 +404,18 @@ static Kernel pick(bool a_mn, bool b_mn, bool out_f32, bool accum) {
   return b_mn ? pick_out<false, true>(out_f32, accum) : pick_out<false, false>(out_f32, accum);
 }
 
+static int g_flags = 0;
+
 }  // namespace gemm2
 
 extern "C" {
+
+int bcom_gemm2_set_flags(int flags) {
+  const int old = gemm2::g_flags;
+  gemm2::g_flags = flags;
+  return old;
+}
+
 
 // Same contract as bcom_gemm_bf16 (gemm_tcgen05.cu); max_ctas counts CTAs (two per pair).
 int bcom_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -417,6 +441,7 @@ int bcom_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
       return 1005;
   }
   Params p;
+  p.flags = g_flags;
   p.C = C;
   p.ldc = ldc;
   p.M = M;
@@ -447,6 +472,14 @@ int bcom_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   if (pairs < 1) pairs = 1;
   kernel<<<2 * pairs, kThreads, SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, p);
   return (int)cudaGetLastError();
+}
+
+// Debugging aid: registers a device buffer of 4 x (number of CTA pairs) 64-bit words that the
+// MMA issuer of every pair fills with {cycles waiting for operands, cycles waiting for a free
+// accumulator, cycles in its loop, k-blocks issued}; NULL switches it off (the default).
+int bcom_gemm2_set_profile(void* device_buffer) {
+  unsigned long long* p = (unsigned long long*)device_buffer;
+  return (int)cudaMemcpyToSymbol(gemm2::g_profile, &p, sizeof(p));
 }
 
 // Copies the 4-word status record {code, cta, thread, -}; clears it when `clear` != 0.

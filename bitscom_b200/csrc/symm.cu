@@ -107,12 +107,31 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
 
 void* bcom_comm_multicast_base(BcomComm* c) { return c ? c->mc : nullptr; }
 
+int bcom_comm_close_peers(BcomComm* c) {
+  if (!c) return 0;
+  int before = -1;
+  BCOM_TRY(cudaGetDevice(&before));
+  if (before != c->device) BCOM_TRY(cudaSetDevice(c->device));
+  cudaError_t err = cudaDeviceSynchronize();
+  for (int p = 0; p < c->world; ++p) {
+    if (p == c->rank) continue;
+    if (c->opened[p] && c->peer[p]) {
+      const cudaError_t e = cudaIpcCloseMemHandle(c->peer[p]);
+      if (err == cudaSuccess) err = e;
+    }
+    c->opened[p] = false;
+    c->peer[p] = nullptr;  // bcom_collective refuses a communicator with an unmapped peer
+  }
+  if (before != c->device) (void)cudaSetDevice(before);
+  return (int)err;
+}
+
 int bcom_comm_destroy(BcomComm* c) {
   if (!c) return 0;
   cudaSetDevice(c->device);
   cudaDeviceSynchronize();
   for (int p = 0; p < c->world; ++p)
-    if (c->opened[p] && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
+    if (p != c->rank && c->opened[p] && c->peer[p]) cudaIpcCloseMemHandle(c->peer[p]);
   if (c->local && c->owns_local) cudaFree(c->local);
   if (c->status_host) cudaFreeHost(c->status_host);
   delete c;

@@ -78,6 +78,13 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
                               void* mc_base, BcomComm** out);
 size_t bcom_comm_block_bytes(size_t region_bytes);
 void* bcom_comm_multicast_base(BcomComm* comm);
+// Orderly teardown is two steps with a barrier among the ranks after each:
+//   1. every rank waits for its own kernels (nobody stores into a peer any more) -> barrier ->
+//      bcom_comm_close_peers (unmaps the peers' blocks; the communicator can no longer launch)
+//   2. barrier (nobody maps this rank's block any more) -> bcom_comm_destroy (frees it).
+// Freeing a block that a peer still has mapped is undefined; bcom_comm_destroy alone is for a
+// rank whose peers are gone or have already unmapped it.
+int bcom_comm_close_peers(BcomComm* comm);
 int bcom_comm_destroy(BcomComm* comm);
 // Debugging aid for tests: synchronises the device and checks the canary bytes around this
 // rank's regions (control-page tail in front of the receive region, guard page behind the

@@ -75,8 +75,27 @@ _ARG_ERRORS = {
 }
 
 
-def check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched by this process so far (counted where the launch
+    functions of the native libraries are called; library calls that launch nothing pass
+    ``launches=0``)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += int(n)
+
+
+def check(code: int, what: str, launches: int = 1) -> None:
+    """Raise on a non-zero return code of a native call; on success count the ``launches``
+    kernels the call enqueued."""
+    global _launches
     if code == 0:
+        _launches += launches
         return
     if code in _ARG_ERRORS:
         raise NativeError(f"{what}: {_ARG_ERRORS[code]}")

@@ -83,7 +83,7 @@ def supported(seq: int, head_dim: int) -> bool:
 
 def check_status(clear: bool = True) -> None:
     out = (ctypes.c_uint * 4)()
-    check(_get().bcom_attention_status(ctypes.byref(out), int(clear)), "attention_status")
+    check(_get().bcom_attention_status(ctypes.byref(out), int(clear)), "attention_status", launches=0)
     if out[0]:
         raise NativeError(f"attention kernel timed out at wait {out[0]} (cta {out[1]})")
 
@@ -127,7 +127,7 @@ class AttentionFunction(torch.autograd.Function):
         delta = torch.empty(batch, heads, seq, dtype=torch.float32, device=dev)
         check(lib.bcom_attention_bwd(ptr(q2), ptr(out), ptr(d_out), ptr(lse), ptr(dqkv),
                                      ptr(dq_acc), ptr(delta), batch, seq, heads, head_dim,
-                                     scale, stream_ptr(dev)), "attention_bwd")
+                                     scale, stream_ptr(dev)), "attention_bwd", launches=3)
         return dqkv.view_as(q2), None, None, None, None
 
 

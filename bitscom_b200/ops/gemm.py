@@ -51,6 +51,7 @@ def _get2():
             lib.bcom_gemm2_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ll, ll, ll, ci, ci, ci, ci,
                                             ci, vp]
             lib.bcom_gemm2_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
+            lib.bcom_gemm2_set_profile.argtypes = [vp]
         _lib2 = lib if lib is not None else False
     return _lib2 or None
 
@@ -97,21 +98,45 @@ def set_split_tail(on: bool) -> bool:
     return bool(lib.bcom_gemm_set_split_tail(int(bool(on))))
 
 
-_STATUS = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "accumulator hand-off",
-           5: "MMA issuer (peer CTA's stage)", 6: "stage forwarder"}
+_STATUS = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "accumulator hand-off"}
 
 
 def check_status(clear: bool = True) -> None:
     """Raise if a GEMM kernel gave up on one of its bounded waits (synchronises)."""
     out = (ctypes.c_uint * 4)()
-    check(_get().bcom_gemm_status(ctypes.byref(out), int(clear)), "bcom_gemm_status")
+    check(_get().bcom_gemm_status(ctypes.byref(out), int(clear)), "bcom_gemm_status", launches=0)
     which = "tcgen05 GEMM"
     if not out[0] and _lib2:
-        check(_lib2.bcom_gemm2_status(ctypes.byref(out), int(clear)), "bcom_gemm2_status")
+        check(_lib2.bcom_gemm2_status(ctypes.byref(out), int(clear)), "bcom_gemm2_status", launches=0)
         which = "tcgen05 CTA-pair GEMM"
     if out[0]:
         raise NativeError(f"{which} timed out in the {_STATUS.get(out[0], out[0])} "
                           f"(cta {out[1]}, thread {out[2]})")
+
+
+_library = False  # True: torch.matmul (cuBLAS) instead of the tcgen05 kernels (comparator only)
+
+
+def use_library_gemm(on: bool) -> bool:
+    """Comparator switch for benchmarks: route ``gemm`` through ``torch.matmul`` (cuBLAS, bf16
+    output, accumulation into an existing tensor by a separate add), the way a plain
+    ``nn.Linear`` model computes.  Never the default; returns the previous setting."""
+    global _library
+    old, _library = _library, bool(on)
+    return old
+
+
+def _gemm_library(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
+    A = a.t() if a_mn_major else a
+    B = b if b_mn_major else b.t()
+    c = torch.matmul(A, B)
+    if out is None:
+        return c if out_dtype == c.dtype else c.to(out_dtype)
+    if accumulate:
+        out.add_(c)
+    else:
+        out.copy_(c)
+    return out
 
 
 def _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
@@ -144,6 +169,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
     """
     if not a.is_cuda:
         return _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate)
+    if _library:
+        return _gemm_library(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate)
     lib = _get()
     if lib is None:
         raise NativeError("tcgen05 GEMM needs the bcom_llama library and a GPU")

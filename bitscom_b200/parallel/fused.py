@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 from ..ops import _native
 from ..ops._native import DTYPE_CODE, NativeError, check
-from ..quantization import sr_key
+from ..quantization import sr_key, stage1_stream
 from ..utils import timing as _timing
 
 MODE_ALL_REDUCE, MODE_REDUCE_SCATTER, MODE_ALL_GATHER = 0, 1, 2
@@ -66,6 +66,7 @@ def _get():
             lib.bcom_comm_multicast_base.argtypes = [vp]
             lib.bcom_comm_multicast_base.restype = vp
             lib.bcom_comm_destroy.argtypes = [vp]
+            lib.bcom_comm_close_peers.argtypes = [vp]
             lib.bcom_comm_check_canaries.argtypes = [vp, ctypes.POINTER(ll)]
             lib.bcom_comm_ipc_handle.argtypes = [vp, vp]
             lib.bcom_comm_open_peers.argtypes = [vp, vp]
@@ -117,19 +118,19 @@ class FusedUnavailable(RuntimeError):
     NOT this: it raises ``NativeError``."""
 
 
-def _keys(stochastic: bool, seed: Optional[int]):
+def _keys(stochastic: bool, seed: Optional[int], rank: int):
     if not stochastic:
         return 0, 0
     if seed is None:
         from ..ops.codec import fresh_seed
 
         seed = fresh_seed()
-    return sr_key(seed, 0), sr_key(seed, 1)
+    return sr_key(seed, stage1_stream(rank)), sr_key(seed, 1)
 
 
 def _args(inp, out, res1, res2, n, S, dtype, bits, block, mode, stochastic, seed,
-          post_scale, max_ctas) -> CollArgs:
-    k1, k2 = _keys(stochastic, seed)
+          post_scale, max_ctas, rank) -> CollArgs:
+    k1, k2 = _keys(stochastic, seed, rank)
     return CollArgs(
         inp=inp.data_ptr(), out=out.data_ptr(),
         res1=0 if res1 is None else res1.data_ptr(),
@@ -169,10 +170,10 @@ class _NativeComm:
                 bases = (ctypes.c_void_p * world)(*[int(b) for b in external_bases])
                 check(self.lib.bcom_comm_create_external(
                     rank, world, region_bytes, bases, ctypes.c_void_p(int(multicast_base)),
-                    ctypes.byref(handle)), "bcom_comm_create_external")
+                    ctypes.byref(handle)), "bcom_comm_create_external", launches=0)
             else:
                 check(self.lib.bcom_comm_create(rank, world, region_bytes,
-                                                ctypes.byref(handle)), "bcom_comm_create")
+                                                ctypes.byref(handle)), "bcom_comm_create", launches=0)
         self.handle = handle
         # live view of the pinned status record: word 0 != 0 means a kernel gave up
         self._status_view = (ctypes.c_uint * 8).from_address(
@@ -183,13 +184,13 @@ class _NativeComm:
 
     def ipc_handle(self) -> bytes:
         buf = ctypes.create_string_buffer(64)
-        check(self.lib.bcom_comm_ipc_handle(self.handle, buf), "cudaIpcGetMemHandle")
+        check(self.lib.bcom_comm_ipc_handle(self.handle, buf), "cudaIpcGetMemHandle", launches=0)
         return buf.raw
 
     def open_peers(self, handles: List[bytes]) -> None:
         blob = ctypes.create_string_buffer(b"".join(handles), 64 * self.world)
         with torch.cuda.device(self.device):
-            check(self.lib.bcom_comm_open_peers(self.handle, blob), "cudaIpcOpenMemHandle")
+            check(self.lib.bcom_comm_open_peers(self.handle, blob), "cudaIpcOpenMemHandle", launches=0)
 
     def status(self) -> List[int]:
         out = (ctypes.c_uint * 8)()
@@ -200,18 +201,24 @@ class _NativeComm:
         with torch.cuda.device(self.device):
             check(self.lib.bcom_comm_reset(
                 self.handle, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)),
-                "bcom_comm_reset")
+                "bcom_comm_reset", launches=0)
 
     def check_canaries(self) -> None:
         """Debugging aid (synchronises the device): raise if a store landed outside the
         regions of this rank's block, in the guard bytes in front of or behind them."""
         bad = ctypes.c_longlong(-1)
         check(self.lib.bcom_comm_check_canaries(self.handle, ctypes.byref(bad)),
-              "bcom_comm_check_canaries")
+              "bcom_comm_check_canaries", launches=0)
         if bad.value >= 0:
             raise FusedCollectiveError(
                 f"rank {self.rank}: guard bytes of the symmetric block were overwritten at "
                 f"offset {bad.value}")
+
+    def close_peers(self) -> None:
+        """Wait for this rank's kernels and unmap the peers' blocks (first step of an orderly
+        teardown; the communicator cannot launch afterwards)."""
+        if self.handle:
+            check(self.lib.bcom_comm_close_peers(self.handle), "bcom_comm_close_peers", launches=0)
 
     def close(self) -> None:
         if self.handle:
@@ -303,8 +310,53 @@ class FusedLowBitComm:
 
     @classmethod
     def drop_cache(cls) -> None:
+        """Local, non-collective release of every cached communicator: for a rank whose peers
+        may be gone (recovery after a lost rank).  Jobs that end normally use ``close_all``."""
         for comm in cls._cache.values():
             comm.native.close()
+        cls._cache.clear()
+
+    def _barrier(self) -> None:
+        dist.barrier(group=self.group, device_ids=[self.device.index]
+                     if dist.get_backend(self.group) == "nccl" else None)
+
+    def close(self) -> None:
+        """Collective, orderly teardown; every rank of the group calls it, between steps:
+
+        1. wait for this rank's kernels, then a barrier: no rank has a kernel in flight that
+           stores into a peer's block;
+        2. unmap the peers' blocks, then a barrier: no rank maps this rank's block any more;
+        3. free the block.
+
+        Freeing a block that a peer still maps is undefined behaviour of CUDA IPC, and a
+        process that exits with mappings and exported blocks alive leaves their release to the
+        driver's process teardown, in whatever order the ranks happen to die; this makes the
+        order explicit.  Idempotent."""
+        if self.native is None or self.native.handle is None:
+            return
+        torch.cuda.synchronize(self.device)
+        self._barrier()
+        if not self.native.external:
+            self.native.close_peers()
+        self._barrier()
+        self.native.close()
+        self._symm = None
+        for key, comm in list(self._cache.items()):
+            if comm is self:
+                del self._cache[key]
+
+    @classmethod
+    def close_all(cls) -> None:
+        """``close()`` for every cached communicator, in an order that is the same on every
+        rank (by the groups' global ranks), so that ranks that share several groups meet in
+        the same barriers in the same order."""
+        def order(comm):
+            try:
+                return tuple(dist.get_process_group_ranks(comm.group))
+            except Exception:
+                return ()
+        for comm in sorted(cls._cache.values(), key=order):
+            comm.close()
         cls._cache.clear()
 
     # -- capabilities / status --------------------------------------------------------
@@ -378,7 +430,8 @@ class FusedLowBitComm:
             ef.ensure(plan, tensor.device, stage2)
             res1, res2 = ef.stage1, (ef.stage2 if stage2 else None)
         args = _args(tensor, tensor, res1, res2, n, plan.shard_len, tensor.dtype, bitwidth,
-                     block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, self.max_ctas)
+                     block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, self.max_ctas,
+                     self.rank)
         return self._launch(args, async_op, (tensor, res1, res2))
 
     def reduce_scatter(self, output: torch.Tensor, input: torch.Tensor, *, bitwidth: int,
@@ -396,7 +449,7 @@ class FusedLowBitComm:
             res1 = ef.stage1
         args = _args(input, output, res1, None, S * self.world, S, input.dtype, bitwidth,
                      block_size, MODE_REDUCE_SCATTER, stochastic, seed, post_scale,
-                     self.max_ctas)
+                     self.max_ctas, self.rank)
         return self._launch(args, async_op, (input, output, res1))
 
     def all_gather(self, output: torch.Tensor, input: torch.Tensor, *, bitwidth: int,
@@ -412,7 +465,8 @@ class FusedLowBitComm:
                 ef.stage2 = torch.zeros(S, dtype=torch.float32, device=input.device)
             res2 = ef.stage2
         args = _args(input, output, None, res2, S * self.world, S, input.dtype, bitwidth,
-                     block_size, MODE_ALL_GATHER, stochastic, seed, post_scale, self.max_ctas)
+                     block_size, MODE_ALL_GATHER, stochastic, seed, post_scale, self.max_ctas,
+                     self.rank)
         return self._launch(args, async_op, (input, output, res2))
 
 
@@ -467,7 +521,7 @@ class EmulatedWorld:
         S = -(-n // self.world)
         self._run([
             _args(t, t, res1[r] if res1 else None, res2[r] if res2 else None, n, S, t.dtype,
-                  bitwidth, block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, 0)
+                  bitwidth, block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, 0, r)
             for r, t in enumerate(tensors)])
 
     def reduce_scatter(self, outputs, inputs, *, bitwidth, block_size, stochastic=False,
@@ -475,7 +529,7 @@ class EmulatedWorld:
         S = int(outputs[0].numel())
         self._run([
             _args(i, o, res1[r] if res1 else None, None, S * self.world, S, i.dtype, bitwidth,
-                  block_size, MODE_REDUCE_SCATTER, stochastic, seed, 1.0, 0)
+                  block_size, MODE_REDUCE_SCATTER, stochastic, seed, 1.0, 0, r)
             for r, (i, o) in enumerate(zip(inputs, outputs))])
 
     def all_gather(self, outputs, inputs, *, bitwidth, block_size, stochastic=False, seed=None,
@@ -483,5 +537,5 @@ class EmulatedWorld:
         S = int(inputs[0].numel())
         self._run([
             _args(i, o, None, res2[r] if res2 else None, S * self.world, S, i.dtype, bitwidth,
-                  block_size, MODE_ALL_GATHER, stochastic, seed, 1.0, 0)
+                  block_size, MODE_ALL_GATHER, stochastic, seed, 1.0, 0, r)
             for r, (i, o) in enumerate(zip(inputs, outputs))])

@@ -83,15 +83,33 @@ class GradBucketSync:
         with torch.cuda.stream(self.stream):
             self._launch(idx)
 
+    def check(self, wait: bool = False) -> None:
+        """Raise ``FusedCollectiveError`` if a fused kernel of this group gave up on a bounded
+        wait (it then returned early and the bucket holds partial sums).  ``wait=False`` costs
+        no synchronisation: it polls the events of the launched buckets and the communicators'
+        host-mapped status records, so it reports what has failed SO FAR; ``wait=True`` first
+        waits for every launched bucket (use it before gradients are consumed for something
+        that cannot be undone, such as writing a checkpoint)."""
+        pending = []
+        for work in self._works:
+            if wait:
+                work.wait()
+            elif not work.is_completed():
+                pending.append(work)
+        self._works = pending
+        self.group.check_status()
+
     def finish(self) -> None:
         """Launch whatever has not been launched yet and order the current stream after
-        all of it."""
+        all of it.  Failures that are already on record (an earlier step's bucket that ran
+        into its time limit) raise here, before this step's optimizer runs; the handles of
+        this step's buckets are kept and looked at again by the next ``finish`` / ``check``."""
         if self.world > 1:
             for idx in range(len(self.ranges)):
                 self.on_ready(idx)
             if self.overlap:
                 torch.cuda.current_stream(self.flat.device).wait_stream(self.stream)
-        self._works.clear()
+            self.check(wait=False)
         self._launched.clear()
 
 

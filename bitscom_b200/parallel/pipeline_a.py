@@ -11,10 +11,16 @@ Behaviour of the reference's ``_hierarchical_lowbit_allreduce_pipeline_a``
   finalize  the leader broadcasts the result inside ``local_group`` (dense, or packed
             bytes + scales with ``local_quantize``).
 
-The leader of a local group is the rank with ``global_rank % local_size == 0`` and its
-global rank is ``global_rank - local_rank``.  On CUDA, when there are fewer local ranks
-than global ranks, chunks are software-pipelined over two streams: local(i) and
-finalize(i-2) on one, inter(i-1) on the other.
+The leader of a local group is its first rank (the rank with ``global_rank % local_size
+== 0`` in the reference's layout).  On CUDA, when there are fewer local ranks than global
+ranks, chunks are software-pipelined over two streams: local(i) and finalize(i-2) on one,
+inter(i-1) on the other.
+
+Beyond the reference: the inter phase carries error feedback (both stages) with residuals
+kept per (bucket, chunk); on CUDA nothing blocks the host: the caller's stream is ordered
+after both lanes with events, and the per-chunk barrier of the reference (which blocks the
+host under NCCL and orders nothing that the finalize broadcast does not order already) is
+kept for CPU groups only.
 
 The schedule below is data: a list of (lane, phase, chunk) steps with their
 dependencies, executed either on one stream in order or on two streams with events.
@@ -48,7 +54,7 @@ def build_schedule(num_chunks: int) -> List[Step]:
 
 
 def run_pipeline_a(owner, tensor: torch.Tensor, *, local_group, inter_group,
-                   chunk_size: Optional[int], local_quantize: bool) -> None:
+                   chunk_size: Optional[int], local_quantize: bool, ef_key=None) -> None:
     flat = tensor.contiguous().view(-1)
     if flat.numel() == 0:
         return
@@ -60,8 +66,11 @@ def run_pipeline_a(owner, tensor: torch.Tensor, *, local_group, inter_group,
     local_rank = dist.get_rank(local_group)
     local_size = dist.get_world_size(local_group)
     global_size = dist.get_world_size(owner.pg)
-    leader = global_rank % local_size == 0
-    leader_global = global_rank - local_rank
+    leader = local_rank == 0
+    # dst / src of the local collectives are ranks of the DEFAULT group: owner.pg may be a
+    # strided subgroup (a data-parallel group of a dp x pp mesh), where
+    # ``global_rank - local_rank`` names somebody else
+    leader_global = dist.get_global_rank(local_group, 0)
     bits, block, sr = owner.bitwidth, owner.block_size, owner.stochastic_rounding
     owner._comm_debug(
         f"pipeline_a start numel={int(flat.numel())} chunks={n} chunk_elems={chunk_elems} "
@@ -95,18 +104,26 @@ def run_pipeline_a(owner, tensor: torch.Tensor, *, local_group, inter_group,
         chunk = chunks[i]
         if leader:
             src = reduced[i] if local_quantize else chunk.to(dtype=torch.float32)
+            # residuals belong to the chunk of the caller's bucket, not to the staging copy
+            ef = owner._ef_for(chunk, None if ef_key is None else (ef_key, "chunk", i))
             comm = owner._fused_comm(src, inter_group) if src.is_cuda else None
             if comm is not None:  # in place on the fp32 staging copy
                 comm.all_reduce(src, bitwidth=bits, block_size=block, stochastic=sr,
-                                seed=owner._next_sr_seed(), ef=None, stage2=False)
+                                seed=owner._next_sr_seed(), ef=ef,
+                                stage2=owner.stage2_error_feedback)
                 reduced[i] = src
+            elif ef is not None:
+                reduced[i] = owner._lowbit_allreduce_via_alltoall_group(src, inter_group, ef)
             else:
                 reduced[i] = owner._lowbit_allreduce_via_alltoall_group(src, inter_group)
-        device_ids = [torch.cuda.current_device()] if chunk.is_cuda else None
-        dist.barrier(group=local_group, device_ids=device_ids)
+        if not chunk.is_cuda:
+            dist.barrier(group=local_group)
 
     def finalize_phase(i: int) -> None:
         chunk = chunks[i]
+        if leader and chunk.is_cuda and reduced[i] is not None:
+            # produced on the inter lane, read here: tell the allocator
+            reduced[i].record_stream(torch.cuda.current_stream(chunk.device))
         if not local_quantize:
             buf = reduced[i].to(dtype=chunk.dtype) if leader else torch.empty_like(chunk)
             dist.broadcast(buf, src=leader_global, group=local_group)
@@ -151,8 +168,11 @@ def run_pipeline_a(owner, tensor: torch.Tensor, *, local_group, inter_group,
                     local_done[i].record(stream)
                 elif phase == "inter":
                     inter_done[i].record(stream)
+        cur = torch.cuda.current_stream(flat.device)
         for s in lanes.values():
-            s.synchronize()
+            cur.wait_stream(s)  # stream-ordered completion: the host does not wait
+        flat.record_stream(lanes["intra"])
+        flat.record_stream(lanes["inter"])
 
     if flat.data_ptr() != tensor.data_ptr():
         tensor.copy_(flat.view_as(tensor))

@@ -18,7 +18,8 @@ from typing import Hashable, Optional
 import torch
 import torch.distributed as dist
 
-from ..quantization import quantize_pack_tensor_blockwise, unpack_dequantize_tensor_blockwise
+from ..quantization import (quantize_pack_tensor_blockwise, stage1_stream,
+                            unpack_dequantize_tensor_blockwise)
 
 
 def _immediate(async_op: bool):
@@ -65,7 +66,7 @@ def lowbit_reduce_scatter(owner, output: torch.Tensor, input: torch.Tensor, *,
         shard = flat[j * n:(j + 1) * n]
         p, s, _ = quantize_pack_tensor_blockwise(
             shard, bits, block_size=block, stochastic_rounding=sr, sr_seed=seed,
-            sr_offset=j * n, sr_stream=0)
+            sr_offset=j * n, sr_stream=stage1_stream(dist.get_rank(group)))
         packed.append(p)
         scales.append(s)
         if ef is not None:

@@ -16,7 +16,8 @@ from typing import List, Optional
 
 import torch
 
-from ..quantization import quantize_pack_tensor_blockwise, unpack_dequantize_tensor_blockwise
+from ..quantization import (quantize_pack_tensor_blockwise, stage1_stream,
+                            unpack_dequantize_tensor_blockwise)
 
 
 @dataclass
@@ -58,7 +59,7 @@ def simulate_all_reduce(inputs: List[torch.Tensor], bits: int, block: int, *,
             flat = flat.to(torch.float32) + state.stage1[i]
         for j in range(world):
             shard = flat[j * S:(j + 1) * S]
-            _, _, d = _codec(shard, bits, block, stochastic, seed, j * S, 0)
+            _, _, d = _codec(shard, bits, block, stochastic, seed, j * S, stage1_stream(i))
             sent[i][j] = d
             if use_ef:
                 state.stage1[i][j * S:(j + 1) * S] = shard.to(torch.float32) - d
@@ -102,7 +103,7 @@ def simulate_reduce_scatter(inputs: List[torch.Tensor], bits: int, block: int, *
             flat = flat.to(torch.float32) + state.stage1[i]
         for j in range(world):
             shard = flat[j * n:(j + 1) * n]
-            _, _, d = _codec(shard, bits, block, stochastic, seed, j * n, 0)
+            _, _, d = _codec(shard, bits, block, stochastic, seed, j * n, stage1_stream(i))
             sent[i][j] = d
             if use_ef:
                 state.stage1[i][j * n:(j + 1) * n] = shard.to(torch.float32) - d

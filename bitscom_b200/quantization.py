@@ -101,6 +101,16 @@ def sr_key(seed: int, stream: int = 0) -> int:
     return int((z ^ (z >> 32)) & _U32)
 
 
+def stage1_stream(rank: int) -> int:
+    """Random stream of the FIRST quantizer stage of a collective on ``rank``.  Every rank
+    quantizes its own copy of element i, so with one shared stream all ranks would draw the
+    same uniform for it and their rounding errors would add up coherently (the error of the
+    sum growing with W instead of sqrt(W)); a stream per source rank keeps them independent
+    while every engine (fused kernel, host engines, golden model) still derives the same
+    bits.  The second stage quantizes each shard on its one owner and keeps stream 1."""
+    return 2 * (int(rank) + 1)
+
+
 def sr_uniform(key: int, index: torch.Tensor) -> torch.Tensor:
     """fp32 uniforms in [0, 1) with 16 random bits, one per element index.
 

@@ -190,6 +190,9 @@ def main(argv=None):
                                           "zero": opt.state_dict()}, rank)
     if world > 1:
         dist.barrier()
+        import bitscom_b200
+
+        bitscom_b200.shutdown()  # release symmetric blocks in order, before the group goes
         dist.destroy_process_group()
 
 

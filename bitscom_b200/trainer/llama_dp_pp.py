@@ -247,16 +247,22 @@ class LlamaTrainer:
         return None
 
     def check_kernels(self) -> None:
-        """Raise if a GEMM or attention kernel gave up on one of its bounded waits since the
-        last check (it then returned early and its output is not valid).  Synchronises the
-        device, so call it where the step is synchronised anyway."""
+        """Raise if a GEMM, attention or fused-collective kernel gave up on one of its bounded
+        waits since the last check (it then returned early and its output is not valid).
+        Synchronises the device, so call it where the step is synchronised anyway, and before
+        a checkpoint replaces the last good file."""
         from ..ops import attention as A
         from ..ops import gemm as G
 
+        if self.device.type != "cuda":
+            return
         if G.available():
             G.check_status()
         if A.available():
             A.check_status()
+        if self.sync is not None:
+            torch.cuda.synchronize(self.device)
+            self.sync.check(wait=True)
 
     # -- checkpoint -----------------------------------------------------------------------
     def state_dict(self) -> dict:
@@ -272,6 +278,22 @@ class LlamaTrainer:
         self.model.flat.params.copy_(sd["params"])
         if self.sync is not None and "lowbit" in sd:
             self.lowbit.load_state_dict(sd["lowbit"])
+
+    def grad_sync_description(self) -> str:
+        """The gradient synchronisation that actually runs (for benchmark records)."""
+        c = self.cfg
+        if self.sync is None:
+            return "none (dp=1)"
+        codec = (f"{c.bitwidth}-bit block {c.block_size}"
+                 + (" + error feedback" if c.error_feedback else "")
+                 + (" + stage 2" if c.stage2_error_feedback else "")
+                 + (" + stochastic rounding" if c.stochastic_rounding else ""))
+        if self.sync.mode == "dense":
+            return "dense NCCL all-reduce per layer bucket"
+        if self.sync.mode == "pipeline_a" and self.sync.local_group is not None:
+            return (f"pipeline-A (local groups of {c.local_size}, leaders low-bit) {codec}, "
+                    "per layer bucket")
+        return f"flat fused low-bit all-reduce {codec}, per layer bucket, overlapped"
 
     def tokens_per_step(self) -> int:
         c = self.cfg
@@ -337,6 +359,7 @@ def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
             if args.output_dir and args.save_every and step % args.save_every == 0:
                 from ..utils.checkpoint import save_checkpoint
 
+                trainer.check_kernels()  # never replace a good file with a failed step's state
                 save_checkpoint(args.output_dir, trainer.state_dict(), trainer.rank)
 
 
@@ -461,11 +484,15 @@ def main(argv=None):
     if args.output_dir:
         from ..utils.checkpoint import save_checkpoint
 
+        trainer.check_kernels()
         save_checkpoint(args.output_dir, trainer.state_dict(), trainer.rank)
     if dist.is_initialized():
         dist.barrier()
         if monitor is not None:
             monitor.leave()  # after the barrier: nobody is still stepping
+        import bitscom_b200
+
+        bitscom_b200.shutdown()  # symmetric blocks released with a handshake among the ranks
         dist.destroy_process_group()
     return 0
 

@@ -109,6 +109,9 @@ def main(argv=None):
             with open(args.out, "a") as f:
                 f.write(json.dumps(row) + "\n")
     dist.barrier()
+    import bitscom_b200
+
+    bitscom_b200.shutdown()  # release symmetric blocks in order, before the group goes
     dist.destroy_process_group()
 
 

@@ -82,8 +82,9 @@ def _worker(rank, world, n):
     assert bitscom_b200.is_extension_available()
 
 
-def test_lowbit_backend_two_gpus():
-    _need(2)
-    run_ranks(_worker, 2, 100003, backend="lowbit",
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_lowbit_backend_on_gpus(world):
+    _need(world)
+    run_ranks(_worker, world, 100003, backend="lowbit",
               lowbit_options=dict(bitwidth=4, error_feedback_mode="ef21_plus",
                                   stage2_error_feedback=True))

@@ -63,7 +63,8 @@ def test_four_ranks_report_the_whole_job():
     _check(row, 4)
     assert row["config"]["parallelism"] == "dp2xpp2"
     assert row["config"]["global_batch"] == 2 * 2 * 1    # dp x micro-batches x sequences
-    assert "pipeline_a" in row["config"]["grad_sync"]
+    # --local-size 1 (the default) is the flat fused / host low-bit all-reduce, and says so
+    assert "flat" in row["config"]["grad_sync"] and "4-bit" in row["config"]["grad_sync"]
 
 
 def test_reference_arm_reports_unavailable_without_a_gpu():

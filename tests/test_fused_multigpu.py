@@ -1,6 +1,11 @@
-"""Fused collectives across real GPUs (one process per GPU, NCCL for the plumbing)."""
+"""Fused collectives across real GPUs (one process per GPU, NCCL for the plumbing).
+
+The golden model (``parallel/simulate.py``: the wire protocol replayed with the host quantizer)
+runs ONCE, in the parent, and every rank loads its inputs and its expected bits from a file:
+W ranks that each replay W quantizers compete for the same cores and tell nothing new."""
 
 import os
+import tempfile
 
 import pytest
 import torch
@@ -22,20 +27,38 @@ def _input(rank, n, it, dtype):
     return (torch.randn(n, generator=g) * 1e-3).to(dtype)
 
 
-def _worker(rank, world, n, bits, dtype, iters):
-    from bitscom_b200 import LowBitGroup
-
-    torch.set_num_threads(1)  # every rank replays the golden model on the CPU
-
-    group = LowBitGroup(bitwidth=bits, error_feedback=True, stage2_error_feedback=True,
-                        stochastic_rounding=True, sr_seed=5, fused=True)
+def _golden(folder, world, n, bits, dtype, iters, stochastic=True):
+    """Per rank: ``{"inputs": [iters tensors], "wants": [iters tensors]}`` in
+    ``folder/rank<r>.pt``.  Seeds follow ``LowBitGroup._next_sr_seed`` for ``sr_seed=5``."""
     state = SimState()
+    per_rank = [{"inputs": [], "wants": []} for _ in range(world)]
     for it in range(iters):
         everyone = [_input(r, n, it, dtype) for r in range(world)]
         seed = (5 * 0x9E3779B97F4A7C15 + it + 1) & 0xFFFFFFFFFFFFFFFF
-        want = simulate_all_reduce(everyone, bits, 256, stochastic=True, seed=seed,
-                                   state=state, stage2=True)[rank]
-        x = everyone[rank].cuda()
+        outs = simulate_all_reduce(everyone, bits, 256, stochastic=stochastic,
+                                   seed=seed if stochastic else None, state=state, stage2=True)
+        for r in range(world):
+            per_rank[r]["inputs"].append(everyone[r])
+            per_rank[r]["wants"].append(outs[r].clone())
+    for r in range(world):
+        torch.save(per_rank[r], os.path.join(folder, f"rank{r}.pt"))
+
+
+def _run_with_golden(worker, world, n, bits, dtype, iters, stochastic=True, **kw):
+    with tempfile.TemporaryDirectory() as folder:
+        _golden(folder, world, n, bits, dtype, iters, stochastic)
+        run_ranks(worker, world, folder, n, bits, dtype, iters, backend="nccl", **kw)
+
+
+def _worker(rank, world, folder, n, bits, dtype, iters):
+    from bitscom_b200 import LowBitGroup
+
+    gold = torch.load(os.path.join(folder, f"rank{rank}.pt"))
+    group = LowBitGroup(bitwidth=bits, error_feedback=True, stage2_error_feedback=True,
+                        stochastic_rounding=True, sr_seed=5, fused=True)
+    for it in range(iters):
+        want = gold["wants"][it]
+        x = gold["inputs"][it].cuda()
         if it % 2:
             group.all_reduce(x, async_op=True, ef_key="b").wait()
         else:
@@ -66,51 +89,61 @@ def _worker(rank, world, n, bits, dtype, iters):
     dense = full.float().clone()
     dist.all_reduce(dense)
     rel = (back.float() - dense).norm() / dense.norm()
-    assert rel < {2: 2.5, 4: 0.5}[bits], rel
+    assert torch.isfinite(rel)
+    if bits > 1:  # the 1-bit code keeps magnitudes only: no meaningful distance to the dense sum
+        assert rel < {2: 2.5, 4: 0.5}[bits], rel
 
 
 @pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
                                           (2, torch.bfloat16, 300001)])
 def test_two_gpu_all_reduce_bit_exact(bits, dtype, n):
     _need(2)
-    run_ranks(_worker, 2, n, bits, dtype, 3, backend="nccl")
+    _run_with_golden(_worker, 2, n, bits, dtype, 3)
 
 
-def test_all_gpus_all_reduce_bit_exact():
-    n_gpus = torch.cuda.device_count() if torch.cuda.is_available() else 0
-    if n_gpus < 4:
-        pytest.skip("needs 4 or more GPUs")
-    run_ranks(_worker, n_gpus, 1 << 17, 4, torch.float32, 2, backend="nccl", timeout=600)
+@pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
+                                          (1, torch.bfloat16, 300001)])
+def test_four_gpu_all_reduce_bit_exact(bits, dtype, n):
+    _need(4)
+    _run_with_golden(_worker, 4, n, bits, dtype, 3)
+
+
+@pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
+                                          (4, torch.bfloat16, 3000001)])
+def test_eight_gpu_all_reduce_bit_exact(bits, dtype, n):
+    _need(8)
+    _run_with_golden(_worker, 8, n, bits, dtype, 3)
 
 
 @pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
                     reason="the NVLS (multimem) path has not been run on GPUs yet; "
                            "set BITSCOM_EXPERIMENTAL=1 to try it")
+@pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
                                           (8, torch.bfloat16, 300032)])
-def test_two_gpu_all_reduce_bit_exact_over_nvls(bits, dtype, n, monkeypatch):
+def test_all_reduce_bit_exact_over_nvls(world, bits, dtype, n, monkeypatch):
     """The same bit-exact check with the all-gather half on multimem stores (the children
     inherit the environment).  Not for failure tests: a rank that dies while its memory is
     bound to a multicast object can fault its peers."""
-    _need(2)
+    _need(world)
     monkeypatch.setenv("BITSCOM_NVLS", "1")
     monkeypatch.setenv("BITSCOM_REQUIRE_NVLS", "1")
-    run_ranks(_worker8 if bits == 8 else _worker, 2, n, bits, dtype, 3, backend="nccl")
+    _run_with_golden(_worker8 if bits == 8 else _worker, world, n, bits, dtype, 3,
+                     stochastic=bits != 8)
 
 
-def _worker8(rank, world, n, bits, dtype, iters):
+def _worker8(rank, world, folder, n, bits, dtype, iters):
     """8-bit goes through the communicator directly (LowBitGroup all-reduces 8-bit densely)."""
     from bitscom_b200.api import ErrorFeedbackState
     from bitscom_b200.parallel.fused import FusedLowBitComm
 
-    torch.set_num_threads(1)
+    gold = torch.load(os.path.join(folder, f"rank{rank}.pt"))
     comm = FusedLowBitComm.for_group(dist.group.WORLD, torch.device("cuda", rank))
     assert comm.multicast or not os.environ.get("BITSCOM_REQUIRE_NVLS")
-    state, ef = SimState(), ErrorFeedbackState()
+    ef = ErrorFeedbackState()
     for it in range(iters):
-        everyone = [_input(r, n, it, dtype) for r in range(world)]
-        want = simulate_all_reduce(everyone, bits, 256, state=state, stage2=True)[rank]
-        x = everyone[rank].cuda()
+        want = gold["wants"][it]
+        x = gold["inputs"][it].cuda()
         comm.all_reduce(x, bitwidth=bits, block_size=256, ef=ef, stage2=True)
         torch.cuda.synchronize()
         assert torch.equal(x.cpu(), want), f"rank {rank} iter {it}"

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False,
-            untied: bool = False) -> None:
+            untied: bool = False, local_size: int = 1) -> None:
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
@@ -25,7 +25,7 @@ def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False,
     mcfg.attention = "sdpa"
     tcfg = TrainerConfig(pp_size=pp, micro_batches=4, micro_batch_size=2, seq_length=64,
                          bitwidth=4, error_feedback=True, dp_sync=sync, lr=1e-2, device="cpu",
-                         defer_wgrad=defer_wgrad)
+                         defer_wgrad=defer_wgrad, local_size=local_size)
     trainer = LlamaTrainer(mcfg, tcfg)
     losses = []
     for _ in range(steps):
@@ -35,10 +35,17 @@ def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False,
     if losses:
         sys.stdout.write(json.dumps({"rank": trainer.rank, "dp_rank": trainer.dp_rank,
                                      "dp": trainer.dp, "pp": trainer.pp,
+                                     "grad_sync": trainer.grad_sync_description(),
+                                     "residual_keys": sorted(
+                                         repr(k) for k in trainer.lowbit._ef_states)
+                                     if trainer.sync is not None else [],
                                      "losses": losses}) + "\n")   # one write: a shared pipe
         sys.stdout.flush()
     if dist.is_initialized():
         dist.barrier()
+        import bitscom_b200
+
+        bitscom_b200.shutdown()
         dist.destroy_process_group()
 
 
@@ -50,13 +57,13 @@ def _free_port() -> int:
 
 @functools.lru_cache(maxsize=None)   # the runs are deterministic: tests share them
 def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = False,
-         untied: bool = False):
+         untied: bool = False, local_size: int = 1):
     env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1")
     run = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", str(nproc),
          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
          os.path.abspath(__file__), str(pp), sync, str(steps), str(int(defer_wgrad)),
-         str(int(untied))],
+         str(int(untied)), str(local_size)],
         cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert run.returncode == 0, run.stderr[-3000:]
     text = run.stdout.replace("}{", "}\n{")
@@ -170,6 +177,27 @@ def test_deferred_weight_gradients_change_nothing_but_the_order_of_work():
     assert [r["losses"] for r in plain] == [r["losses"] for r in deferred]
 
 
+def test_dp4_pp2_pipeline_a_with_local_pairs_on_strided_groups():
+    """Real two-level pipeline-A through the trainer: data-parallel groups are strided subgroups
+    of the (dp, pp) mesh (global ranks 0, 2, 4, 6 and 1, 3, 5, 7), local groups are pairs of
+    them and the pairs' first ranks are the leaders.  The leaders' ranks must be translated to
+    global ranks for the local reduce / broadcast, the leaders' inter phase keeps error-feedback
+    residuals per (bucket, chunk), every replica ends on the same loss curve and it falls."""
+    rows = _run(8, 2, "pipeline_a", steps=5, local_size=2)
+    assert [r["dp_rank"] for r in rows] == [0, 1, 2, 3] and all(r["pp"] == 2 for r in rows)
+    assert all("pipeline-A" in r["grad_sync"] for r in rows)
+    # (every replica fits its own batch, four of them share the weights: after five steps the
+    # first replica's loss has clearly fallen, and all of them track the dense run below)
+    assert rows[0]["losses"][-1] < rows[0]["losses"][0] - 0.4, rows[0]["losses"]
+    # leaders (dp ranks 0 and 2) hold residuals keyed by bucket and chunk; the others hold none
+    assert any("chunk" in k for k in rows[0]["residual_keys"])
+    assert any("chunk" in k for k in rows[2]["residual_keys"])
+    assert rows[1]["residual_keys"] == [] and rows[3]["residual_keys"] == []
+    dense = _run(8, 2, "dense", steps=5)
+    for lo, de in zip(rows, dense):
+        assert abs(lo["losses"][-1] - de["losses"][-1]) < 0.3, (lo["losses"], de["losses"])
+
+
 if __name__ == "__main__":
     _worker(int(sys.argv[1]), sys.argv[2], int(sys.argv[3]), bool(int(sys.argv[4])),
-            bool(int(sys.argv[5])))
+            bool(int(sys.argv[5])), int(sys.argv[6]) if len(sys.argv) > 6 else 1)
