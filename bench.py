@@ -61,7 +61,8 @@ def run_ours(args):
     tcfg = TrainerConfig(pp_size=pp, micro_batches=args.micro_batches or 4 * pp,
                          micro_batch_size=args.micro_batch_size, seq_length=seq, bitwidth=4,
                          error_feedback=True, dp_sync=args.dp_sync, local_size=args.local_size,
-                         defer_wgrad=args.defer_wgrad, device=args.device)
+                         defer_wgrad=args.defer_wgrad, device=args.device,
+                         sync_max_ctas=args.sync_ctas)
     if args.impl == "torch":
         from bitscom_b200.ops import gemm as G
 
@@ -128,6 +129,12 @@ def run_ours(args):
     # where the native launch functions are called (ops/_native.py)
     launches = _native.launch_count() - launches_before
     clocks = sampler.stop() if rank == 0 else None
+    # where the device-timed steps went, per rank, then the slowest rank's figure of each phase
+    breakdown = trainer.step_breakdown(last=args.steps) if cuda else None
+    if breakdown is not None and world > 1:
+        box = torch.tensor([breakdown[k] for k in sorted(breakdown)], device=dev)
+        dist.all_reduce(box, op=dist.ReduceOp.MAX)
+        breakdown = {k: float(v) for k, v in zip(sorted(breakdown), box.tolist())}
     ms_e2e, loss_e2e = timed(args.steps, True, args.warmup + args.steps)
     trainer.check_kernels()  # a kernel that gave up on a bounded wait must not yield a number
 
@@ -168,6 +175,10 @@ def run_ours(args):
         "clocks": clocks,
         "loss": loss_dev,
     }
+    if breakdown is not None:
+        out["step_breakdown_ms"] = dict(breakdown, note="max over ranks of each phase, device "
+                                        "time on the compute stream; exposed_grad_sync = wait "
+                                        "for gradient buckets after backward had ended")
     if allreduce is not None:
         out["allreduce"] = allreduce
     if rank == 0:
@@ -225,9 +236,13 @@ def main():
     ap.add_argument("--allreduce-mb", type=float, nargs="+", default=[64, 1024],
                     help="bucket sizes (MB) of the all-reduce block reported at N >= 2")
     ap.add_argument("--no-allreduce-block", action="store_true")
-    ap.add_argument("--defer-wgrad", action="store_true",
+    ap.add_argument("--sync-ctas", type=int, default=148,
+                    help="grid cap of gradient buckets launched while backward is still "
+                         "running (0 = no cap)")
+    ap.add_argument("--defer-wgrad", action="store_true", default=True,
                     help="pipeline stages send the input gradient before running the "
-                         "weight-gradient GEMMs (off by default)")
+                         "weight-gradient GEMMs (the default; measured faster at dp2 x pp2)")
+    ap.add_argument("--no-defer-wgrad", dest="defer_wgrad", action="store_false")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

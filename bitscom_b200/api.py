@@ -730,10 +730,12 @@ class LowBitGroup:
         group: Optional[dist.ProcessGroup] = None,
         post_scale: float = 1.0,
         ef_key: Optional[Hashable] = None,
+        max_ctas: Optional[int] = None,
     ):
         """Enqueue the whole all-reduce on ``stream`` and return an event-backed handle
         (``wait`` / ``block_current_stream`` / ``is_completed``); ``post_scale`` is
-        applied to the result on the same stream (reference ``api.py:577-629``)."""
+        applied to the result on the same stream (reference ``api.py:577-629``).
+        ``max_ctas`` caps the fused kernel's grid for launches that overlap other kernels."""
         self._precheck()
         pg = group or self.pg
         lowbit = op == dist.ReduceOp.SUM and self._should_use_lowbit_path_for_group(op, pg)
@@ -758,7 +760,8 @@ class LowBitGroup:
                 done.record(stream)
             return _CudaEventWork(done)
         return self._lowbit_allreduce_via_alltoall_stream_(
-            tensor, pg, stream=stream, post_scale=post_scale, ef_key=ef_key)
+            tensor, pg, stream=stream, post_scale=post_scale, ef_key=ef_key,
+            max_ctas=max_ctas)
 
     def _should_use_lowbit_path(self, op) -> bool:
         return self.bitwidth < 8 and self.world_size > 1 and op == dist.ReduceOp.SUM
@@ -839,7 +842,8 @@ class LowBitGroup:
 
     def _lowbit_allreduce_via_alltoall_stream_(self, tensor: torch.Tensor, group, *,
                                                stream, post_scale: float,
-                                               ef_key: Optional[Hashable] = None):
+                                               ef_key: Optional[Hashable] = None,
+                                               max_ctas: Optional[int] = None):
         """Stream-ordered variant; the caller has already ordered ``stream`` after the
         producer of ``tensor``."""
         done = torch.cuda.Event()
@@ -853,7 +857,8 @@ class LowBitGroup:
                 comm.all_reduce(
                     tensor, bitwidth=self.bitwidth, block_size=self.block_size,
                     stochastic=self.stochastic_rounding, seed=self._next_sr_seed(), ef=ef,
-                    stage2=self.stage2_error_feedback, post_scale=post_scale)
+                    stage2=self.stage2_error_feedback, post_scale=post_scale,
+                    max_ctas=max_ctas)
                 done.record(stream)
                 return _CudaEventWork(done, on_complete=comm.check_status)
             keep: list = []

@@ -158,6 +158,14 @@ def main(argv=None):
                     w = csv.writer(f)
                     w.writerow(["step", "rel_error", "lowbit_ms", "baseline_ms"])
                     w.writerows(rows)
+                from ..utils.plot import save_line_plot
+
+                steps = [r[0] for r in rows]
+                save_line_plot(path[:-4] + ".png",
+                               {"lowbit_ms": (steps, [r[2] for r in rows]),
+                                "baseline_ms": (steps, [r[3] for r in rows])},
+                               title=f"{args.collective} bw{bw} world {world}: time per call",
+                               xlabel="step", ylabel="ms")
     dist.barrier()
     import bitscom_b200
 

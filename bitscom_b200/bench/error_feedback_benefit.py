@@ -78,6 +78,14 @@ def main(argv=None):
                 w = csv.writer(f)
                 w.writerow(["step", "no_ef_rel_error", "ef_rel_error"])
                 w.writerows(rows)
+            from ..utils.plot import save_line_plot
+
+            steps = [r[0] for r in rows]
+            save_line_plot(os.path.join(args.out_dir, f"ef_comparison_bw{b}.png"),
+                           {"no error feedback": (steps, [r[1] for r in rows]),
+                            "error feedback": (steps, [r[2] for r in rows])},
+                           title=f"relative cumulative error, {b}-bit", xlabel="step",
+                           ylabel="rel err", logy=True)
 
 
 if __name__ == "__main__":

@@ -284,6 +284,12 @@ def save_outputs(out_dir: str, name: str, bitwidth: int, window: int,
             row += [runs[a]["losses"][i] if i < len(runs[a]["losses"]) else "" for a in arms]
             row += [smooth[a][i] if i < len(smooth[a]) else "" for a in arms]
             w.writerow(row)
+    from ..utils.plot import save_line_plot
+
+    save_line_plot(curve[:-4] + ".png",
+                   {a: (list(range(1, len(smooth[a]) + 1)), smooth[a]) for a in arms},
+                   title=f"{name} loss (moving average {window}), {bitwidth}-bit",
+                   xlabel="step", ylabel="loss")
     thr = os.path.join(out_dir, f"{name}_throughput_bw{bitwidth}.csv")
     with open(thr, "w", newline="") as f:
         w = csv.writer(f)

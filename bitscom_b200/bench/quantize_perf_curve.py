@@ -140,6 +140,15 @@ def main(argv=None) -> List[Dict[str, float]]:
             w.writeheader()
             w.writerows(rows)
         print(f"saved {path}")
+        from ..utils.plot import save_line_plot
+
+        xs = [r["numel"] for r in rows]
+        series = {k: (xs, [r[k] for r in rows]) for k in
+                  ("cpu_torch_ms", "cpu_native_ms", "gpu_ms", "gpu_device_ms")
+                  if all(isinstance(r.get(k), (int, float)) for r in rows)}
+        save_line_plot(path[:-4] + ".png", series,
+                       title=f"quantize latency, {args.mode}, {args.bitwidth}-bit",
+                       xlabel="elements", ylabel="ms", logx=True, logy=True)
     return rows
 
 

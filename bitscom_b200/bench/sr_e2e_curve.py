@@ -128,6 +128,12 @@ def main(argv=None):
                 w.writerow(["step"] + [f"loss_{k}" for k in curves])
                 for i in range(args.steps):
                     w.writerow([i + 1] + [curves[k][i] for k in curves])
+            from ..utils.plot import save_line_plot
+
+            steps = list(range(1, args.steps + 1))
+            save_line_plot(path[:-4] + ".png", {k: (steps, v) for k, v in curves.items()},
+                           title=f"TinyMLP loss, {args.bitwidth}-bit, world {world}",
+                           xlabel="step", ylabel="loss")
     dist.barrier()
     import bitscom_b200
 

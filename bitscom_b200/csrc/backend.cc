@@ -212,7 +212,7 @@ class ProcessGroupLowBit : public c10d::Backend {
   bool fused_ok(const at::Tensor& t) const {
     const int b = options_.bitwidth;
     return t.is_cuda() && t.is_contiguous() && dtype_code(t.scalar_type()) >= 0 &&
-           (b == 1 || b == 2 || b == 4 || b == 8) &&
+           (b == 1 || b == 2 || b == 4 || b == 8 || b == 12) &&
            bcom_collective_supported(dtype_code(t.scalar_type()), b, options_.block_size);
   }
   bool use_lowbit_allreduce(const at::Tensor& t, const c10d::AllreduceOptions& opts) const {

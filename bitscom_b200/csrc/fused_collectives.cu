@@ -94,9 +94,13 @@ __device__ __forceinline__ Packed8<BITS> load_group_cg(const unsigned char* base
     p.w[0] = __ldcg(reinterpret_cast<const unsigned short*>(src));
   } else if constexpr (BITS == 4) {
     p.w[0] = __ldcg(reinterpret_cast<const unsigned int*>(src));
-  } else {
+  } else if constexpr (BITS == 8) {
     const uint2 v = __ldcg(reinterpret_cast<const uint2*>(src));
     p.w[0] = v.x; p.w[1] = v.y;
+  } else {
+    static_assert(BITS == 12, "fused kernel: 1, 2, 4, 8 or 12 bits");
+    const unsigned int* s3 = reinterpret_cast<const unsigned int*>(src);  // 12-byte groups
+    p.w[0] = __ldcg(s3); p.w[1] = __ldcg(s3 + 1); p.w[2] = __ldcg(s3 + 2);
   }
   return p;
 }
@@ -464,6 +468,7 @@ static bool pick_bits(int bits, bool sr, bool aligned, RealKernel* real, EmuKern
     case 2: pick<T, 2>(sr, aligned, real, emu); return true;
     case 4: pick<T, 4>(sr, aligned, real, emu); return true;
     case 8: pick<T, 8>(sr, aligned, real, emu); return true;
+    case 12: pick<T, 12>(sr, aligned, real, emu); return true;
     default: return false;
   }
 }

@@ -54,7 +54,7 @@ typedef struct {
   long long n;
   long long S;
   int dtype;       // 0 fp32, 1 fp16, 2 bf16
-  int bits;        // 1, 2, 4, 8
+  int bits;        // 1, 2, 4, 8, 12
   int block;       // 8 * power of two, <= 256
   int mode;        // BCOM_MODE_*
   int stochastic;  // 0 nearest, 1 stochastic rounding

@@ -28,7 +28,7 @@ from ..quantization import sr_key, stage1_stream
 from ..utils import timing as _timing
 
 MODE_ALL_REDUCE, MODE_REDUCE_SCATTER, MODE_ALL_GATHER = 0, 1, 2
-FUSED_BITS = (1, 2, 4, 8)
+FUSED_BITS = (1, 2, 4, 8, 12)
 
 _STATUS_TEXT = {
     1: "a peer never announced its packed shards (phase-1 flags)",
@@ -417,8 +417,13 @@ class FusedLowBitComm:
 
     def all_reduce(self, tensor: torch.Tensor, *, bitwidth: int, block_size: int,
                    stochastic: bool = False, seed: Optional[int] = None, ef=None,
-                   stage2: bool = False, post_scale: float = 1.0, async_op: bool = False):
-        """In-place low-bit sum of a contiguous CUDA tensor over the group."""
+                   stage2: bool = False, post_scale: float = 1.0, async_op: bool = False,
+                   max_ctas: Optional[int] = None):
+        """In-place low-bit sum of a contiguous CUDA tensor over the group.  ``max_ctas`` caps
+        the kernel's grid (default: the communicator's setting, 0 = as many CTAs as fit an
+        empty GPU): a launch that has to run NEXT TO other kernels (gradient buckets under a
+        persistent GEMM) must be small enough to become co-resident with them, because every
+        CTA of the cooperative grid has to be on the device before the first flag wait ends."""
         from ..api import ShardPlan
 
         n = int(tensor.numel())
@@ -430,8 +435,8 @@ class FusedLowBitComm:
             ef.ensure(plan, tensor.device, stage2)
             res1, res2 = ef.stage1, (ef.stage2 if stage2 else None)
         args = _args(tensor, tensor, res1, res2, n, plan.shard_len, tensor.dtype, bitwidth,
-                     block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale, self.max_ctas,
-                     self.rank)
+                     block_size, MODE_ALL_REDUCE, stochastic, seed, post_scale,
+                     self.max_ctas if max_ctas is None else int(max_ctas), self.rank)
         return self._launch(args, async_op, (tensor, res1, res2))
 
     def reduce_scatter(self, output: torch.Tensor, input: torch.Tensor, *, bitwidth: int,

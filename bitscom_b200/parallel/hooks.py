@@ -27,7 +27,7 @@ class GradBucketSync:
     def __init__(self, lowbit_group, flat_grads: torch.Tensor,
                  ranges: Sequence[Tuple[int, int]], *, mode: str = "flat",
                  local_group=None, inter_group=None, chunk_size: Optional[int] = None,
-                 average: bool = True, overlap: bool = True):
+                 average: bool = True, overlap: bool = True, max_ctas: Optional[int] = None):
         if mode not in ("flat", "pipeline_a", "dense"):
             raise ValueError(f"unknown mode {mode!r}")
         self.group = lowbit_group
@@ -39,6 +39,10 @@ class GradBucketSync:
         self.world = lowbit_group.world_size
         self.post_scale = 1.0 / self.world if average else 1.0
         self.overlap = overlap and flat_grads.is_cuda
+        # grid cap of the fused kernel for buckets launched WHILE backward is still running:
+        # the cooperative grid must fit next to the compute kernels that own the SMs then
+        self.max_ctas = max_ctas
+        self._overlapping = False
         self.stream = torch.cuda.Stream(device=flat_grads.device) if flat_grads.is_cuda else None
         self._works: List = []
         self._launched = set()
@@ -63,7 +67,8 @@ class GradBucketSync:
         elif bucket.is_cuda:
             self._works.append(self.group.all_reduce_stream(
                 bucket, stream=torch.cuda.current_stream(bucket.device),
-                post_scale=self.post_scale, ef_key=key))
+                post_scale=self.post_scale, ef_key=key,
+                max_ctas=self.max_ctas if self._overlapping else None))
         else:
             self.group.all_reduce(bucket, ef_key=key)
             if self.post_scale != 1.0:
@@ -82,6 +87,15 @@ class GradBucketSync:
         self.stream.wait_stream(cur)
         with torch.cuda.stream(self.stream):
             self._launch(idx)
+
+    def on_ready_overlapped(self, idx: int) -> None:
+        """``on_ready`` for a bucket that becomes final while compute kernels keep running (a
+        layer of the last micro-batch's backward): launched with the grid cap."""
+        self._overlapping = True
+        try:
+            self.on_ready(idx)
+        finally:
+            self._overlapping = False
 
     def check(self, wait: bool = False) -> None:
         """Raise ``FusedCollectiveError`` if a fused kernel of this group gave up on a bounded

@@ -51,8 +51,9 @@ class TrainerConfig:
     dp_sync: str = "pipeline_a"   # "pipeline_a" | "flat" | "dense"
     local_size: int = 1           # ranks per local group of pipeline-A
     overlap: bool = True
+    sync_max_ctas: int = 148      # grid cap of gradient buckets launched under backward (0: none)
     simulate_quantization: bool = False   # reference flag: quantize round trip before dense ops
-    defer_wgrad: bool = False  # pipeline stages send input gradients before weight-gradient GEMMs
+    defer_wgrad: bool = True   # pipeline stages send input gradients before weight-gradient GEMMs
     device: str = "cuda"       # "cpu": CPU ranks over gloo with the ops' host paths (plumbing)
     pg_timeout_s: Optional[float] = None  # process-group timeout (None: torch's default)
     lr: float = 1e-4
@@ -136,9 +137,11 @@ class LlamaTrainer:
                 local_group, inter_group = self._hierarchy(cfg.local_size)
             self.sync = GradBucketSync(
                 self.lowbit, flat.grads, self._sync_ranges(), mode=mode,
-                local_group=local_group, inter_group=inter_group, overlap=cfg.overlap)
+                local_group=local_group, inter_group=inter_group, overlap=cfg.overlap,
+                max_ctas=cfg.sync_max_ctas or None)
         self.step_count = 0
         self._pinned: Optional[torch.Tensor] = None
+        self._marks: List[tuple] = []   # per step: CUDA events at the phase boundaries
 
     # -- topology helpers --------------------------------------------------------------
     def _hierarchy(self, local_size: int):
@@ -189,8 +192,19 @@ class LlamaTrainer:
         if layer == self.model.layer_range[1] - 1:
             for key in ("lm_head", "final_norm"):
                 if key in self._range_index:
-                    self.sync.on_ready(self._range_index[key])
-        self.sync.on_ready(self._range_index[f"l{layer}"])
+                    self.sync.on_ready_overlapped(self._range_index[key])
+        self.sync.on_ready_overlapped(self._range_index[f"l{layer}"])
+
+    def _layer_done_after_deferred(self, layer: int) -> None:
+        """``_layer_done`` for a backward whose weight-gradient GEMMs are queued: the bucket of
+        the layer is launched from the queue, right behind those GEMMs."""
+        from ..parallel.deferred import DeferredWork
+
+        queue = DeferredWork.active()
+        if queue is None:
+            self._layer_done(layer)
+        else:
+            queue.add(lambda: self._layer_done(layer))
 
     # -- data ---------------------------------------------------------------------------
     def synthetic_batch(self, step: int, pinned: bool = True) -> torch.Tensor:
@@ -206,6 +220,7 @@ class LlamaTrainer:
         """``ids``: ``[micro_batches, micro_batch_size, seq]`` int64, pinned host or device.
         Returns the mean loss as a device scalar on the last stage, else ``None``."""
         c = self.cfg
+        t_start = self._event() if self.device.type == "cuda" else None
         ids = ids_host_or_dev.to(self.device, non_blocking=True)
         model = self.model
         scale = 1.0 / c.micro_batches
@@ -215,12 +230,13 @@ class LlamaTrainer:
 
         def forward_fn(mb: int, x: Optional[torch.Tensor]):
             # with deferred weight gradients the last backward's GEMMs run after its input
-            # gradient has been sent (the deferral that shortens the pipeline's drain), so the
-            # per-layer bucket launches, which need finished gradients, give way to one sync
-            # after the step
-            model.on_layer_backward = self._layer_done if (
-                mb == last_mb and self.sync is not None and c.overlap
-                and not (c.defer_wgrad and self.runner is not None)) else None
+            # gradient has been sent (the deferral that shortens the pipeline's drain); the
+            # per-layer bucket launches, which need finished gradients, then ride in the same
+            # queue, each behind the weight-gradient GEMMs of its layer
+            model.on_layer_backward = None
+            if mb == last_mb and self.sync is not None and c.overlap:
+                model.on_layer_backward = self._layer_done_after_deferred if (
+                    c.defer_wgrad and self.runner is not None) else self._layer_done
             if not model.is_first:
                 model.set_shape(c.micro_batch_size, c.seq_length)
             inp = ids[mb] if model.is_first else x
@@ -238,13 +254,46 @@ class LlamaTrainer:
             losses = self.runner.run(c.micro_batches, forward_fn)
 
         model.on_layer_backward = None
+        marks = self._mark_begin(t_start) if self.device.type == "cuda" else None
         if self.sync is not None:
             self.sync.finish()
+        if marks is not None:
+            marks.append(self._event())
         self.opt.step(grad_scale=1.0, zero_grad=True)
+        if marks is not None:
+            marks.append(self._event())
+            self._marks.append(tuple(marks))
+            del self._marks[:-64]
         self.step_count += 1
         if model.is_last:
             return torch.stack(losses).sum()
         return None
+
+    # -- where the step's time goes ---------------------------------------------------------
+    def _event(self):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(self.device))
+        return ev
+
+    def _mark_begin(self, t_start):
+        return [t_start, self._event()]
+
+    def step_breakdown(self, last: int = 0) -> Optional[dict]:
+        """Device time of the phases of the last ``last`` steps (0 = all recorded, at most 64),
+        in ms per step, on this rank's compute stream: ``fwd_bwd`` (micro-batches, pipeline
+        waits included), ``exposed_grad_sync`` (what the compute stream still had to wait for
+        after backward had ended: gradient buckets not hidden behind it) and ``optimizer``.
+        Synchronises the device."""
+        if not self._marks:
+            return None
+        torch.cuda.synchronize(self.device)
+        rows = self._marks[-last:] if last else self._marks
+        out = {"fwd_bwd": 0.0, "exposed_grad_sync": 0.0, "optimizer": 0.0}
+        for t0, t1, t2, t3 in rows:
+            out["fwd_bwd"] += t0.elapsed_time(t1)
+            out["exposed_grad_sync"] += t1.elapsed_time(t2)
+            out["optimizer"] += t2.elapsed_time(t3)
+        return {k: v / len(rows) for k, v in out.items()}
 
     def check_kernels(self) -> None:
         """Raise if a GEMM, attention or fused-collective kernel gave up on one of its bounded
@@ -376,9 +425,11 @@ def main(argv=None):
     ap.add_argument("--no_error_feedback", action="store_true")
     ap.add_argument("--dp_sync", default="pipeline_a", choices=["pipeline_a", "flat", "dense"])
     ap.add_argument("--local_size", type=int, default=1)
-    ap.add_argument("--defer_wgrad", action="store_true",
+    ap.add_argument("--defer_wgrad", action="store_true", default=True,
                     help="pipeline stages run weight-gradient GEMMs after sending the input "
-                         "gradient (shrinks the 1F1B bubble)")
+                         "gradient (shrinks the 1F1B bubble; the default)")
+    ap.add_argument("--no_defer_wgrad", dest="defer_wgrad", action="store_false",
+                    help="weight-gradient GEMMs inside backward, before the input gradient goes")
     ap.add_argument("--max_steps", type=int, default=10)
     ap.add_argument("--epochs", type=int, default=1)
     ap.add_argument("--dataset", default="synthetic",

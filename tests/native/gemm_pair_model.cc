@@ -2,12 +2,14 @@
 // tests/test_gemm_pair_model.py.
 //
 // Threads: per CTA of the pair a TMA producer and four epilogue warps; the leader's MMA issuer;
-// the odd CTA's stage forwarder; one tensor pipe that executes the issued MMAs and commits in
-// order; one copy engine per CTA that completes loads after a random delay.  mbarriers carry an
-// arrival count and a phase, waits are parity waits, ring stages and accumulator buffers carry
-// a tag (which k-block / which tile they hold) and a count of asynchronous readers.
+// one tensor pipe that executes the issued MMAs and commits in order; one copy engine per CTA
+// that completes loads after a random delay.  Both CTAs' loads of a stage complete on the
+// LEADER's "stage full" barrier, which the leader's producer arms for the bytes of both (modelled
+// as three arrivals: the arming and one per CTA's bytes).  mbarriers carry an arrival count and
+// a phase, waits are parity waits, ring stages and accumulator buffers carry a tag (which
+// k-block / which tile they hold) and a count of asynchronous readers.
 //
-//   -DBUG=1  the issuer does not wait for the odd CTA's stage                (must be detected)
+//   -DBUG=1  the leader's barrier counts its own CTA's bytes only            (must be detected)
 //   -DBUG=2  the accumulator hand-back barrier counts one CTA's warps only   (must be detected)
 //   -DBUG=3  the stage-release commit reaches the leader only                (must be detected)
 #include <atomic>
@@ -97,9 +99,9 @@ static void nap(std::mt19937& rng, int max_us) {
 struct Pair {
   int tiles, num_kb;
   // per CTA
-  MBar full[2][STAGES], empty[2][STAGES], acc_full[2][2];
+  MBar empty[2][STAGES], acc_full[2][2];
   // leader only
-  MBar peer_full[STAGES], acc_empty[2];
+  MBar full[STAGES], acc_empty[2];
   std::atomic<long long> stage_tag[2][STAGES];  // global k-block index held by the stage
   std::atomic<int> stage_readers[STAGES];       // MMAs reading the stage (in both CTAs)
   std::atomic<long long> acc_tag[2];            // tile whose sum the buffer holds
@@ -111,8 +113,15 @@ struct Pair {
 
   Pair(int t, int k) : tiles(t), num_kb(k) {
     for (int c = 0; c < 2; ++c)
-      for (int s = 0; s < STAGES; ++s) { full[c][s].init(1); empty[c][s].init(1); stage_tag[c][s] = -1; }
-    for (int s = 0; s < STAGES; ++s) { peer_full[s].init(1); stage_readers[s] = 0; }
+      for (int s = 0; s < STAGES; ++s) { empty[c][s].init(1); stage_tag[c][s] = -1; }
+    for (int s = 0; s < STAGES; ++s) {
+#if BUG == 1
+      full[s].init(2);
+#else
+      full[s].init(3);
+#endif
+      stage_readers[s] = 0;
+    }
     for (int b = 0; b < 2; ++b) {
       acc_full[0][b].init(1); acc_full[1][b].init(1);
 #if BUG == 2
@@ -132,12 +141,16 @@ struct Pair {
       for (int kb = 0; kb < num_kb; ++kb, ++id) {
         if (!empty[c][stage].wait(phase ^ 1u)) die("producer: stage never released", id);
         const int s = stage; const long long my = id; const unsigned seed = (unsigned)(id * 2 + c);
+        if (c == 0) full[s].arrive();  // the leader arms its barrier for the bytes of both CTAs
         copy[c].push([this, c, s, my, seed] {
           std::mt19937 r(seed);
-          nap(r, 120);
+          nap(r, c == 1 ? 240 : 120);  // the odd CTA's bytes travel further
           if (stage_readers[s] != 0) fail("stage overwritten while MMAs were reading it", my);
           stage_tag[c][s] = my;
-          full[c][s].arrive();
+#if BUG == 1
+          if (c == 0)
+#endif
+          full[s].arrive();  // complete_tx on the LEADER's barrier, from either CTA
         });
         nap(rng, 10);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -150,16 +163,6 @@ struct Pair {
     tail_done[c] = 1;
   }
 
-  void forwarder() {
-    int stage = 0; unsigned phase = 0; long long id = 0;
-    for (int t = 0; t < tiles; ++t)
-      for (int kb = 0; kb < num_kb; ++kb, ++id) {
-        if (!full[1][stage].wait(phase)) die("forwarder: stage never landed", id);
-        peer_full[stage].arrive();
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-      }
-  }
-
   void issuer() {
     std::mt19937 rng(7u);
     int stage = 0; unsigned phase = 0; long long id = 0;
@@ -168,10 +171,7 @@ struct Pair {
       const unsigned acc_phase = (unsigned)(t >> 1) & 1u;
       if (!acc_empty[buf].wait(acc_phase ^ 1u)) die("issuer: accumulator never handed back", t);
       for (int kb = 0; kb < num_kb; ++kb, ++id) {
-        if (!full[0][stage].wait(phase)) die("issuer: own stage never landed", id);
-#if BUG != 1
-        if (!peer_full[stage].wait(phase)) die("issuer: peer stage never landed", id);
-#endif
+        if (!full[stage].wait(phase)) die("issuer: stage never landed", id);
         const int s = stage; const long long my = id; const int first = kb == 0; const int tile = t;
         tensor.push([this, s, my, buf, first, tile] {  // the four MMAs of the k-block
           ++stage_readers[s];
@@ -223,7 +223,6 @@ struct Pair {
       for (int w = 0; w < 4; ++w) th.emplace_back([this, c, w] { epilogue(c, w); });
     }
     th.emplace_back([this] { issuer(); });
-    th.emplace_back([this] { forwarder(); });
     for (auto& t : th) t.join();
     tensor.finish(); copy[0].finish(); copy[1].finish();
     tp.join(); c0.join(); c1.join();

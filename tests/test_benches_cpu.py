@@ -14,6 +14,13 @@ from bitscom_b200.bench import multimodel_e2e_curve as MM
 from bitscom_b200.bench import quantize_perf_curve as QC
 from bitscom_b200.bench import trace_stable_window as TW
 
+def _assert_png(path):
+    """Every bench CSV has a plot beside it (the reference writes one with matplotlib)."""
+    with open(path, "rb") as f:
+        head = f.read(8)
+    assert head == b"\x89PNG\r\n\x1a\n", path
+
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -140,6 +147,7 @@ def test_multimodel_bench_two_cpu_ranks(tmp_path):
                     for a in ("lowbit_sr", "no_compression", "ef_ef21_plus")}
     assert all(r["final_loss"] == r["final_loss"] and r["throughput_samples_per_s"] > 0
                for r in recs)
+    _assert_png(os.path.join(out, "bert_loss_curve_bw4.png"))
     with open(os.path.join(out, "bert_loss_curve_bw4.csv")) as f:
         rows = list(csv.reader(f))
     assert rows[0][:4] == ["step", "loss_lowbit_sr", "loss_no_compression", "loss_ef_ef21_plus"]
@@ -162,6 +170,7 @@ def test_collective_compare_two_cpu_ranks(kind, tmp_path):
     assert set(by_bits) == {2, 4}
     assert 0 < by_bits[4]["rel_error_mean"] < by_bits[2]["rel_error_mean"] < 0.5
     assert by_bits[4]["rel_error_mean"] < 0.12
+    _assert_png(tmp_path / f"{kind}_compare_bw4.png")
     with open(tmp_path / f"{kind}_compare_bw4.csv") as f:
         rows = list(csv.reader(f))
     assert rows[0] == ["step", "rel_error", "lowbit_ms", "baseline_ms"] and len(rows) == 5
@@ -174,6 +183,7 @@ def test_quantize_curve_host_columns(tmp_path):
     assert [r["numel"] for r in rows] == [1024, 2048, 4096]
     assert all(r["cpu_torch_ms"] > 0 for r in rows)
     assert os.path.exists(tmp_path / "quantize_curve_blockwise_bw4.csv")
+    _assert_png(tmp_path / "quantize_curve_blockwise_bw4.png")
     rows = QC.main(["--min-pow2", "10", "--max-pow2", "10", "--max-iters", "3", "--warmup", "1",
                     "--device", "cpu"])
     assert "gpu_ms" not in rows[0] and rows[0]["cpu_melems_per_s"] > 0

@@ -1,7 +1,7 @@
 """The barrier protocol of the CTA-pair GEMM (csrc/gemm_tcgen05_2cta.cu) as a host model
 (tests/native/gemm_pair_model.cc): both CTAs' producers and epilogue warps, the leader's MMA
-issuer, the odd CTA's stage forwarder, a tensor pipe and two copy engines as threads; ring
-stages and accumulator buffers tagged with what they hold.  The protocol must run clean for
+issuer, a tensor pipe and two copy engines as threads (both CTAs' loads complete on the leader's
+barrier); ring stages and accumulator buffers tagged with what they hold.  The protocol must run clean for
 1 to 8 tiles of 1 to 64 k-blocks; three seeded bugs must be noticed."""
 
 import os

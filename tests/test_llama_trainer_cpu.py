@@ -175,6 +175,11 @@ def test_deferred_weight_gradients_change_nothing_but_the_order_of_work():
     plain = _run(4, 2, "dense")
     deferred = _run(4, 2, "dense", defer_wgrad=True)
     assert [r["losses"] for r in plain] == [r["losses"] for r in deferred]
+    # the same with the low-bit gradient buckets, which are then launched from the queue, each
+    # behind the weight-gradient GEMMs of its layer
+    low = _run(4, 2, "flat")
+    low_deferred = _run(4, 2, "flat", defer_wgrad=True)
+    assert [r["losses"] for r in low] == [r["losses"] for r in low_deferred]
 
 
 def test_dp4_pp2_pipeline_a_with_local_pairs_on_strided_groups():
