@@ -43,6 +43,62 @@ def run_reference(args) -> None:
         _unavailable(f"{type(exc).__name__}: {str(exc)[:200]}")
 
 
+def _allreduce_block(bitscom, torch, dist, dev, world, sizes_mb) -> dict:
+    """The reference's ``LowBitGroup(...).all_reduce`` (its Python pipeline over NCCL with its
+    own CUDA quantize kernels: 4-bit, block 256, stochastic rounding; it has no error feedback
+    on this path) against NCCL bf16 / fp32 on the same buckets as the other arm's block.
+    CUDA events, rotating buffers larger than L2 in total, max over ranks."""
+    group = bitscom.LowBitGroup(bitwidth=4, process_group=dist.group.WORLD,
+                                stochastic_rounding=True, block_size=256)
+
+    def time_ms(fn, bufs, iters=5, warmup=3):
+        for i in range(warmup):
+            fn(bufs[i % len(bufs)])
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(iters):
+            fn(bufs[i % len(bufs)])
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    rows = []
+    for mb in sizes_mb:
+        size = int(mb * (1 << 20))
+        for dname, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+            n = size // (4 if dtype == torch.float32 else 2)
+            copies = max(2, min(8, -(-(252 << 20) // size)))
+            row = {"bytes": size, "bucket_dtype": dname, "numel": n, "world": world, "bits": 4,
+                   "stochastic_rounding": True, "error_feedback": False}
+            try:
+                bufs = [(torch.randn(n, device=dev) * 1e-3).to(dtype) for _ in range(copies)]
+                other = torch.bfloat16 if dtype == torch.float32 else torch.float32
+                obufs = [torch.zeros(n, device=dev, dtype=other) for _ in range(copies)]
+                same = time_ms(lambda t: dist.all_reduce(t), bufs)
+                oth = time_ms(lambda t: dist.all_reduce(t), obufs)
+                del obufs
+                ms = time_ms(lambda t: group.all_reduce(t), bufs)
+                bf16_ms = oth if dtype == torch.float32 else same
+                fp32_ms = same if dtype == torch.float32 else oth
+                row.update(lowbit_ms=ms, nccl_bf16_ms=bf16_ms, nccl_fp32_ms=fp32_ms,
+                           lowbit_effective_gbs=n * 4 / ms / 1e6, vs_nccl_bf16=bf16_ms / ms,
+                           vs_nccl_fp32=fp32_ms / ms)
+                del bufs
+            except BaseException as exc:  # e.g. out of memory in the reference's temporaries
+                row["error"] = f"{type(exc).__name__}: {str(exc)[:160]}"
+            torch.cuda.empty_cache()
+            rows.append(row)
+    return {"setting": "reference LowBitGroup Python pipeline over NCCL: 4-bit, block 256, "
+                       "stochastic rounding, no error feedback (its C++ backend, the path with "
+                       "error feedback, crashes in its constructor under torch 2.11)",
+            "world": world, "rows": rows,
+            "timing": "CUDA events, 5 calls after 3 warm-ups on rotating buffers, max over ranks"}
+
+
 def _run(args) -> None:
     sys.path.insert(0, REF)
     import torch
@@ -63,6 +119,11 @@ def _run(args) -> None:
         from datetime import timedelta
 
         dist.init_process_group("nccl", device_id=dev, timeout=timedelta(seconds=240))
+
+    allreduce = None
+    if world > 1 and not getattr(args, "no_allreduce_block", False):
+        allreduce = _allreduce_block(bitscom, torch, dist, dev, world,
+                                     getattr(args, "allreduce_mb", [64, 1024]))
 
     seq, micro_batches = 2048, 4
     cfg = LlamaConfig(vocab_size=32000, hidden_size=4096, intermediate_size=11008,
@@ -145,6 +206,7 @@ def _run(args) -> None:
                               "pp=1 (reference PP path depends on the missing model class)"],
             "e2e": {"value": value, "unit": "tokens/s",
                     "h2d_bytes_per_step": micro_batches * seq * 8, "d2h_bytes_per_step": 4},
-            "loss": last}), flush=True)
+            "loss": last, **({"allreduce": allreduce} if allreduce is not None else {})}),
+            flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -104,8 +104,6 @@ def gemm(args):
 
     _, tflops, tag = _peaks()
     G.set_variant(args.gemm_variant)
-    if args.split_tail:
-        G.set_split_tail(True)
     M, N, K = args.m, args.n, args.k
     copies = max(1, min(8, (256 << 20) // max(1, (M * K + N * K) * 2)))
     As = [(torch.randn(M, K, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(copies)]
@@ -174,8 +172,6 @@ def attention(args):
 def elementwise(args):
     from bitscom_b200.ops import nn as K
 
-    if args.rmsnorm_bwd_rows != 1:
-        K.set_rmsnorm_bwd_rows(args.rmsnorm_bwd_rows)
 
     hbm, _, tag = _peaks()
     T, H, F, V = args.tokens, 4096, 11008, 32000
@@ -236,16 +232,104 @@ def elementwise(args):
         for nm, ms, b in rows]}))
 
 
+def norms_raw(args):
+    """Device time of the normalisation / activation backward kernels themselves: the native
+    entry points are called directly on preallocated buffers, back to back, so that neither
+    autograd nor the allocator sits between two launches (at these sizes a Python-level
+    forward + backward costs more host time than the kernels take on the device)."""
+    from bitscom_b200.ops import nn as K
+    from bitscom_b200.ops._native import ptr, stream_ptr
+
+    lib = K._need()
+    hbm, _, tag = _peaks()
+    T = args.tokens
+    dev = torch.device("cuda")
+    st = stream_ptr(dev)
+
+    def bf(*shape):
+        return (torch.randn(*shape, device="cuda") * 0.5).to(torch.bfloat16)
+
+    rows = []
+    copies = 4  # rotate over buffers larger than L2 in total
+
+    def rms(H):
+        xs, dys = [bf(T, H) for _ in range(copies)], [bf(T, H) for _ in range(copies)]
+        w, rstd = bf(H), torch.rand(T, device="cuda") + 0.5
+        dx, dw = torch.empty_like(xs[0]), torch.zeros(H, device="cuda")
+        scratch = torch.empty(int(lib.bcom_norm_bwd_scratch_elems(H, 0)), device="cuda")
+        res = bf(T, H)
+        plain = lambda i: lib.bcom_rmsnorm_bwd(  # noqa: E731
+            ptr(dys[i % copies]), ptr(xs[i % copies]), ptr(w), ptr(rstd), None, ptr(dx), ptr(dw),
+            ptr(scratch), T, H, st)
+        fused = lambda i: lib.bcom_rmsnorm_bwd(  # noqa: E731
+            ptr(dys[i % copies]), ptr(xs[i % copies]), ptr(w), ptr(rstd), ptr(res), ptr(dx),
+            ptr(dw), ptr(scratch), T, H, st)
+        for name, fn, nb in (("rmsnorm_bwd", plain, 3), ("rmsnorm_bwd_plus_residual", fused, 4)):
+            for i in range(3):
+                fn(i)
+            rows.append((f"{name}_H{H}", _timed(fn, 20), nb * T * H * 2))
+
+    def ln(H):
+        xs, dys = [bf(T, H) for _ in range(copies)], [bf(T, H) for _ in range(copies)]
+        w = bf(H)
+        mean, rstd = torch.randn(T, device="cuda") * 0.1, torch.rand(T, device="cuda") + 0.5
+        dx = torch.empty_like(xs[0])
+        dw, db = torch.zeros(H, device="cuda"), torch.zeros(H, device="cuda")
+        scratch = torch.empty(int(lib.bcom_norm_bwd_scratch_elems(H, 1)), device="cuda")
+        bwd = lambda i: lib.bcom_layernorm_bwd(  # noqa: E731
+            ptr(dys[i % copies]), ptr(xs[i % copies]), ptr(w), ptr(mean), ptr(rstd), ptr(dx),
+            ptr(dw), ptr(db), ptr(scratch), T, H, st)
+        for i in range(3):
+            bwd(i)
+        rows.append((f"layernorm_bwd_H{H}", _timed(bwd, 20), 3 * T * H * 2))
+        y, mo, ro, b = torch.empty_like(xs[0]), torch.empty(T, device="cuda"), \
+            torch.empty(T, device="cuda"), bf(H)
+        fwd = lambda i: lib.bcom_layernorm_fwd(  # noqa: E731
+            ptr(xs[i % copies]), ptr(w), ptr(b), ptr(y), ptr(mo), ptr(ro), T, H, 1e-5, st)
+        for i in range(3):
+            fwd(i)
+        rows.append((f"layernorm_fwd_H{H}", _timed(fwd, 20), 2 * T * H * 2))
+
+    def swiglu(F):
+        gus, dhs = [bf(T, 2 * F) for _ in range(2)], [bf(T, F) for _ in range(2)]
+        h, dgu = torch.empty(T, F, device="cuda", dtype=torch.bfloat16), torch.empty_like(gus[0])
+        fwd = lambda i: lib.bcom_swiglu_fwd(ptr(gus[i % 2]), ptr(h), T, F, st)  # noqa: E731
+        bwd = lambda i: lib.bcom_swiglu_bwd(ptr(gus[i % 2]), ptr(dhs[i % 2]), ptr(dgu), T, F,  # noqa: E731
+                                            st)
+        for name, fn, nb in (("swiglu_fwd", fwd, 3), ("swiglu_bwd", bwd, 5)):
+            for i in range(3):
+                fn(i)
+            rows.append((name, _timed(fn, 20), nb * T * F * 2))
+
+    def gelu(C):
+        xs, dys = [bf(T, C) for _ in range(copies)], [bf(T, C) for _ in range(copies)]
+        b, dx, db = bf(C), torch.empty_like(xs[0]), torch.zeros(C, device="cuda")
+        bwd = lambda i: lib.bcom_bias_gelu_bwd(  # noqa: E731
+            ptr(dys[i % copies]), ptr(xs[i % copies]), ptr(b), ptr(dx), ptr(db), T, C, st)
+        for i in range(3):
+            bwd(i)
+        rows.append((f"bias_gelu_bwd_C{C}", _timed(bwd, 20), 3 * T * C * 2))
+
+    rms(4096)
+    ln(1024)
+    swiglu(11008)
+    gelu(4096)
+    print(json.dumps({"case": "norms_raw", "tokens": T, "peaks": tag, "kernels": [
+        {"name": nm, "ms": ms, "gbs": b / ms / 1e6, "frac_hbm": b / ms / 1e6 / hbm}
+        for nm, ms, b in rows]}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["fused", "codec", "gemm", "attention", "elementwise"])
+    ap.add_argument("case", choices=["fused", "codec", "gemm", "attention", "elementwise",
+                                     "norms_raw"])
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
     ap.add_argument("--fwd-variant", default="pipelined",
-                    choices=["simple", "pipelined", "pipelined8"])
-    ap.add_argument("--bwd-dq", default="tma", choices=["atomic", "tma", "tma_early"])
+                    choices=["simple", "pipelined"])
+    ap.add_argument("--bwd-dq", default="tma", choices=["atomic", "tma"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--elems", type=int, default=1 << 25)
     ap.add_argument("--bits", type=int, default=4)
@@ -259,14 +343,11 @@ def main(argv=None):
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--wgrad", action="store_true")
     ap.add_argument("--gemm-variant", default="1cta", choices=["1cta", "2cta"])
-    ap.add_argument("--rmsnorm-bwd-rows", type=int, default=1, choices=[1, 4])
-    ap.add_argument("--split-tail", action="store_true",
-                    help="one-CTA GEMM: half tiles for a sparsely filled last wave")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
     {"fused": fused, "codec": codec, "gemm": gemm, "attention": attention,
-     "elementwise": elementwise}[args.case](args)
+     "elementwise": elementwise, "norms_raw": norms_raw}[args.case](args)
 
 
 if __name__ == "__main__":

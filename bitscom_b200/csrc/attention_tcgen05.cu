@@ -599,354 +599,6 @@ attention_fwd_pipelined_kernel(const __grid_constant__ CUtensorMap tm_q,    // b
 }
 
 // ---------------------------------------------------------------------------
-// forward, software-pipelined variant with eight softmax warps
-// ---------------------------------------------------------------------------
-// The issuer and the barrier protocol are those of attention_fwd_pipelined_kernel; what
-// changes is that two threads share a row, which halves the serial work per block of the
-// softmax warps (the resource that kernel is bound by) and doubles the warps per scheduler.
-constexpr int kPipe8Threads = 288;
-constexpr unsigned int kKeyNegInf = 0x007FFFFFu;  // float_key(-inf)
-
-struct Pipe8Shared {
-  uint64_t bar_q, bar_k[2], bar_v[2], bar_s[2], bar_p, bar_o;
-  uint64_t bar_x[4], bar_y[4];   // per lane quarter: maximum contributed / maximum read
-  uint32_t tmem_base;
-  volatile int abort;
-  unsigned int rowmax[BQ];       // running raw row maximum as an order-preserving key
-};
-
-template <int HD> struct FwdPipe8 {
-  // the same tiles as FwdPipe; the control block (656 bytes) still fits the kilobyte that two
-  // resident CTAs of 112 KiB leave
-  static constexpr int SMEM = FwdPipe<HD>::DATA + 704;
-};
-
-// order-preserving map float -> unsigned (and back), so that atomicMax on shared memory
-// finds the maximum of signed floats
-__device__ __forceinline__ unsigned int float_key(float f) {
-  const unsigned int u = __float_as_uint(f);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ float key_float(unsigned int k) {
-  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
-}
-
-template <int HD>
-__global__ void __launch_bounds__(kPipe8Threads, 2)
-attention_fwd_pipelined8_kernel(const __grid_constant__ CUtensorMap tm_q,    // box {64, 128}
-                               const __grid_constant__ CUtensorMap tm_kv,   // box {64, 64}
-                               const FwdParams p) {
-  extern __shared__ __align__(1024) uint8_t smem[];
-  constexpr int Q_BYTES = FwdPipe<HD>::Q_BYTES, K_BYTES = FwdPipe<HD>::K_BYTES;
-  uint8_t* sQ = smem;
-  uint8_t* sK0 = sQ + Q_BYTES;
-  uint8_t* sV0 = sK0 + 2 * K_BYTES;
-  uint8_t* sP = sV0 + 2 * K_BYTES;
-  Pipe8Shared* sh = reinterpret_cast<Pipe8Shared*>(sP + FWD_P_BYTES);
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if ((tc::smem_u32(smem) & 1023u) != 0u) {  // same answer in every thread of the CTA
-    if (tid == 0) record_fail(20);
-    return;
-  }
-  const int qblocks = p.seq / BQ;
-  const int qb = qblocks - 1 - (int)(blockIdx.x % qblocks);  // heavy query blocks first
-  const int bh = blockIdx.x / qblocks;
-  const int h = bh % p.heads, b = bh / p.heads;
-  const int H = p.heads * HD;
-  const int row0 = b * p.seq + qb * BQ;
-  const int q_col = h * HD, k_col = H + h * HD, v_col = 2 * H + h * HD;
-  const int n = (qb * BQ + BQ) / BKF;  // causal: keys 0 .. q0 + 127
-
-  if (tid == 0) {
-    tc::mbar_init(&sh->bar_q, 1);
-    for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&sh->bar_k[i], 1);
-      tc::mbar_init(&sh->bar_v[i], 1);
-      tc::mbar_init(&sh->bar_s[i], 1);
-    }
-    tc::mbar_init(&sh->bar_p, 256);
-    tc::mbar_init(&sh->bar_o, 1);
-    for (int i = 0; i < 4; ++i) {
-      tc::mbar_init(&sh->bar_x[i], 64);
-      tc::mbar_init(&sh->bar_y[i], 64);
-    }
-    sh->abort = 0;
-    tc::fence_mbar_init();
-  }
-  if (tid < BQ) sh->rowmax[tid] = kKeyNegInf;  // running row maximum, order-preserving key
-  if (warp == 8) tc::tmem_alloc(&sh->tmem_base, FwdPipe<HD>::TMEM_COLS);
-  tc::tc_fence_before_sync();
-  __syncthreads();
-  tc::tc_fence_after_sync();
-  const uint32_t tmem = sh->tmem_base;
-  const uint32_t tO = tmem + 128;
-
-  if (warp == 8) {
-    // ------------------------------- issuer -------------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = tc::make_idesc_bf16(BQ, BKF, false, false);
-      constexpr uint32_t idesc_o = tc::make_idesc_bf16(BQ, HD, false, true);
-      const uint32_t aQ = tc::smem_u32(sQ), aK0 = tc::smem_u32(sK0), aV0 = tc::smem_u32(sV0),
-                     aP = tc::smem_u32(sP);
-      bool ok = true;
-      auto wait = [&](uint64_t* bar, uint32_t parity, unsigned code) {
-        if (ok && !tc::mbar_wait(bar, parity, kBudgetNs)) {
-          ok = false;
-          sh->abort = 1;
-          record_fail(code);
-        }
-      };
-      auto load_k = [&](int j) {
-        uint64_t* bar = &sh->bar_k[j & 1];
-        tc::mbar_expect_tx(bar, K_BYTES);
-#pragma unroll
-        for (int c = 0; c < HD / 64; ++c)
-          tc::tma_load_2d(sK0 + (j & 1) * K_BYTES + c * BKF * 128, &tm_kv, bar, k_col + 64 * c,
-                          b * p.seq + j * BKF);
-      };
-      auto load_v = [&](int j) {
-        uint64_t* bar = &sh->bar_v[j & 1];
-        tc::mbar_expect_tx(bar, K_BYTES);
-#pragma unroll
-        for (int c = 0; c < HD / 64; ++c)
-          tc::tma_load_2d(sV0 + (j & 1) * K_BYTES + c * BKF * 128, &tm_kv, bar, v_col + 64 * c,
-                          b * p.seq + j * BKF);
-      };
-      auto issue_qk = [&](int j) {
-        const uint32_t aK = aK0 + (j & 1) * K_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          tc::umma_bf16(tmem + (j & 1) * 64, desc_kmajor(aQ, BQ, ks), desc_kmajor(aK, BKF, ks),
-                        idesc_s, ks != 0);
-        tc::umma_commit(&sh->bar_s[j & 1]);
-      };
-      auto issue_pv = [&](int j) {
-        const uint32_t aV = aV0 + (j & 1) * K_BYTES;
-#pragma unroll
-        for (int ks = 0; ks < BKF / 16; ++ks)
-          tc::umma_bf16(tO, desc_kmajor(aP, BQ, ks), desc_mnmajor(aV, BKF, ks), idesc_o,
-                        (j != 0) || (ks != 0));
-        tc::umma_commit(&sh->bar_o);
-      };
-
-      tc::mbar_expect_tx(&sh->bar_q, Q_BYTES);
-#pragma unroll
-      for (int c = 0; c < HD / 64; ++c)
-        tc::tma_load_2d(sQ + c * BQ * 128, &tm_q, &sh->bar_q, q_col + 64 * c, row0);
-      load_k(0);
-      load_v(0);
-      if (n > 1) {
-        load_k(1);
-        load_v(1);
-      }
-      wait(&sh->bar_q, 0, 21);
-      wait(&sh->bar_k[0], 0, 22);
-      if (ok) {
-        tc::tc_fence_after_sync();
-        issue_qk(0);
-      }
-      if (n > 1) {
-        wait(&sh->bar_k[1], 0, 22);
-        if (ok) {
-          tc::tc_fence_after_sync();
-          issue_qk(1);
-        }
-      }
-      for (int j = 0; j < n && ok; ++j) {
-        const uint32_t par2 = (uint32_t)(j >> 1) & 1u;
-        if (j + 2 < n) {  // K buffer j & 1 is free once QK_j has completed
-          wait(&sh->bar_s[j & 1], par2, 23);
-          if (ok) load_k(j + 2);
-        }
-        if (j >= 1 && j + 1 < n) {  // V buffer (j + 1) & 1 is free once PV_{j-1} has completed
-          wait(&sh->bar_o, (uint32_t)(j - 1) & 1u, 24);
-          if (ok) load_v(j + 1);
-        }
-        wait(&sh->bar_p, (uint32_t)j & 1u, 25);  // P_j written, S_j consumed, O rescaled
-        wait(&sh->bar_v[j & 1], par2, 26);
-        if (!ok) break;
-        tc::tc_fence_after_sync();
-        issue_pv(j);
-        if (j + 2 < n) {
-          wait(&sh->bar_k[j & 1], (uint32_t)((j + 2) >> 1) & 1u, 22);
-          if (!ok) break;
-          tc::tc_fence_after_sync();
-          issue_qk(j + 2);
-        }
-      }
-      // every MMA issued must have finished before TMEM is handed back
-      if (ok && n > 0) wait(&sh->bar_o, (uint32_t)(n - 1) & 1u, 27);
-    }
-    __syncwarp();
-  } else {
-    // ------------------------------- softmax warps ------------------------------------
-    // Warps w and w + 4 own the same 32 rows (TMEM lanes 32 * (w & 3) ..) and split the
-    // columns: 32 of the 64 scores of a block, half of the columns of O.  The only value the
-    // two threads of a row must agree on per block is the running maximum; it lives in
-    // sh->rowmax[row] as an order-preserving integer key that both raise with atomicMax.
-    // bar_x: both have contributed (the maximum may be read); bar_y: both have read it (the
-    // next block may contribute).  The row sums stay split until the epilogue.
-    const int quarter = warp & 3, half = warp >> 2;
-    const int row = quarter * 32 + lane;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int q_idx = qb * BQ + row;  // position of this thread's query inside the sequence
-    constexpr int HC = BKF / 2;       // score columns per thread
-    constexpr int OC = HD / 64;       // 32-column chunks of O per thread
-    float m_run = -INFINITY, l_run = 0.0f;
-    bool ok = true;
-    for (int j = 0; j < n; ++j) {
-      if (!warp_wait(&sh->bar_s[j & 1], (uint32_t)(j >> 1) & 1u)) {
-        ok = false;
-        if (lane == 0) { sh->abort = 1; record_fail(28); }
-        break;
-      }
-      tc::tc_fence_after_sync();
-      const uint32_t tS = tmem + (j & 1) * 64 + half * HC;
-      float s[HC];  // raw scores (unscaled), then probabilities
-      {
-        uint32_t r[HC];
-        tc::tmem_ld_32x32(tS + lane_addr, r);
-        tc::tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < HC; ++i) s[i] = __uint_as_float(r[i]);
-      }
-      const int k0 = j * BKF + half * HC;
-      if (j * BKF + BKF - 1 > qb * BQ) {  // block touches the diagonal
-#pragma unroll
-        for (int i = 0; i < HC; ++i)
-          if (k0 + i > q_idx) s[i] = -INFINITY;
-      }
-      float mx[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-      for (int i = 4; i < HC; i += 4) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], s[i + q]);
-      }
-      const float mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      // the partner must have read the previous block's maximum before it is raised again
-      if (j > 0 && !warp_wait(&sh->bar_y[quarter], (uint32_t)(j - 1) & 1u)) {
-        ok = false;
-        if (lane == 0) { sh->abort = 1; record_fail(31); }
-        break;
-      }
-      atomicMax(&sh->rowmax[row], float_key(mine));
-      tc::mbar_arrive(&sh->bar_x[quarter]);
-      if (!warp_wait(&sh->bar_x[quarter], (uint32_t)j & 1u)) {
-        ok = false;
-        if (lane == 0) { sh->abort = 1; record_fail(32); }
-        break;
-      }
-      const float m_blk = key_float(sh->rowmax[row]) * p.scale_log2;  // same in both halves
-      tc::mbar_arrive(&sh->bar_y[quarter]);
-      const float alpha = ex2_fast(m_run - m_blk);  // first block: 2^(-inf) = 0
-      float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-      for (int i = 0; i < HC; i += 4) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          s[i + q] = ex2_fast(fmaf(s[i + q], p.scale_log2, -m_blk));
-          sm[q] += s[i + q];
-        }
-      }
-      l_run = l_run * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
-      m_run = m_blk;
-      if (j > 0) {
-        // PV_{j-1} done: the P buffer may be overwritten and O is at rest
-        if (!warp_wait(&sh->bar_o, (uint32_t)(j - 1) & 1u)) {
-          ok = false;
-          if (lane == 0) { sh->abort = 1; record_fail(29); }
-          break;
-        }
-        tc::tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-          for (int c = half * OC; c < (half + 1) * OC; ++c) {
-            uint32_t r[32];
-            tc::tmem_ld_32x32(tO + lane_addr + c * 32, r);
-            tc::tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tc::tmem_st_32x32(tO + lane_addr + c * 32, r);
-          }
-          tc::tmem_wait_st();
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < HC / 8; ++u) {
-        uint4 v;
-        v.x = pack_bf16(s[u * 8 + 0], s[u * 8 + 1]);
-        v.y = pack_bf16(s[u * 8 + 2], s[u * 8 + 3]);
-        v.z = pack_bf16(s[u * 8 + 4], s[u * 8 + 5]);
-        v.w = pack_bf16(s[u * 8 + 6], s[u * 8 + 7]);
-        *reinterpret_cast<uint4*>(sP + swz(row, half * (HC / 8) + u)) = v;
-      }
-      tc::fence_proxy_async();       // generic-proxy smem writes -> visible to the MMA
-      tc::tc_fence_before_sync();    // orders the TMEM reads / writes above before the arrival
-      tc::mbar_arrive(&sh->bar_p);
-      if (__any_sync(0xffffffffu, sh->abort != 0)) {
-        ok = false;
-        break;
-      }
-    }
-    // ---- epilogue: the two halves of a row add up their sums, then O / l -> out ----
-    // half 1 publishes its sum (after the partner has read the last maximum), half 0 replies
-    // with the total; rowmax[] is reused as the mailbox
-    float l_total = 0.0f;
-    if (ok && n > 0 && warp_wait(&sh->bar_y[quarter], (uint32_t)(n - 1) & 1u)) {
-      if (half == 1) sh->rowmax[row] = __float_as_uint(l_run);
-      tc::mbar_arrive(&sh->bar_x[quarter]);
-      if (warp_wait(&sh->bar_x[quarter], (uint32_t)n & 1u)) {
-        if (half == 0) {
-          l_total = l_run + __uint_as_float(sh->rowmax[row]);
-          sh->rowmax[row] = __float_as_uint(l_total);
-        }
-        tc::mbar_arrive(&sh->bar_y[quarter]);
-        if (warp_wait(&sh->bar_y[quarter], (uint32_t)n & 1u)) {
-          if (half == 1) l_total = __uint_as_float(sh->rowmax[row]);
-        } else {
-          ok = false;
-        }
-      } else {
-        ok = false;
-      }
-    } else {
-      ok = false;
-    }
-    if (ok && warp_wait(&sh->bar_o, (uint32_t)(n - 1) & 1u)) {
-      tc::tc_fence_after_sync();
-      const float inv = 1.0f / l_total;
-      __nv_bfloat16* dst = p.out + (size_t)(row0 + row) * H + q_col;
-#pragma unroll 1
-      for (int c = half * OC; c < (half + 1) * OC; ++c) {
-        uint32_t r[32];
-        tc::tmem_ld_32x32(tO + lane_addr + c * 32, r);
-        tc::tmem_wait_ld();
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 v;
-          v.x = pack_bf16(__uint_as_float(r[u * 8 + 0]) * inv, __uint_as_float(r[u * 8 + 1]) * inv);
-          v.y = pack_bf16(__uint_as_float(r[u * 8 + 2]) * inv, __uint_as_float(r[u * 8 + 3]) * inv);
-          v.z = pack_bf16(__uint_as_float(r[u * 8 + 4]) * inv, __uint_as_float(r[u * 8 + 5]) * inv);
-          v.w = pack_bf16(__uint_as_float(r[u * 8 + 6]) * inv, __uint_as_float(r[u * 8 + 7]) * inv);
-          reinterpret_cast<uint4*>(dst + c * 32)[u] = v;
-        }
-      }
-      if (half == 0) p.lse2[((size_t)b * p.heads + h) * p.seq + q_idx] = m_run + log2f(l_total);
-    } else if (lane == 0 && !sh->abort) {
-      sh->abort = 1;
-      record_fail(30);
-    }
-  }
-  tc::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 8) {
-    tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tmem, FwdPipe<HD>::TMEM_COLS);
-  }
-}
-
-// ---------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------
 struct BwdParams {
@@ -961,7 +613,6 @@ struct BwdParams {
 
 struct BwdShared {
   uint64_t bar_kv, bar_q, bar_1, bar_2;
-  uint64_t bar_2a;  // EARLY: dV and dK have read Q and dO (dQ may still be running)
   uint32_t tmem_base;
   volatile int abort;
   float lse[BQ];
@@ -979,12 +630,7 @@ template <int HD> struct Bwd {
 // idle at that point; 128-byte swizzled so that the row-per-thread stores do not collide)
 // and added to global memory by TMA reductions of [128 rows x 32 floats] boxes, which the L2
 // performs at full-line granularity while the next block's MMAs run.
-// EARLY (with TMA_DQ): two latencies of the query-block loop are taken off its critical path.
-// dV / dK are committed on a barrier of their own, so the next block's Q and dO tiles are
-// requested as soon as those two products have read the current ones, under the dQ product
-// and its drain; and the next block's log-sum-exp / delta rows are fetched into registers
-// during the current block instead of at the top of the next one.
-template <int HD, bool TMA_DQ, bool EARLY = false>
+template <int HD, bool TMA_DQ>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 128} over qkv
                      const __grid_constant__ CUtensorMap tm_do,    // box {64, 128} over dO
@@ -1021,7 +667,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
     tc::mbar_init(&sh->bar_q, 1);
     tc::mbar_init(&sh->bar_1, 1);
     tc::mbar_init(&sh->bar_2, 1);
-    tc::mbar_init(&sh->bar_2a, 1);
     sh->abort = 0;
     tc::fence_mbar_init();
   }
@@ -1063,31 +708,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
 
   if (!tc::mbar_wait(&sh->bar_kv, 0, kBudgetNs)) { sh->abort = 1; record_fail(11); }
 
-  // EARLY: row statistics of the NEXT query block, fetched one block ahead
-  float lse_next = 0.0f, delta_next = 0.0f;
-  if constexpr (EARLY) {
-    if (tid < BQ) {
-      const size_t base = ((size_t)b * p.heads + h) * p.seq + (size_t)kb * BQ;
-      lse_next = p.lse2[base + tid];
-      delta_next = p.delta[base + tid];
-    }
-  }
-
   for (int qi = 0; qi < nq; ++qi) {
     const uint32_t par = (uint32_t)qi & 1u;
     const int qpos0 = (kb + qi) * BQ;  // first query position of this block
     // row statistics of the 128 queries of this block
-    if constexpr (EARLY) {
-      if (tid < BQ) {
-        sh->lse[tid] = lse_next;
-        sh->delta[tid] = delta_next;
-        if (qi + 1 < nq) {  // issue the next block's loads now, consume them a block later
-          const size_t base = ((size_t)b * p.heads + h) * p.seq + qpos0 + BQ;
-          lse_next = p.lse2[base + tid];
-          delta_next = p.delta[base + tid];
-        }
-      }
-    } else {
+    {
       const size_t base = ((size_t)b * p.heads + h) * p.seq + qpos0;
       if (tid < BQ) {
         sh->lse[tid] = p.lse2[base + tid];
@@ -1166,23 +791,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv,   // box {64, 1
       for (int ks = 0; ks < BQ / 16; ++ks)
         tc::umma_bf16(tDK, desc_kmajor(aDS, 128, ks), desc_mnmajor(aQ, 128, ks), idesc_kn,
                       acc | (ks != 0));
-      if constexpr (EARLY) tc::umma_commit(&sh->bar_2a);  // dV, dK issued: Q / dO readers
 #pragma unroll
       for (int ks = 0; ks < BKB / 16; ++ks)
         tc::umma_bf16(tDQ, desc_mnmajor(aDS, 128, ks), desc_mnmajor(aK, 128, ks), idesc_nn,
                       ks != 0);
       tc::umma_commit(&sh->bar_2);
-      if constexpr (EARLY) {
-        // Q and dO are free once dV and dK are done; dQ (reads dS^T and K) may still run
-        if (!tc::mbar_wait(&sh->bar_2a, par, kBudgetNs)) { sh->abort = 1; record_fail(15); }
-        if (!sh->abort && qi + 1 < nq) load_q(qi + 1);
-      }
     }
     if (!tc::mbar_wait(&sh->bar_2, par, kBudgetNs)) { sh->abort = 1; record_fail(14); }
     tc::tc_fence_after_sync();
-    if constexpr (!EARLY) {
-      if (tid == 0 && qi + 1 < nq) load_q(qi + 1);  // Q and dO tiles are free again
-    }
+    if (tid == 0 && qi + 1 < nq) load_q(qi + 1);  // Q and dO tiles are free again
 
     // ---- dQ rows (thread t <-> query row t) into the fp32 buffer ----
     if constexpr (TMA_DQ) {
@@ -1361,9 +978,9 @@ static int launch_fwd(const void* qkv, void* out, void* lse2, int batch, int seq
   return (int)cudaGetLastError();
 }
 
-// 0: float4 atomics, 1: TMA reduce-add from shared memory, 2: 1 + early loads of the next block
+// 0: float4 atomics, 1: TMA reduce-add from shared memory
 static int g_bwd_dq_variant = 1;
-// 0: attention_fwd_kernel, 1: attention_fwd_pipelined_kernel, 2: attention_fwd_pipelined8_kernel
+// 0: attention_fwd_kernel, 1: attention_fwd_pipelined_kernel
 static int g_fwd_variant = 1;
 
 template <int HD>
@@ -1398,51 +1015,18 @@ static int launch_fwd_pipelined(const void* qkv, void* out, void* lse2, int batc
   return (int)cudaGetLastError();
 }
 
-template <int HD>
-static int launch_fwd_pipelined8(const void* qkv, void* out, void* lse2, int batch, int seq,
-                                 int heads, float scale, cudaStream_t st) {
-  const long long tokens = (long long)batch * seq;
-  const int W = 3 * heads * HD;
-  CUtensorMap tm_q, tm_kv;
-  if (make_map(&tm_q, qkv, tokens, W, 64, BQ)) return 1003;
-  if (make_map(&tm_kv, qkv, tokens, W, 64, BKF)) return 1004;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute((const void*)attention_fwd_pipelined8_kernel<HD>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    FwdPipe8<HD>::SMEM);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute((const void*)attention_fwd_pipelined8_kernel<HD>,
-                                      cudaFuncAttributePreferredSharedMemoryCarveout,
-                                      cudaSharedmemCarveoutMaxShared);
-  });
-  if (attr_err != cudaSuccess) return 1005;
-  FwdParams p;
-  p.out = (__nv_bfloat16*)out;
-  p.lse2 = (float*)lse2;
-  p.batch = batch;
-  p.seq = seq;
-  p.heads = heads;
-  p.scale_log2 = scale * kLog2e;
-  const int grid = batch * heads * (seq / BQ);
-  attention_fwd_pipelined8_kernel<HD><<<grid, kPipe8Threads, FwdPipe8<HD>::SMEM, st>>>(tm_q, tm_kv,
-                                                                                     p);
-  return (int)cudaGetLastError();
-}
-
-template <int HD, bool TMA_DQ, bool EARLY = false>
+template <int HD, bool TMA_DQ>
 static int launch_bwd_kernel(const CUtensorMap& tm_qkv, const CUtensorMap& tm_do,
                              const CUtensorMap& tm_dq, const BwdParams& p, int grid,
                              cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel<HD, TMA_DQ, EARLY>,
+    attr_err = cudaFuncSetAttribute((const void*)attention_bwd_kernel<HD, TMA_DQ>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd<HD>::SMEM);
   });
   if (attr_err != cudaSuccess) return 1005;
-  attention_bwd_kernel<HD, TMA_DQ, EARLY><<<grid, kBwdThreads, Bwd<HD>::SMEM, st>>>(
+  attention_bwd_kernel<HD, TMA_DQ><<<grid, kBwdThreads, Bwd<HD>::SMEM, st>>>(
       tm_qkv, tm_do, tm_dq, p);
   return 0;
 }
@@ -1480,10 +1064,8 @@ static int launch_bwd(const void* qkv, const void* out, const void* d_out, const
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   const int grid = batch * heads * (seq / BKB);
-  const int rc = g_bwd_dq_variant == 2
-                     ? launch_bwd_kernel<HD, true, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
-                 : tma_dq ? launch_bwd_kernel<HD, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
-                          : launch_bwd_kernel<HD, false>(tm_qkv, tm_do, tm_dq, p, grid, st);
+  const int rc = tma_dq ? launch_bwd_kernel<HD, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
+                        : launch_bwd_kernel<HD, false>(tm_qkv, tm_do, tm_dq, p, grid, st);
   if (rc) return rc;
   attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
   return (int)cudaGetLastError();
@@ -1498,11 +1080,10 @@ static bool shape_ok(int batch, int seq, int heads, int head_dim) {
 extern "C" {
 
 // 0: dQ tiles are added to the fp32 accumulator with float4 atomics; 1: with TMA reductions
-// from a shared-memory staging tile; 2: as 1, with the next query block's loads issued early.
-// Returns the previous value.
+// from a shared-memory staging tile.  Returns the previous value.
 int bcom_attention_set_bwd_dq_variant(int variant) {
   const int old = attn::g_bwd_dq_variant;
-  if (variant >= 0 && variant <= 2) attn::g_bwd_dq_variant = variant;
+  if (variant >= 0 && variant <= 1) attn::g_bwd_dq_variant = variant;
   return old;
 }
 
@@ -1516,10 +1097,6 @@ int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int se
   if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15)) return 1002;
   tc::bind_context_once();
   cudaStream_t st = (cudaStream_t)stream;
-  if (g_fwd_variant == 2)
-    return head_dim == 128
-               ? launch_fwd_pipelined8<128>(qkv, out, lse2, batch, seq, heads, scale, st)
-               : launch_fwd_pipelined8<64>(qkv, out, lse2, batch, seq, heads, scale, st);
   if (g_fwd_variant == 1)
     return head_dim == 128
                ? launch_fwd_pipelined<128>(qkv, out, lse2, batch, seq, heads, scale, st)
@@ -1529,11 +1106,10 @@ int bcom_attention_fwd(const void* qkv, void* out, void* lse2, int batch, int se
 }
 
 // 0 selects the forward kernel whose MMA and softmax take turns, 1 the software-pipelined one
-// (issuer warp, double-buffered S in TMEM, O accumulated in TMEM), 2 the same with eight
-// softmax warps (two threads per row).  Returns the previous value.
+// (issuer warp, double-buffered S in TMEM, O accumulated in TMEM).  Returns the previous value.
 int bcom_attention_set_fwd_variant(int variant) {
   const int old = attn::g_fwd_variant;
-  if (variant >= 0 && variant <= 2) attn::g_fwd_variant = variant;
+  if (variant >= 0 && variant <= 1) attn::g_fwd_variant = variant;
   return old;
 }
 

@@ -102,17 +102,22 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   }
 }
 
-// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw += sum_rows dy * x * rstd (fp32)
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)) [+ dres];  dw += sum_rows dy * x * rstd (fp32)
 // Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dw partial in registers
-// (thread t owns columns t*8 + k*blockDim*8), adding it to dw once at the end.  A row is read
-// once: x and dy stay in registers (as packed bf16) across the reduction, the next row's loads
-// are issued before the reduction of the current one, and the reduction costs one barrier
-// (warp partials in a double-buffered scratch, every thread adds them up itself).
-template <int MAX_ITERS>
+// (thread t owns columns t*8 + k*blockDim*8).  A row is read once: x and dy stay in registers
+// (as packed bf16) across the reduction, the next row's loads are issued before the reduction
+// of the current one, and the reduction costs one barrier (warp partials in a double-buffered
+// scratch, every thread adds them up itself).  At the end a CTA writes its dw partial to its
+// row of `partials` ([gridDim.x][H] fp32) and colsum_add_kernel folds the rows into dw: H
+// atomic adds per CTA on the same H addresses used to cost a third of the kernel's time.
+// `dres` (HAS_RES): the gradient that reaches the same input through the residual connection,
+// added to dx here instead of by a separate add kernel.
+template <int MAX_ITERS, bool HAS_RES>
 __global__ void __launch_bounds__(512)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                    const bf16* __restrict__ w, const float* __restrict__ rstd,
-                   bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
+                   const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                   float* __restrict__ partials, int rows, int H) {
   __shared__ float partial[2][16];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
@@ -173,6 +178,12 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
           const float fx = __bfloat162float(cx[k].v[i]), fg = __bfloat162float(cg[k].v[i]);
           o[i] = fg * fw[k][i] * rs - fx * coef;
         }
+        if constexpr (HAS_RES) {
+          float rr[8];
+          load8(dres + (size_t)row * H + c, rr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += rr[i];
+        }
         store8(dr + c, o);
         cx[k] = nx[k];
         cg[k] = ng[k];
@@ -183,90 +194,42 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   for (int k = 0; k < MAX_ITERS; ++k) {
     const int c = (threadIdx.x + k * blockDim.x) * 8;
     if (c < H) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(dw + c + i, acc[k][i]);
+      float* dst = partials + (size_t)blockIdx.x * H + c;
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[k][0], acc[k][1], acc[k][2], acc[k][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[k][4], acc[k][5], acc[k][6], acc[k][7]);
     }
   }
 }
 
-// Variant of the kernel above for H <= 512 * 8 (one 8-element pack per thread): ROWS rows per
-// CTA barrier instead of one.  The thread-to-column mapping (and with it the weight gradient
-// in registers) stays; what changes is that the loads of ROWS rows are in flight at once and
-// that the ROWS dot products share one barrier.  Off by default (bcom_rmsnorm_bwd_set_rows).
-template <int ROWS>
-__global__ void __launch_bounds__(512)
-rmsnorm_bwd_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
-                        const bf16* __restrict__ w, const float* __restrict__ rstd,
-                        bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H) {
-  __shared__ float partial[2][ROWS][16];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nwarps = blockDim.x >> 5;
-  const int c = threadIdx.x * 8;
-  const bool live = c < H;
-  float acc[8], fw[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = fw[i] = 0.0f;
-  if (live) load8(w + c, fw);
-  Bf8 cx[ROWS], cg[ROWS], nx[ROWS], ng[ROWS];
-  auto fetch = [&](int row0, Bf8 (&bx)[ROWS], Bf8 (&bg)[ROWS]) {
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      const int row = row0 + r;
-      if (live && row < rows) {
-        bx[r] = *reinterpret_cast<const Bf8*>(x + (size_t)row * H + c);
-        bg[r] = *reinterpret_cast<const Bf8*>(dy + (size_t)row * H + c);
-      }
+// out[c] += sum over p < nparts of partials[p * width + c] for the `width` columns of a
+// partial row; columns [0, split) belong to out_a, columns [split, width) to out_b (at
+// out_b[c - split]).  blockDim = (32, 32): a CTA owns 32 columns, its 32 thread rows split
+// the partial rows (a few loads each, all in flight at once), shared memory folds them.
+__global__ void __launch_bounds__(1024)
+colsum_add_kernel(const float* __restrict__ partials, float* __restrict__ out_a,
+                  float* __restrict__ out_b, int nparts, int width, int split) {
+  __shared__ float fold[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float s = 0.0f;
+  if (c < width) {
+    int p = threadIdx.y;
+    for (; p + 96 < nparts; p += 128) {
+      const float a0 = partials[(size_t)p * width + c];
+      const float a1 = partials[(size_t)(p + 32) * width + c];
+      const float a2 = partials[(size_t)(p + 64) * width + c];
+      const float a3 = partials[(size_t)(p + 96) * width + c];
+      s += (a0 + a1) + (a2 + a3);
     }
-  };
-  // CTA b owns the row groups b, b + gridDim.x, ... of ROWS consecutive rows each
-  int row0 = blockIdx.x * ROWS;
-  if (row0 < rows) fetch(row0, cx, cg);
-  int parity = 0;
-  for (; row0 < rows; row0 += gridDim.x * ROWS, parity ^= 1) {
-    const int next0 = row0 + gridDim.x * ROWS;
-    if (next0 < rows) fetch(next0, nx, ng);
-    float rs[ROWS], dot[ROWS];
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      const bool ok = row0 + r < rows;
-      rs[r] = ok ? rstd[row0 + r] : 0.0f;
-      dot[r] = 0.0f;
-      if (live && ok) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float fx = __bfloat162float(cx[r].v[i]), fg = __bfloat162float(cg[r].v[i]);
-          dot[r] += fg * fw[i] * fx;
-          acc[i] += fg * fx * rs[r];
-        }
-      }
-      dot[r] = warp_sum(dot[r]);
-      if (lane == 0) partial[parity][r][warp] = dot[r];
-    }
-    __syncthreads();  // the other buffer is free again: its readers passed the previous barrier
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      if (row0 + r < rows) {
-        float total = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) total += i < nwarps ? partial[parity][r][i] : 0.0f;
-        const float coef = total * rs[r] * rs[r] * rs[r] / (float)H;
-        if (live) {
-          float o[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float fx = __bfloat162float(cx[r].v[i]), fg = __bfloat162float(cg[r].v[i]);
-            o[i] = fg * fw[i] * rs[r] - fx * coef;
-          }
-          store8(dx + (size_t)(row0 + r) * H + c, o);
-        }
-      }
-      cx[r] = nx[r];
-      cg[r] = ng[r];
-    }
+    for (; p < nparts; p += 32) s += partials[(size_t)p * width + c];
   }
-  if (live) {
+  fold[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < width) {
+    float t = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) atomicAdd(dw + c + i, acc[i]);
+    for (int i = 0; i < 32; ++i) t += fold[i][threadIdx.x];
+    if (c < split) out_a[c] += t;
+    else out_b[c - split] += t;
   }
 }
 
@@ -332,13 +295,17 @@ layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
 }
 
 // g = dy * w; dx = rstd * (g - mean(g) - xhat * mean(g * xhat));
-// dw += sum_rows dy * xhat, db += sum_rows dy (fp32 atomics, one set per warp at the end).
+// dw += sum_rows dy * xhat, db += sum_rows dy: every warp keeps partials in registers, the
+// CTA's warps fold them through shared memory and the CTA writes one [dw | db] row of
+// `partials` ([gridDim.x][2 * H] fp32) that colsum_add_kernel folds into dw and db (2 * H
+// atomics per WARP on the same addresses used to dominate this kernel).
 template <int MAX_ITERS>
 __global__ void __launch_bounds__(256)
 layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                      const bf16* __restrict__ w, const float* __restrict__ mean,
                      const float* __restrict__ rstd, bf16* __restrict__ dx,
-                     float* __restrict__ dw, float* __restrict__ db, int rows, int H) {
+                     float* __restrict__ partials, int rows, int H) {
+  __shared__ float fold[2 * 1024];
   const int lane = threadIdx.x & 31;
   const int warps_per_cta = blockDim.x >> 5;
   float aw[MAX_ITERS][8], ab[MAX_ITERS][8], fw[MAX_ITERS][8];
@@ -388,16 +355,26 @@ layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
       }
     }
   }
+  // fold[j * (H / 8) + pack] holds element j of a pack: the lanes of a warp then hit
+  // consecutive words (element-major order would put them 8 words apart, on 4 banks)
+  const int packs = H / 8;
+  for (int c = threadIdx.x; c < 2 * H; c += blockDim.x) fold[c] = 0.0f;
+  __syncthreads();
 #pragma unroll
   for (int k = 0; k < MAX_ITERS; ++k) {
-    const int c = (lane + k * 32) * 8;
-    if (c < H) {
+    const int pack = lane + k * 32;
+    if (pack < packs) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        atomicAdd(dw + c + i, aw[k][i]);
-        atomicAdd(db + c + i, ab[k][i]);
+        atomicAdd(fold + i * packs + pack, aw[k][i]);       // 8 warps per address
+        atomicAdd(fold + H + i * packs + pack, ab[k][i]);
       }
     }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * H; c += blockDim.x) {
+    const int half = c >= H, cc = c - half * H;              // column cc of dw (0) or db (1)
+    partials[(size_t)blockIdx.x * 2 * H + c] = fold[half * H + (cc & 7) * packs + (cc >> 3)];
   }
 }
 
@@ -445,20 +422,34 @@ bias_gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   load8(bias + c, bb);
 #pragma unroll
   for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
-  for (long long r = blockIdx.y; r < rows; r += gridDim.y) {
-    float u[8], d[8];
-    load8(x + r * C + c, u);
-    load8(dy + r * C + c, d);
+  // four rows of loads in flight per thread (one row at a time left the kernel at a third of
+  // the copy rate)
+  for (long long r0 = blockIdx.y; r0 < rows; r0 += 4LL * gridDim.y) {
+    Bf8 bu[4], bd[4];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float v = u[k] + bb[k];
-      const float t = tanh_fast(kGeluK * (v + kGeluC * v * v * v));
-      const float dg = 0.5f * (1.0f + t) +
-                       0.5f * v * (1.0f - t * t) * kGeluK * (1.0f + 3.0f * kGeluC * v * v);
-      d[k] *= dg;
-      acc[k] += d[k];
+    for (int j = 0; j < 4; ++j) {
+      const long long r = r0 + (long long)j * gridDim.y;
+      if (r < rows) {
+        bu[j] = *reinterpret_cast<const Bf8*>(x + r * C + c);
+        bd[j] = *reinterpret_cast<const Bf8*>(dy + r * C + c);
+      }
     }
-    store8(dx + r * C + c, d);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long r = r0 + (long long)j * gridDim.y;
+      if (r >= rows) continue;
+      float d[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float v = __bfloat162float(bu[j].v[k]) + bb[k];
+        const float t = tanh_fast(kGeluK * (v + kGeluC * v * v * v));
+        const float dg = 0.5f * (1.0f + t) +
+                         0.5f * v * (1.0f - t * t) * kGeluK * (1.0f + 3.0f * kGeluC * v * v);
+        d[k] = __bfloat162float(bd[j].v[k]) * dg;
+        acc[k] += d[k];
+      }
+      store8(dx + r * C + c, d);
+    }
   }
 #pragma unroll
   for (int k = 0; k < 8; ++k) atomicAdd(dbias + c + k, acc[k]);
@@ -504,20 +495,52 @@ rope_kernel(bf16* __restrict__ x, const float* __restrict__ cos_t, const float* 
 // ---------------------------------------------------------------------------
 // SwiGLU on a fused [tokens, 2F] projection (gate | up): h = silu(gate) * up
 // ---------------------------------------------------------------------------
+// Two independent 8-element groups per thread and iteration: all loads of both are issued
+// before the first result is needed (one group per iteration left the kernels at half the copy
+// rate: too few bytes in flight per thread for five streams).
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, long long tokens, int F) {
   const int vec = F / 8;
   const long long total = tokens * vec;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / vec;
-    const int c = (int)(i - t * vec) * 8;
-    float g[8], u[8];
-    load8(gu + t * 2 * F + c, g);
-    load8(gu + t * 2 * F + F + c, u);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total;
+       i0 += 2 * stride) {
+    const long long i1 = i0 + stride;
+    const bool two = i1 < total;
+    const long long t0 = i0 / vec, t1 = two ? i1 / vec : t0;
+    const int c0 = (int)(i0 - t0 * vec) * 8, c1 = two ? (int)(i1 - t1 * vec) * 8 : c0;
+    Bf8 g0 = *reinterpret_cast<const Bf8*>(gu + t0 * 2 * F + c0);
+    Bf8 u0 = *reinterpret_cast<const Bf8*>(gu + t0 * 2 * F + F + c0);
+    Bf8 g1 = *reinterpret_cast<const Bf8*>(gu + t1 * 2 * F + c1);
+    Bf8 u1 = *reinterpret_cast<const Bf8*>(gu + t1 * 2 * F + F + c1);
+    float o[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.0f + __expf(-g[k])) * u[k];
-    store8(h + t * F + c, g);
+    for (int k = 0; k < 8; ++k) {
+      const float g = __bfloat162float(g0.v[k]);
+      o[k] = g / (1.0f + __expf(-g)) * __bfloat162float(u0.v[k]);
+    }
+    store8(h + t0 * F + c0, o);
+    if (two) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float g = __bfloat162float(g1.v[k]);
+        o[k] = g / (1.0f + __expf(-g)) * __bfloat162float(u1.v[k]);
+      }
+      store8(h + t1 * F + c1, o);
+    }
+  }
+}
+
+__device__ __forceinline__ void swiglu_bwd8(const Bf8& g, const Bf8& u, const Bf8& d,
+                                            float (&dg)[8], float (&du)[8]) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float gk = __bfloat162float(g.v[k]), uk = __bfloat162float(u.v[k]);
+    const float dk = __bfloat162float(d.v[k]);
+    const float sg = 1.0f / (1.0f + __expf(-gk));
+    const float silu = gk * sg;
+    dg[k] = dk * uk * (sg + silu * (1.0f - sg));
+    du[k] = dk * silu;
   }
 }
 
@@ -526,23 +549,28 @@ swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dh,
                   bf16* __restrict__ dgu, long long tokens, int F) {
   const int vec = F / 8;
   const long long total = tokens * vec;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / vec;
-    const int c = (int)(i - t * vec) * 8;
-    float g[8], u[8], d[8], dg[8], du[8];
-    load8(gu + t * 2 * F + c, g);
-    load8(gu + t * 2 * F + F + c, u);
-    load8(dh + t * F + c, d);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float sg = 1.0f / (1.0f + __expf(-g[k]));
-      const float silu = g[k] * sg;
-      dg[k] = d[k] * u[k] * (sg + silu * (1.0f - sg));
-      du[k] = d[k] * silu;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total;
+       i0 += 2 * stride) {
+    const long long i1 = i0 + stride;
+    const bool two = i1 < total;
+    const long long t0 = i0 / vec, t1 = two ? i1 / vec : t0;
+    const int c0 = (int)(i0 - t0 * vec) * 8, c1 = two ? (int)(i1 - t1 * vec) * 8 : c0;
+    const Bf8 g0 = *reinterpret_cast<const Bf8*>(gu + t0 * 2 * F + c0);
+    const Bf8 u0 = *reinterpret_cast<const Bf8*>(gu + t0 * 2 * F + F + c0);
+    const Bf8 d0 = *reinterpret_cast<const Bf8*>(dh + t0 * F + c0);
+    const Bf8 g1 = *reinterpret_cast<const Bf8*>(gu + t1 * 2 * F + c1);
+    const Bf8 u1 = *reinterpret_cast<const Bf8*>(gu + t1 * 2 * F + F + c1);
+    const Bf8 d1 = *reinterpret_cast<const Bf8*>(dh + t1 * F + c1);
+    float dg[8], du[8];
+    swiglu_bwd8(g0, u0, d0, dg, du);
+    store8(dgu + t0 * 2 * F + c0, dg);
+    store8(dgu + t0 * 2 * F + F + c0, du);
+    if (two) {
+      swiglu_bwd8(g1, u1, d1, dg, du);
+      store8(dgu + t1 * 2 * F + c1, dg);
+      store8(dgu + t1 * 2 * F + F + c1, du);
     }
-    store8(dgu + t * 2 * F + c, dg);
-    store8(dgu + t * 2 * F + F + c, du);
   }
 }
 
@@ -714,45 +742,43 @@ int bcom_rmsnorm_fwd(const void* x, const void* w, void* y, void* rstd, int rows
   return (int)cudaGetLastError();
 }
 
-// 1: one row per CTA barrier (default); 4: four rows per barrier for H <= 4096 (off by default)
-static int g_rmsnorm_bwd_rows = 1;
+// `partials`: fp32 scratch of at least bcom_norm_bwd_scratch_elems(H, layernorm) elements,
+// private to the call until it has run.  `dres`: optional bf16 [rows, H] added to dx.
+static const int kRmsBwdMaxCtas = 148 * 2;
+static const int kLnBwdMaxCtas = 148 * 4;
 
-int bcom_rmsnorm_bwd_set_rows(int rows_per_barrier) {
-  const int old = g_rmsnorm_bwd_rows;
-  if (rows_per_barrier == 1 || rows_per_barrier == 4) g_rmsnorm_bwd_rows = rows_per_barrier;
-  return old;
+long long bcom_norm_bwd_scratch_elems(int H, int layernorm) {
+  return layernorm ? (long long)kLnBwdMaxCtas * 2 * H : (long long)kRmsBwdMaxCtas * H;
 }
 
-int bcom_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd, void* dx,
-                     void* dw_fp32, int rows, int H, void* stream) {
+int bcom_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rstd,
+                     const void* dres, void* dx, void* dw_fp32, void* partials, int rows, int H,
+                     void* stream) {
   if (rows <= 0) return 0;
   if (H % 8) return (int)cudaErrorInvalidValue;
-  // few, fat CTAs: every CTA ends with H atomic adds into dw, so their number matters
-  const int grid = rows < 148 * 2 ? rows : 148 * 2;
+  const int grid = rows < kRmsBwdMaxCtas ? rows : kRmsBwdMaxCtas;
   const int iters = (H / 8 + 511) / 512;
   cudaStream_t st = (cudaStream_t)stream;
-  if (g_rmsnorm_bwd_rows == 4 && iters <= 1) {
-    const int groups = (rows + 3) / 4;
-    const int g4 = groups < 148 ? groups : 148;  // 128 registers x 512 threads: one CTA per SM
-    rmsnorm_bwd_rows_kernel<4><<<g4, 512, 0, st>>>((const bf16*)dy, (const bf16*)x,
-                                                   (const bf16*)w, (const float*)rstd, (bf16*)dx,
-                                                   (float*)dw_fp32, rows, H);
-    return (int)cudaGetLastError();
-  }
-  if (iters <= 1)
-    rmsnorm_bwd_kernel<1><<<grid, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
-                                                (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
-                                                rows, H);
-  else if (iters <= 2)
-    rmsnorm_bwd_kernel<2><<<grid, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
-                                                (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
-                                                rows, H);
-  else if (iters <= 4)
-    rmsnorm_bwd_kernel<4><<<grid, 512, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
-                                                (const float*)rstd, (bf16*)dx, (float*)dw_fp32,
-                                                rows, H);
-  else
-    return (int)cudaErrorInvalidValue;  // H up to 16384
+#define BCOM_RMS_BWD(N)                                                                       \
+  do {                                                                                        \
+    if (dres)                                                                                 \
+      rmsnorm_bwd_kernel<N, true><<<grid, 512, 0, st>>>(                                      \
+          (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd,                \
+          (const bf16*)dres, (bf16*)dx, (float*)partials, rows, H);                           \
+    else                                                                                      \
+      rmsnorm_bwd_kernel<N, false><<<grid, 512, 0, st>>>(                                     \
+          (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)rstd, nullptr,       \
+          (bf16*)dx, (float*)partials, rows, H);                                              \
+  } while (0)
+  if (iters <= 1) BCOM_RMS_BWD(1);
+  else if (iters <= 2) BCOM_RMS_BWD(2);
+  else if (iters <= 4) BCOM_RMS_BWD(4);
+  else return (int)cudaErrorInvalidValue;  // H up to 16384
+#undef BCOM_RMS_BWD
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return (int)err;
+  colsum_add_kernel<<<(H + 31) / 32, dim3(32, 32), 0, st>>>(
+      (const float*)partials, (float*)dw_fp32, nullptr, grid, H, H);
   return (int)cudaGetLastError();
 }
 
@@ -777,24 +803,29 @@ int bcom_layernorm_fwd(const void* x, const void* w, const void* b, void* y, voi
   return (int)cudaGetLastError();
 }
 
-// dw / db: fp32 [H], accumulated into (not overwritten).
+// dw / db: fp32 [H], accumulated into (not overwritten); `partials`: see bcom_rmsnorm_bwd.
 int bcom_layernorm_bwd(const void* dy, const void* x, const void* w, const void* mean,
-                       const void* rstd, void* dx, void* dw_fp32, void* db_fp32, int rows, int H,
-                       void* stream) {
+                       const void* rstd, void* dx, void* dw_fp32, void* db_fp32, void* partials,
+                       int rows, int H, void* stream) {
   if (rows <= 0) return 0;
   if (H % 8 || H > 1024) return (int)cudaErrorInvalidValue;
   const int warps = 8;
   const int want = (rows + warps - 1) / warps;
-  const int grid = want < 148 ? want : 148;  // every warp ends with 2 * H atomics
+  const int grid = want < kLnBwdMaxCtas ? want : kLnBwdMaxCtas;
   cudaStream_t st = (cudaStream_t)stream;
   const int iters = (H / 8 + 31) / 32;
 #define BCOM_LN_BWD(N)                                                                        \
   layernorm_bwd_kernel<N><<<grid, warps * 32, 0, st>>>(                                        \
       (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean, (const float*)rstd, \
-      (bf16*)dx, (float*)dw_fp32, (float*)db_fp32, rows, H)
+      (bf16*)dx, (float*)partials, rows, H)
   if (iters <= 2) BCOM_LN_BWD(2);
   else BCOM_LN_BWD(4);
 #undef BCOM_LN_BWD
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return (int)err;
+  // a partial row is [dw | db]
+  colsum_add_kernel<<<(2 * H + 31) / 32, dim3(32, 32), 0, st>>>(
+      (const float*)partials, (float*)dw_fp32, (float*)db_fp32, grid, 2 * H, H);
   return (int)cudaGetLastError();
 }
 
@@ -814,7 +845,7 @@ int bcom_bias_gelu_bwd(const void* dy, const void* x, const void* bias, void* dx
   if (C % 8) return (int)cudaErrorInvalidValue;
   const int threads = 128;
   const int col_tiles = (C / 8 + threads - 1) / threads;
-  int strips = (148 * 8 + col_tiles - 1) / col_tiles;
+  int strips = (148 * 4 + col_tiles - 1) / col_tiles;
   if (strips > rows) strips = (int)rows;
   if (strips > 65535) strips = 65535;
   bias_gelu_bwd_kernel<<<dim3(col_tiles, strips), threads, 0, (cudaStream_t)stream>>>(

@@ -10,9 +10,14 @@ namespace gemm {
 
 // taddr: TMEM address of the warp's first lane at the tile's first column.
 // C row `row`, columns [n0, n0 + BN) are written where row < M and column < N (N % 8 == 0).
+// R (bf16 [M, N] with leading dimension ldr, or null): added to the product before the bf16
+// result is rounded; only read by the bf16, non-accumulating form (a linear layer whose output
+// joins a residual stream: C = R + A x B in one pass instead of a GEMM and an add kernel).
 template <int BN, bool OUT_F32, bool ACCUM>
 __device__ __forceinline__ void store_accumulator_rows(uint32_t taddr, void* C, long long ldc,
-                                                       int row, int n0, int M, int N) {
+                                                       int row, int n0, int M, int N,
+                                                       const void* R = nullptr,
+                                                       long long ldr = 0) {
   if constexpr (OUT_F32 && ACCUM) {
     // Accumulating fp32 epilogue (weight gradients): the old values of chunk c+1 are
     // requested before chunk c is finished, so their latency hides behind the TMEM
@@ -60,8 +65,19 @@ __device__ __forceinline__ void store_accumulator_rows(uint32_t taddr, void* C, 
     for (int c = 0; c < BN / 32; ++c) {
       uint32_t r[32];
       tc::tmem_ld_32x32(taddr + c * 32, r);
-      tc::tmem_wait_ld();
       const int col0 = n0 + c * 32;
+      uint4 res[4];
+      if constexpr (!OUT_F32 && !ACCUM) {
+        // the residual row segment is requested before the wait on the TMEM load
+        if (R != nullptr && row < M) {
+          const __nv_bfloat16* rrow =
+              reinterpret_cast<const __nv_bfloat16*>(R) + (long long)row * ldr + col0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            if (col0 + v * 8 < N) res[v] = *reinterpret_cast<const uint4*>(rrow + v * 8);
+        }
+      }
+      tc::tmem_wait_ld();
       if (row < M && col0 < N) {
         if constexpr (OUT_F32) {
           float* dst = reinterpret_cast<float*>(C) + (long long)row * ldc + col0;
@@ -90,6 +106,10 @@ __device__ __forceinline__ void store_accumulator_rows(uint32_t taddr, void* C, 
                 const __nv_bfloat16* oh = reinterpret_cast<const __nv_bfloat16*>(&old);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[i] += __bfloat162float(oh[i]);
+              } else if (R != nullptr) {
+                const __nv_bfloat16* rh = reinterpret_cast<const __nv_bfloat16*>(&res[v]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] += __bfloat162float(rh[i]);
               }
               uint4 o;
               __nv_bfloat162* oh2 = reinterpret_cast<__nv_bfloat162*>(&o);

@@ -59,12 +59,10 @@ __device__ unsigned int g_status[4];
 
 struct Params {
   void* C;
-  long long ldc;
+  const void* R;  // optional bf16 residual added in the bf16 epilogue (see gemm_epilogue.cuh)
+  long long ldc, ldr;
   int M, N, K;
   int tiles_m, tiles_n;
-  // SPLIT_TAIL kernels only: tiles [0, full_tiles) are whole 128x256 tiles; every later tile is
-  // cut into two 128x128 halves, so work items [full_tiles, work_items) are half tiles
-  int full_tiles, work_items;
 };
 
 struct Shared {
@@ -84,19 +82,13 @@ __device__ __forceinline__ void fail(Shared* sh, unsigned int code) {
   }
 }
 
-// One unit of work of a CTA: rows [m0, m0 + BM), columns [n0, n0 + bn) of C.
-// SPLIT_TAIL: the tiles of the last, partly filled wave are processed as half tiles (bn = 128)
-// by twice as many CTAs, which halves the time of that wave: with 512 tiles on 148 CTAs (any
-// 4096 x 4096 output) the kernel takes 3.5 tile times instead of 4.
+// One unit of work of a CTA: rows [m0, m0 + BM), columns [n0, n0 + BN) of C.
 using gemm_sched::WorkItem;
-template <bool SPLIT_TAIL>
 __device__ __forceinline__ WorkItem work_item(const Params& p, int w) {
-  return gemm_sched::work_item<BM, BN, GROUP_M, SPLIT_TAIL>(p.tiles_m, p.tiles_n, p.full_tiles,
-                                                            w);
+  return gemm_sched::work_item<BM, BN, GROUP_M>(p.tiles_m, p.tiles_n, w);
 }
 
-// With SPLIT_TAIL the K-major B tensor map has a 128-row box (whole tiles issue two loads).
-template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM, bool SPLIT_TAIL = false>
+template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const Params p) {
@@ -108,7 +100,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int total_tiles = SPLIT_TAIL ? p.work_items : p.tiles_m * p.tiles_n;
+  const int total_tiles = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -136,7 +128,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < total_tiles && !sh->abort; t += gridDim.x) {
-        const WorkItem wi = work_item<SPLIT_TAIL>(p, t);
+        const WorkItem wi = work_item(p, t);
         const int m0 = wi.m0, n0 = wi.n0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!tc::mbar_wait(&sh->empty[stage], phase ^ 1u, kWaitBudgetNs)) {
@@ -145,8 +137,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           uint8_t* sA = smem + stage * STAGE_BYTES;
           uint8_t* sB = sA + A_BYTES;
-          tc::mbar_expect_tx(&sh->full[stage],
-                             SPLIT_TAIL ? A_BYTES + wi.bn * BK * 2 : STAGE_BYTES);
+          tc::mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
           const int k0 = kb * BK;
           if constexpr (A_MN) {
 #pragma unroll
@@ -158,12 +149,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if constexpr (B_MN) {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              if (!SPLIT_TAIL || c * 64 < wi.bn)
-                tc::tma_load_2d(sB + c * CHUNK_BYTES, &tmB, &sh->full[stage], n0 + c * 64, k0);
-          } else if constexpr (SPLIT_TAIL) {
-            tc::tma_load_2d(sB, &tmB, &sh->full[stage], k0, n0);
-            if (wi.bn == BN)
-              tc::tma_load_2d(sB + B_BYTES / 2, &tmB, &sh->full[stage], k0, n0 + BN / 2);
+              tc::tma_load_2d(sB + c * CHUNK_BYTES, &tmB, &sh->full[stage], n0 + c * 64, k0);
           } else {
             tc::tma_load_2d(sB, &tmB, &sh->full[stage], k0, n0);
           }
@@ -174,14 +160,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc_full = tc::make_idesc_bf16(BM, BN, A_MN, B_MN);
-      constexpr uint32_t idesc_half = tc::make_idesc_bf16(BM, BN / 2, A_MN, B_MN);
+      constexpr uint32_t idesc = tc::make_idesc_bf16(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int iter = 0;
       for (int t = blockIdx.x; t < total_tiles && !sh->abort; t += gridDim.x, ++iter) {
-        const uint32_t idesc =
-            (SPLIT_TAIL && work_item<SPLIT_TAIL>(p, t).bn != BN) ? idesc_half : idesc_full;
         const int buf = iter & 1;
         const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
         if (!tc::mbar_wait(&sh->acc_empty[buf], acc_phase ^ 1u, kWaitBudgetNs)) {
@@ -222,7 +205,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter ..
     int iter = 0;
     for (int t = blockIdx.x; t < total_tiles && !sh->abort; t += gridDim.x, ++iter) {
-      const WorkItem wi = work_item<SPLIT_TAIL>(p, t);
+      const WorkItem wi = work_item(p, t);
       const int buf = iter & 1;
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       if (!tc::mbar_wait(&sh->acc_full[buf], acc_phase, kWaitBudgetNs)) {
@@ -233,10 +216,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = wi.m0 + quarter * 32 + lane;
       const int n0 = wi.n0;
       const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
-      if (SPLIT_TAIL && wi.bn != BN)
-        store_accumulator_rows<BN / 2, OUT_F32, ACCUM>(taddr, p.C, p.ldc, row, n0, p.M, p.N);
-      else
-        store_accumulator_rows<BN, OUT_F32, ACCUM>(taddr, p.C, p.ldc, row, n0, p.M, p.N);
+      store_accumulator_rows<BN, OUT_F32, ACCUM>(taddr, p.C, p.ldc, row, n0, p.M, p.N, p.R,
+                                                 p.ldr);
       tc::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->acc_empty[buf]);
@@ -258,35 +239,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // 2-D bf16 row-major matrix [rows, cols] with leading dimension ld (elements).
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
                     long long ld, int box_cols, int box_rows) {
-  return tc::make_tensor_map_2d(map, ptr, 2, rows, cols, ld, box_cols, box_rows);
+  return tc::cached_tensor_map_2d(map, ptr, 2, rows, cols, ld, box_cols, box_rows);
 }
 
 typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const Params);
 
-template <bool A_MN, bool B_MN, bool SPLIT>
+template <bool A_MN, bool B_MN>
 static Kernel pick_out(bool out_f32, bool accum) {
-  if (out_f32) return accum ? gemm_bf16_kernel<A_MN, B_MN, true, true, SPLIT>
-                            : gemm_bf16_kernel<A_MN, B_MN, true, false, SPLIT>;
-  return accum ? gemm_bf16_kernel<A_MN, B_MN, false, true, SPLIT>
-               : gemm_bf16_kernel<A_MN, B_MN, false, false, SPLIT>;
+  if (out_f32) return accum ? gemm_bf16_kernel<A_MN, B_MN, true, true>
+                            : gemm_bf16_kernel<A_MN, B_MN, true, false>;
+  return accum ? gemm_bf16_kernel<A_MN, B_MN, false, true>
+               : gemm_bf16_kernel<A_MN, B_MN, false, false>;
 }
 
-template <bool SPLIT>
-static Kernel pick_layout(bool a_mn, bool b_mn, bool out_f32, bool accum) {
-  if (a_mn) return b_mn ? pick_out<true, true, SPLIT>(out_f32, accum)
-                        : pick_out<true, false, SPLIT>(out_f32, accum);
-  return b_mn ? pick_out<false, true, SPLIT>(out_f32, accum)
-              : pick_out<false, false, SPLIT>(out_f32, accum);
+static Kernel pick(bool a_mn, bool b_mn, bool out_f32, bool accum) {
+  if (a_mn) return b_mn ? pick_out<true, true>(out_f32, accum)
+                        : pick_out<true, false>(out_f32, accum);
+  return b_mn ? pick_out<false, true>(out_f32, accum) : pick_out<false, false>(out_f32, accum);
 }
-
-static Kernel pick(bool a_mn, bool b_mn, bool out_f32, bool accum, bool split_tail) {
-  return split_tail ? pick_layout<true>(a_mn, b_mn, out_f32, accum)
-                    : pick_layout<false>(a_mn, b_mn, out_f32, accum);
-}
-
-// 0: whole tiles only; 1: the tiles of a last wave that fills at most half of the grid are
-// processed as half tiles (see SPLIT_TAIL)
-static int g_split_tail = 0;
 
 }  // namespace gemm
 
@@ -297,15 +267,19 @@ extern "C" {
 //   b_mn_major = 0: B is [N, K] row-major (ldb >= K); 1: B is stored [K, N] (ldb >= N)
 //   out_fp32: C is fp32 instead of bf16; accumulate: add to the existing C
 // Leading dimensions are in elements and must keep rows 16-byte aligned.
-int bcom_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                   long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_fp32,
-                   int accumulate, int max_ctas, void* stream) {
+//   residual (optional, bf16 [M, N], leading dimension ldr): C = residual + A x B; only with a
+//   bf16, non-accumulating C
+int bcom_gemm_bf16_ex(const void* A, const void* B, void* C, const void* residual, int M, int N,
+                      int K, long long lda, long long ldb, long long ldc, long long ldr,
+                      int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int max_ctas,
+                      void* stream) {
   using namespace gemm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // argument errors get codes of their own (1001..1005) so that they cannot be mistaken
   // for a CUDA error
   if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8)) || (N % 8)) return 1001;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return 1002;
+  if (residual && (out_fp32 || accumulate || (ldr % 8) || ((uintptr_t)residual & 15))) return 1001;
   (void)cudaGetLastError();  // do not inherit an error left behind by an earlier call
   CUtensorMap tmA, tmB;
   // the tensor-map encoder is a driver call: make sure this thread (it may be an autograd
@@ -313,7 +287,9 @@ int bcom_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   tc::bind_context_once();
   Params p;
   p.C = C;
+  p.R = residual;
   p.ldc = ldc;
+  p.ldr = ldr;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -326,33 +302,22 @@ int bcom_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, l
   int grid = tiles;
   if (grid > sms) grid = sms;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  // split the last wave when it would leave at least half of the grid idle
-  const bool split_tail =
-      gemm_sched::plan_tail(tiles, grid, g_split_tail != 0, &p.full_tiles, &p.work_items);
   if (a_mn_major ? make_map(&tmA, A, K, M, lda, 64, BK) : make_map(&tmA, A, M, K, lda, BK, BM))
     return 1003;
   if (b_mn_major ? make_map(&tmB, B, K, N, ldb, 64, BK)
-                 : make_map(&tmB, B, N, K, ldb, BK, split_tail ? BN / 2 : BN))
+                 : make_map(&tmB, B, N, K, ldb, BK, BN))
     return 1004;
-  Kernel kernel =
-      pick(a_mn_major != 0, b_mn_major != 0, out_fp32 != 0, accumulate != 0, split_tail);
-  static std::mutex mu;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    cudaError_t err = cudaFuncSetAttribute((const void*)kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (err != cudaSuccess) return 1005;
-  }
+  Kernel kernel = pick(a_mn_major != 0, b_mn_major != 0, out_fp32 != 0, accumulate != 0);
+  if (!tc::ensure_dynamic_smem((const void*)kernel, SMEM_BYTES)) return 1005;
   kernel<<<grid, kThreads, SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, p);
   return (int)cudaGetLastError();
 }
 
-// 1: split the tiles of a sparsely filled last wave into half tiles (off by default).  Returns
-// the previous setting.
-int bcom_gemm_set_split_tail(int on) {
-  const int old = gemm::g_split_tail;
-  gemm::g_split_tail = on ? 1 : 0;
-  return old;
+int bcom_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                   long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_fp32,
+                   int accumulate, int max_ctas, void* stream) {
+  return bcom_gemm_bf16_ex(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, a_mn_major, b_mn_major,
+                           out_fp32, accumulate, max_ctas, stream);
 }
 
 // Copies the 4-word status record {code, cta, thread, -}; clears it when `clear` != 0.

@@ -64,7 +64,8 @@ __device__ unsigned long long* g_profile;
 
 struct Params {
   void* C;
-  long long ldc;
+  const void* R;  // optional bf16 residual added in the bf16 epilogue
+  long long ldc, ldr;
   int M, N, K;
   int tiles_m, tiles_n;
   int flags;  // experiment switches of the MMA issuer loop (bcom_gemm2_set_flags)
@@ -358,7 +359,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row = tm * BM + (int)rank * BM_CTA + quarter * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + (uint32_t)buf * BN + ((uint32_t)(quarter * 32) << 16);
-      gemm::store_accumulator_rows<BN, OUT_F32, ACCUM>(taddr, p.C, p.ldc, row, n0, p.M, p.N);
+      gemm::store_accumulator_rows<BN, OUT_F32, ACCUM>(taddr, p.C, p.ldc, row, n0, p.M, p.N, p.R,
+                                                       p.ldr);
       tc::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -386,7 +388,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 // 2-D bf16 row-major matrix [rows, cols] with leading dimension ld (elements).
 static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
                     long long ld, int box_cols, int box_rows) {
-  return tc::make_tensor_map_2d(map, ptr, 2, rows, cols, ld, box_cols, box_rows);
+  return tc::cached_tensor_map_2d(map, ptr, 2, rows, cols, ld, box_cols, box_rows);
 }
 
 typedef void (*Kernel)(const CUtensorMap, const CUtensorMap, const Params);
@@ -406,6 +408,35 @@ static Kernel pick(bool a_mn, bool b_mn, bool out_f32, bool accum) {
 
 static int g_flags = 0;
 
+// CTA pairs that can be resident at once (pairs live inside one GPC, so this can be fewer than
+// half the SM count); asked once per kernel.
+static int resident_pairs(const void* kernel) {
+  struct Seen {
+    const void* kernel;
+    int pairs;
+  };
+  static std::mutex mu;
+  static Seen seen[64];
+  static int count = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < count; ++i)
+    if (seen[i].kernel == kernel) return seen[i].pairs;
+  int pairs = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  if (cudaOccupancyMaxActiveClusters(&pairs, kernel, &cfg) != cudaSuccess || pairs <= 0) {
+    (void)cudaGetLastError();
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    pairs = sms / 2;
+  }
+  if (count < 64) seen[count++] = Seen{kernel, pairs};
+  return pairs;
+}
+
 }  // namespace gemm2
 
 extern "C" {
@@ -418,13 +449,15 @@ int bcom_gemm2_set_flags(int flags) {
 
 
 // Same contract as bcom_gemm_bf16 (gemm_tcgen05.cu); max_ctas counts CTAs (two per pair).
-int bcom_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                    long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_fp32,
-                    int accumulate, int max_ctas, void* stream) {
+int bcom_gemm2_bf16_ex(const void* A, const void* B, void* C, const void* residual, int M, int N,
+                       int K, long long lda, long long ldb, long long ldc, long long ldr,
+                       int a_mn_major, int b_mn_major, int out_fp32, int accumulate,
+                       int max_ctas, void* stream) {
   using namespace gemm2;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8)) || (N % 8)) return 1001;
   if (((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return 1002;
+  if (residual && (out_fp32 || accumulate || (ldr % 8) || ((uintptr_t)residual & 15))) return 1001;
   (void)cudaGetLastError();
   CUtensorMap tmA, tmB;
   tc::bind_context_once();
@@ -433,17 +466,13 @@ int bcom_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   if (b_mn_major ? make_map(&tmB, B, K, N, ldb, 64, BK) : make_map(&tmB, B, N, K, ldb, BK, BN_CTA))
     return 1004;
   Kernel kernel = pick(a_mn_major != 0, b_mn_major != 0, out_fp32 != 0, accumulate != 0);
-  static std::mutex mu;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SMEM_BYTES) != cudaSuccess)
-      return 1005;
-  }
+  if (!tc::ensure_dynamic_smem((const void*)kernel, SMEM_BYTES)) return 1005;
   Params p;
   p.flags = g_flags;
   p.C = C;
+  p.R = residual;
   p.ldc = ldc;
+  p.ldr = ldr;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -451,27 +480,20 @@ int bcom_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, 
   p.tiles_n = (N + BN - 1) / BN;
   // persistent grid: as many pairs as can be resident at once (pairs live inside one GPC, so
   // this can be fewer than half the SM count), never more than there are tiles
-  int pairs = 0;
-  {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
-    if (cudaOccupancyMaxActiveClusters(&pairs, (const void*)kernel, &cfg) != cudaSuccess ||
-        pairs <= 0) {
-      (void)cudaGetLastError();
-      int dev = 0, sms = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      pairs = sms / 2;
-    }
-  }
+  int pairs = resident_pairs((const void*)kernel);
   const int tiles = p.tiles_m * p.tiles_n;
   if (pairs > tiles) pairs = tiles;
   if (max_ctas >= 2 && pairs > max_ctas / 2) pairs = max_ctas / 2;
   if (pairs < 1) pairs = 1;
   kernel<<<2 * pairs, kThreads, SMEM_BYTES, (cudaStream_t)stream>>>(tmA, tmB, p);
   return (int)cudaGetLastError();
+}
+
+int bcom_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                    long long ldb, long long ldc, int a_mn_major, int b_mn_major, int out_fp32,
+                    int accumulate, int max_ctas, void* stream) {
+  return bcom_gemm2_bf16_ex(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, a_mn_major, b_mn_major,
+                            out_fp32, accumulate, max_ctas, stream);
 }
 
 // Debugging aid: registers a device buffer of 4 x (number of CTA pairs) 64-bit words that the

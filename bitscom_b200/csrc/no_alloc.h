@@ -29,6 +29,16 @@ extern "C" {
 //   * The first call on a device looks up the device address of the scratch array
 //     (cudaGetSymbolAddress) with that device current; make that first call outside any
 //     stream capture.
+//   * The array is part of the library's device image.  With CUDA's default lazy module
+//     loading the image (and with it the 36 MiB) is placed on a device when the first kernel
+//     or symbol of this library is used there, which may be this entry point's own first
+//     call.  A host that gives all device memory to an arena must therefore touch the library
+//     BEFORE it does so (one warm-up call of any entry point of this library on that device,
+//     or CUDA_MODULE_LOADING=EAGER in the environment); otherwise that first call can fail
+//     with an out-of-memory error from the module load, although it allocates nothing itself.
+//   * Return codes: 0; 1001-1006 for argument errors (1006: larger than the scratch); any
+//     other value is the cudaError_t of the failing runtime call (for example 2,
+//     cudaErrorMemoryAllocation, from the module load described above).
 //   * All calls on a device share the one array, and it keeps whatever the previous call
 //     left: the accumulator part is cleared on the stream at the start of every call.
 //     Two calls whose kernels overlap on the GPU (different streams, no ordering) race

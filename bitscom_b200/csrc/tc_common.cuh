@@ -283,6 +283,70 @@ inline int make_tensor_map_2d(CUtensorMap* map, const void* ptr, int elem_bytes,
   return (int)r;
 }
 
+// Tensor maps are pure functions of (address, shape, leading dimension, box): a training step
+// presents the same few hundred operands again and again (weights, and activations that the
+// caching allocator hands back at the same addresses), so the encoded maps are kept in a small
+// per-thread direct-mapped cache and the driver call is skipped on a hit.
+struct TensorMapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int elem_bytes, box_cols, box_rows;
+  bool operator==(const TensorMapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
+           elem_bytes == o.elem_bytes && box_cols == o.box_cols && box_rows == o.box_rows;
+  }
+};
+
+inline int cached_tensor_map_2d(CUtensorMap* map, const void* ptr, int elem_bytes, long long rows,
+                                long long cols, long long ld, int box_cols, int box_rows) {
+  constexpr int kSlots = 1024;
+  struct Slot {
+    TensorMapKey key;
+    CUtensorMap map;
+    bool valid;
+  };
+  static thread_local Slot* slots = nullptr;
+  if (!slots) slots = new Slot[kSlots]();
+  const TensorMapKey key{ptr, rows, cols, ld, elem_bytes, box_cols, box_rows};
+  unsigned long long h = (unsigned long long)(uintptr_t)ptr * 0x9E3779B97F4A7C15ull;
+  h ^= (unsigned long long)rows * 0xC2B2AE3D27D4EB4Full + (unsigned long long)cols * 0x165667B19E3779F9ull;
+  h ^= (unsigned long long)ld * 0x27D4EB2F165667C5ull + (unsigned long long)(box_cols * 131 + box_rows);
+  Slot& s = slots[(h >> 32) % kSlots];
+  if (s.valid && s.key == key) {
+    *map = s.map;
+    return 0;
+  }
+  const int r = make_tensor_map_2d(map, ptr, elem_bytes, rows, cols, ld, box_cols, box_rows);
+  if (r == 0) {
+    s.key = key;
+    s.map = *map;
+    s.valid = true;
+  }
+  return r;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of on every
+// launch.  Returns false if the attribute could not be set.
+inline bool ensure_dynamic_smem(const void* kernel, int bytes) {
+  struct Seen {
+    const void* kernel;
+    int device;
+  };
+  static std::mutex mu;
+  static Seen seen[256];
+  static int count = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < count; ++i)
+    if (seen[i].kernel == kernel && seen[i].device == dev) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
+      cudaSuccess)
+    return false;
+  if (count < 256) seen[count++] = Seen{kernel, dev};
+  return true;
+}
+
 // Driver calls such as the tensor-map encoder need the device's primary context
 // bound to the calling thread, which an autograd worker thread may not have yet: a no-op
 // runtime call binds it.  Done once per (thread, device), so that later calls issue nothing

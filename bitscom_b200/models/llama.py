@@ -142,14 +142,16 @@ class LlamaStage(torch.nn.Module):
     def layer(self, i: int, x: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
         cfg = self.cfg
         cos, sin = self._rope_tables(seq, x.device)
-        h = K.rmsnorm(x, self._w(f"l{i}.norm1"), cfg.rms_eps)
+        # residual adds live in the epilogue of the output / down projections, and the two
+        # gradients that meet at each norm's input are added inside the norm's backward kernel
+        h, x = K.rmsnorm_fork(x, self._w(f"l{i}.norm1"), cfg.rms_eps)
         qkv = G.linear(h, self._w(f"l{i}.wqkv"))
         qkv = K.rope_qk_(qkv, cos, sin, cfg.num_heads, cfg.head_dim, seq)
         a = _attention(qkv, batch, seq, cfg.num_heads, cfg.head_dim, cfg.attention)
-        x = x + G.linear(a, self._w(f"l{i}.wo"))
-        h = K.rmsnorm(x, self._w(f"l{i}.norm2"), cfg.rms_eps)
+        x = G.linear(a, self._w(f"l{i}.wo"), residual=x)
+        h, x = K.rmsnorm_fork(x, self._w(f"l{i}.norm2"), cfg.rms_eps)
         gu = G.linear(h, self._w(f"l{i}.wgu"))
-        x = x + G.linear(K.swiglu(gu), self._w(f"l{i}.wdown"))
+        x = G.linear(K.swiglu(gu), self._w(f"l{i}.wdown"), residual=x)
         return x
 
     def forward(self, inp: torch.Tensor, targets: Optional[torch.Tensor] = None,

@@ -17,12 +17,11 @@ from ._native import NativeError, check, ptr, stream_ptr
 _lib = None
 _scratch: Dict[Tuple, torch.Tensor] = {}
 # forward kernels: "simple" alternates MMA and softmax inside a CTA; "pipelined" has an issuer
-# warp, double-buffered scores in TMEM and the output accumulated in TMEM; "pipelined8" is the
-# same with eight softmax warps (two threads per row)
-_FWD_VARIANTS = {"simple": 0, "pipelined": 1, "pipelined8": 2}
+# warp, double-buffered scores in TMEM and the output accumulated in TMEM
+_FWD_VARIANTS = {"simple": 0, "pipelined": 1}
 # how the backward kernel adds a dQ tile to the fp32 accumulator: float4 atomics from
 # registers, or TMA reductions from a shared-memory staging tile
-_BWD_DQ_VARIANTS = {"atomic": 0, "tma": 1, "tma_early": 2}
+_BWD_DQ_VARIANTS = {"atomic": 0, "tma": 1}
 
 
 def _get():
@@ -53,20 +52,19 @@ def available() -> bool:
 
 
 def set_forward_variant(name: str) -> str:
-    """Select the forward kernel ("simple", "pipelined" or "pipelined8", also
-    ``BITSCOM_ATTN_FWD``); returns the name that was active before."""
+    """Select the forward kernel ("simple" or "pipelined", also ``BITSCOM_ATTN_FWD``); returns
+    the name that was active before."""
     if name not in _FWD_VARIANTS:
         raise ValueError(f"unknown attention forward variant {name!r}")
     lib = _get()
     if lib is None:
         raise NativeError("attention kernel needs the bcom_llama library and a GPU")
     old = lib.bcom_attention_set_fwd_variant(_FWD_VARIANTS[name])
-    return {0: "simple", 1: "pipelined", 2: "pipelined8"}[old]
+    return {0: "simple", 1: "pipelined"}[old]
 
 
 def set_backward_dq_variant(name: str) -> str:
-    """Select how dQ tiles are accumulated ("atomic", "tma", or "tma_early": "tma" with the
-    next query block's loads issued under the dQ product; also ``BITSCOM_ATTN_BWD_DQ``);
+    """Select how dQ tiles are accumulated ("atomic" or "tma", also ``BITSCOM_ATTN_BWD_DQ``);
     returns the name that was active before."""
     if name not in _BWD_DQ_VARIANTS:
         raise ValueError(f"unknown attention backward dQ variant {name!r}")
@@ -74,7 +72,7 @@ def set_backward_dq_variant(name: str) -> str:
     if lib is None:
         raise NativeError("attention kernel needs the bcom_llama library and a GPU")
     old = lib.bcom_attention_set_bwd_dq_variant(_BWD_DQ_VARIANTS[name])
-    return {0: "atomic", 1: "tma", 2: "tma_early"}[old]
+    return {0: "atomic", 1: "tma"}[old]
 
 
 def supported(seq: int, head_dim: int) -> bool:

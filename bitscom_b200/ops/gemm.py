@@ -29,10 +29,9 @@ def _get():
             vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
             lib.bcom_gemm_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ll, ll, ll, ci, ci, ci, ci,
                                            ci, vp]
+            lib.bcom_gemm_bf16_ex.argtypes = [vp, vp, vp, vp, ci, ci, ci, ll, ll, ll, ll, ci, ci,
+                                              ci, ci, ci, vp]
             lib.bcom_gemm_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
-            lib.bcom_gemm_set_split_tail.argtypes = [ci]
-            if os.environ.get("BITSCOM_GEMM_SPLIT_TAIL", "0") == "1":
-                lib.bcom_gemm_set_split_tail(1)
         _lib = lib if lib is not None else False
     return _lib or None
 
@@ -50,6 +49,8 @@ def _get2():
             vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
             lib.bcom_gemm2_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ll, ll, ll, ci, ci, ci, ci,
                                             ci, vp]
+            lib.bcom_gemm2_bf16_ex.argtypes = [vp, vp, vp, vp, ci, ci, ci, ll, ll, ll, ll, ci,
+                                               ci, ci, ci, ci, vp]
             lib.bcom_gemm2_status.argtypes = [ctypes.POINTER(ctypes.c_uint * 4), ci]
             lib.bcom_gemm2_set_profile.argtypes = [vp]
         _lib2 = lib if lib is not None else False
@@ -87,17 +88,6 @@ def set_variant(name: str) -> str:
     return old
 
 
-def set_split_tail(on: bool) -> bool:
-    """One-CTA kernel only: when the last wave of 128x256 tiles fills at most half of the grid
-    (512 tiles on 148 SMs: every 4096 x 4096 output), process its tiles as 128x128 halves on
-    twice as many CTAs.  Off by default (also ``BITSCOM_GEMM_SPLIT_TAIL=1``); returns the
-    previous setting."""
-    lib = _get()
-    if lib is None:
-        raise NativeError("tcgen05 GEMM needs the bcom_llama library and a GPU")
-    return bool(lib.bcom_gemm_set_split_tail(int(bool(on))))
-
-
 _STATUS = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "accumulator hand-off"}
 
 
@@ -126,10 +116,12 @@ def use_library_gemm(on: bool) -> bool:
     return old
 
 
-def _gemm_library(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
+def _gemm_library(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate, residual=None):
     A = a.t() if a_mn_major else a
     B = b if b_mn_major else b.t()
     c = torch.matmul(A, B)
+    if residual is not None:
+        c = c + residual
     if out is None:
         return c if out_dtype == c.dtype else c.to(out_dtype)
     if accumulate:
@@ -139,7 +131,7 @@ def _gemm_library(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
     return out
 
 
-def _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
+def _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate, residual=None):
     """The kernel's contract for tensors that live on the CPU (fp32 accumulation, result
     rounded once): CPU ranks run the trainers' plumbing with it."""
     A = a.float().t() if a_mn_major else a.float()
@@ -147,6 +139,8 @@ def _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
     if A.shape[1] != B.shape[0]:
         raise ValueError(f"reduction dimensions differ: {A.shape[1]} vs {B.shape[0]}")
     c = A @ B
+    if residual is not None:
+        c = c + residual.float()
     if out is None:
         if accumulate:
             raise ValueError("accumulate=True needs an output tensor")
@@ -160,17 +154,22 @@ def _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate):
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
          b_mn_major: bool = False, out: Optional[torch.Tensor] = None,
          out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
-         max_ctas: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``C[M, N] (+)= A x B`` with bf16 operands and fp32 accumulation.
 
     ``a``: ``[M, K]`` (K-major) or, with ``a_mn_major``, stored ``[K, M]``.
     ``b``: ``[N, K]`` (K-major) or, with ``b_mn_major``, stored ``[K, N]``.
     Operands are 2-D with unit stride in the last dimension; row strides are free.
+    ``residual`` (bf16 ``[M, N]``, bf16 non-accumulating output only): ``C = residual + A x B``,
+    added in the epilogue before the result is rounded.
     """
+    if residual is not None and (accumulate or (out is not None and out.dtype != torch.bfloat16)
+                                 or (out is None and out_dtype != torch.bfloat16)):
+        raise ValueError("residual needs a bf16, non-accumulating output")
     if not a.is_cuda:
-        return _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate)
+        return _gemm_host(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate, residual)
     if _library:
-        return _gemm_library(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate)
+        return _gemm_library(a, b, a_mn_major, b_mn_major, out, out_dtype, accumulate, residual)
     lib = _get()
     if lib is None:
         raise NativeError("tcgen05 GEMM needs the bcom_llama library and a GPU")
@@ -189,10 +188,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False,
     if out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16,
                                                                       torch.float32):
         raise ValueError("bad output tensor")
-    launch = lib.bcom_gemm_bf16 if variant() == "1cta" else _get2().bcom_gemm2_bf16
+    if residual is not None and (residual.shape != (M, N) or residual.stride(1) != 1
+                                 or residual.dtype != torch.bfloat16):
+        raise ValueError("bad residual tensor")
+    launch = lib.bcom_gemm_bf16_ex if variant() == "1cta" else _get2().bcom_gemm2_bf16_ex
     with _native.on_device(a.device):
         check(launch(
-            ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            ptr(a), ptr(b), ptr(out), ptr(residual), M, N, K, a.stride(0), b.stride(0),
+            out.stride(0), 0 if residual is None else residual.stride(0),
             int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32),
             int(accumulate), int(max_ctas), stream_ptr(a.device)), "bcom_gemm_bf16")
     return out
@@ -207,13 +210,21 @@ class LinearFunction(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, weight):
+    def forward(ctx, x, weight, residual=None):
+        """``residual`` (same shape as the output): ``y = residual + x W^T`` in the GEMM's
+        epilogue; its gradient is the output gradient itself."""
         ctx.save_for_backward(x, weight)
+        ctx.has_residual = residual is not None
         x2 = x.reshape(-1, x.shape[-1])
         # allocate with the final shape: the result must not be a view, later kernels
         # (RoPE, cross-entropy) update it in place
         y = torch.empty(*x.shape[:-1], weight.shape[0], dtype=x.dtype, device=x.device)
-        gemm(x2, weight, out=y.view(-1, weight.shape[0]))
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, weight.shape[0])
+            if res2.stride(-1) != 1:
+                res2 = res2.contiguous()
+        gemm(x2, weight, out=y.view(-1, weight.shape[0]), residual=res2)
         return y
 
     @staticmethod
@@ -242,8 +253,10 @@ class LinearFunction(torch.autograd.Function):
                 dw = None
             else:
                 dw = gemm(dy2, x2, a_mn_major=True, b_mn_major=True)
-        return dx, dw
+        return dx, dw, (dy if ctx.has_residual and ctx.needs_input_grad[2] else None)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    return LinearFunction.apply(x, weight)
+def linear(x: torch.Tensor, weight: torch.Tensor,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x W^T`` (``+ residual``, added inside the GEMM) on the tcgen05 kernels."""
+    return LinearFunction.apply(x, weight, residual)

@@ -23,13 +23,12 @@ def _get():
         if lib is not None:
             vp, ll, ci, cf = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float
             lib.bcom_rmsnorm_fwd.argtypes = [vp, vp, vp, vp, ci, ci, cf, vp]
-            lib.bcom_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, vp]
-            lib.bcom_rmsnorm_bwd_set_rows.argtypes = [ci]
-            if os.environ.get("BITSCOM_RMSNORM_BWD_ROWS", "1") == "4":
-                lib.bcom_rmsnorm_bwd_set_rows(4)
+            lib.bcom_rmsnorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, vp]
+            lib.bcom_norm_bwd_scratch_elems.argtypes = [ci, ci]
+            lib.bcom_norm_bwd_scratch_elems.restype = ll
             lib.bcom_rope.argtypes = [vp, vp, vp, ll, ci, ci, ll, ci, ci, vp]
             lib.bcom_layernorm_fwd.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, cf, vp]
-            lib.bcom_layernorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, vp]
+            lib.bcom_layernorm_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, ci, ci, vp]
             lib.bcom_bias_gelu_fwd.argtypes = [vp, vp, vp, ll, ci, vp]
             lib.bcom_bias_gelu_bwd.argtypes = [vp, vp, vp, vp, vp, ll, ci, vp]
             lib.bcom_swiglu_fwd.argtypes = [vp, vp, ll, ci, vp]
@@ -80,37 +79,74 @@ class RMSNormFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight, rstd = ctx.saved_tensors
-        H = x2.shape[1]
-        dy2 = dy.reshape(-1, H)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
-        main = getattr(weight, "main_grad", None)
-        dw = main if main is not None else torch.zeros(H, dtype=torch.float32, device=dy.device)
-        if not dy.is_cuda:  # CPU ranks
-            xf, gf, rs = x2.float(), dy2.float(), rstd[:, None]
-            gw = gf * weight.float()
-            coef = (gw * xf).sum(-1, keepdim=True) * rs.pow(3) / H
-            dxh = (gw * rs - xf * coef).to(x2.dtype)
-            dw.add_((gf * xf * rs).sum(0))
-            return dxh.view(ctx.shape), (None if main is not None else dw.to(weight.dtype)), None
-        lib = _need()
-        dx = torch.empty_like(x2)
-        check(lib.bcom_rmsnorm_bwd(ptr(dy2), ptr(x2), ptr(weight), ptr(rstd), ptr(dx), ptr(dw),
-                                   x2.shape[0], H, stream_ptr(dy.device)), "rmsnorm_bwd")
-        return dx.view(ctx.shape), (None if main is not None else dw.to(weight.dtype)), None
+        dx, dw = _rmsnorm_backward(ctx, dy, None)
+        return dx, dw, None
 
 
-def set_rmsnorm_bwd_rows(rows_per_barrier: int) -> int:
-    """RMSNorm backward: rows processed per CTA barrier, 1 (default) or 4 (more loads in flight;
-    hidden sizes up to 4096; also ``BITSCOM_RMSNORM_BWD_ROWS=4``).  Returns the previous value."""
-    if rows_per_barrier not in (1, 4):
-        raise ValueError("rows_per_barrier must be 1 or 4")
-    return int(_need().bcom_rmsnorm_bwd_set_rows(int(rows_per_barrier)))
+def _rmsnorm_backward(ctx, dy, dres):
+    """Shared by ``RMSNormFunction`` and ``RMSNormForkFunction``: ``dres`` (or None) is the
+    gradient that reaches the same input through the residual connection; it is added to dx
+    inside the kernel."""
+    x2, weight, rstd = ctx.saved_tensors
+    H = x2.shape[1]
+    dy2 = dy.reshape(-1, H)
+    if not dy2.is_contiguous():
+        dy2 = dy2.contiguous()
+    if dres is not None:
+        dres = dres.reshape(-1, H)
+        if not dres.is_contiguous():
+            dres = dres.contiguous()
+    main = getattr(weight, "main_grad", None)
+    dw = main if main is not None else torch.zeros(H, dtype=torch.float32, device=dy.device)
+    if not dy.is_cuda:  # CPU ranks
+        xf, gf, rs = x2.float(), dy2.float(), rstd[:, None]
+        gw = gf * weight.float()
+        coef = (gw * xf).sum(-1, keepdim=True) * rs.pow(3) / H
+        dxf = gw * rs - xf * coef
+        if dres is not None:
+            dxf = dxf + dres.float()
+        dw.add_((gf * xf * rs).sum(0))
+        return dxf.to(x2.dtype).view(ctx.shape), (None if main is not None
+                                                  else dw.to(weight.dtype))
+    lib = _need()
+    dx = torch.empty_like(x2)
+    # per-CTA weight-gradient partials, folded into dw by a second small kernel
+    scratch = torch.empty(int(lib.bcom_norm_bwd_scratch_elems(H, 0)), dtype=torch.float32,
+                          device=dy.device)
+    check(lib.bcom_rmsnorm_bwd(
+        ptr(dy2), ptr(x2), ptr(weight), ptr(rstd), ptr(dres), ptr(dx), ptr(dw), ptr(scratch),
+        x2.shape[0], H, stream_ptr(dy.device)), "rmsnorm_bwd", launches=2)
+    return dx.view(ctx.shape), (None if main is not None else dw.to(weight.dtype))
+
+
+class RMSNormForkFunction(torch.autograd.Function):
+    """``(rmsnorm(x), x)``: the normalised branch and the residual branch of a pre-norm block
+    as ONE node.  Forward is ``RMSNormFunction``'s; the point is backward, where the gradients
+    of both branches meet: ``dx = rmsnorm_backward(dh) + dx_residual`` is produced by one kernel
+    instead of the norm's backward followed by autograd's own add kernel."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        h = RMSNormFunction.forward(ctx, x, weight, eps)
+        return h, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dh, dres):
+        if dh is None:  # only the residual branch was used
+            return dres, None, None
+        dx, dw = _rmsnorm_backward(ctx, dh, dres)
+        return dx, dw, None
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
     return RMSNormFunction.apply(x, weight, eps)
+
+
+def rmsnorm_fork(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5
+                 ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(rmsnorm(x), x)`` for a pre-norm residual block: feed the first into the block and
+    carry the second as the residual; see ``RMSNormForkFunction``."""
+    return RMSNormForkFunction.apply(x, weight, eps)
 
 
 # ----------------------------------------------------------------------------------
@@ -214,9 +250,11 @@ class LayerNormFunction(torch.autograd.Function):
         dx = torch.empty_like(x2)
         dw, w_main = _grad_target(weight, H, dy.device)
         db, b_main = _grad_target(bias, H, dy.device)
-        check(lib.bcom_layernorm_bwd(ptr(dy2), ptr(x2), ptr(weight), ptr(mean), ptr(rstd),
-                                     ptr(dx), ptr(dw), ptr(db), x2.shape[0], H,
-                                     stream_ptr(dy.device)), "layernorm_bwd")
+        scratch = torch.empty(int(lib.bcom_norm_bwd_scratch_elems(H, 1)), dtype=torch.float32,
+                              device=dy.device)
+        check(lib.bcom_layernorm_bwd(
+            ptr(dy2), ptr(x2), ptr(weight), ptr(mean), ptr(rstd), ptr(dx), ptr(dw), ptr(db),
+            ptr(scratch), x2.shape[0], H, stream_ptr(dy.device)), "layernorm_bwd", launches=2)
         return (dx.view(ctx.shape), None if w_main else dw.to(weight.dtype),
                 None if b_main else db.to(bias.dtype), None)
 

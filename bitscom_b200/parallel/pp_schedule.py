@@ -243,3 +243,239 @@ class PipelineRunner:
         if flush is not None:
             flush()
         return losses
+
+
+# ----------------------------------------------------------------------------------
+# Interleaved 1F1B: several model chunks per rank ("virtual stages")
+# ----------------------------------------------------------------------------------
+# With v chunks per rank the model is cut into V = P * v virtual stages; virtual stage s lives
+# on rank s % P as chunk s // P, so a micro-batch visits every rank v times and the pipeline's
+# fill / drain costs (P - 1) / v stage times instead of P - 1: the idle share of a step drops
+# from (P - 1) / (M + P - 1) to (P - 1) / (v M + P - 1) (2 stages x 8 micro-batches: 11.1 % ->
+# 5.9 % with two chunks).  The price is v times as many (smaller) point-to-point messages and
+# up to (P - r - 1) * 2 + (v - 1) * P + 1 live micro-batch activations on rank r.  The reference
+# has no pipeline schedule of its own (torch's GPipe, train_llama7b_dp_pp_lowbit.py:240-264).
+
+VAction = Tuple[str, int, int]  # ("F" | "B", micro-batch, chunk)
+
+
+def interleaved_warmup(rank: int, stages: int, microbatches: int, chunks: int) -> int:
+    """Forwards a rank runs before its first backward."""
+    P, M, v = stages, microbatches, chunks
+    if v == 1:
+        return min(P - rank - 1, M)
+    # with exactly P micro-batches the first ranks would run all their forwards first while the
+    # last ones alternate, and their batches no longer line up: every rank then runs all
+    # forwards before any backward
+    return M * v if M == P else min((P - rank - 1) * 2 + (v - 1) * P, M * v)
+
+
+def build_interleaved(rank: int, stages: int, microbatches: int, chunks: int) -> List[VAction]:
+    """Action list of ``rank``: micro-batches go through the chunks in groups of ``stages``
+    (the first P micro-batches through chunk 0, the same P through chunk 1, ..., then the next
+    P), backwards with the chunks reversed; ``(P - rank - 1) * 2 + (chunks - 1) * P`` warm-up
+    forwards, then one forward / one backward, then the remaining backwards.
+    ``microbatches`` must be a multiple of ``stages``."""
+    P, M, v = stages, microbatches, chunks
+    if v == 1:
+        return [(k, mb, 0) for k, mb in build_1f1b(rank, P, M)]
+    if M % P:
+        raise ValueError(f"interleaved schedule: micro-batches ({M}) must be a multiple of the "
+                         f"pipeline stages ({P})")
+    total = M * v
+
+    def fwd(k: int) -> Tuple[int, int]:
+        group, within = divmod(k, P * v)
+        chunk, pos = divmod(within, P)
+        return group * P + pos, chunk
+
+    def bwd(k: int) -> Tuple[int, int]:
+        mb, chunk = fwd(k)
+        return mb, v - 1 - chunk
+
+    warm = interleaved_warmup(rank, P, M, v)
+    actions: List[VAction] = [("F",) + fwd(k) for k in range(warm)]
+    f, b = warm, 0
+    while f < total:
+        actions.append(("F",) + fwd(f))
+        f += 1
+        actions.append(("B",) + bwd(b))
+        b += 1
+    while b < total:
+        actions.append(("B",) + bwd(b))
+        b += 1
+    return actions
+
+
+class Message:
+    """One tensor on the wire: activation ("act") of micro-batch ``mb`` leaving virtual stage
+    ``vstage``, or gradient ("grad") w.r.t. the input of virtual stage ``vstage``."""
+
+    __slots__ = ("kind", "mb", "vstage", "src", "dst")
+
+    def __init__(self, kind: str, mb: int, vstage: int, src: int, dst: int):
+        self.kind, self.mb, self.vstage, self.src, self.dst = kind, mb, vstage, src, dst
+
+    def tag(self) -> Tuple[str, int, int]:
+        return (self.kind, self.mb, self.vstage)
+
+    def __repr__(self):
+        return f"{self.kind}(mb{self.mb}, vs{self.vstage}, {self.src}->{self.dst})"
+
+
+def _needs(rank: int, P: int, v: int, action: VAction) -> Optional[Message]:
+    kind, mb, chunk = action
+    vs, V = chunk * P + rank, P * v
+    if kind == "F":
+        return None if vs == 0 else Message("act", mb, vs - 1, (rank - 1) % P, rank)
+    return None if vs == V - 1 else Message("grad", mb, vs + 1, (rank + 1) % P, rank)
+
+
+def _yields(rank: int, P: int, v: int, action: VAction) -> Optional[Message]:
+    kind, mb, chunk = action
+    vs, V = chunk * P + rank, P * v
+    if kind == "F":
+        return None if vs == V - 1 else Message("act", mb, vs, rank, (rank + 1) % P)
+    return None if vs == 0 else Message("grad", mb, vs, rank, (rank - 1) % P)
+
+
+def schedule_units(actions: Sequence[VAction], warmup: int) -> List[List[VAction]]:
+    """Cuts an action list into the units after which a rank communicates: each of the
+    ``warmup`` leading forwards, then forward + backward pairs, then single backwards."""
+    units: List[List[VAction]] = [[a] for a in actions[:warmup]]
+    i = warmup
+    while i < len(actions):
+        if actions[i][0] == "F":
+            units.append([actions[i], actions[i + 1]])
+            i += 2
+        else:
+            units.append([actions[i]])
+            i += 1
+    return units
+
+
+def virtual_plan(rank: int, stages: int, microbatches: int, chunks: int
+                 ) -> List[Tuple[List[VAction], List[Message], List[Message]]]:
+    """[(unit, sends, receives)]: after the actions of ``unit`` (empty for the priming entry)
+    the rank posts ONE batch that sends what the unit produced and receives what the NEXT
+    unit consumes, activations before gradients in both lists.  In the steady state a unit is
+    one forward plus one backward, so the gradient of the next backward arrives a whole unit
+    before it is used: that slack is what keeps neighbouring ranks, whose units are offset
+    against each other, from waiting on one another in a cycle (a receive posted only one
+    ACTION ahead deadlocks: the peer's matching send sits behind a receive of its own)."""
+    actions = build_interleaved(rank, stages, microbatches, chunks)
+    units = schedule_units(actions, interleaved_warmup(rank, stages, microbatches, chunks))
+
+    def needs(unit):
+        got = [m for m in (_needs(rank, stages, chunks, a) for a in unit) if m is not None]
+        return sorted(got, key=lambda m: m.kind)      # "act" < "grad"
+
+    def yields(unit):
+        out = [m for m in (_yields(rank, stages, chunks, a) for a in unit) if m is not None]
+        return sorted(out, key=lambda m: m.kind)
+
+    plan: List[Tuple[List[VAction], List[Message], List[Message]]] = []
+    if units and needs(units[0]):
+        plan.append(([], [], needs(units[0])))
+    for i, unit in enumerate(units):
+        plan.append((unit, yields(unit), needs(units[i + 1]) if i + 1 < len(units) else []))
+    return plan
+
+
+def check_virtual_plan(stages: int, microbatches: int, chunks: int) -> int:
+    """Plays all ranks' plans under NCCL's rules and raises ``RuntimeError`` on a deadlock or a
+    mismatched tensor; returns the number of messages delivered.  Rules: the operations of a
+    batch run concurrently; between one (sender, receiver) pair messages match in the order
+    they were posted on both sides (inside a batch: list order); a rank moves on when every
+    operation of its batch has matched; a backward runs only after its forward."""
+    P = stages
+    plans = [[(u, list(s), list(r)) for u, s, r in virtual_plan(k, P, microbatches, chunks)]
+             for k in range(P)]
+    pos = [0] * P
+    sends: List[List[Message]] = [[] for _ in range(P)]
+    recvs: List[List[Message]] = [[] for _ in range(P)]
+    have: List[set] = [set() for _ in range(P)]     # tags of the inputs a rank holds
+    seen_fwd: List[set] = [set() for _ in range(P)]
+
+    def load(k: int) -> None:
+        if pos[k] < len(plans[k]):
+            unit, s, r = plans[k][pos[k]]
+            for act in unit:                          # the unit's compute comes first
+                need = _needs(k, P, chunks, act)
+                if need is not None and need.tag() not in have[k]:
+                    raise RuntimeError(f"rank {k} runs {act} before it holds {need}")
+                if act[0] == "F":
+                    seen_fwd[k].add(act[1:])
+                elif act[1:] not in seen_fwd[k]:
+                    raise RuntimeError(f"rank {k} runs {act} before its forward")
+            sends[k], recvs[k] = list(s), list(r)
+
+    for k in range(P):
+        load(k)
+    delivered = 0
+    for _ in range(16 * P * microbatches * chunks + 64):
+        if all(pos[k] >= len(plans[k]) for k in range(P)):
+            return delivered
+        progressed = False
+        for k in range(P):
+            for s in list(sends[k]):
+                first_to_dst = next(m for m in sends[k] if m.dst == s.dst)
+                if first_to_dst is not s:
+                    continue
+                r = next((m for m in recvs[s.dst] if m.src == k), None)
+                if r is None:
+                    continue
+                if r.tag() != s.tag():
+                    raise RuntimeError(f"rank {s.dst} expected {r} but rank {k} sent {s}")
+                sends[k].remove(s)
+                recvs[s.dst].remove(r)
+                have[s.dst].add(s.tag())
+                delivered += 1
+                progressed = True
+        for k in range(P):
+            if pos[k] < len(plans[k]) and not sends[k] and not recvs[k]:
+                pos[k] += 1
+                load(k)
+                progressed = True
+        if not progressed:
+            raise RuntimeError(f"the plan deadlocks at positions {pos}: sends {sends}, "
+                               f"receives {recvs}")
+    raise RuntimeError("the plan did not terminate")
+
+
+def simulate_interleaved_timeline(stages: int, microbatches: int, chunks: int,
+                                  t_forward: float = 1.0, t_backward: float = 2.0) -> dict:
+    """Event simulation of the interleaved schedule with per-chunk costs ``t_forward / chunks``
+    and ``t_backward / chunks`` (a chunk is 1 / chunks of a stage): step time, ideal time and
+    their ratio."""
+    P, v = stages, chunks
+    plans = [build_interleaved(k, P, microbatches, v) for k in range(P)]
+    tf, tb = t_forward / v, t_backward / v
+    done: dict = {}
+    clock = [0.0] * P
+    pos = [0] * P
+    remaining = sum(len(p) for p in plans)
+    while remaining:
+        progressed = False
+        for k in range(P):
+            if pos[k] >= len(plans[k]):
+                continue
+            act = plans[k][pos[k]]
+            need = _needs(k, P, v, act)
+            ready = 0.0
+            if need is not None:
+                if need.tag() not in done:
+                    continue
+                ready = done[need.tag()]
+            start = max(clock[k], ready)
+            clock[k] = start + (tf if act[0] == "F" else tb)
+            out = _yields(k, P, v, act)
+            if out is not None:
+                done[out.tag()] = clock[k]
+            pos[k] += 1
+            remaining -= 1
+            progressed = True
+        if not progressed:
+            raise RuntimeError("the schedule deadlocks")
+    ideal = microbatches * (t_forward + t_backward)
+    return {"step_time": max(clock), "ideal_time": ideal, "efficiency": ideal / max(clock)}

@@ -5,10 +5,12 @@ optimizer moments.  One step is
 
   low-bit reduce-scatter of the flat fp32 gradient  ->  each rank holds the summed
       gradient of its shard (error feedback on the sender side),
-  fused AdamW on the shard,
-  low-bit all-gather of the updated shard into the flat parameter buffer (error
-      feedback on the owner side, so quantization error of the broadcast parameters is
-      carried to the next step instead of accumulating).
+  fused AdamW on the shard, which also writes the bf16 copy of the shard straight into its
+      place in the flat parameter buffer,
+  low-bit all-gather of that bf16 shard into the flat parameter buffer IN PLACE (the shard is
+      a slice of the output; error feedback on the owner side, so quantization error of the
+      broadcast parameters is carried to the next step instead of accumulating).  No fp32
+      staging buffer of the whole model and no conversion pass afterwards.
 
 The reference has only the low-bit reduce-scatter primitive in its C++ backend
 (``cpp/src/process_group_lowbit.cc:1670-1777``) and forwards all-gather to NCCL; sharded
@@ -41,10 +43,10 @@ class ShardedAdamW:
         dev = flat.params.device
         self.master_shard = flat.params[lo:lo + self.shard].float().clone()
         self.grad_shard = torch.zeros(self.shard, dtype=torch.float32, device=dev)
-        self.opt = K.FlatAdamW(self.master_shard, self.grad_shard, None, lr=lr, betas=betas,
-                               eps=eps, weight_decay=weight_decay)
-        self.new_params = torch.empty(self.shard, dtype=torch.float32, device=dev)
-        self.gathered = torch.empty(n, dtype=torch.float32, device=dev)
+        # the optimizer kernel refreshes the bf16 working copy of the shard where it lives
+        self.param_shard = flat.params[lo:lo + self.shard]
+        self.opt = K.FlatAdamW(self.master_shard, self.grad_shard, self.param_shard, lr=lr,
+                               betas=betas, eps=eps, weight_decay=weight_decay)
 
     def step(self) -> None:
         flat = self.flat
@@ -55,17 +57,15 @@ class ShardedAdamW:
         self.opt.step(grad_scale=1.0 / self.world, zero_grad=True)
         flat.grads.zero_()
         if self.world > 1:
-            self.pgroup.all_gather_lowbit(self.gathered, self.master_shard,
-                                          ef_key="zero_params")
-            flat.params.copy_(self.gathered)
-        else:
-            flat.params.copy_(self.master_shard)
+            # in place: every rank, the owner included, ends up with the dequantized shard, so
+            # all replicas of the bf16 model stay bit-identical
+            self.pgroup.all_gather_lowbit(flat.params, self.param_shard, ef_key="zero_params")
 
     def state_dict(self):
         return {"opt": self.opt.state_dict(), "master_shard": self.master_shard}
 
     def load_state_dict(self, sd):
-        self.opt.load_state_dict(sd["opt"])
+        self.opt.load_state_dict(sd["opt"])   # also refreshes the bf16 copy of the shard
         self.master_shard.copy_(sd["master_shard"])
 
 

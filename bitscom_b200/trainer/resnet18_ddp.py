@@ -33,7 +33,10 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--bitwidth", type=int, default=2)
-    ap.add_argument("--mode", default="lowbit", choices=["lowbit", "nccl"])
+    ap.add_argument("--mode", default="lowbit", choices=["lowbit", "backend", "nccl"],
+                    help="lowbit: NCCL group + the Python DDP comm hook; backend: the C++ "
+                         "`lowbit` torch.distributed backend under DDP's own reducer (no Python "
+                         "on the gradient path); nccl: plain DDP")
     ap.add_argument("--bucket-mb", type=int, default=25)
     ap.add_argument("--no-error-feedback", action="store_true")
     ap.add_argument("--out", default="bench_outputs/resnet18_ddp.jsonl")
@@ -45,7 +48,16 @@ def main(argv=None):
     local = int(os.environ.get("LOCAL_RANK", rank))
     world = int(os.environ.get("WORLD_SIZE", 1))
     cuda = args.device == "cuda"
-    if cuda:
+    if cuda and args.mode == "backend":
+        import bitscom_b200
+
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        bitscom_b200.init(bitwidth=args.bitwidth, block_size=256,
+                          error_feedback_mode="none" if args.no_error_feedback else "ef21_plus",
+                          stage2_error_feedback=not args.no_error_feedback)
+        dist.init_process_group("lowbit")
+    elif cuda:
         torch.cuda.set_device(local)
         dev = torch.device("cuda", local)
         dist.init_process_group("nccl", device_id=dev)
@@ -98,7 +110,7 @@ def main(argv=None):
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
         row = {"workload": "resnet18_cifar_ddp", "mode": args.mode, "world": world,
-               "bitwidth": args.bitwidth if args.mode == "lowbit" else 32,
+               "bitwidth": args.bitwidth if args.mode != "nccl" else 32,
                "device": args.device, "batch_per_gpu": args.batch,
                "ms_per_step": float(ms.item()),
                "samples_per_s": world * args.batch / float(ms.item()) * 1e3,

@@ -104,44 +104,6 @@ def test_backward_dq_variants_match_reference(B, S, nh, hd, dq):
         A.set_backward_dq_variant(before)
 
 
-@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
-                    reason="kernel variants that have not been run on a GPU yet; "
-                           "set BITSCOM_EXPERIMENTAL=1 to try them")
-@pytest.mark.parametrize("hd", [128, 64])
-@pytest.mark.parametrize("B,S,nh", [(1, 128, 1), (2, 384, 2), (1, 2048, 2)])
-def test_experimental_forward_variant_pipelined8(B, S, nh, hd):
-    """The eight-softmax-warp forward kernel (two threads per row) against fp32 SDPA."""
-    H = nh * hd
-    g = torch.Generator(device="cuda").manual_seed(S + nh + hd)
-    qkv = (torch.randn(B * S, 3 * H, device="cuda", generator=g) * 0.7).to(torch.bfloat16)
-    d_out = (torch.randn(B * S, H, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
-    before = A.set_forward_variant("pipelined8")
-    try:
-        x = qkv.clone().requires_grad_()
-        out = A.attention(x, B, S, nh, hd)
-        out.backward(d_out)
-        torch.cuda.synchronize()
-        A.check_status()
-    finally:
-        A.set_forward_variant(before)
-    xr = qkv.float().requires_grad_()
-    ref = _ref(xr, B, S, nh, hd)
-    ref.backward(d_out.float())
-    assert (out.float() - ref).abs().max().item() < 2e-2
-    e = (x.grad.float() - xr.grad).abs().max().item()
-    assert e < 3e-2 * max(1.0, xr.grad.abs().max().item())
-
-
-@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
-                    reason="kernel variants that have not been run on a GPU yet; "
-                           "set BITSCOM_EXPERIMENTAL=1 to try them")
-@pytest.mark.parametrize("hd", [128, 64])
-@pytest.mark.parametrize("B,S,nh", [(1, 128, 1), (2, 384, 2), (1, 1024, 3)])
-def test_experimental_backward_variant_tma_early(B, S, nh, hd):
-    """The backward kernel that requests the next Q / dO tiles and row statistics early."""
-    test_backward_dq_variants_match_reference(B, S, nh, hd, "tma_early")
-
-
 def test_attention_second_call_reuses_zeroed_scratch():
     B, S, nh, hd = 1, 256, 2, 128
     H = nh * hd

@@ -139,7 +139,7 @@ def test_peer_that_never_arrives_times_out_with_status(make_world):
     w = make_world(2, timeout_ms=200.0)
     x = torch.ones(4096, device="cuda")
     args = fused._args(x, x, None, None, 4096, 2048, x.dtype, 4, 256,
-                       fused.MODE_ALL_REDUCE, False, None, 1.0, 0)
+                       fused.MODE_ALL_REDUCE, False, None, 1.0, 0, 0)
     rc = w.lib.bcom_collective(w.comms[0].handle, ctypes.byref(args),
                                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0

@@ -114,15 +114,12 @@ def test_linear_autograd_matches_torch():
     G.check_status()
 
 
-@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
-                    reason="kernel variants that have not been run on a GPU yet; "
-                           "set BITSCOM_EXPERIMENTAL=1 to try them")
 @pytest.mark.parametrize("a_mn", [False, True])
 @pytest.mark.parametrize("b_mn", [False, True])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 256), (512, 256, 1024),
                                    (200, 264, 136), (1024, 1024, 4096), (77, 8, 40),
                                    (4096, 4096, 512)])
-def test_experimental_cta_pair_gemm(a_mn, b_mn, M, N, K):
+def test_cta_pair_gemm(a_mn, b_mn, M, N, K):
     """The CTA-pair kernel (256x256 tiles, tcgen05 cta_group::2) against fp32 matmul, bf16 and
     accumulating fp32 outputs; exact on small integers, so a swapped half tile cannot hide in
     the tolerance."""
@@ -148,42 +145,6 @@ def test_experimental_cta_pair_gemm(a_mn, b_mn, M, N, K):
     assert torch.equal(exact, _ref(ai, bi, a_mn, b_mn))
 
 
-@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
-                    reason="kernel variants that have not been run on a GPU yet; "
-                           "set BITSCOM_EXPERIMENTAL=1 to try them")
-@pytest.mark.parametrize("a_mn", [False, True])
-@pytest.mark.parametrize("b_mn", [False, True])
-@pytest.mark.parametrize("M,N,K,max_ctas", [
-    (4096, 4096, 256, 0),    # 512 tiles on 148 SMs: 68 tail tiles -> 136 halves
-    (1024, 1024, 512, 24),   # 32 tiles on 24 CTAs: 8 tail tiles -> 16 halves
-    (384, 264, 136, 4),      # ragged edges, tail of 2 on 4 CTAs, second half partly outside N
-    (256, 512, 64, 3),       # tail 1 of 3
-    (128, 256, 64, 0),       # one tile, no tail: whole-tile path of the split kernel unused
-])
-def test_experimental_split_tail_gemm(a_mn, b_mn, M, N, K, max_ctas):
-    """Half-tile processing of a sparsely filled last wave: exact on small integers (bf16,
-    fp32 and accumulating fp32 outputs), so a misplaced half cannot hide in a tolerance."""
-    a = torch.randint(-3, 4, (K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
-    b = torch.randint(-3, 4, (K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
-    if (a.shape[1] % 8) or (b.shape[1] % 8):
-        pytest.skip("row stride must stay 16-byte aligned")
-    ref = _ref(a, b, a_mn, b_mn)
-    before = G.set_split_tail(True)
-    try:
-        out = G.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, max_ctas=max_ctas)
-        acc = G.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out_dtype=torch.float32,
-                     max_ctas=max_ctas)
-        G.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=acc, accumulate=True,
-               max_ctas=max_ctas)
-        torch.cuda.synchronize()
-        G.check_status()
-    finally:
-        G.set_split_tail(before)
-    assert torch.equal(acc, 2 * ref)
-    assert torch.equal(out.float(), ref.to(torch.bfloat16).float())
-
-
-@pytest.mark.performance
 def test_gemm_throughput_report():
     M = N = K = 8192
     a, b = _mk(M, K, 1), _mk(N, K, 2)

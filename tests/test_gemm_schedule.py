@@ -1,6 +1,6 @@
 """The GEMM kernels' tile scheduler (csrc/gemm_schedule.cuh, host/device code) on the host:
-every element of C is produced exactly once for many shapes and grid sizes, with and without
-the split of a sparsely filled last wave into half tiles (tests/native/gemm_schedule_check.cc)."""
+every element of C is produced exactly once for many shapes and both tile sizes
+(tests/native/gemm_schedule_check.cc)."""
 
 import os
 import shutil

@@ -10,10 +10,12 @@ from bitscom_b200.parallel.deferred import DeferredWork
 
 
 def _fake_gemm(a, b, *, a_mn_major=False, b_mn_major=False, out=None,
-               out_dtype=torch.bfloat16, accumulate=False, max_ctas=0):
+               out_dtype=torch.bfloat16, accumulate=False, max_ctas=0, residual=None):
     A = a.t() if a_mn_major else a          # [M, K]
     B = b if b_mn_major else b.t()          # [K, N]
     c = A.float() @ B.float()
+    if residual is not None:
+        c = c + residual.float()
     if out is None:
         return c.to(out_dtype)
     if accumulate:
@@ -53,6 +55,40 @@ def test_forward_and_gradients(fake_gemm, main_grad):
         assert torch.allclose(w.main_grad - 0.5, wr.grad, atol=0.05)
     else:
         assert torch.allclose(w.grad.float(), wr.grad, atol=0.1)
+
+
+def test_residual_is_added_in_the_gemm_and_its_gradient_is_the_output_gradient(fake_gemm):
+    x, w, dy = _case(True)
+    res = torch.randn(2, 6, 24, generator=torch.Generator().manual_seed(5)).to(
+        torch.bfloat16).requires_grad_()
+    y = G.linear(x, w, residual=res)
+    want = res.detach().float() + x.detach().float() @ w.detach().float().t()
+    assert torch.allclose(y.float(), want, atol=0.05)
+    y.backward(dy)
+    assert torch.equal(res.grad, dy)
+    assert x.grad is not None and w.grad is None
+
+
+def test_rmsnorm_fork_adds_the_residual_gradient_inside_the_norm_backward():
+    from bitscom_b200.ops import nn as K
+
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(10, 32, generator=g).to(torch.bfloat16).requires_grad_()
+    w = (1 + 0.1 * torch.randn(32, generator=g)).to(torch.bfloat16).requires_grad_()
+    h, xr = K.rmsnorm_fork(x, w)
+    (h.float().sum() * 2 + (xr.float() * 3).sum()).backward()
+    x2 = x.detach().clone().requires_grad_()
+    w2 = w.detach().clone().requires_grad_()
+    h2 = K.rmsnorm(x2, w2)
+    (h2.float().sum() * 2 + (x2.float() * 3).sum()).backward()
+    assert torch.equal(h, h2)
+    assert torch.allclose(x.grad.float(), x2.grad.float(), atol=0.05)
+    assert torch.allclose(w.grad.float(), w2.grad.float(), atol=0.05)
+    # the residual branch alone
+    x3 = x.detach().clone().requires_grad_()
+    _, only = K.rmsnorm_fork(x3, w.detach())
+    only.float().sum().backward()
+    assert torch.equal(x3.grad, torch.ones_like(x3))
 
 
 def test_deferred_weight_gradient_runs_at_flush(fake_gemm):

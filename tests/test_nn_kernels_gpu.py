@@ -23,7 +23,8 @@ def _close(a, b, rtol=2e-2, atol=2e-2):
         f"max diff {(a.float() - b.float()).abs().max().item()}"
 
 
-@pytest.mark.parametrize("rows,H", [(64, 256), (300, 4096), (7, 8192), (1000, 1024)])
+@pytest.mark.parametrize("rows,H", [(64, 256), (300, 4096), (7, 8192), (1000, 1024),
+                                    (4097, 4096), (5, 8), (33, 16384)])
 def test_rmsnorm_fwd_bwd(rows, H):
     x = _bf(rows, H, seed=1).requires_grad_()
     w = (1 + 0.1 * _bf(H, seed=2).float()).to(torch.bfloat16).requires_grad_()
@@ -44,29 +45,20 @@ def test_rmsnorm_fwd_bwd(rows, H):
     assert torch.allclose(w2.main_grad, wr.grad, rtol=2e-2, atol=0.01 * rows ** 0.5 + 0.02)
 
 
-@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
-                    reason="kernel variants that have not been run on a GPU yet; "
-                           "set BITSCOM_EXPERIMENTAL=1 to try them")
-@pytest.mark.parametrize("rows,H", [(64, 256), (1000, 4096), (37, 1024), (5, 8), (4097, 4096),
-                                    (3, 4096), (8192, 4096)])
-def test_experimental_rmsnorm_bwd_four_rows_per_barrier(rows, H):
-    """The variant that handles four rows per CTA barrier gives the same gradients as the
-    default kernel (same formula per element; dw differs by summation order)."""
-    x, dy = _bf(rows, H, seed=1), _bf(rows, H, seed=3)
-    w = (1 + 0.1 * _bf(H, seed=2).float()).to(torch.bfloat16)
-    grads = {}
-    for variant in (1, 4):
-        before = K.set_rmsnorm_bwd_rows(variant)
-        try:
-            xv, wv = x.clone().requires_grad_(), w.clone().requires_grad_()
-            K.rmsnorm(xv, wv, 1e-5).backward(dy)
-            torch.cuda.synchronize()
-            grads[variant] = (xv.grad.clone(), wv.grad.float().clone())
-        finally:
-            K.set_rmsnorm_bwd_rows(before)
-    # the compiler may contract multiply-adds differently in the two kernels: one bf16 ulp
-    assert torch.allclose(grads[1][0].float(), grads[4][0].float(), rtol=1e-2, atol=1e-3)
-    assert torch.allclose(grads[1][1], grads[4][1], rtol=2e-2, atol=0.01 * rows ** 0.5 + 0.02)
+def test_rmsnorm_fork_adds_the_residual_gradient_in_the_kernel():
+    """``rmsnorm_fork`` returns (norm(x), x); in backward the gradient of the residual branch is
+    added to the norm's input gradient inside the backward kernel."""
+    rows, H = 777, 4096
+    x = _bf(rows, H, seed=1).requires_grad_()
+    w = (1 + 0.1 * _bf(H, seed=2).float()).to(torch.bfloat16).requires_grad_()
+    dh, dres = _bf(rows, H, seed=3), _bf(rows, H, seed=4)
+    h, xr = K.rmsnorm_fork(x, w, 1e-5)
+    torch.autograd.backward([h, xr], [dh, dres])
+    x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    K.rmsnorm(x2, w2, 1e-5).backward(dh)
+    want = x2.grad.float() + dres.float()
+    _close(x.grad, want, atol=3e-2)
+    assert torch.allclose(w.grad.float(), w2.grad.float(), rtol=1e-2, atol=1e-2)
 
 
 def _rope_ref(t, cos, sin):
@@ -75,7 +67,7 @@ def _rope_ref(t, cos, sin):
     return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
 
 
-@pytest.mark.parametrize("rows,H", [(64, 256), (1000, 1024), (37, 768), (5, 8)])
+@pytest.mark.parametrize("rows,H", [(64, 256), (1000, 1024), (37, 768), (5, 8), (8191, 1024)])
 def test_layernorm_fwd_bwd(rows, H):
     x = (_bf(rows, H, seed=1).float() * 2 + 0.5).to(torch.bfloat16).requires_grad_()
     w = (1 + 0.1 * _bf(H, seed=2).float()).to(torch.bfloat16).requires_grad_()

@@ -102,3 +102,62 @@ def test_timeline_simulation_matches_the_bubble_formula_and_shows_what_deferral_
     uneven = simulate_timeline(2, 8, t_forward=1.0, t_input_grad=1.4, t_weight_grad=0.6,
                                defer_wgrad=True, defer_last=True, t_send=0.05)
     assert 0.9 < uneven["efficiency"] < 1.0
+
+
+# ---- interleaved (virtual-stage) schedule ------------------------------------------------
+
+from bitscom_b200.parallel.pp_schedule import (build_interleaved, check_virtual_plan,  # noqa: E402
+                                               interleaved_warmup, schedule_units,
+                                               simulate_interleaved_timeline, virtual_plan)
+
+
+@pytest.mark.parametrize("stages,mbs,chunks", [(2, 8, 2), (2, 4, 2), (4, 8, 2), (2, 8, 4),
+                                               (4, 16, 2), (8, 16, 2), (3, 6, 2), (4, 4, 2),
+                                               (2, 2, 3), (2, 8, 1), (4, 8, 1)])
+def test_interleaved_order(stages, mbs, chunks):
+    for rank in range(stages):
+        acts = build_interleaved(rank, stages, mbs, chunks)
+        want = sorted((mb, c) for mb in range(mbs) for c in range(chunks))
+        assert sorted(a[1:] for a in acts if a[0] == "F") == want
+        assert sorted(a[1:] for a in acts if a[0] == "B") == want
+        seen = set()
+        for kind, mb, c in acts:
+            if kind == "F":
+                # a micro-batch climbs the chunks in order
+                assert c == 0 or (mb, c - 1) in seen
+                seen.add((mb, c))
+            else:
+                assert (mb, c) in seen
+        units = schedule_units(acts, interleaved_warmup(rank, stages, mbs, chunks))
+        assert [a for u in units for a in u] == acts
+        assert all(len(u) == 1 or (u[0][0], u[1][0]) == ("F", "B") for u in units)
+
+
+@pytest.mark.parametrize("stages", [2, 3, 4, 8])
+@pytest.mark.parametrize("mult", [1, 2, 4])
+@pytest.mark.parametrize("chunks", [1, 2, 3])
+def test_interleaved_plan_has_no_deadlock(stages, mult, chunks):
+    mbs = stages * mult
+    delivered = check_virtual_plan(stages, mbs, chunks)
+    # every virtual-stage boundary carries one activation and one gradient per micro-batch
+    assert delivered == 2 * mbs * (stages * chunks - 1)
+    # each message is sent once and received once
+    sent, got = [], []
+    for rank in range(stages):
+        for _, s, r in virtual_plan(rank, stages, mbs, chunks):
+            sent += [m.tag() for m in s]
+            got += [m.tag() for m in r]
+    assert sorted(sent) == sorted(got) and len(set(sent)) == len(sent)
+
+
+@pytest.mark.parametrize("stages,mbs,chunks", [(2, 8, 1), (2, 8, 2), (2, 8, 4), (4, 8, 2),
+                                               (4, 16, 2), (8, 16, 2)])
+def test_interleaved_bubble_matches_formula(stages, mbs, chunks):
+    t = simulate_interleaved_timeline(stages, mbs, chunks)
+    want = chunks * mbs / (chunks * mbs + stages - 1)
+    assert abs(t["efficiency"] - want) < 1e-9
+
+
+def test_interleaved_rejects_ragged_microbatches():
+    with pytest.raises(ValueError):
+        build_interleaved(0, 4, 6, 2)

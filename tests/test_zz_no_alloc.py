@@ -57,12 +57,16 @@ def test_no_alloc_backward_matches_regular_entry_point_twice():
 
         # allocation-free entry point: inputs and outputs only
         got = torch.empty_like(qkv)
+        torch.cuda.synchronize()
         allocated = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]   # sees a cudaMalloc made by ANY library
         rc = lib.bcom_attention_bwd_no_alloc(_p(qkv), _p(out), _p(d_out), _p(lse), _p(got),
                                              B, S, nh, hd, scale, stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == allocated
+        if call == 1:   # the first call may still load the module; the second must not move
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert torch.isfinite(got.float()).all()
         diff = (got.float() - want.float()).abs().max().item()
         tol = 3e-2 * max(1.0, want.float().abs().max().item())
@@ -78,3 +82,50 @@ def test_no_alloc_rejects_problems_larger_than_the_scratch():
                                          0.1, stream)
     assert rc == 1006
     torch.cuda.synchronize()
+
+
+def test_no_alloc_entry_point_can_be_the_first_call_of_the_library_in_a_process():
+    """A fresh process whose FIRST use of the library is the allocation-free entry point (so
+    the module load and the symbol lookup happen inside it): it must succeed, and a second
+    call must agree with the ordinary entry point."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = textwrap.dedent(f"""
+        import ctypes, math, sys, torch
+        sys.path.insert(0, {root!r})
+        sys.path.insert(0, {os.path.join(root, "tests")!r})
+        import test_zz_no_alloc as T
+        lib = T._lib()
+        B, S, nh, hd = 1, 256, 2, 128
+        H, scale = nh * hd, 1.0 / math.sqrt(hd)
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        qkv = (torch.randn(B * S, 3 * H, device="cuda") * 0.7).to(torch.bfloat16)
+        d_out = (torch.randn(B * S, H, device="cuda") * 0.5).to(torch.bfloat16)
+        out = torch.zeros(B * S, H, dtype=torch.bfloat16, device="cuda")
+        lse = torch.zeros(B, nh, S, dtype=torch.float32, device="cuda")
+        got = torch.empty_like(qkv)
+        # first touch of the library: placeholder statistics, only the return code matters
+        rc = lib.bcom_attention_bwd_no_alloc(T._p(qkv), T._p(out), T._p(d_out), T._p(lse),
+                                             T._p(got), B, S, nh, hd, scale, st)
+        torch.cuda.synchronize()
+        assert rc == 0, rc
+        assert lib.bcom_attention_fwd(T._p(qkv), T._p(out), T._p(lse), B, S, nh, hd, scale, st) == 0
+        want = torch.empty_like(qkv)
+        dq = torch.zeros(B * S, H, dtype=torch.float32, device="cuda")
+        delta = torch.empty(B, nh, S, dtype=torch.float32, device="cuda")
+        assert lib.bcom_attention_bwd(T._p(qkv), T._p(out), T._p(d_out), T._p(lse), T._p(want),
+                                      T._p(dq), T._p(delta), B, S, nh, hd, scale, st) == 0
+        assert lib.bcom_attention_bwd_no_alloc(T._p(qkv), T._p(out), T._p(d_out), T._p(lse),
+                                               T._p(got), B, S, nh, hd, scale, st) == 0
+        torch.cuda.synchronize()
+        diff = (got.float() - want.float()).abs().max().item()
+        assert diff < 3e-2 * max(1.0, want.float().abs().max().item()), diff
+        print("ok")
+    """)
+    run = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
+                         timeout=300, cwd=root)
+    assert run.returncode == 0 and "ok" in run.stdout, run.stdout[-1000:] + run.stderr[-3000:]
