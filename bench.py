@@ -58,7 +58,8 @@ def run_ours(args):
     cuda = args.device == "cuda"
     mcfg.attention = args.attention or (_default_attention() if cuda else "sdpa")
     seq = 2048 if args.model == "llama7b" else 256
-    tcfg = TrainerConfig(pp_size=pp, micro_batches=args.micro_batches or 4 * pp,
+    tcfg = TrainerConfig(pp_size=pp, pp_chunks=args.pp_chunks if pp > 1 else 1,
+                         micro_batches=args.micro_batches or 4 * pp,
                          micro_batch_size=args.micro_batch_size, seq_length=seq, bitwidth=4,
                          error_feedback=True, dp_sync=args.dp_sync, local_size=args.local_size,
                          defer_wgrad=args.defer_wgrad, device=args.device,
@@ -160,8 +161,9 @@ def run_ours(args):
                    if args.model == "llama7b" else "tiny",
                    "global_batch": trainer.dp * c.micro_batches * c.micro_batch_size,
                    "seq_len": c.seq_length, "parallelism": f"dp{trainer.dp}xpp{trainer.pp}",
-                   "micro_batches": c.micro_batches,
-                   "schedule": "1F1B" + (" + deferred weight gradients" if c.defer_wgrad else ""),
+                   "micro_batches": c.micro_batches, "pp_chunks": trainer.chunks,
+                   "schedule": ("interleaved 1F1B" if trainer.chunks > 1 else "1F1B")
+                   + (" + deferred weight gradients" if c.defer_wgrad else ""),
                    "grad_sync": trainer.grad_sync_description(),
                    "attention": mcfg.attention, "optimizer": "AdamW fp32 master",
                    "l2": ("per-step working set (>100 GB weights+activations) exceeds the "
@@ -225,6 +227,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
     ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
     ap.add_argument("--pp", type=int, default=0)
+    ap.add_argument("--pp-chunks", type=int, default=1,
+                    help="model chunks per pipeline rank (2 or more: interleaved 1F1B)")
     ap.add_argument("--micro-batches", type=int, default=0)
     ap.add_argument("--micro-batch-size", type=int, default=2, help="sequences per micro-batch")
     ap.add_argument("--attention", default=None, choices=[None, "tcgen05", "sdpa"])

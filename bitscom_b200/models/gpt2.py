@@ -101,6 +101,10 @@ class GPT2(torch.nn.Module):
         gelu = K.bias_gelu if self.fused_ops else (
             lambda t, b: F.gelu(t + b, approximate="tanh"))
         for i in range(cfg.n_layer):
+            if self.on_layer_backward is not None and x.requires_grad:
+                # fires once the gradient w.r.t. this layer's input exists: every gradient of
+                # the layer's own parameters has been produced by then
+                x.register_hook(self._make_hook(i))
             h = ln(x, self._w(f"h{i}.ln1_w"), self._w(f"h{i}.ln1_b"))
             qkv = G.linear(h, self._w(f"h{i}.wqkv")) + self._w(f"h{i}.bqkv")
             if fused_attn:
@@ -122,10 +126,23 @@ class GPT2(torch.nn.Module):
         shifted[:, :-1] = targets[:, 1:]
         return K.cross_entropy(logits, shifted.reshape(-1), ignore_index=-100)
 
-    def collect_autograd_grads(self) -> None:
+    on_layer_backward = None  # optional callable(layer_index), set by a trainer
+
+    def _make_hook(self, layer_index: int):
+        cb = self.on_layer_backward
+
+        def hook(grad):
+            cb(layer_index)
+            return None
+
+        return hook
+
+    def collect_autograd_grads(self, prefix: Optional[str] = None) -> None:
         """Parameters updated by torch ops (LayerNorm, biases, position embedding) receive
-        ``.grad``; fold them into the flat fp32 gradient buffer."""
-        for p in self.p.values():
-            if p.grad is not None:
+        ``.grad``; fold them into the flat fp32 gradient buffer.  ``prefix`` limits the pass
+        to the parameters whose name starts with it (one layer: ``"h3."``)."""
+        want = None if prefix is None else prefix.replace(".", "_")
+        for name, p in self.p.items():
+            if p.grad is not None and (want is None or name.startswith(want)):
                 p.main_grad.add_(p.grad.float())
                 p.grad = None

@@ -27,7 +27,8 @@ class GradBucketSync:
     def __init__(self, lowbit_group, flat_grads: torch.Tensor,
                  ranges: Sequence[Tuple[int, int]], *, mode: str = "flat",
                  local_group=None, inter_group=None, chunk_size: Optional[int] = None,
-                 average: bool = True, overlap: bool = True, max_ctas: Optional[int] = None):
+                 average: bool = True, overlap: bool = True, max_ctas: Optional[int] = None,
+                 key_prefix: Optional[tuple] = None):
         if mode not in ("flat", "pipeline_a", "dense"):
             raise ValueError(f"unknown mode {mode!r}")
         self.group = lowbit_group
@@ -42,6 +43,9 @@ class GradBucketSync:
         # grid cap of the fused kernel for buckets launched WHILE backward is still running:
         # the cooperative grid must fit next to the compute kernels that own the SMs then
         self.max_ctas = max_ctas
+        # error-feedback residuals are kept per key by the group: two synchronisers that share
+        # a group (one per model chunk) need distinct prefixes
+        self.key_prefix = tuple(key_prefix) if key_prefix else ()
         self._overlapping = False
         self.stream = torch.cuda.Stream(device=flat_grads.device) if flat_grads.is_cuda else None
         self._works: List = []
@@ -53,7 +57,7 @@ class GradBucketSync:
 
     def _launch(self, idx: int) -> None:
         bucket = self._bucket(idx)
-        key = ("bucket", idx)
+        key = self.key_prefix + ("bucket", idx)
         if self.mode == "dense":
             dist.all_reduce(bucket, group=self.group.pg)
             if self.post_scale != 1.0:

@@ -479,3 +479,123 @@ def simulate_interleaved_timeline(stages: int, microbatches: int, chunks: int,
             raise RuntimeError("the schedule deadlocks")
     ideal = microbatches * (t_forward + t_backward)
     return {"step_time": max(clock), "ideal_time": ideal, "efficiency": ideal / max(clock)}
+
+
+def simulate_plan_timeline(stages: int, microbatches: int, chunks: int,
+                           t_forward: float = 1.0, t_backward: float = 2.0) -> dict:
+    """Like ``simulate_interleaved_timeline`` but with the coupling the batches add: a send or
+    receive completes when BOTH sides have posted it, and a rank starts its next unit only when
+    its whole batch has completed (transfers themselves take no time).  For two or more chunks
+    the unit-batched plan loses nothing against the pure data-flow bound; for ONE chunk it
+    halves the throughput (the steady-state unit then waits for a gradient the peer can only
+    produce after this unit's activation), which is why a single chunk runs under
+    ``PipelineRunner`` with its batch-per-action plan instead."""
+    P, v = stages, chunks
+    plans = [[(u, list(s), list(r)) for u, s, r in virtual_plan(k, P, microbatches, v)]
+             for k in range(P)]
+    pos, post, last = [0] * P, [0.0] * P, [0.0] * P
+    sends: List[List[Message]] = [[] for _ in range(P)]
+    recvs: List[List[Message]] = [[] for _ in range(P)]
+
+    def load(k: int, now: float) -> None:
+        if pos[k] < len(plans[k]):
+            unit, s, r = plans[k][pos[k]]
+            post[k] = now + sum((t_forward if a[0] == "F" else t_backward) / v for a in unit)
+            last[k] = post[k]
+            sends[k], recvs[k] = list(s), list(r)
+
+    for k in range(P):
+        load(k, 0.0)
+    while not all(pos[k] >= len(plans[k]) for k in range(P)):
+        progressed = False
+        for k in range(P):
+            for s in list(sends[k]):
+                if next(m for m in sends[k] if m.dst == s.dst) is not s:
+                    continue
+                r = next((m for m in recvs[s.dst] if m.src == k), None)
+                if r is None:
+                    continue
+                when = max(post[k], post[s.dst])
+                last[k], last[s.dst] = max(last[k], when), max(last[s.dst], when)
+                sends[k].remove(s)
+                recvs[s.dst].remove(r)
+                progressed = True
+        for k in range(P):
+            if pos[k] < len(plans[k]) and not sends[k] and not recvs[k]:
+                pos[k] += 1
+                load(k, last[k])
+                progressed = True
+        if not progressed:
+            raise RuntimeError("the plan deadlocks")
+    ideal = microbatches * (t_forward + t_backward)
+    return {"step_time": max(last), "ideal_time": ideal, "efficiency": ideal / max(last)}
+
+
+class InterleavedRunner:
+    """Executes one training step of one rank that holds ``chunks`` >= 2 model chunks.
+
+    ``forward_fn(mb, chunk, input_or_None) -> output`` runs chunk ``chunk`` on micro-batch
+    ``mb`` (virtual stage 0 ignores the input, the last virtual stage returns the scalar
+    loss).  ``ring`` lists the global ranks of the pipeline group in stage order; activations
+    leave the last rank for the first one between chunks, gradients the other way round."""
+
+    def __init__(self, rank: int, stages: int, chunks: int, group, ring: Sequence[int],
+                 act_shape: Tuple[int, ...], dtype: torch.dtype = torch.bfloat16, device="cuda",
+                 defer_wgrad: bool = False):
+        if chunks < 2:
+            raise ValueError("InterleavedRunner needs two or more chunks per rank; one chunk "
+                             "runs under PipelineRunner")
+        self.rank, self.stages, self.chunks, self.group = rank, stages, chunks, group
+        self.ring = list(ring)
+        self.act_shape, self.dtype, self.device = tuple(act_shape), dtype, device
+        self.defer_wgrad = defer_wgrad
+
+    def run(self, microbatches: int, forward_fn: Callable) -> List[torch.Tensor]:
+        """Returns the per-micro-batch losses (rank of the last virtual stage) or []."""
+        P, v, rank = self.stages, self.chunks, self.rank
+        held: dict = {}      # tag -> tensor received and not yet consumed
+        inputs: dict = {}    # (mb, chunk) -> leaf input of a forward awaiting its backward
+        outputs: dict = {}
+        losses: List[torch.Tensor] = []
+        for unit, sends, recvs in virtual_plan(rank, P, microbatches, v):
+            payload: dict = {}
+            flush = None
+            for action in unit:
+                kind, mb, chunk = action
+                need = _needs(rank, P, v, action)
+                out_msg = _yields(rank, P, v, action)
+                if kind == "F":
+                    x = None
+                    if need is not None:
+                        x = held.pop(need.tag()).requires_grad_()
+                        inputs[(mb, chunk)] = x
+                    out = forward_fn(mb, chunk, x)
+                    outputs[(mb, chunk)] = out
+                    if out_msg is None:
+                        losses.append(out.detach())
+                    else:
+                        payload[out_msg.tag()] = out.detach()
+                else:
+                    out = outputs.pop((mb, chunk))
+                    deferred = DeferredWork() if self.defer_wgrad else None
+                    with deferred if deferred is not None else contextlib.nullcontext():
+                        if need is None:
+                            out.backward()
+                        else:
+                            torch.autograd.backward(out, grad_tensors=held.pop(need.tag()))
+                    if out_msg is not None:
+                        payload[out_msg.tag()] = inputs.pop((mb, chunk)).grad
+                    if deferred is not None:
+                        flush = deferred.flush
+            ops = [dist.P2POp(dist.isend, payload[m.tag()], self.ring[m.dst], self.group)
+                   for m in sends]
+            for m in recvs:
+                buf = torch.empty(self.act_shape, dtype=self.dtype, device=self.device)
+                held[m.tag()] = buf
+                ops.append(dist.P2POp(dist.irecv, buf, self.ring[m.src], self.group))
+            reqs = dist.batch_isend_irecv(ops) if ops else []
+            if flush is not None:      # weight-gradient GEMMs overlap the transfer
+                flush()
+            for req in reqs:
+                req.wait()             # stream-ordered; the host does not block
+        return losses

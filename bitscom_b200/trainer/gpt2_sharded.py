@@ -24,7 +24,7 @@ import torch.distributed as dist
 from ..api import LowBitGroup
 from ..models.gpt2 import GPT2, GPT2Config
 from ..ops import nn as K
-from ..parallel.zero import ShardedAdamW
+from ..parallel.zero import BucketedShardedAdamW, ShardedAdamW, bucket_cuts
 
 
 class DenseShardedAdamW:
@@ -57,6 +57,11 @@ def main(argv=None):
                     help="bitwidth of the parameter all-gather (4 is the configured setting; 8 "
                          "is reported as a variant)")
     ap.add_argument("--mode", default="lowbit", choices=["lowbit", "nccl"])
+    ap.add_argument("--zero-buckets", default="layer", choices=["layer", "one"],
+                    help="'layer': one bucket per transformer layer, reduce-scattered on a side "
+                         "stream while backward runs, parameters gathered under the next "
+                         "bucket's AdamW; 'one': the whole buffer in one reduce-scatter and one "
+                         "all-gather after backward")
     ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
     ap.add_argument("--cuda-graph", action="store_true",
                     help="capture forward + backward into one CUDA graph (launch-bound model)")
@@ -98,7 +103,20 @@ def main(argv=None):
     if args.mode == "lowbit" and world > 1:
         ggrp = LowBitGroup(bitwidth=args.grad_bits, block_size=256, error_feedback=True)
         pgrp = LowBitGroup(bitwidth=args.param_bits, block_size=256, error_feedback=True)
-        opt = ShardedAdamW(flat, ggrp, lr=args.lr, param_bits_group=pgrp)
+        if args.zero_buckets == "layer":
+            starts = [flat.offsets[f"h{i}.ln1_w"][0] for i in range(cfg.n_layer)]
+            starts.append(flat.offsets["lnf_w"][0])
+            opt = BucketedShardedAdamW(flat, ggrp, bucket_cuts(starts, flat.numel, world),
+                                       lr=args.lr, param_bits_group=pgrp)
+            if not args.cuda_graph:   # a captured backward cannot call back into Python
+
+                def layer_done(i: int) -> None:
+                    model.collect_autograd_grads(prefix=f"h{i}.")
+                    opt.ready_from(flat.offsets[f"h{i}.ln1_w"][0])
+
+                model.on_layer_backward = layer_done
+        else:
+            opt = ShardedAdamW(flat, ggrp, lr=args.lr, param_bits_group=pgrp)
     elif world > 1:
         opt = DenseShardedAdamW(flat, world, rank, args.lr)
     else:
@@ -111,9 +129,11 @@ def main(argv=None):
     def master_sum():
         """Sum of the fp32 master weights over all shards (float64): a fingerprint of the
         optimizer's weights that does not depend on how they are partitioned."""
-        if not isinstance(opt, ShardedAdamW):
+        if not isinstance(opt, (ShardedAdamW, BucketedShardedAdamW)):
             return None
-        t = opt.master_shard.double().sum().reshape(1)
+        shards = opt.master_shards if isinstance(opt, BucketedShardedAdamW) else [
+            opt.master_shard]
+        t = sum(m.double().sum() for m in shards).reshape(1)
         if world > 1:
             dist.all_reduce(t)
         return float(t.item())
@@ -174,7 +194,10 @@ def main(argv=None):
                "mode": args.mode, "world": world, "device": args.device,
                "fused_ops": not args.torch_ops,
                "cuda_graph": bool(args.cuda_graph), "grad_bits": args.grad_bits,
-               "param_bits": args.param_bits, "ms_per_step": float(ms.item()),
+               "param_bits": args.param_bits,
+               "zero_buckets": (f"{len(opt.parts)} buckets, overlapped" if isinstance(
+                   opt, BucketedShardedAdamW) else "one"),
+               "ms_per_step": float(ms.item()),
                "tokens_per_s": tokens / float(ms.item()) * 1e3,
                "loss_first": float(first.item()), "loss_last": float(last.item()),
                "steps_done_before": done, "master_sum_start": fingerprint_start,
@@ -184,7 +207,7 @@ def main(argv=None):
             os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
             with open(args.out, "a") as f:
                 f.write(json.dumps(row) + "\n")
-    if args.output_dir and isinstance(opt, ShardedAdamW):
+    if args.output_dir and isinstance(opt, (ShardedAdamW, BucketedShardedAdamW)):
         from ..utils.checkpoint import save_checkpoint
 
         save_checkpoint(args.output_dir, {"step": done + args.warmup + args.steps,
@@ -201,24 +224,32 @@ def main(argv=None):
 def _resume(directory: str, opt, flat, rank: int, world: int) -> int:
     """Load the sharded optimizer state written by a run of ``old_world`` ranks (any number)
     and rebuild the bf16 parameters from the fp32 master shards.  Returns the steps done."""
-    from ..parallel.zero import reshard_state
+    from ..parallel.zero import reshard_bucketed_state, reshard_state
     from ..utils.checkpoint import load_checkpoint
 
-    if not isinstance(opt, ShardedAdamW):
+    bucketed = isinstance(opt, BucketedShardedAdamW)
+    if not bucketed and not isinstance(opt, ShardedAdamW):
         raise SystemExit("--resume needs the sharded optimizer (lowbit mode, 2 or more ranks)")
     head = load_checkpoint(directory, 0)
     old_world = int(head["world"])
+    if ("buckets" in head["zero"]) != bucketed:
+        raise SystemExit("the checkpoint was written with another --zero-buckets setting")
     if old_world == world:
         mine = load_checkpoint(directory, rank)["zero"]
     else:
         states = [head["zero"]] + [load_checkpoint(directory, r)["zero"]
                                    for r in range(1, old_world)]
-        mine = reshard_state(states, world, int(head["used"]))[rank]
+        if bucketed:
+            mine = reshard_bucketed_state(states, world, opt.cuts, int(head["used"]))[rank]
+        else:
+            mine = reshard_state(states, world, int(head["used"]))[rank]
     opt.load_state_dict(mine)
     # every rank needs the whole bf16 model: gather the master shards densely, once
-    full = torch.empty(flat.numel, dtype=torch.float32, device=flat.params.device)
-    dist.all_gather_into_tensor(full, opt.master_shard)
-    flat.params.copy_(full)
+    parts = opt.parts if bucketed else [opt]
+    for part in parts:
+        full = torch.empty(part.flat.numel, dtype=torch.float32, device=flat.params.device)
+        dist.all_gather_into_tensor(full, part.master_shard)
+        part.flat.params.copy_(full)
     return int(head["step"])
 
 

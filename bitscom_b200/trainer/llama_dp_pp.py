@@ -34,12 +34,13 @@ from ..api import LowBitGroup
 from ..models.llama import LlamaConfig, LlamaStage
 from ..ops import nn as K
 from ..parallel.hooks import GradBucketSync
-from ..parallel.pp_schedule import PipelineRunner
+from ..parallel.pp_schedule import InterleavedRunner, PipelineRunner
 
 
 @dataclass
 class TrainerConfig:
     pp_size: int = 1
+    pp_chunks: int = 1            # model chunks per pipeline rank (>= 2: interleaved 1F1B)
     micro_batches: int = 4
     micro_batch_size: int = 1
     seq_length: int = 2048
@@ -110,19 +111,40 @@ class LlamaTrainer:
                 if p == self.pp_rank:
                     self.dp_group = g
 
-        self.model = LlamaStage(model_cfg, self.pp_rank, self.pp, self.device,
-                                seed=cfg.seed)
-        flat = self.model.flat
-        self.opt = K.FlatAdamW(flat.master, flat.grads, flat.params, lr=cfg.lr,
-                               weight_decay=cfg.weight_decay)
-        self.runner = PipelineRunner(
-            self.pp_rank, self.pp, self.pp_group,
-            prev_rank=self.rank - 1 if self.pp_rank > 0 else None,
-            next_rank=self.rank + 1 if self.pp_rank < self.pp - 1 else None,
-            act_shape=(cfg.micro_batch_size * cfg.seq_length, model_cfg.hidden_size),
-            device=self.device, defer_wgrad=cfg.defer_wgrad,
-            defer_last=cfg.defer_wgrad) if self.pp > 1 else None
+        # chunk c of this rank is virtual stage c * pp + pp_rank of pp * chunks; one chunk is
+        # the plain contiguous split
+        self.chunks = max(1, int(cfg.pp_chunks)) if self.pp > 1 else 1
+        if self.chunks > 1 and cfg.micro_batches % self.pp:
+            raise RuntimeError(f"interleaved pipeline: micro_batches ({cfg.micro_batches}) must "
+                               f"be a multiple of pp_size ({self.pp})")
+        if model_cfg.num_layers < self.pp * self.chunks:
+            raise RuntimeError(f"{model_cfg.num_layers} layers cannot be cut into "
+                               f"{self.pp * self.chunks} virtual stages")
+        self.models = [LlamaStage(model_cfg, c * self.pp + self.pp_rank, self.pp * self.chunks,
+                                  self.device, seed=cfg.seed) for c in range(self.chunks)]
+        self.model = self.models[0]
+        self.opts = [K.FlatAdamW(m.flat.master, m.flat.grads, m.flat.params, lr=cfg.lr,
+                                 weight_decay=cfg.weight_decay) for m in self.models]
+        self.opt = self.opts[0]
+        self._layer_chunk = {i: c for c, m in enumerate(self.models)
+                             for i in range(*m.layer_range)}
+        act_shape = (cfg.micro_batch_size * cfg.seq_length, model_cfg.hidden_size)
+        self.runner = None
+        if self.pp > 1 and self.chunks > 1:
+            self.runner = InterleavedRunner(
+                self.pp_rank, self.pp, self.chunks, self.pp_group,
+                ring=[self.dp_rank * self.pp + p for p in range(self.pp)], act_shape=act_shape,
+                device=self.device, defer_wgrad=cfg.defer_wgrad)
+        elif self.pp > 1:
+            self.runner = PipelineRunner(
+                self.pp_rank, self.pp, self.pp_group,
+                prev_rank=self.rank - 1 if self.pp_rank > 0 else None,
+                next_rank=self.rank + 1 if self.pp_rank < self.pp - 1 else None,
+                act_shape=act_shape, device=self.device, defer_wgrad=cfg.defer_wgrad,
+                defer_last=cfg.defer_wgrad)
 
+        self.syncs: List[GradBucketSync] = []
+        self._range_indexes: List[dict] = []
         self.sync: Optional[GradBucketSync] = None
         if self.dp > 1:
             self.lowbit = LowBitGroup(
@@ -135,10 +157,15 @@ class LlamaTrainer:
             mode = cfg.dp_sync
             if mode == "pipeline_a":
                 local_group, inter_group = self._hierarchy(cfg.local_size)
-            self.sync = GradBucketSync(
-                self.lowbit, flat.grads, self._sync_ranges(), mode=mode,
-                local_group=local_group, inter_group=inter_group, overlap=cfg.overlap,
-                max_ctas=cfg.sync_max_ctas or None)
+            for c, m in enumerate(self.models):
+                ranges, index = self._sync_ranges(m)
+                self._range_indexes.append(index)
+                self.syncs.append(GradBucketSync(
+                    self.lowbit, m.flat.grads, ranges, mode=mode,
+                    local_group=local_group, inter_group=inter_group, overlap=cfg.overlap,
+                    max_ctas=cfg.sync_max_ctas or None,
+                    key_prefix=("chunk", c) if self.chunks > 1 else None))
+            self.sync = self.syncs[0]
         self.step_count = 0
         self._pinned: Optional[torch.Tensor] = None
         self._marks: List[tuple] = []   # per step: CUDA events at the phase boundaries
@@ -163,10 +190,11 @@ class LlamaTrainer:
                 inter = g
         return local, inter
 
-    def _sync_ranges(self) -> List[Tuple[int, int]]:
-        """One slice per transformer layer (plus embedding / head), in the order backward
-        finishes them: last layer first."""
-        flat = self.model.flat
+    @staticmethod
+    def _sync_ranges(model) -> Tuple[List[Tuple[int, int]], dict]:
+        """One slice per transformer layer (plus embedding / head) of ``model``, in the order
+        backward finishes them (last layer first), and the slice index of every key."""
+        flat = model.flat
         names = list(flat.offsets)
         groups: List[Tuple[int, int]] = []
         keys: List[str] = []
@@ -181,19 +209,20 @@ class LlamaTrainer:
             cur_key = key
         groups.reverse()
         keys.reverse()
-        self._range_index = {k: i for i, k in enumerate(keys)}
-        return groups
+        return groups, {k: i for i, k in enumerate(keys)}
 
     def _layer_done(self, layer: int) -> None:
         """Backward of the last micro-batch has passed ``layer``: its slice, and the
         head / final norm when it is the stage's last layer, are final."""
-        if self.sync is None:
+        if not self.syncs:
             return
-        if layer == self.model.layer_range[1] - 1:
+        chunk = self._layer_chunk[layer]
+        sync, index = self.syncs[chunk], self._range_indexes[chunk]
+        if layer == self.models[chunk].layer_range[1] - 1:
             for key in ("lm_head", "final_norm"):
-                if key in self._range_index:
-                    self.sync.on_ready_overlapped(self._range_index[key])
-        self.sync.on_ready_overlapped(self._range_index[f"l{layer}"])
+                if key in index:
+                    sync.on_ready_overlapped(index[key])
+        sync.on_ready_overlapped(index[f"l{layer}"])
 
     def _layer_done_after_deferred(self, layer: int) -> None:
         """``_layer_done`` for a backward whose weight-gradient GEMMs are queued: the bucket of
@@ -222,19 +251,19 @@ class LlamaTrainer:
         c = self.cfg
         t_start = self._event() if self.device.type == "cuda" else None
         ids = ids_host_or_dev.to(self.device, non_blocking=True)
-        model = self.model
         scale = 1.0 / c.micro_batches
         losses: List[torch.Tensor] = []
 
         last_mb = c.micro_batches - 1
 
-        def forward_fn(mb: int, x: Optional[torch.Tensor]):
+        def forward_chunk(mb: int, chunk: int, x: Optional[torch.Tensor]):
+            model = self.models[chunk]
             # with deferred weight gradients the last backward's GEMMs run after its input
             # gradient has been sent (the deferral that shortens the pipeline's drain); the
             # per-layer bucket launches, which need finished gradients, then ride in the same
             # queue, each behind the weight-gradient GEMMs of its layer
             model.on_layer_backward = None
-            if mb == last_mb and self.sync is not None and c.overlap:
+            if mb == last_mb and self.syncs and c.overlap:
                 model.on_layer_backward = self._layer_done_after_deferred if (
                     c.defer_wgrad and self.runner is not None) else self._layer_done
             if not model.is_first:
@@ -247,25 +276,29 @@ class LlamaTrainer:
 
         if self.runner is None:
             for mb in range(c.micro_batches):
-                loss = forward_fn(mb, None)
+                loss = forward_chunk(mb, 0, None)
                 losses.append(loss.detach())
                 loss.backward()
+        elif self.chunks > 1:
+            losses = self.runner.run(c.micro_batches, forward_chunk)
         else:
-            losses = self.runner.run(c.micro_batches, forward_fn)
+            losses = self.runner.run(c.micro_batches, lambda mb, x: forward_chunk(mb, 0, x))
 
-        model.on_layer_backward = None
+        for model in self.models:
+            model.on_layer_backward = None
         marks = self._mark_begin(t_start) if self.device.type == "cuda" else None
-        if self.sync is not None:
-            self.sync.finish()
+        for sync in self.syncs:
+            sync.finish()
         if marks is not None:
             marks.append(self._event())
-        self.opt.step(grad_scale=1.0, zero_grad=True)
+        for opt in self.opts:
+            opt.step(grad_scale=1.0, zero_grad=True)
         if marks is not None:
             marks.append(self._event())
             self._marks.append(tuple(marks))
             del self._marks[:-64]
         self.step_count += 1
-        if model.is_last:
+        if self.models[-1].is_last:
             return torch.stack(losses).sum()
         return None
 
@@ -309,14 +342,18 @@ class LlamaTrainer:
             G.check_status()
         if A.available():
             A.check_status()
-        if self.sync is not None:
+        if self.syncs:
             torch.cuda.synchronize(self.device)
-            self.sync.check(wait=True)
+            for sync in self.syncs:
+                sync.check(wait=True)
 
     # -- checkpoint -----------------------------------------------------------------------
     def state_dict(self) -> dict:
         sd = {"step": self.step_count, "opt": self.opt.state_dict(),
               "params": self.model.flat.params}
+        if self.chunks > 1:   # chunk 0 keeps the single-chunk keys; the others follow
+            sd["more_chunks"] = [{"opt": o.state_dict(), "params": m.flat.params}
+                                 for o, m in zip(self.opts[1:], self.models[1:])]
         if self.sync is not None:
             sd["lowbit"] = self.lowbit.state_dict()
         return sd
@@ -325,6 +362,13 @@ class LlamaTrainer:
         self.step_count = int(sd["step"])
         self.opt.load_state_dict(sd["opt"])
         self.model.flat.params.copy_(sd["params"])
+        if self.chunks > 1:
+            if len(sd.get("more_chunks", ())) != self.chunks - 1:
+                raise RuntimeError(f"the checkpoint holds {1 + len(sd.get('more_chunks', ()))} "
+                                   f"model chunk(s) per rank, this trainer {self.chunks}")
+            for o, m, part in zip(self.opts[1:], self.models[1:], sd["more_chunks"]):
+                o.load_state_dict(part["opt"])
+                m.flat.params.copy_(part["params"])
         if self.sync is not None and "lowbit" in sd:
             self.lowbit.load_state_dict(sd["lowbit"])
 
@@ -415,6 +459,9 @@ def _train_loop(args, trainer, loader, tcfg, monitor) -> None:
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--pp_size", type=int, default=1)
+    ap.add_argument("--pp_chunks", type=int, default=1,
+                    help="model chunks per pipeline rank; 2 or more runs the interleaved 1F1B "
+                         "schedule (micro_batches must then be a multiple of pp_size)")
     ap.add_argument("--micro_batches", type=int, default=4)
     ap.add_argument("--batch_size", type=int, default=1, help="sequences per micro-batch")
     ap.add_argument("--seq_length", type=int, default=2048)
@@ -468,7 +515,7 @@ def main(argv=None):
     if args.model == "tiny":
         args.seq_length = min(args.seq_length, mcfg.max_seq)
     tcfg = TrainerConfig(
-        pp_size=args.pp_size, micro_batches=args.micro_batches,
+        pp_size=args.pp_size, pp_chunks=args.pp_chunks, micro_batches=args.micro_batches,
         micro_batch_size=args.batch_size, seq_length=args.seq_length, bitwidth=args.bitwidth,
         stochastic_rounding=args.stochastic_rounding,
         error_feedback=not args.no_error_feedback,

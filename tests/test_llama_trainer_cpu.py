@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False,
-            untied: bool = False, local_size: int = 1) -> None:
+            untied: bool = False, local_size: int = 1, chunks: int = 1) -> None:
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
 
@@ -25,7 +25,7 @@ def _worker(pp: int, sync: str, steps: int, defer_wgrad: bool = False,
     mcfg.attention = "sdpa"
     tcfg = TrainerConfig(pp_size=pp, micro_batches=4, micro_batch_size=2, seq_length=64,
                          bitwidth=4, error_feedback=True, dp_sync=sync, lr=1e-2, device="cpu",
-                         defer_wgrad=defer_wgrad, local_size=local_size)
+                         defer_wgrad=defer_wgrad, local_size=local_size, pp_chunks=chunks)
     trainer = LlamaTrainer(mcfg, tcfg)
     losses = []
     for _ in range(steps):
@@ -57,13 +57,13 @@ def _free_port() -> int:
 
 @functools.lru_cache(maxsize=None)   # the runs are deterministic: tests share them
 def _run(nproc: int, pp: int, sync: str, steps: int = 6, defer_wgrad: bool = False,
-         untied: bool = False, local_size: int = 1):
+         untied: bool = False, local_size: int = 1, chunks: int = 1):
     env = dict(os.environ, TORCH_DISTRIBUTED_DEBUG="OFF", OMP_NUM_THREADS="1")
     run = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nproc-per-node", str(nproc),
          "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
          os.path.abspath(__file__), str(pp), sync, str(steps), str(int(defer_wgrad)),
-         str(int(untied)), str(local_size)],
+         str(int(untied)), str(local_size), str(chunks)],
         cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert run.returncode == 0, run.stderr[-3000:]
     text = run.stdout.replace("}{", "}\n{")
@@ -84,6 +84,25 @@ def test_pipeline_split_computes_what_the_unsplit_model_computes():
     assert whole[0]["losses"][-1] < whole[0]["losses"][0] - 0.5
     assert two[0]["losses"] == whole[0]["losses"]
     assert four[0]["losses"] == whole[0]["losses"]
+
+
+def test_interleaved_pipeline_computes_what_the_unsplit_model_computes():
+    """Two chunks per rank (four virtual stages on two ranks, interleaved 1F1B): the same loss
+    curve as the unsplit model, bit for bit, with and without deferred weight gradients; and
+    with two replicas the per-chunk gradient buckets keep error-feedback residuals of their
+    own."""
+    whole = _run(1, 1, "dense", untied=True)
+    inter = _run(2, 2, "dense", untied=True, chunks=2)
+    inter_deferred = _run(2, 2, "dense", untied=True, chunks=2, defer_wgrad=True)
+    assert inter[0]["losses"] == whole[0]["losses"]
+    assert inter_deferred[0]["losses"] == whole[0]["losses"]
+    low = _run(4, 2, "flat", chunks=2, defer_wgrad=True)
+    plain = _run(4, 2, "flat", defer_wgrad=True)
+    assert [r["dp_rank"] for r in low] == [0, 1]
+    for a, b in zip(low, plain):
+        assert a["losses"][-1] < a["losses"][0] - 0.5
+        assert abs(a["losses"][-1] - b["losses"][-1]) < 0.3
+    assert any("chunk" in k for k in low[0]["residual_keys"])
 
 
 def test_dp2_pp2_behaves_like_dp2_pp1_with_dense_gradient_sync():
@@ -205,4 +224,5 @@ def test_dp4_pp2_pipeline_a_with_local_pairs_on_strided_groups():
 
 if __name__ == "__main__":
     _worker(int(sys.argv[1]), sys.argv[2], int(sys.argv[3]), bool(int(sys.argv[4])),
-            bool(int(sys.argv[5])), int(sys.argv[6]) if len(sys.argv) > 6 else 1)
+            bool(int(sys.argv[5])), int(sys.argv[6]) if len(sys.argv) > 6 else 1,
+            int(sys.argv[7]) if len(sys.argv) > 7 else 1)
