@@ -139,6 +139,7 @@ def measure(comm, sizes_mb: Sequence[float] = (64, 1024), dtypes: Sequence[str] 
 
             ms = time_ms(run, bufs, iters, warmup, group)
             comm.check_status()
+            phases = comm.phase_times_us() if hasattr(comm, "phase_times_us") else None
             floor = roofline_ms(n, esize, bits, world, ef, hbm_gbs, link_gbs)
             rows.append({
                 "bytes": size, "bucket_dtype": dname, "numel": n, "world": world, "bits": bits,
@@ -148,7 +149,9 @@ def measure(comm, sizes_mb: Sequence[float] = (64, 1024), dtypes: Sequence[str] 
                 "nccl_bf16_effective_gbs": n * 4 / nccl_bf16 / 1e6,
                 "nccl_fp32_effective_gbs": n * 4 / nccl_fp32 / 1e6,
                 "vs_nccl_bf16": nccl_bf16 / ms, "vs_nccl_fp32": nccl_fp32 / ms,
-                "roofline_ms": floor, "roofline_frac": floor / ms, "peaks": tag})
+                "roofline_ms": floor, "roofline_frac": floor / ms, "peaks": tag,
+                # this rank's last launch, from time stamps its first CTA took on the device
+                "phases_us_rank0": phases})
             del bufs, efs, index
             torch.cuda.empty_cache()
     return rows

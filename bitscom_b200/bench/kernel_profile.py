@@ -75,6 +75,8 @@ def fused(args):
         run(i)
     ms = _timed(run, args.iters)
     assert all(s[0] == 0 for s in world.status())
+    torch.cuda.synchronize()
+    phases = world.phase_times_us()[0]   # rank 0's first CTA, last launch
     esize = 4 if dtype == torch.float32 else 2
     pk = args.bits / 8 + 2 / 256
     phase1 = n * (esize + (8 if ef else 0) + pk)
@@ -91,7 +93,8 @@ def fused(args):
                       "rounding": "nearest" if args.nearest else "stochastic",
                       "dtype": args.dtype, "bits": args.bits, "ef": ef, "ms": ms,
                       "hbm_bytes": total, "gbs": total / ms / 1e6,
-                      "frac_hbm": total / ms / 1e6 / hbm, "peaks": tag}))
+                      "frac_hbm": total / ms / 1e6 / hbm, "peaks": tag,
+                      "phases_us_rank0": phases}))
     world.close()
 
 

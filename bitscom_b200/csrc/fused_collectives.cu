@@ -34,7 +34,13 @@
 
 namespace bcom {
 
-constexpr int kCollThreads = 512;
+#ifndef BCOM_COLL_THREADS
+#define BCOM_COLL_THREADS 512
+#endif
+#ifndef BCOM_PHASE2_GROUPS
+#define BCOM_PHASE2_GROUPS 1
+#endif
+constexpr int kCollThreads = BCOM_COLL_THREADS;
 
 struct RankParams {
   unsigned char* peer[BCOM_MAX_WORLD];
@@ -81,6 +87,13 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// phase time stamp of the rank's first CTA into the host-mapped record (six stores per launch)
+__device__ __forceinline__ void stamp(unsigned int* status, int cta, int slot) {
+  if (cta == 0 && threadIdx.x == 0)
+    reinterpret_cast<volatile unsigned long long*>(status + BCOM_STATUS_TIMES)[slot] =
+        global_timer_ns();
 }
 
 // L2-coherent loads for slots that peers wrote during this kernel
@@ -243,6 +256,7 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   const T* in = static_cast<const T*>(p.in);
   T* out = static_cast<T*>(p.out);
 
+  stamp(p.status, cta, 0);
   // ---------------- phase 1: quantize every destination's shard and push it ----------
   if (p.mode != BCOM_MODE_ALL_GATHER) {
     const bool ef = p.res1 != nullptr;
@@ -257,22 +271,22 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
       const T* src = in + base_idx;
       float* res = ef ? p.res1 + base_idx : nullptr;
       const uint32_t idx_lo = (uint32_t)base_idx;
-      for (int g = gfirst; g < gp; g += gstride) {
+      // Two groups per thread and iteration: the loads of both are issued before the first
+      // is used, so a warp keeps twice the bytes in flight (the kernel waits on loads more
+      // than on anything else).  gp is a multiple of 32 and a warp's first group is too, so
+      // `second` is uniform over the warp and the shuffles below stay convergent.
+      auto quantize_push = [&](int g, float (&v)[GROUP], const float (&r)[GROUP]) {
         const int e0 = g * GROUP;
         const bool live = g < gs;
         const int lim = live ? min(max(valid - e0, 0), GROUP) : 0;
-        float v[GROUP];
-        load_vals<T, ALIGNED>(src, e0, lim, v);
         if (ef) {
-          float r[GROUP];
-          load_vals<float, ALIGNED>(res, e0, lim, r);
 #pragma unroll
           for (int i = 0; i < GROUP; ++i) v[i] = __fadd_rn(v[i], r[i]);
         }
         const float m = block_absmax(absmax8(v), lanes);
         const __half sh = scale_from_absmax<BITS>(m);
         const float sf = __half2float(sh);
-        if (!live) continue;
+        if (!live) return;
         int q[GROUP];
         if (ef) {
           float d[GROUP];
@@ -284,28 +298,87 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
           quant8<BITS, SR>(v, sf, p.key1, idx_lo + (uint32_t)e0, q);
         }
         push_group<BITS>(slot, p.scale_off, g, lanes, llog, pack8<BITS>(q), sh);
+      };
+      auto load_group_inputs = [&](int g, float (&v)[GROUP], float (&r)[GROUP]) {
+        const int e0 = g * GROUP;
+        const int lim = g < gs ? min(max(valid - e0, 0), GROUP) : 0;
+        load_vals<T, ALIGNED>(src, e0, lim, v);
+        if (ef) load_vals<float, ALIGNED>(res, e0, lim, r);
+      };
+      for (int g = gfirst; g < gp; g += 2 * gstride) {
+        const int g2 = g + gstride;
+        const bool second = g2 < gp;
+        float v0[GROUP], r0[GROUP], v1[GROUP], r1[GROUP];
+        load_group_inputs(g, v0, r0);
+        if (second) load_group_inputs(g2, v1, r1);
+        quantize_push(g, v0, r0);
+        if (second) quantize_push(g2, v1, r1);
       }
     }
   }
+  stamp(p.status, cta, 1);
   arrive_and_publish(p, ncta, BCOM_CTL_ARRIVE1, BCOM_CTL_ARRIVE2, BCOM_CTL_FLAG1);
   if (!wait_flags(p, BCOM_CTL_FLAG1, BCOM_TIMEOUT_PHASE1_FLAGS)) return;
+  stamp(p.status, cta, 2);
 
   // ---------------- phase 2: reduce own shard, re-quantize, push to everybody ---------
   {
-    const bool ef2 = p.res2 != nullptr;
-    for (long long g = first; g < Gp; g += nthreads) {
+    const bool ef2 = p.res2 != nullptr && p.mode != BCOM_MODE_REDUCE_SCATTER;
+    // Everything a group needs from memory is requested before anything is used: the first
+    // eight sources' packed words and scales and the stage-2 residual (one latency instead of
+    // two in a row).
+    struct Inputs {
+      Packed8<BITS> pk[8];
+      float sc[8];
+      float r[GROUP];
+    };
+    auto request = [&](long long g, Inputs& x) {
       const bool live = g < Gs;
       const long long off = p.c0 + g * GROUP;
-      long long lim = live ? min(shard_end - off, (long long)GROUP) : 0;
+      const long long lim = live ? min(shard_end - off, (long long)GROUP) : 0;
+      if (p.mode == BCOM_MODE_ALL_GATHER) {
+        load_vals<T, ALIGNED>(in, off, lim, x.r);       // the shard itself travels in r
+      } else if (live) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (u < W) {
+            const unsigned char* slot = recv_region + (size_t)u * p.slot_stride;
+            x.pk[u] = load_group_cg<BITS>(slot, g);
+            x.sc[u] = load_scale_cg(slot, p.scale_off, g >> llog);
+          }
+        }
+      }
+      if (ef2 && p.mode != BCOM_MODE_ALL_GATHER) load_vals<float, ALIGNED>(p.res2, off, lim, x.r);
+    };
+    auto reduce_push = [&](long long g, Inputs& x) {
+      const bool live = g < Gs;
+      const long long off = p.c0 + g * GROUP;
+      const long long lim = live ? min(shard_end - off, (long long)GROUP) : 0;
       float acc[GROUP];
 #pragma unroll
       for (int i = 0; i < GROUP; ++i) acc[i] = 0.0f;
       if (p.mode == BCOM_MODE_ALL_GATHER) {
-        load_vals<T, ALIGNED>(in, off, lim, acc);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) acc[i] = x.r[i];
+        if (ef2) {
+          float r2[GROUP];
+          load_vals<float, ALIGNED>(p.res2, off, lim, r2);
+#pragma unroll
+          for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], r2[i]);
+        }
       } else if (live) {
-        // issue the loads of up to 8 sources back to back, then accumulate in ascending
-        // source order (the order is part of the wire contract)
-        for (int s0 = 0; s0 < W; s0 += 8) {
+        // ascending source order: the order is part of the wire contract
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (u < W) {
+            float c[GROUP];
+            unpack8f<BITS>(x.pk[u], c);
+#pragma unroll
+            for (int i = 0; i < GROUP; ++i)
+              acc[i] = __fadd_rn(acc[i], __fmul_rn(c[i], x.sc[u]));
+          }
+        }
+        for (int s0 = 8; s0 < W; s0 += 8) {     // worlds above eight: the rest, eight at a time
           Packed8<BITS> pk[8];
           float sc[8];
 #pragma unroll
@@ -334,18 +407,16 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
           for (int i = 0; i < GROUP; ++i) acc[i] = cast_roundtrip<T>(acc[i], p.post_scale);
           store_vals<T, ALIGNED>(out, off, lim, acc);
         }
-        continue;
+        return;
       }
-      if (ef2) {
-        float r[GROUP];
-        load_vals<float, ALIGNED>(p.res2, off, lim, r);
+      if (ef2 && p.mode != BCOM_MODE_ALL_GATHER) {
 #pragma unroll
-        for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
+        for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], x.r[i]);
       }
       const float m = block_absmax(absmax8(acc), lanes);
       const __half sh = scale_from_absmax<BITS>(m);
       const float sf = __half2float(sh);
-      if (!live) continue;
+      if (!live) return;
       int q[GROUP];
       const uint32_t idx2 = (uint32_t)((long long)p.rank * p.S + off);
       if (ef2) {
@@ -378,11 +449,34 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
           push_group<BITS>(slot, p.scale_off, g, lanes, llog, pk, sh);
         }
       }
+    };
+#if BCOM_PHASE2_GROUPS == 2
+    // Gp is a multiple of 32 and so is a warp's first group: `second` is uniform over the warp
+    for (long long g = first; g < Gp; g += 2 * nthreads) {
+      const long long g2 = g + nthreads;
+      const bool second = g2 < Gp;
+      Inputs x0, x1;
+      request(g, x0);
+      if (second) request(g2, x1);
+      reduce_push(g, x0);
+      if (second) reduce_push(g2, x1);
     }
+#else
+    for (long long g = first; g < Gp; g += nthreads) {
+      Inputs x;   // (two groups in flight do not fit 64 registers: they spill 600 bytes)
+      request(g, x);
+      reduce_push(g, x);
+    }
+#endif
   }
+  stamp(p.status, cta, 3);
   arrive_and_publish(p, ncta, BCOM_CTL_ARRIVE2, BCOM_CTL_ARRIVE1, BCOM_CTL_FLAG2);
   if (!wait_flags(p, BCOM_CTL_FLAG2, BCOM_TIMEOUT_PHASE2_FLAGS)) return;
-  if (p.mode == BCOM_MODE_REDUCE_SCATTER) return;
+  stamp(p.status, cta, 4);
+  if (p.mode == BCOM_MODE_REDUCE_SCATTER) {
+    stamp(p.status, cta, 5);
+    return;
+  }
 
   // ---------------- phase 3: dequantize all shards into the bucket --------------------
   {
@@ -394,21 +488,36 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
       const long long valid_ll = min(shard_end - p.c0, p.n - base_idx);
       const int valid = (int)max(0LL, min(valid_ll, (long long)gs * GROUP));
       T* dst = out + base_idx;
-      for (int g = gfirst; g < gs; g += gstride) {
-        const int e0 = g * GROUP;
-        const int lim = min(valid - e0, GROUP);
-        if (lim <= 0) continue;
-        const Packed8<BITS> pk = load_group_cg<BITS>(slot, g);
-        const float sf = load_scale_cg(slot, p.scale_off, g >> llog);
-        float y[GROUP];
-        unpack8f<BITS>(pk, y);
+      // four groups per thread and iteration, all loads first (see phase 1)
+      constexpr int U = 4;
+      for (int g0 = gfirst; g0 < gs; g0 += U * gstride) {
+        Packed8<BITS> pk[U];
+        float sf[U];
 #pragma unroll
-        for (int i = 0; i < GROUP; ++i)
-          y[i] = cast_roundtrip<T>(__fmul_rn(y[i], sf), p.post_scale);
-        store_vals<T, ALIGNED>(dst, e0, lim, y);
+        for (int u = 0; u < U; ++u) {
+          const int g = g0 + u * gstride;
+          if (g < gs) {
+            pk[u] = load_group_cg<BITS>(slot, g);
+            sf[u] = load_scale_cg(slot, p.scale_off, g >> llog);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int g = g0 + u * gstride;
+          const int e0 = g * GROUP;
+          const int lim = min(valid - e0, GROUP);
+          if (g >= gs || lim <= 0) continue;
+          float y[GROUP];
+          unpack8f<BITS>(pk[u], y);
+#pragma unroll
+          for (int i = 0; i < GROUP; ++i)
+            y[i] = cast_roundtrip<T>(__fmul_rn(y[i], sf[u]), p.post_scale);
+          store_vals<T, ALIGNED>(dst, e0, lim, y);
+        }
       }
     }
   }
+  stamp(p.status, cta, 5);
 }
 
 template <typename T, int BITS, bool SR, bool ALIGNED>

@@ -44,9 +44,10 @@ int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out) {
   if (err == cudaSuccess) err = cudaMemset(c->local, 0, BCOM_CONTROL_BYTES);
   if (err == cudaSuccess) err = write_canaries(c);
   if (err == cudaSuccess)
-    err = cudaHostAlloc((void**)&c->status_host, 8 * sizeof(unsigned int), cudaHostAllocMapped);
+    err = cudaHostAlloc((void**)&c->status_host, BCOM_STATUS_WORDS * sizeof(unsigned int),
+                        cudaHostAllocMapped);
   if (err == cudaSuccess) {
-    std::memset(c->status_host, 0, 8 * sizeof(unsigned int));
+    std::memset(c->status_host, 0, BCOM_STATUS_WORDS * sizeof(unsigned int));
     err = cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0);
   }
   if (err != cudaSuccess) {
@@ -91,9 +92,10 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
   if (err == cudaSuccess) err = write_canaries(c);
   if (err == cudaSuccess) err = cudaDeviceSynchronize();
   if (err == cudaSuccess)
-    err = cudaHostAlloc((void**)&c->status_host, 8 * sizeof(unsigned int), cudaHostAllocMapped);
+    err = cudaHostAlloc((void**)&c->status_host, BCOM_STATUS_WORDS * sizeof(unsigned int),
+                        cudaHostAllocMapped);
   if (err == cudaSuccess) {
-    std::memset(c->status_host, 0, 8 * sizeof(unsigned int));
+    std::memset(c->status_host, 0, BCOM_STATUS_WORDS * sizeof(unsigned int));
     err = cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0);
   }
   if (err != cudaSuccess) {
@@ -208,6 +210,16 @@ int bcom_comm_status(BcomComm* c, unsigned int out[8]) {
   return 0;
 }
 
+// Device time stamps (ns, %globaltimer) the first CTA of the last kernel took at its phase
+// boundaries: [0] entry, [1] phase-1 loop done, [2] all phase-1 flags seen, [3] phase-2 loop
+// done, [4] all phase-2 flags seen, [5] phase-3 loop done.  Valid once that kernel has finished.
+int bcom_comm_phase_times(BcomComm* c, unsigned long long out[6]) {
+  const volatile unsigned long long* t =
+      reinterpret_cast<const volatile unsigned long long*>(c->status_host + BCOM_STATUS_TIMES);
+  for (int i = 0; i < 6; ++i) out[i] = t[i];
+  return 0;
+}
+
 // Host address of the 8-word status record (pinned, written by the kernels): lets a caller
 // poll status[0] without a library call.
 void* bcom_comm_status_host(BcomComm* c) { return c->status_host; }
@@ -215,7 +227,7 @@ void* bcom_comm_status_host(BcomComm* c) { return c->status_host; }
 int bcom_comm_reset(BcomComm* c, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   BCOM_TRY(cudaStreamSynchronize(st));
-  std::memset(c->status_host, 0, 8 * sizeof(unsigned int));
+  std::memset(c->status_host, 0, BCOM_STATUS_WORDS * sizeof(unsigned int));
   BCOM_TRY(cudaMemsetAsync(c->local + BCOM_CTL_ARRIVE1, 0, 16, st));
   BCOM_TRY(cudaStreamSynchronize(st));
   return 0;

@@ -25,6 +25,9 @@
 #define BCOM_GUARD_BYTES 4096
 #define BCOM_CANARY_BYTE 0xA5
 #define BCOM_IPC_HANDLE_BYTES 64
+// host-mapped status record: words 0-7 error record, words 8-19 six 64-bit phase time stamps
+#define BCOM_STATUS_WORDS 32
+#define BCOM_STATUS_TIMES 8
 
 #ifdef __cplusplus
 extern "C" {
@@ -104,6 +107,9 @@ size_t bcom_comm_region_bytes(BcomComm* comm);
 long long bcom_comm_max_chunk(BcomComm* comm, int bits, int block);
 // copies the 8-word status record; status[0] != 0 means the last kernels gave up
 int bcom_comm_status(BcomComm* comm, unsigned int out[8]);
+// time stamps (ns) of the phase boundaries of the last kernel's first CTA: entry, phase-1 loop
+// done, phase-1 flags seen, phase-2 loop done, phase-2 flags seen, phase-3 loop done
+int bcom_comm_phase_times(BcomComm* comm, unsigned long long out[6]);
 // host address of that record (pinned memory the kernels write), for polling without a call
 void* bcom_comm_status_host(BcomComm* comm);
 // clears status, flags stay; zeroes the local arrival counters (after an error)

@@ -80,6 +80,7 @@ def _get():
             lib.bcom_comm_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint * 8)]
             lib.bcom_comm_status_host.argtypes = [vp]
             lib.bcom_comm_status_host.restype = vp
+            lib.bcom_comm_phase_times.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong * 6)]
             lib.bcom_comm_reset.argtypes = [vp, vp]
             lib.bcom_comm_set_timeout_ms.argtypes = [vp, ctypes.c_double]
             lib.bcom_comm_epoch.argtypes = [vp]
@@ -196,6 +197,18 @@ class _NativeComm:
         out = (ctypes.c_uint * 8)()
         self.lib.bcom_comm_status(self.handle, ctypes.byref(out))
         return list(out)
+
+    def phase_times_us(self) -> dict:
+        """Where the LAST kernel of this communicator spent its time, from the time stamps its
+        first CTA wrote at the phase boundaries (microseconds; read after a synchronize):
+        ``phase1`` quantize + push, ``wait1`` until every rank's phase-1 flag was seen,
+        ``phase2`` reduce + re-quantize + push, ``wait2``, ``phase3`` dequantize + write."""
+        t = (ctypes.c_ulonglong * 6)()
+        self.lib.bcom_comm_phase_times(self.handle, ctypes.byref(t))
+        names = ("phase1", "wait1", "phase2", "wait2", "phase3")
+        out = {n: max(0, int(t[i + 1]) - int(t[i])) / 1e3 for i, n in enumerate(names)}
+        out["total"] = max(0, int(t[5]) - int(t[0])) / 1e3
+        return out
 
     def reset(self) -> None:
         with torch.cuda.device(self.device):
@@ -377,6 +390,12 @@ class FusedLowBitComm:
     def set_timeout_ms(self, ms: float) -> None:
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle, float(ms))
 
+    def phase_times_us(self) -> dict:
+        """Phase breakdown of this rank's last kernel (see ``_NativeComm.phase_times_us``);
+        synchronises the device first."""
+        torch.cuda.synchronize(self.device)
+        return self.native.phase_times_us()
+
     def check_canaries(self) -> None:
         """Debugging aid for tests: see ``_NativeComm.check_canaries``."""
         self.native.check_canaries()
@@ -497,6 +516,9 @@ class EmulatedWorld:
 
     def status(self) -> List[List[int]]:
         return [c.status() for c in self.comms]
+
+    def phase_times_us(self) -> List[dict]:
+        return [c.phase_times_us() for c in self.comms]
 
     def check_canaries(self) -> None:
         for c in self.comms:
