@@ -327,6 +327,103 @@ __device__ __forceinline__ Packed8<BITS> pack8(const int (&q)[GROUP]) {
   return out;
 }
 
+// ---------------------------------------------------------------------------
+// Lean quantize + pack of one group for the common case: finite absmax, finite non-zero fp16
+// scale, whole-word codes (1, 2, 4, 8 bit).  Same codes as quant8_dq + pack8, fewer
+// instructions per element (the kernels that call it are bound by instruction issue):
+//   * no NaN rule and no underflow branch per element: those cases are decided once per group
+//     (lean_group_ok) and take the general path;
+//   * nearest rounding works on the SIGNED quotient (round-half-even is symmetric), so there is
+//     no |x| and no sign transfer;
+//   * the clamped code c is turned into its stored form by ONE add, t = c + (1.5 * 2^23 - qmin):
+//     the float's bit pattern is 0x4B400000 + (c - qmin);
+//   * the bit pattern is multiplied into its place with an integer multiply-add; the constant
+//     that the 0x4B400000 parts add up to (mod 2^32) is subtracted once per word.
+// d (if wanted) receives code * sf with the code as a float that is never -0.
+// ---------------------------------------------------------------------------
+template <int BITS> struct LeanOk {
+  static constexpr bool value = BITS == 1 || BITS == 2 || BITS == 4 || BITS == 8;
+};
+
+__device__ __forceinline__ bool lean_group_ok(float absmax, float sf) {
+  // false for NaN / inf absmax, for a scale that underflowed to 0 and for one that
+  // overflowed fp16 (inf)
+  return absmax < 3.0e38f && sf > 0.0f && sf <= 65504.0f;
+}
+
+template <int BITS, bool SR, bool WANT_D>
+__device__ __forceinline__ Packed8<BITS> quant8_pack_lean(const float (&x)[GROUP], float sf,
+                                                          uint32_t key, uint32_t idx0,
+                                                          float (&d)[GROUP]) {
+  static_assert(LeanOk<BITS>::value, "lean path: whole-word codes only");
+  constexpr float lo = (float)Range<BITS>::qmin, hi = (float)Range<BITS>::qmax;
+  constexpr float magic = kMagic - (float)Range<BITS>::qmin;  // exact: small integer offset
+  constexpr uint32_t magic_bits = 0x4B400000u;                // bits of `magic` + (c - qmin)
+  constexpr int PER_WORD = BITS == 8 ? 4 : 8;
+  const float y = __frcp_rn(sf);
+  float u[GROUP];
+  if constexpr (SR) {
+    if ((idx0 & 1u) == 0u) {  // the usual case: two elements share one hash
+#pragma unroll
+      for (int i = 0; i < GROUP; i += 2) {
+        const uint32_t h = sr_hash(key, (idx0 + i) >> 1);
+        u[i] = sr_u16(h & 0xFFFFu);
+        u[i + 1] = sr_u16(h >> 16);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) u[i] = sr_uniform(key, idx0 + i);
+    }
+  }
+  Packed8<BITS> out;
+#pragma unroll
+  for (int k = 0; k < Packed8<BITS>::WORDS; ++k) out.w[k] = 0u;
+#pragma unroll
+  for (int i = 0; i < GROUP; ++i) {
+    float s;
+    if constexpr (SR) {
+      const float a = fabsf(x[i]);
+      const float q0 = __fmul_rn(a, y);
+      const float n = __fmaf_rn(__fmaf_rn(-q0, sf, a), y, q0);   // IEEE a / sf (see Divider)
+      const float fl = __fsub_rn(__fadd_rd(n, kTwo23), kTwo23);  // floor(n)
+      const float frac = __fsub_rn(n, fl);
+      const float mag = u[i] < frac ? __fadd_rn(fl, 1.0f) : fl;
+      s = BITS == 1 ? mag
+                    : __uint_as_float(__float_as_uint(mag) | (__float_as_uint(x[i]) & 0x80000000u));
+    } else {
+      const float a = BITS == 1 ? fabsf(x[i]) : x[i];
+      const float q0 = __fmul_rn(a, y);
+      s = __fmaf_rn(__fmaf_rn(-q0, sf, a), y, q0);               // signed IEEE quotient
+    }
+    const float c = fminf(fmaxf(s, lo), hi);   // integer bounds: clamping commutes with rounding
+    const float t = __fadd_rn(c, magic);       // nearest: rounds half to even here
+    const int bit = (i % PER_WORD) * BITS;
+    out.w[i / PER_WORD] = __float_as_uint(t) * (1u << bit) + out.w[i / PER_WORD];
+    if constexpr (WANT_D) d[i] = __fmul_rn(__fsub_rn(t, magic), sf);
+  }
+  // what the magic_bits parts added up to, modulo 2^32
+  uint32_t garbage = 0u;
+#pragma unroll
+  for (int i = 0; i < PER_WORD; ++i) garbage += magic_bits << (i * BITS);
+#pragma unroll
+  for (int k = 0; k < Packed8<BITS>::WORDS; ++k) out.w[k] -= garbage;
+  return out;
+}
+
+// Quantize (+ dequantize) + pack one group: the lean path when it applies, else the general one.
+template <int BITS, bool SR, bool WANT_D>
+__device__ __forceinline__ Packed8<BITS> quant8_packed(const float (&x)[GROUP], float absmax,
+                                                       float sf, uint32_t key, uint32_t idx0,
+                                                       float (&d)[GROUP]) {
+  if constexpr (LeanOk<BITS>::value) {
+    if (__builtin_expect(lean_group_ok(absmax, sf), 1))
+      return quant8_pack_lean<BITS, SR, WANT_D>(x, sf, key, idx0, d);
+  }
+  int q[GROUP];
+  quant8_dq<BITS, SR>(x, sf, key, idx0, q, d);
+  return pack8<BITS>(q);
+}
+
 template <int BITS>
 __device__ __forceinline__ void unpack8(const Packed8<BITS>& in, int (&q)[GROUP]) {
   constexpr uint32_t mask = (1u << BITS) - 1u;

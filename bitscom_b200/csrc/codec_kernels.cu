@@ -55,19 +55,19 @@ __device__ __forceinline__ void quantize_group(const float (&v)[GROUP], long lon
   const float sf = __half2float(sh);
   if (g >= groups) return;
   if ((g & (lanes_per_block - 1)) == 0) scales[g / lanes_per_block] = sh;
+  if (full) {
+    float unused[GROUP];
+    store_group<BITS>(packed, g, quant8_packed<BITS, SR, false>(
+        v, m, sf, key, idx_offset + (uint32_t)base, unused));
+    return;
+  }
   int q[GROUP];
   quant8<BITS, SR>(v, sf, key, idx_offset + (uint32_t)base, q);
-  if (!full) {  // positions past the end carry code 0, like the host packer's padding
+  // positions past the end carry code 0, like the host packer's padding
 #pragma unroll
-    for (int i = 0; i < GROUP; ++i)
-      if (base + i >= n) q[i] = Range<BITS>::qmin;
-  }
-  const Packed8<BITS> p = pack8<BITS>(q);
-  if (full) {
-    store_group<BITS>(packed, g, p);
-  } else {
-    store_group_bytes<BITS>(packed, g, p, (int)packed_nbytes(n - base, BITS));
-  }
+  for (int i = 0; i < GROUP; ++i)
+    if (base + i >= n) q[i] = Range<BITS>::qmin;
+  store_group_bytes<BITS>(packed, g, pack8<BITS>(q), (int)packed_nbytes(n - base, BITS));
 }
 
 // Two groups per thread and iteration (a stride apart, so that both stay coalesced): the loads

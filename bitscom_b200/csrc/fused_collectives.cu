@@ -287,17 +287,17 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
         const __half sh = scale_from_absmax<BITS>(m);
         const float sf = __half2float(sh);
         if (!live) return;
-        int q[GROUP];
+        Packed8<BITS> pk;
+        float d[GROUP];
         if (ef) {
-          float d[GROUP];
-          quant8_dq<BITS, SR>(v, sf, p.key1, idx_lo + (uint32_t)e0, q, d);
+          pk = quant8_packed<BITS, SR, true>(v, m, sf, p.key1, idx_lo + (uint32_t)e0, d);
 #pragma unroll
           for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(v[i], d[i]);
           store_vals<float, ALIGNED>(res, e0, lim, d);
         } else {
-          quant8<BITS, SR>(v, sf, p.key1, idx_lo + (uint32_t)e0, q);
+          pk = quant8_packed<BITS, SR, false>(v, m, sf, p.key1, idx_lo + (uint32_t)e0, d);
         }
-        push_group<BITS>(slot, p.scale_off, g, lanes, llog, pack8<BITS>(q), sh);
+        push_group<BITS>(slot, p.scale_off, g, lanes, llog, pk, sh);
       };
       auto load_group_inputs = [&](int g, float (&v)[GROUP], float (&r)[GROUP]) {
         const int e0 = g * GROUP;
@@ -367,7 +367,9 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
           for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], r2[i]);
         }
       } else if (live) {
-        // ascending source order: the order is part of the wire contract
+        // ascending source order: the order is part of the wire contract.  A code (at most 12
+        // bits) times an fp16-valued scale (11 significant bits) is exact in fp32, so the fma
+        // rounds once, exactly where add(acc, mul(code, scale)) of the host model rounds
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           if (u < W) {
@@ -375,7 +377,7 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
             unpack8f<BITS>(x.pk[u], c);
 #pragma unroll
             for (int i = 0; i < GROUP; ++i)
-              acc[i] = __fadd_rn(acc[i], __fmul_rn(c[i], x.sc[u]));
+              acc[i] = __fmaf_rn(c[i], x.sc[u], acc[i]);  // exact product: see below
           }
         }
         for (int s0 = 8; s0 < W; s0 += 8) {     // worlds above eight: the rest, eight at a time
@@ -395,8 +397,7 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
               float c[GROUP];
               unpack8f<BITS>(pk[u], c);
 #pragma unroll
-              for (int i = 0; i < GROUP; ++i)
-                acc[i] = __fadd_rn(acc[i], __fmul_rn(c[i], sc[u]));
+              for (int i = 0; i < GROUP; ++i) acc[i] = __fmaf_rn(c[i], sc[u], acc[i]);
             }
           }
         }
@@ -417,18 +418,17 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
       const __half sh = scale_from_absmax<BITS>(m);
       const float sf = __half2float(sh);
       if (!live) return;
-      int q[GROUP];
       const uint32_t idx2 = (uint32_t)((long long)p.rank * p.S + off);
+      Packed8<BITS> pk;
+      float d[GROUP];
       if (ef2) {
-        float d[GROUP];
-        quant8_dq<BITS, SR>(acc, sf, p.key2, idx2, q, d);
+        pk = quant8_packed<BITS, SR, true>(acc, m, sf, p.key2, idx2, d);
 #pragma unroll
         for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(acc[i], d[i]);
         store_vals<float, ALIGNED>(p.res2, off, lim, d);
       } else {
-        quant8<BITS, SR>(acc, sf, p.key2, idx2, q);
+        pk = quant8_packed<BITS, SR, false>(acc, m, sf, p.key2, idx2, d);
       }
-      const Packed8<BITS> pk = pack8<BITS>(q);
       if constexpr (MC) {
         static_assert(BITS == 4 || BITS == 8, "multimem path: whole-word groups only");
         const size_t slot_off = BCOM_CONTROL_BYTES + p.region_bytes + (size_t)p.rank * p.slot_stride;
