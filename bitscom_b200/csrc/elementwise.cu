@@ -294,87 +294,86 @@ layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
   }
 }
 
-// g = dy * w; dx = rstd * (g - mean(g) - xhat * mean(g * xhat));
-// dw += sum_rows dy * xhat, db += sum_rows dy: every warp keeps partials in registers, the
-// CTA's warps fold them through shared memory and the CTA writes one [dw | db] row of
-// `partials` ([gridDim.x][2 * H] fp32) that colsum_add_kernel folds into dw and db (2 * H
-// atomics per WARP on the same addresses used to dominate this kernel).
-template <int MAX_ITERS>
-__global__ void __launch_bounds__(256)
-layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
-                     const bf16* __restrict__ w, const float* __restrict__ mean,
-                     const float* __restrict__ rstd, bf16* __restrict__ dx,
-                     float* __restrict__ partials, int rows, int H) {
-  __shared__ float fold[2 * 1024];
-  const int lane = threadIdx.x & 31;
-  const int warps_per_cta = blockDim.x >> 5;
-  float aw[MAX_ITERS][8], ab[MAX_ITERS][8], fw[MAX_ITERS][8];
+// LayerNorm backward, one row per CTA pass (H <= 1024: at most 128 threads, thread t owns
+// columns [8t, 8t + 8)).  Same shape as rmsnorm_bwd_kernel: the next row's x and dy are
+// requested before the current row's reduction, the two row sums cost one barrier (warp
+// partials in a double-buffered scratch), dw / db partials stay in registers and leave as one
+// [dw | db] row of `partials` per CTA.  Against the one-warp-per-row kernel it keeps 16 x
+// fewer values per thread (40 instead of 160 registers of row state), so sixteen CTAs fit an
+// SM and a row's latency chain is an eighth as long.
+__global__ void __launch_bounds__(128)
+layernorm_bwd_row_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                         const bf16* __restrict__ w, const float* __restrict__ mean,
+                         const float* __restrict__ rstd, bf16* __restrict__ dx,
+                         float* __restrict__ partials, int rows, int H) {
+  __shared__ float partial[2][2][4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int c = threadIdx.x * 8;
+  const bool live = c < H;
+  float aw[8], ab[8], fw[8];
 #pragma unroll
-  for (int k = 0; k < MAX_ITERS; ++k) {
-    const int c = (lane + k * 32) * 8;
-    if (c < H) load8(w + c, fw[k]);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) aw[k][i] = ab[k][i] = 0.0f;
-  }
-  for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows;
-       row += gridDim.x * warps_per_cta) {
-    const bf16* xr = x + (size_t)row * H;
-    const bf16* gr = dy + (size_t)row * H;
+  for (int i = 0; i < 8; ++i) aw[i] = ab[i] = fw[i] = 0.0f;
+  if (live) load8(w + c, fw);
+  Bf8 cx, cg, nx, ng;
+  auto fetch = [&](int row, Bf8& bx, Bf8& bg) {
+    if (live) {
+      bx = *reinterpret_cast<const Bf8*>(x + (size_t)row * H + c);
+      bg = *reinterpret_cast<const Bf8*>(dy + (size_t)row * H + c);
+    }
+  };
+  int row = blockIdx.x;
+  if (row < rows) fetch(row, cx, cg);
+  int parity = 0;
+  const float inv_h = 1.0f / (float)H;
+  for (; row < rows; row += gridDim.x, parity ^= 1) {
+    const int next = row + gridDim.x;
+    if (next < rows) fetch(next, nx, ng);
     const float mu = mean[row], rs = rstd[row];
-    float xh[MAX_ITERS][8], g[MAX_ITERS][8];
+    float xh[8], g[8];
     float s1 = 0.0f, s2 = 0.0f;
-#pragma unroll
-    for (int k = 0; k < MAX_ITERS; ++k) {
-      const int c = (lane + k * 32) * 8;
-      if (c < H) {
-        float fx[8], fg[8];
-        load8(xr + c, fx);
-        load8(gr + c, fg);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          xh[k][i] = (fx[i] - mu) * rs;
-          g[k][i] = fg[i] * fw[k][i];
-          s1 += g[k][i];
-          s2 += g[k][i] * xh[k][i];
-          aw[k][i] += fg[i] * xh[k][i];
-          ab[k][i] += fg[i];
-        }
-      }
-    }
-    s1 = warp_sum(s1) / (float)H;
-    s2 = warp_sum(s2) / (float)H;
-    bf16* dr = dx + (size_t)row * H;
-#pragma unroll
-    for (int k = 0; k < MAX_ITERS; ++k) {
-      const int c = (lane + k * 32) * 8;
-      if (c < H) {
-        float o[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = rs * (g[k][i] - s1 - xh[k][i] * s2);
-        store8(dr + c, o);
-      }
-    }
-  }
-  // fold[j * (H / 8) + pack] holds element j of a pack: the lanes of a warp then hit
-  // consecutive words (element-major order would put them 8 words apart, on 4 banks)
-  const int packs = H / 8;
-  for (int c = threadIdx.x; c < 2 * H; c += blockDim.x) fold[c] = 0.0f;
-  __syncthreads();
-#pragma unroll
-  for (int k = 0; k < MAX_ITERS; ++k) {
-    const int pack = lane + k * 32;
-    if (pack < packs) {
+    if (live) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        atomicAdd(fold + i * packs + pack, aw[k][i]);       // 8 warps per address
-        atomicAdd(fold + H + i * packs + pack, ab[k][i]);
+        const float fx = __bfloat162float(cx.v[i]), fg = __bfloat162float(cg.v[i]);
+        xh[i] = (fx - mu) * rs;
+        g[i] = fg * fw[i];
+        s1 += g[i];
+        s2 += g[i] * xh[i];
+        aw[i] += fg * xh[i];
+        ab[i] += fg;
       }
     }
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane == 0) {
+      partial[parity][0][warp] = s1;
+      partial[parity][1][warp] = s2;
+    }
+    __syncthreads();  // the other buffer is free again: its readers passed the previous barrier
+    float t1 = 0.0f, t2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      t1 += i < nwarps ? partial[parity][0][i] : 0.0f;
+      t2 += i < nwarps ? partial[parity][1][i] : 0.0f;
+    }
+    t1 *= inv_h;
+    t2 *= inv_h;
+    if (live) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = rs * (g[i] - t1 - xh[i] * t2);
+      store8(dx + (size_t)row * H + c, o);
+      cx = nx;
+      cg = ng;
+    }
   }
-  __syncthreads();
-  for (int c = threadIdx.x; c < 2 * H; c += blockDim.x) {
-    const int half = c >= H, cc = c - half * H;              // column cc of dw (0) or db (1)
-    partials[(size_t)blockIdx.x * 2 * H + c] = fold[half * H + (cc & 7) * packs + (cc >> 3)];
+  if (live) {
+    float* dst = partials + (size_t)blockIdx.x * 2 * H + c;
+    *reinterpret_cast<float4*>(dst) = make_float4(aw[0], aw[1], aw[2], aw[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(aw[4], aw[5], aw[6], aw[7]);
+    *reinterpret_cast<float4*>(dst + H) = make_float4(ab[0], ab[1], ab[2], ab[3]);
+    *reinterpret_cast<float4*>(dst + H + 4) = make_float4(ab[4], ab[5], ab[6], ab[7]);
   }
 }
 
@@ -809,18 +808,12 @@ int bcom_layernorm_bwd(const void* dy, const void* x, const void* w, const void*
                        int rows, int H, void* stream) {
   if (rows <= 0) return 0;
   if (H % 8 || H > 1024) return (int)cudaErrorInvalidValue;
-  const int warps = 8;
-  const int want = (rows + warps - 1) / warps;
-  const int grid = want < kLnBwdMaxCtas ? want : kLnBwdMaxCtas;
+  const int grid = rows < kLnBwdMaxCtas ? rows : kLnBwdMaxCtas;
+  const int threads = ((H / 8 + 31) / 32) * 32;
   cudaStream_t st = (cudaStream_t)stream;
-  const int iters = (H / 8 + 31) / 32;
-#define BCOM_LN_BWD(N)                                                                        \
-  layernorm_bwd_kernel<N><<<grid, warps * 32, 0, st>>>(                                        \
-      (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean, (const float*)rstd, \
-      (bf16*)dx, (float*)partials, rows, H)
-  if (iters <= 2) BCOM_LN_BWD(2);
-  else BCOM_LN_BWD(4);
-#undef BCOM_LN_BWD
+  layernorm_bwd_row_kernel<<<grid, threads, 0, st>>>(
+      (const bf16*)dy, (const bf16*)x, (const bf16*)w, (const float*)mean, (const float*)rstd,
+      (bf16*)dx, (float*)partials, rows, H);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return (int)err;
   // a partial row is [dw | db]

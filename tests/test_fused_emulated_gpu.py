@@ -120,6 +120,27 @@ def test_reduce_scatter_and_all_gather(make_world, bits):
             assert torch.equal(fulls[r].cpu(), want_full)
 
 
+def test_phase_time_stamps_are_ordered_and_add_up(make_world):
+    """Every rank's first CTA stamps the device timer at its phase boundaries; after a launch
+    the five intervals are non-negative, sum to the total, and a reduce-scatter leaves the
+    third phase empty."""
+    world, n = 4, 1 << 20
+    w = make_world(world, region_bytes=16 << 20)
+    bufs = [t.cuda() for t in _inputs(world, n, torch.float32)]
+    w.all_reduce(bufs, bitwidth=4, block_size=256)
+    torch.cuda.synchronize()
+    for phases in w.phase_times_us():
+        parts = [phases[k] for k in ("phase1", "wait1", "phase2", "wait2", "phase3")]
+        assert all(v >= 0 for v in parts) and phases["phase1"] > 0 and phases["phase3"] > 0
+        assert abs(sum(parts) - phases["total"]) < 1e-3
+        assert phases["total"] < 50_000     # microseconds: a 4 MB bucket, not a timeout
+    outs = [torch.empty(n // world, device="cuda") for _ in range(world)]
+    w.reduce_scatter(outs, bufs, bitwidth=4, block_size=256)
+    torch.cuda.synchronize()
+    # the last two stamps of a reduce-scatter are taken back to back: a timer tick at most
+    assert all(p["phase3"] < 1.0 and p["phase1"] > 0 for p in w.phase_times_us())
+
+
 def test_back_to_back_calls_need_no_barrier(make_world):
     w = make_world(4)
     ins = _inputs(4, 50000, torch.float32, seed=9)
