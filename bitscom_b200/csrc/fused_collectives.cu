@@ -62,6 +62,7 @@ struct RankParams {
   unsigned int key1, key2;
   float post_scale;
   unsigned char* mc;    // NVLink multicast mapping of the symmetric blocks, or null
+  size_t ll_off;        // flag-in-data launches: offset of their slots inside a region
 };
 
 // ---------------------------------------------------------------------------
@@ -520,6 +521,247 @@ __device__ void run_rank(const RankParams& p, int cta, int ncta) {
   stamp(p.status, cta, 5);
 }
 
+// ---------------------------------------------------------------------------
+// small buckets: the flags travel inside the data words
+// ---------------------------------------------------------------------------
+// Below a few megabytes the two flag handshakes of run_rank (fence, CTA arrivals, flag stores,
+// polling: 13-19 us each on NVLink) cost more than the three phases together.  Here every
+// 32-bit word of packed codes, and every fp16 scale, is stored as an 8-byte pair {word, epoch}
+// with ONE store instruction; the consumer polls the pair it needs until its second half shows
+// the epoch of this launch.  An 8-byte aligned store is performed as a whole, so a pair whose
+// epoch matches carries this launch's data: no fence, no arrival counter, no flag array, and a
+// thread starts on a group as soon as THAT group has arrived instead of when all of them have.
+// The slots live in the tail of the two data regions (RankParams::ll_off), which no other
+// kernel writes and which starts out as zeros; epochs are never zero and never repeat.
+// Reuse of a slot by the next launch needs no barrier either: a rank enters launch k + 1 only
+// after its phase 3 of launch k has seen every peer's reduced shard, which a peer produces
+// only after it has read all it needed from its receive slots; and a rank's phase-2 stores of
+// launch k + 1 wait for every peer's phase-1 words of launch k + 1, which a peer sends after
+// its own phase 3 of launch k.
+// The grid is NOT cooperative: no CTA waits for a CTA of its own rank.  It must still be
+// resident as a whole (a CTA that has not started cannot have sent the phase-1 words a peer's
+// resident CTAs are waiting for), so the host caps it at what an empty GPU holds.
+__device__ __forceinline__ void st_pair(void* addr, uint32_t word, uint32_t epoch) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(addr), "r"(word), "r"(epoch)
+               : "memory");
+}
+__device__ __forceinline__ uint2 ld_pair(const void* addr) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(addr)
+               : "memory");
+  return v;
+}
+
+// Waits for `words` pairs starting at `addr`; false when the time budget ran out.
+template <int WORDS>
+__device__ __forceinline__ bool poll_pairs(const unsigned char* addr, uint32_t epoch,
+                                           unsigned long long timeout_ns, uint32_t (&w)[WORDS]) {
+#pragma unroll
+  for (int k = 0; k < WORDS; ++k) {
+    uint2 v = ld_pair(addr + 8 * k);
+    if (v.y != epoch) {
+      const unsigned long long t0 = global_timer_ns();
+      unsigned int spins = 0;
+      while ((v = ld_pair(addr + 8 * k)).y != epoch) {
+        if ((++spins & 255u) == 0u && global_timer_ns() - t0 > timeout_ns) return false;
+      }
+    }
+    w[k] = v.x;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void record_ll_timeout(const RankParams& p, unsigned int code,
+                                                  int peer) {
+  if (atomicCAS(p.status, 0u, code) == 0u) {
+    p.status[1] = code;
+    p.status[2] = (unsigned int)peer;
+    p.status[3] = (unsigned int)p.rank;
+    p.status[4] = 0u;
+    p.status[5] = 0u;
+    p.status[6] = (unsigned int)p.epoch;
+    p.status[7] = (unsigned int)(p.epoch >> 32);
+    __threadfence_system();
+  }
+}
+
+// All-reduce of one rank, whole shard in one launch (p.c0 == 0, p.L == p.S), aligned tensors.
+template <typename T, int BITS, bool SR>
+__device__ void run_rank_ll(const RankParams& p, int cta, int ncta) {
+  static_assert(BITS == 4 || BITS == 8, "flag-in-data path: whole-word groups");
+  constexpr int WORDS = BITS / 4;       // 32-bit words of packed codes per group
+  constexpr int GBYTES = 8 * WORDS;     // bytes of one group's pairs
+  const int tid = threadIdx.x;
+  const int W = p.world;
+  const int lanes = p.lanes_per_block, llog = p.lanes_log2;
+  const int gs = (int)((p.L + GROUP - 1) / GROUP);
+  const int gp = (gs + 31) & ~31;
+  const int gfirst = cta * blockDim.x + tid, gstride = ncta * blockDim.x;
+  const uint32_t epoch = (uint32_t)p.epoch == 0u ? 0x80000000u : (uint32_t)p.epoch;
+  const size_t ll_base = BCOM_CONTROL_BYTES + p.ll_off;
+  const unsigned char* recv = p.peer[p.rank] + ll_base;
+  const unsigned char* gather = recv + p.region_bytes;
+  const T* in = static_cast<const T*>(p.in);
+  T* out = static_cast<T*>(p.out);
+  const bool ef = p.res1 != nullptr, ef2 = p.res2 != nullptr;
+  stamp(p.status, cta, 0);
+
+  // ---- phase 1: quantize every destination's shard, send pairs ----
+  for (int k = 0; k < W; ++k) {
+    const int j = (p.rank + k) % W;
+    unsigned char* slot = p.peer[j] + ll_base + (size_t)p.rank * p.slot_stride;
+    const long long base_idx = (long long)j * p.S;
+    const int valid = (int)max(0LL, min(p.L, p.n - base_idx));
+    const T* src = in + base_idx;
+    float* res = ef ? p.res1 + base_idx : nullptr;
+    for (int g = gfirst; g < gp; g += gstride) {
+      const int e0 = g * GROUP;
+      const bool live = g < gs;
+      const int lim = live ? min(max(valid - e0, 0), GROUP) : 0;
+      float v[GROUP], d[GROUP];
+      load_vals<T, true>(src, e0, lim, v);
+      if (ef) {
+        load_vals<float, true>(res, e0, lim, d);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) v[i] = __fadd_rn(v[i], d[i]);
+      }
+      const float m = block_absmax(absmax8(v), lanes);
+      const __half sh = scale_from_absmax<BITS>(m);
+      const float sf = __half2float(sh);
+      if (!live) continue;
+      Packed8<BITS> pk;
+      const uint32_t idx = (uint32_t)base_idx + (uint32_t)e0;
+      if (ef) {
+        pk = quant8_packed<BITS, SR, true>(v, m, sf, p.key1, idx, d);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(v[i], d[i]);
+        store_vals<float, true>(res, e0, lim, d);
+      } else {
+        pk = quant8_packed<BITS, SR, false>(v, m, sf, p.key1, idx, d);
+      }
+#pragma unroll
+      for (int q = 0; q < WORDS; ++q) st_pair(slot + (size_t)g * GBYTES + 8 * q, pk.w[q], epoch);
+      if ((g & (lanes - 1)) == 0)
+        st_pair(slot + p.scale_off + (size_t)(g >> llog) * 8, (uint32_t)__half_as_ushort(sh), epoch);
+    }
+  }
+  stamp(p.status, cta, 1);
+  stamp(p.status, cta, 2);
+
+  // ---- phase 2: own shard: wait for each group's W sources, reduce, re-quantize, send ----
+  for (int g = gfirst; g < gp; g += gstride) {
+    const bool live = g < gs;
+    const long long off = (long long)g * GROUP;
+    const long long lim = live ? min(p.L - off, (long long)GROUP) : 0;
+    float acc[GROUP], d[GROUP];
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) acc[i] = 0.0f;
+    if (ef2) load_vals<float, true>(p.res2, off, lim, d);
+    bool ok = true;
+    int late = 0;
+    if (live) {
+      for (int s = 0; s < W && ok; ++s) {   // ascending source order: part of the wire contract
+        const unsigned char* slot = recv + (size_t)s * p.slot_stride;
+        uint32_t w[WORDS], sw[1];
+        ok = poll_pairs<WORDS>(slot + (size_t)g * GBYTES, epoch, p.timeout_ns, w) &&
+             poll_pairs<1>(slot + p.scale_off + (size_t)(g >> llog) * 8, epoch, p.timeout_ns, sw);
+        late = s;
+        Packed8<BITS> pk;
+#pragma unroll
+        for (int q = 0; q < WORDS; ++q) pk.w[q] = w[q];
+        const float sc = __half2float(__ushort_as_half((unsigned short)sw[0]));
+        float c[GROUP];
+        unpack8f<BITS>(pk, c);
+#pragma unroll
+        for (int i = 0; i < GROUP; ++i) acc[i] = __fmaf_rn(c[i], sc, acc[i]);  // exact product
+      }
+    }
+    if (__any_sync(0xffffffffu, !ok)) {   // the whole warp leaves together
+      if (!ok) record_ll_timeout(p, BCOM_TIMEOUT_PHASE1_FLAGS, late);
+      return;
+    }
+    if (ef2) {
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) acc[i] = __fadd_rn(acc[i], d[i]);
+    }
+    const float m = block_absmax(absmax8(acc), lanes);
+    const __half sh = scale_from_absmax<BITS>(m);
+    const float sf = __half2float(sh);
+    if (!live) continue;
+    const uint32_t idx2 = (uint32_t)((long long)p.rank * p.S + off);
+    Packed8<BITS> pk;
+    if (ef2) {
+      pk = quant8_packed<BITS, SR, true>(acc, m, sf, p.key2, idx2, d);
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) d[i] = __fsub_rn(acc[i], d[i]);
+      store_vals<float, true>(p.res2, off, lim, d);
+    } else {
+      pk = quant8_packed<BITS, SR, false>(acc, m, sf, p.key2, idx2, d);
+    }
+    for (int k = 0; k < W; ++k) {
+      const int t = (p.rank + k) % W;
+      unsigned char* slot = p.peer[t] + ll_base + p.region_bytes + (size_t)p.rank * p.slot_stride;
+#pragma unroll
+      for (int q = 0; q < WORDS; ++q) st_pair(slot + (size_t)g * GBYTES + 8 * q, pk.w[q], epoch);
+      if ((g & (lanes - 1)) == 0)
+        st_pair(slot + p.scale_off + (size_t)(g >> llog) * 8, (uint32_t)__half_as_ushort(sh), epoch);
+    }
+  }
+  stamp(p.status, cta, 3);
+  stamp(p.status, cta, 4);
+
+  // ---- phase 3: every shard as it arrives: dequantize into the bucket ----
+  for (int k = 0; k < W; ++k) {
+    const int j = (p.rank + k) % W;
+    const unsigned char* slot = gather + (size_t)j * p.slot_stride;
+    const long long base_idx = (long long)j * p.S;
+    const int valid = (int)max(0LL, min(p.L, p.n - base_idx));
+    T* dst = out + base_idx;
+    for (int g = gfirst; g < gs; g += gstride) {
+      const int e0 = g * GROUP;
+      const int lim = min(valid - e0, GROUP);
+      uint32_t w[WORDS], sw[1];
+      bool ok = true;
+      if (lim > 0)
+        ok = poll_pairs<WORDS>(slot + (size_t)g * GBYTES, epoch, p.timeout_ns, w) &&
+             poll_pairs<1>(slot + p.scale_off + (size_t)(g >> llog) * 8, epoch, p.timeout_ns, sw);
+      if (!ok) {   // nothing below needs the warp as a whole
+        record_ll_timeout(p, BCOM_TIMEOUT_PHASE2_FLAGS, j);
+        return;
+      }
+      if (lim <= 0) continue;
+      Packed8<BITS> pk;
+#pragma unroll
+      for (int q = 0; q < WORDS; ++q) pk.w[q] = w[q];
+      const float sf = __half2float(__ushort_as_half((unsigned short)sw[0]));
+      float y[GROUP];
+      unpack8f<BITS>(pk, y);
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) y[i] = cast_roundtrip<T>(__fmul_rn(y[i], sf), p.post_scale);
+      store_vals<T, true>(dst, e0, lim, y);
+    }
+  }
+  stamp(p.status, cta, 5);
+}
+
+template <typename T, int BITS, bool SR>
+__global__ void __launch_bounds__(kCollThreads, 2)
+lowbit_collective_ll_kernel(const RankParams p) {
+  run_rank_ll<T, BITS, SR>(p, blockIdx.x, gridDim.x);
+}
+
+template <typename T, int BITS, bool SR>
+__global__ void __launch_bounds__(kCollThreads, 2)
+lowbit_collective_ll_emulated_kernel(const RankParams* all, int world) {
+  const int per_rank = gridDim.x / world;
+  const int r = blockIdx.x / per_rank;
+  if (r >= world) return;
+  __shared__ RankParams p;
+  if (threadIdx.x == 0) p = all[r];
+  __syncthreads();
+  run_rank_ll<T, BITS, SR>(p, blockIdx.x - r * per_rank, per_rank);
+}
+
 template <typename T, int BITS, bool SR, bool ALIGNED>
 __global__ void __launch_bounds__(kCollThreads, 2)
 lowbit_collective_kernel(const RankParams p) {
@@ -690,6 +932,7 @@ static void fill_params(const BcomComm* c, const BcomCollArgs& a, long long c0, 
   p->key2 = a.key2;
   p->post_scale = a.post_scale;
   p->mc = c->mc;
+  p->ll_off = 0;
 }
 
 static int ctas_for(const BcomComm* c, const BcomCollArgs& a, long long L, int resident_per_sm) {
@@ -718,6 +961,61 @@ static cudaError_t resident_ctas(const void* kernel, int* out) {
   return err;
 }
 
+
+// ---- flag-in-data path: kernels, layout, when it applies ---------------------------------
+typedef void (*LLEmuKernel)(const RankParams*, int);
+
+template <typename T>
+static bool pick_ll_bits(int bits, bool sr, RealKernel* real, LLEmuKernel* emu) {
+  if (bits == 4) {
+    *real = sr ? lowbit_collective_ll_kernel<T, 4, true> : lowbit_collective_ll_kernel<T, 4, false>;
+    *emu = sr ? lowbit_collective_ll_emulated_kernel<T, 4, true>
+              : lowbit_collective_ll_emulated_kernel<T, 4, false>;
+  } else if (bits == 8) {
+    *real = sr ? lowbit_collective_ll_kernel<T, 8, true> : lowbit_collective_ll_kernel<T, 8, false>;
+    *emu = sr ? lowbit_collective_ll_emulated_kernel<T, 8, true>
+              : lowbit_collective_ll_emulated_kernel<T, 8, false>;
+  } else {
+    return false;
+  }
+  return true;
+}
+
+static bool pick_ll_kernel(int dtype, int bits, bool sr, RealKernel* real, LLEmuKernel* emu) {
+  switch (dtype) {
+    case 0: return pick_ll_bits<float>(bits, sr, real, emu);
+    case 1: return pick_ll_bits<__half>(bits, sr, real, emu);
+    case 2: return pick_ll_bits<__nv_bfloat16>(bits, sr, real, emu);
+    default: return false;
+  }
+}
+
+// one source's slot: 8 bytes per 32-bit word of packed codes, then 8 bytes per block scale
+static SlotLayout ll_slot_layout(long long L, int bits, int block) {
+  const long long groups = ((L + GROUP - 1) / GROUP + 31) & ~31LL;
+  SlotLayout s;
+  s.scale_off = bcom_align_up((size_t)groups * 2 * bits, 256);
+  s.stride = s.scale_off + bcom_align_up((size_t)((L + block - 1) / block + 32) * 8, 256);
+  return s;
+}
+
+// all-reduce of an aligned tensor that is small enough for one flag-in-data launch
+static bool ll_applies(const BcomComm* c, const BcomCollArgs& a) {
+  if (a.mode != BCOM_MODE_ALL_REDUCE || (a.bits != 4 && a.bits != 8) || !is_aligned(a)) return false;
+  if (c->ll_bytes == 0 || c->ll_max_payload <= 0) return false;
+  if (a.n * elem_size(a.dtype) > c->ll_max_payload) return false;
+  return (size_t)c->world * ll_slot_layout(a.S, a.bits, a.block).stride <= c->ll_bytes;
+}
+
+static void fill_ll_params(const BcomComm* c, const BcomCollArgs& a, unsigned long long epoch,
+                           RankParams* p) {
+  fill_params(c, a, 0, a.S, epoch, p);
+  const SlotLayout lay = ll_slot_layout(a.S, a.bits, a.block);
+  p->slot_stride = lay.stride;
+  p->scale_off = lay.scale_off;
+  p->ll_off = c->region_bytes - c->ll_bytes;
+}
+
 }  // namespace bcom
 
 using namespace bcom;
@@ -732,7 +1030,7 @@ int bcom_collective_supported(int dtype, int bits, int block) {
 
 long long bcom_comm_max_chunk(BcomComm* c, int bits, int block) {
   if (!c || !block_ok(block)) return 0;
-  return max_chunk(c->region_bytes, c->world, bits, block);
+  return max_chunk(c->region_bytes - c->ll_bytes, c->world, bits, block);
 }
 
 int bcom_collective(BcomComm* c, const BcomCollArgs* args, void* stream) {
@@ -740,6 +1038,21 @@ int bcom_collective(BcomComm* c, const BcomCollArgs* args, void* stream) {
   if (int err = validate(c, a)) return err;
   RealKernel kernel;
   EmuKernel unused;
+  if (ll_applies(c, a)) {
+    LLEmuKernel unused_emu;
+    if (!pick_ll_kernel(a.dtype, a.bits, a.stochastic != 0, &kernel, &unused_emu))
+      return (int)cudaErrorNotSupported;
+    int resident = 0;
+    cudaError_t err = resident_ctas((const void*)kernel, &resident);
+    if (err != cudaSuccess) return (int)err;
+    if (resident < 1) return (int)cudaErrorLaunchOutOfResources;
+    RankParams p;
+    fill_ll_params(c, a, ++c->epoch, &p);
+    // an ordinary launch: no CTA waits for a CTA of its own rank; the grid is capped at what an
+    // empty GPU holds (ctas_for) because the peers wait for words of CTAs that must have started
+    kernel<<<ctas_for(c, a, a.S, resident), kCollThreads, 0, (cudaStream_t)stream>>>(p);
+    return (int)cudaGetLastError();
+  }
   if (!pick_kernel(a.dtype, a.bits, a.stochastic != 0, is_aligned(a), &kernel, &unused))
     return (int)cudaErrorNotSupported;
   // with a multicast mapping, the modes that have an all-gather half use the multimem kernel
@@ -751,7 +1064,7 @@ int bcom_collective(BcomComm* c, const BcomCollArgs* args, void* stream) {
   cudaError_t err = resident_ctas((const void*)kernel, &resident);
   if (err != cudaSuccess) return (int)err;
   if (resident < 1) return (int)cudaErrorLaunchOutOfResources;
-  long long Lmax = max_chunk(c->region_bytes, c->world, a.bits, a.block);
+  long long Lmax = max_chunk(c->region_bytes - c->ll_bytes, c->world, a.bits, a.block);
   if (Lmax <= 0) return (int)cudaErrorMemoryAllocation;
   Lmax = Lmax / a.block * a.block;  // chunks start on quantization-block boundaries
   if (Lmax <= 0) return (int)cudaErrorMemoryAllocation;
@@ -777,6 +1090,42 @@ int bcom_collective_emulated(BcomComm** comms, const BcomCollArgs* args, int wor
   for (int r = 0; r < world; ++r) aligned = aligned && is_aligned(args[r]);
   RealKernel unused;
   EmuKernel kernel;
+  bool ll = true;
+  for (int r = 0; r < world; ++r) ll = ll && ll_applies(comms[r], args[r]);
+  if (ll) {
+    LLEmuKernel ll_kernel;
+    if (!pick_ll_kernel(a0.dtype, a0.bits, a0.stochastic != 0, &unused, &ll_kernel))
+      return (int)cudaErrorNotSupported;
+    int resident = 0;
+    cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+        &resident, (const void*)ll_kernel, kCollThreads, 0);
+    if (err != cudaSuccess) return (int)err;
+    if (resident < 1) return (int)cudaErrorLaunchOutOfResources;
+    RankParams host[BCOM_MAX_WORLD];
+    for (int r = 0; r < world; ++r) fill_ll_params(comms[r], args[r], ++comms[r]->epoch, &host[r]);
+    RankParams* dev_params = nullptr;
+    err = cudaMallocAsync((void**)&dev_params, sizeof(RankParams) * world, (cudaStream_t)stream);
+    if (err != cudaSuccess) return (int)err;
+    err = cudaMemcpyAsync(dev_params, host, sizeof(RankParams) * world, cudaMemcpyHostToDevice,
+                          (cudaStream_t)stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize((cudaStream_t)stream);
+    if (err == cudaSuccess) {
+      int per_rank = ctas_for(comms[0], a0, a0.S, resident);
+      const int cap = comms[0]->sm_count * resident / world;
+      if (per_rank > cap) per_rank = cap;
+      if (per_rank < 1) {
+        err = cudaErrorLaunchOutOfResources;
+      } else {
+        int w = world;
+        void* kargs[] = {&dev_params, &w};
+        // all emulated ranks share this GPU: cooperative, so that every rank's CTAs are resident
+        err = cudaLaunchCooperativeKernel((const void*)ll_kernel, dim3(per_rank * world),
+                                          dim3(kCollThreads), kargs, 0, (cudaStream_t)stream);
+      }
+    }
+    cudaFreeAsync(dev_params, (cudaStream_t)stream);
+    return (int)err;
+  }
   if (!pick_kernel(a0.dtype, a0.bits, a0.stochastic != 0, aligned, &unused, &kernel))
     return (int)cudaErrorNotSupported;
   int resident = 0;
@@ -785,7 +1134,7 @@ int bcom_collective_emulated(BcomComm** comms, const BcomCollArgs* args, int wor
   if (err != cudaSuccess) return (int)err;
   if (resident < 1) return (int)cudaErrorLaunchOutOfResources;
   BcomComm* c0comm = comms[0];
-  long long Lmax = max_chunk(c0comm->region_bytes, world, a0.bits, a0.block);
+  long long Lmax = max_chunk(c0comm->region_bytes - c0comm->ll_bytes, world, a0.bits, a0.block);
   Lmax = Lmax / a0.block * a0.block;
   if (Lmax <= 0) return (int)cudaErrorMemoryAllocation;
   RankParams* dev_params = nullptr;

@@ -18,6 +18,12 @@
 static cudaError_t write_canaries(BcomComm* c) {
   cudaError_t err = cudaMemset(c->local + BCOM_CTL_CANARY, BCOM_CANARY_BYTE,
                                BCOM_CONTROL_BYTES - BCOM_CTL_CANARY);
+  // the tail of both data regions only ever holds (data, epoch) words of the flag-in-data
+  // path: it starts out as zeros, and epoch 0 is never used
+  for (int region = 0; region < 2 && err == cudaSuccess; ++region)
+    if (c->ll_bytes)
+      err = cudaMemset(c->local + BCOM_CONTROL_BYTES + (region + 1) * c->region_bytes -
+                           c->ll_bytes, 0, c->ll_bytes);
   if (err == cudaSuccess)
     err = cudaMemset(c->local + BCOM_CONTROL_BYTES + 2 * c->region_bytes, BCOM_CANARY_BYTE,
                      BCOM_GUARD_BYTES);
@@ -37,12 +43,15 @@ int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out) {
   c->region_bytes = bcom_align_up(region_bytes, 4096);
   c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes + BCOM_GUARD_BYTES;
   c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
+  c->ll_bytes = c->region_bytes / 8 / 4096 * 4096;
+  c->ll_max_payload = 8ll << 20;
   cudaError_t err = cudaGetDevice(&c->device);
   if (err == cudaSuccess)
     err = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
   if (err == cudaSuccess) err = cudaMalloc((void**)&c->local, c->total_bytes);
   if (err == cudaSuccess) err = cudaMemset(c->local, 0, BCOM_CONTROL_BYTES);
   if (err == cudaSuccess) err = write_canaries(c);
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();  // peers may write as soon as they map us
   if (err == cudaSuccess)
     err = cudaHostAlloc((void**)&c->status_host, BCOM_STATUS_WORDS * sizeof(unsigned int),
                         cudaHostAllocMapped);
@@ -81,6 +90,8 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
   c->region_bytes = bcom_align_up(region_bytes, 4096);
   c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes + BCOM_GUARD_BYTES;
   c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
+  c->ll_bytes = c->region_bytes / 8 / 4096 * 4096;
+  c->ll_max_payload = 8ll << 20;
   c->local = (unsigned char*)bases[rank];
   c->mc = (unsigned char*)mc_base;
   c->owns_local = false;
@@ -202,6 +213,12 @@ unsigned long long bcom_comm_epoch(BcomComm* c) { return c->epoch; }
 int bcom_comm_set_timeout_ms(BcomComm* c, double ms) {
   if (ms <= 0) return (int)cudaErrorInvalidValue;
   c->timeout_ns = (unsigned long long)(ms * 1.0e6);
+  return 0;
+}
+
+int bcom_comm_set_ll_max_bytes(BcomComm* c, long long bytes) {
+  if (bytes < 0) return (int)cudaErrorInvalidValue;
+  c->ll_max_payload = bytes;
   return 0;
 }
 

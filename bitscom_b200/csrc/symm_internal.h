@@ -21,6 +21,8 @@ struct BcomComm {
   unsigned long long epoch;     // collective launches so far (same on every rank)
   unsigned long long timeout_ns;
   int sm_count;
+  size_t ll_bytes;              // tail of each data region kept for flag-in-data launches
+  long long ll_max_payload;     // largest tensor (bytes) that takes that path; 0 = never
 };
 
 // control page layout (byte offsets inside the block)

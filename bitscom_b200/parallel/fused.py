@@ -83,6 +83,7 @@ def _get():
             lib.bcom_comm_phase_times.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong * 6)]
             lib.bcom_comm_reset.argtypes = [vp, vp]
             lib.bcom_comm_set_timeout_ms.argtypes = [vp, ctypes.c_double]
+            lib.bcom_comm_set_ll_max_bytes.argtypes = [vp, ctypes.c_longlong]
             lib.bcom_comm_epoch.argtypes = [vp]
             lib.bcom_comm_epoch.restype = ctypes.c_ulonglong
             lib.bcom_collective.argtypes = [vp, ctypes.POINTER(CollArgs), vp]
@@ -275,6 +276,10 @@ class FusedLowBitComm:
             self.native.open_peers(handles)
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle,
                                                  timeout_ms or default_timeout_ms())
+        # BITSCOM_LL_MAX_MB: largest all-reduce (MiB of the tensor) that runs as one
+        # flag-in-data launch; unset: the library's default (8), 0: never
+        if os.environ.get("BITSCOM_LL_MAX_MB", "").strip():
+            self.set_ll_max_bytes(int(float(os.environ["BITSCOM_LL_MAX_MB"]) * (1 << 20)))
         self.side_stream = torch.cuda.Stream(device=self.device)
         self.max_ctas = int(os.environ.get("BITSCOM_MAX_CTAS", "0"))
         self.launches = 0
@@ -390,6 +395,13 @@ class FusedLowBitComm:
     def set_timeout_ms(self, ms: float) -> None:
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle, float(ms))
 
+    def set_ll_max_bytes(self, nbytes: int) -> None:
+        """All-reduces of at most ``nbytes`` (4- or 8-bit codes, aligned tensors) run as ONE
+        pass whose packed words carry their own arrival flags instead of as three phases with
+        two flag handshakes; 0 switches that off.  Every rank of the group must use the same
+        value (the two forms do not talk to each other)."""
+        self.native.lib.bcom_comm_set_ll_max_bytes(self.native.handle, int(nbytes))
+
     def phase_times_us(self) -> dict:
         """Phase breakdown of this rank's last kernel (see ``_NativeComm.phase_times_us``);
         synchronises the device first."""
@@ -498,7 +510,9 @@ class EmulatedWorld:
     """W ranks on one device, run by one cooperative kernel launch per chunk."""
 
     def __init__(self, world: int, device="cuda:0", region_bytes: int = 8 << 20,
-                 timeout_ms: float = 2000.0):
+                 timeout_ms: float = 2000.0, ll_max_bytes: Optional[int] = None):
+        """``ll_max_bytes``: largest all-reduce (bytes of the tensor) that runs as one
+        flag-in-data launch (``None``: the library's default, 8 MiB; 0: never)."""
         self.world = world
         self.device = torch.device(device)
         self.comms = [_NativeComm(r, world, region_bytes, self.device) for r in range(world)]
@@ -508,6 +522,8 @@ class EmulatedWorld:
                 if a is not b:
                     lib.bcom_comm_set_peer(a.handle, b.rank, lib.bcom_comm_local_base(b.handle))
             lib.bcom_comm_set_timeout_ms(a.handle, float(timeout_ms))
+            if ll_max_bytes is not None:
+                lib.bcom_comm_set_ll_max_bytes(a.handle, int(ll_max_bytes))
         self.lib = lib
 
     def close(self):

@@ -18,12 +18,17 @@ def _inputs(world, n, dtype, scale=1e-2, seed=0):
     return [(torch.randn(n, generator=g) * scale).to(dtype) for _ in range(world)]
 
 
-@pytest.fixture
-def make_world():
+@pytest.fixture(params=["three-phase", "flag-in-data"])
+def make_world(request):
+    """Every test runs twice: with the small-bucket form (packed words that carry their own
+    arrival flags, taken by 4- and 8-bit all-reduces that fit its slots) switched off, and with
+    the library's default threshold."""
     worlds = []
+    ll_max_bytes = 0 if request.param == "three-phase" else None
 
     def make(world, region_bytes=8 << 20, timeout_ms=5000.0):
-        w = fused.EmulatedWorld(world, "cuda:0", region_bytes, timeout_ms)
+        w = fused.EmulatedWorld(world, "cuda:0", region_bytes, timeout_ms,
+                                ll_max_bytes=ll_max_bytes)
         worlds.append(w)
         return w
 

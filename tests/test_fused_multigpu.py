@@ -94,30 +94,53 @@ def _worker(rank, world, folder, n, bits, dtype, iters):
         assert rel < {2: 2.5, 4: 0.5}[bits], rel
 
 
+# "three-phase": the small-bucket form (packed words that carry their own arrival flags) is
+# switched off, so the 4 MB fp32 case runs through the three phases and their two flag
+# handshakes; "default": it takes the small-bucket form.  The other case of each test (odd
+# length, or 1- / 2-bit codes) runs through the three phases either way.
+FORMS = [("three-phase", "0"), ("default", "")]
+
+
+def _form(monkeypatch, form):
+    if form[1]:
+        monkeypatch.setenv("BITSCOM_LL_MAX_MB", form[1])
+    else:
+        monkeypatch.delenv("BITSCOM_LL_MAX_MB", raising=False)
+
+
+@pytest.mark.parametrize("form", FORMS, ids=[f[0] for f in FORMS])
 @pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
                                           (2, torch.bfloat16, 300001)])
-def test_two_gpu_all_reduce_bit_exact(bits, dtype, n):
+def test_two_gpu_all_reduce_bit_exact(bits, dtype, n, form, monkeypatch):
     _need(2)
+    if bits != 4 and form[0] == "default":
+        pytest.skip("same path as three-phase for this case")
+    _form(monkeypatch, form)
     _run_with_golden(_worker, 2, n, bits, dtype, 3)
 
 
+@pytest.mark.parametrize("form", FORMS, ids=[f[0] for f in FORMS])
 @pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
                                           (1, torch.bfloat16, 300001)])
-def test_four_gpu_all_reduce_bit_exact(bits, dtype, n):
+def test_four_gpu_all_reduce_bit_exact(bits, dtype, n, form, monkeypatch):
     _need(4)
+    if bits != 4 and form[0] == "default":
+        pytest.skip("same path as three-phase for this case")
+    _form(monkeypatch, form)
     _run_with_golden(_worker, 4, n, bits, dtype, 3)
 
 
+@pytest.mark.parametrize("form", FORMS, ids=[f[0] for f in FORMS])
 @pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
                                           (4, torch.bfloat16, 3000001)])
-def test_eight_gpu_all_reduce_bit_exact(bits, dtype, n):
+def test_eight_gpu_all_reduce_bit_exact(bits, dtype, n, form, monkeypatch):
     _need(8)
+    if n % 8 and form[0] == "default":
+        pytest.skip("same path as three-phase for this case")
+    _form(monkeypatch, form)
     _run_with_golden(_worker, 8, n, bits, dtype, 3)
 
 
-@pytest.mark.skipif(os.environ.get("BITSCOM_EXPERIMENTAL", "0") != "1",
-                    reason="the NVLS (multimem) path has not been run on GPUs yet; "
-                           "set BITSCOM_EXPERIMENTAL=1 to try it")
 @pytest.mark.parametrize("world", [2, 8])
 @pytest.mark.parametrize("bits,dtype,n", [(4, torch.float32, 1 << 20),
                                           (8, torch.bfloat16, 300032)])
@@ -128,6 +151,7 @@ def test_all_reduce_bit_exact_over_nvls(world, bits, dtype, n, monkeypatch):
     _need(world)
     monkeypatch.setenv("BITSCOM_NVLS", "1")
     monkeypatch.setenv("BITSCOM_REQUIRE_NVLS", "1")
+    monkeypatch.setenv("BITSCOM_LL_MAX_MB", "0")   # small buckets would bypass the multimem stores
     _run_with_golden(_worker8 if bits == 8 else _worker, world, n, bits, dtype, 3,
                      stochastic=bits != 8)
 
