@@ -116,7 +116,8 @@ void* bcom_comm_status_host(BcomComm* comm);
 int bcom_comm_reset(BcomComm* comm, void* stream);
 int bcom_comm_set_timeout_ms(BcomComm* comm, double ms);
 // Largest all-reduce (bytes of the tensor) that runs as ONE pass with the flags inside the data
-// words (see fused_collectives.cu, "small buckets"); 0 switches that path off.  Default 8 MiB.
+// words (see fused_collectives.cu, "small buckets"); 0 switches that path off.  Default 32 MiB
+// (the slots must also fit the tail of the regions that is kept for them: an eighth of each).
 int bcom_comm_set_ll_max_bytes(BcomComm* comm, long long bytes);
 unsigned long long bcom_comm_epoch(BcomComm* comm);
 

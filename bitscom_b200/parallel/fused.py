@@ -277,7 +277,7 @@ class FusedLowBitComm:
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle,
                                                  timeout_ms or default_timeout_ms())
         # BITSCOM_LL_MAX_MB: largest all-reduce (MiB of the tensor) that runs as one
-        # flag-in-data launch; unset: the library's default (8), 0: never
+        # flag-in-data launch; unset: the library's default (32), 0: never
         if os.environ.get("BITSCOM_LL_MAX_MB", "").strip():
             self.set_ll_max_bytes(int(float(os.environ["BITSCOM_LL_MAX_MB"]) * (1 << 20)))
         self.side_stream = torch.cuda.Stream(device=self.device)
@@ -512,7 +512,7 @@ class EmulatedWorld:
     def __init__(self, world: int, device="cuda:0", region_bytes: int = 8 << 20,
                  timeout_ms: float = 2000.0, ll_max_bytes: Optional[int] = None):
         """``ll_max_bytes``: largest all-reduce (bytes of the tensor) that runs as one
-        flag-in-data launch (``None``: the library's default, 8 MiB; 0: never)."""
+        flag-in-data launch (``None``: the library's default, 32 MiB; 0: never)."""
         self.world = world
         self.device = torch.device(device)
         self.comms = [_NativeComm(r, world, region_bytes, self.device) for r in range(world)]
