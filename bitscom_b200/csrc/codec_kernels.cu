@@ -212,7 +212,16 @@ __global__ void __launch_bounds__(kThreads)
 absmax_kernel(const T* __restrict__ x, long long n, unsigned int* __restrict__ absmax_bits) {
   float m = 0.0f;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  // whole 8-element groups as one vector access when the tensor is aligned for it
+  const uintptr_t mask = sizeof(T) == 4 ? 31 : 15;
+  const long long groups = (reinterpret_cast<uintptr_t>(x) & mask) == 0 ? n / GROUP : 0;
+  for (long long g = tid; g < groups; g += stride) {
+    float v[GROUP];
+    load8_vec(x + g * GROUP, v);
+    m = max_nan(m, absmax8(v));
+  }
+  for (long long i = groups * GROUP + tid; i < n; i += stride)
     m = max_nan(m, fabsf(Elem<T>::to_f(x[i])));
   m = block_absmax(m, 32);
   __shared__ float part[kThreads / 32];
@@ -236,8 +245,9 @@ quantize_per_tensor_kernel(const T* __restrict__ x, long long n,
   const float scale = peak != 0.0f ? __fdiv_rn(peak, (float)Range<BITS>::qmax) : 1.0f;
   if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const float r = __fdiv_rn(Elem<T>::to_f(x[i]), scale);
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  auto code = [&](float xv, long long i) -> int16_t {
+    const float r = __fdiv_rn(xv, scale);
     float v;
     if constexpr (SR) {
       const float lo = floorf(r);
@@ -247,15 +257,43 @@ quantize_per_tensor_kernel(const T* __restrict__ x, long long n,
       v = rintf(r);
     }
     const float c = fminf(fmaxf(v, (float)Range<BITS>::qmin), (float)Range<BITS>::qmax);
-    q[i] = (v != v) ? (int16_t)0 : (int16_t)(int)c;
+    return (v != v) ? (int16_t)0 : (int16_t)(int)c;
+  };
+  // whole 8-element groups: one vector load, one 16-byte store of the codes
+  const uintptr_t mask = sizeof(T) == 4 ? 31 : 15;
+  const bool vec = (reinterpret_cast<uintptr_t>(x) & mask) == 0 &&
+                   (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+  const long long groups = vec ? n / GROUP : 0;
+  for (long long g = tid; g < groups; g += stride) {
+    float v[GROUP];
+    load8_vec(x + g * GROUP, v);
+    uint4 raw;
+    int16_t* h = reinterpret_cast<int16_t*>(&raw);
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) h[i] = code(v[i], g * GROUP + i);
+    *reinterpret_cast<uint4*>(q + g * GROUP) = raw;
   }
+  for (long long i = groups * GROUP + tid; i < n; i += stride)
+    q[i] = code(Elem<T>::to_f(x[i]), i);
 }
 
 __global__ void __launch_bounds__(kThreads)
 dequantize_per_tensor_kernel(const int16_t* __restrict__ q, long long n, float scale,
                              float* __restrict__ out) {
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool vec = (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) & 31) == 0;
+  const long long groups = vec ? n / GROUP : 0;
+  for (long long g = tid; g < groups; g += stride) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(q + g * GROUP));
+    const int16_t* h = reinterpret_cast<const int16_t*>(&raw);
+    float y[GROUP];
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) y[i] = __fmul_rn((float)h[i], scale);
+    store8_vec(out + g * GROUP, y);
+  }
+  for (long long i = groups * GROUP + tid; i < n; i += stride)
     out[i] = __fmul_rn((float)q[i], scale);
 }
 
@@ -265,13 +303,21 @@ dequantize_per_tensor_kernel(const int16_t* __restrict__ q, long long n, float s
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
 pack_kernel(const int16_t* __restrict__ q, long long n, uint8_t* __restrict__ packed) {
+  const bool vec16 = (reinterpret_cast<uintptr_t>(q) & 15) == 0;
   const long long groups = (n + GROUP - 1) / GROUP;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += stride) {
     const long long base = g * GROUP;
     int v[GROUP];
+    if (base + GROUP <= n && vec16) {   // eight codes as one 16-byte load
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(q + base));
+      const int16_t* h = reinterpret_cast<const int16_t*>(&raw);
 #pragma unroll
-    for (int i = 0; i < GROUP; ++i) v[i] = base + i < n ? (int)q[base + i] : Range<BITS>::qmin;
+      for (int i = 0; i < GROUP; ++i) v[i] = (int)h[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) v[i] = base + i < n ? (int)q[base + i] : Range<BITS>::qmin;
+    }
     const Packed8<BITS> p = pack8<BITS>(v);
     if (base + GROUP <= n) {
       store_group<BITS>(packed, g, p);
@@ -284,6 +330,7 @@ pack_kernel(const int16_t* __restrict__ q, long long n, uint8_t* __restrict__ pa
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
 unpack_kernel(const uint8_t* __restrict__ packed, long long n, int16_t* __restrict__ q) {
+  const bool vec16 = (reinterpret_cast<uintptr_t>(q) & 15) == 0;
   const long long groups = (n + GROUP - 1) / GROUP;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += stride) {
@@ -294,9 +341,17 @@ unpack_kernel(const uint8_t* __restrict__ packed, long long n, int16_t* __restri
                                                           (int)packed_nbytes(n - base, BITS));
     int v[GROUP];
     unpack8<BITS>(p, v);
+    if (full && vec16) {   // eight codes as one 16-byte store
+      uint4 raw;
+      int16_t* h = reinterpret_cast<int16_t*>(&raw);
 #pragma unroll
-    for (int i = 0; i < GROUP; ++i)
-      if (base + i < n) q[base + i] = (int16_t)v[i];
+      for (int i = 0; i < GROUP; ++i) h[i] = (int16_t)v[i];
+      *reinterpret_cast<uint4*>(q + base) = raw;
+    } else {
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i)
+        if (base + i < n) q[base + i] = (int16_t)v[i];
+    }
   }
 }
 
