@@ -103,7 +103,9 @@ def _flag(name: str) -> bool:
 
 
 def default_region_bytes() -> int:
-    return int(float(os.environ.get("BITSCOM_SYMM_MB", "64")) * (1 << 20))
+    # 128 MiB per region: a 1 GB fp32 bucket at 8 ranks is two launches (three with 64 MiB) and a
+    # Llama-7B layer's gradients at 4 ranks one (two); each launch has a fixed cost of about 60 us
+    return int(float(os.environ.get("BITSCOM_SYMM_MB", "128")) * (1 << 20))
 
 
 def default_timeout_ms() -> float:
