@@ -68,7 +68,6 @@ struct Params {
   long long ldc, ldr;
   int M, N, K;
   int tiles_m, tiles_n;
-  int flags;  // experiment switches of the MMA issuer loop (bcom_gemm2_set_flags)
 };
 
 // Identical layout, at identical shared-memory offsets, in both CTAs of a pair: the MMA and the
@@ -308,14 +307,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         for (int kb = 0; kb < num_kb; ++kb) {
           if (prof) c0 = clock64();
           // the odd CTA's bytes arrive from the other SM: cluster-scope acquire
-          if (!((p.flags & 2) ? tc::mbar_wait(&sh->full[stage], phase, kWaitBudgetNs)
-                              : mbar_wait_cluster(&sh->full[stage], phase, kWaitBudgetNs))) {
+          if (!mbar_wait_cluster(&sh->full[stage], phase, kWaitBudgetNs)) {
             fail(sh, kMmaTimeout);
             ok = false;
             break;
           }
           if (prof) { t_full += clock64() - c0; ++n_kb; }
-          if (!(p.flags & 1)) tc::tc_fence_after_sync();
+          tc::tc_fence_after_sync();
           const uint32_t a_addr = tc::smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
@@ -406,7 +404,6 @@ static Kernel pick(bool a_mn, bool b_mn, bool out_f32, bool accum) {
   return b_mn ? pick_out<false, true>(out_f32, accum) : pick_out<false, false>(out_f32, accum);
 }
 
-static int g_flags = 0;
 
 // CTA pairs that can be resident at once (pairs live inside one GPC, so this can be fewer than
 // half the SM count); asked once per kernel.
@@ -441,12 +438,6 @@ static int resident_pairs(const void* kernel) {
 
 extern "C" {
 
-int bcom_gemm2_set_flags(int flags) {
-  const int old = gemm2::g_flags;
-  gemm2::g_flags = flags;
-  return old;
-}
-
 
 // Same contract as bcom_gemm_bf16 (gemm_tcgen05.cu); max_ctas counts CTAs (two per pair).
 int bcom_gemm2_bf16_ex(const void* A, const void* B, void* C, const void* residual, int M, int N,
@@ -468,7 +459,6 @@ int bcom_gemm2_bf16_ex(const void* A, const void* B, void* C, const void* residu
   Kernel kernel = pick(a_mn_major != 0, b_mn_major != 0, out_fp32 != 0, accumulate != 0);
   if (!tc::ensure_dynamic_smem((const void*)kernel, SMEM_BYTES)) return 1005;
   Params p;
-  p.flags = g_flags;
   p.C = C;
   p.R = residual;
   p.ldc = ldc;

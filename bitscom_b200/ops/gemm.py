@@ -57,6 +57,12 @@ def _get2():
     return _lib2 or None
 
 
+def pair_available() -> bool:
+    """True when the CTA-pair kernel's library is part of this installation (it is a library of
+    its own, left out of some deployments) and a GPU is present."""
+    return _native.cuda_present() and _get2() is not None
+
+
 def available() -> bool:
     return _native.cuda_present() and _get() is not None
 
