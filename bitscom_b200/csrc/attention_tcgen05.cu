@@ -916,22 +916,32 @@ attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
   }
 }
 
-// dqkv[:, 0:H] = bf16(dq_acc); dq_acc is left zeroed for the next call
+// dqkv[:, 0:H] = bf16(dq_acc); dq_acc is left zeroed for the next call.  A thread owns one
+// float4 column (blockIdx.x, threadIdx.x) and walks the tokens four at a time with all four
+// loads issued before the first store: one load in flight per thread, and a 64-bit division per
+// element to find its row, made this pass take as long as a quarter of the backward kernel.
 __global__ void __launch_bounds__(256)
 attention_dq_finish_kernel(float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv,
                            long long tokens, int H) {
-  const long long vecs = tokens * (H / 4);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < vecs;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / (H / 4);
-    const int c = (int)(i - t * (H / 4)) * 4;
-    float4* src = reinterpret_cast<float4*>(dq_acc + t * H + c);
-    const float4 v = *src;
-    *src = make_float4(0.f, 0.f, 0.f, 0.f);
-    uint2 o;
-    o.x = pack_bf16(v.x, v.y);
-    o.y = pack_bf16(v.z, v.w);
-    *reinterpret_cast<uint2*>(dqkv + t * 3 * H + c) = o;
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= H / 4) return;
+  const int c = col * 4;
+  constexpr int U = 4;
+  for (long long t0 = (long long)blockIdx.y * U; t0 < tokens; t0 += (long long)gridDim.y * U) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (t0 + u < tokens) v[u] = *reinterpret_cast<const float4*>(dq_acc + (t0 + u) * H + c);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (t0 + u < tokens) {
+        *reinterpret_cast<float4*>(dq_acc + (t0 + u) * H + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        uint2 o;
+        o.x = pack_bf16(v[u].x, v[u].y);
+        o.y = pack_bf16(v[u].z, v[u].w);
+        *reinterpret_cast<uint2*>(dqkv + (t0 + u) * 3 * H + c) = o;
+      }
+    }
   }
 }
 
@@ -1067,7 +1077,14 @@ static int launch_bwd(const void* qkv, const void* out, const void* d_out, const
   const int rc = tma_dq ? launch_bwd_kernel<HD, true>(tm_qkv, tm_do, tm_dq, p, grid, st)
                         : launch_bwd_kernel<HD, false>(tm_qkv, tm_do, tm_dq, p, grid, st);
   if (rc) return rc;
-  attention_dq_finish_kernel<<<148 * 8, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
+  {
+    const int col_blocks = (H / 4 + 255) / 256;
+    long long rows = (tokens + 3) / 4;
+    const long long cap = (148 * 8 + col_blocks - 1) / col_blocks;
+    if (rows > cap) rows = cap;
+    attention_dq_finish_kernel<<<dim3(col_blocks, (unsigned)rows), 256, 0, st>>>(
+        dq_acc, (__nv_bfloat16*)dqkv, tokens, H);
+  }
   return (int)cudaGetLastError();
 }
 
