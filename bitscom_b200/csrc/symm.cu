@@ -44,7 +44,7 @@ int bcom_comm_create(int rank, int world, size_t region_bytes, BcomComm** out) {
   c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes + BCOM_GUARD_BYTES;
   c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
   c->ll_bytes = c->region_bytes / 8 / 4096 * 4096;
-  c->ll_max_payload = 32ll << 20;
+  c->ll_max_payload = 64ll << 20;
   cudaError_t err = cudaGetDevice(&c->device);
   if (err == cudaSuccess)
     err = cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
@@ -91,7 +91,7 @@ int bcom_comm_create_external(int rank, int world, size_t region_bytes, void* co
   c->total_bytes = BCOM_CONTROL_BYTES + 2 * c->region_bytes + BCOM_GUARD_BYTES;
   c->timeout_ns = 30ull * 1000ull * 1000ull * 1000ull;
   c->ll_bytes = c->region_bytes / 8 / 4096 * 4096;
-  c->ll_max_payload = 32ll << 20;
+  c->ll_max_payload = 64ll << 20;
   c->local = (unsigned char*)bases[rank];
   c->mc = (unsigned char*)mc_base;
   c->owns_local = false;

@@ -115,9 +115,10 @@ void* bcom_comm_status_host(BcomComm* comm);
 // clears status, flags stay; zeroes the local arrival counters (after an error)
 int bcom_comm_reset(BcomComm* comm, void* stream);
 int bcom_comm_set_timeout_ms(BcomComm* comm, double ms);
-// Largest all-reduce (bytes of the tensor) that runs as ONE pass with the flags inside the data
-// words (see fused_collectives.cu, "small buckets"); 0 switches that path off.  Default 32 MiB
-// (the slots must also fit the tail of the regions that is kept for them: an eighth of each).
+// Largest all-reduce that runs as ONE pass with the flags inside the data words (see
+// fused_collectives.cu, "small buckets"), in bytes counted at four per element whatever the
+// dtype; 0 switches that path off.  Default 64 MiB = 16 Mi elements (the slots must also fit the
+// tail of the regions that is kept for them: an eighth of each).
 int bcom_comm_set_ll_max_bytes(BcomComm* comm, long long bytes);
 unsigned long long bcom_comm_epoch(BcomComm* comm);
 

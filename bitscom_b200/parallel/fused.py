@@ -103,9 +103,10 @@ def _flag(name: str) -> bool:
 
 
 def default_region_bytes() -> int:
-    # 128 MiB per region: a 1 GB fp32 bucket at 8 ranks is two launches (three with 64 MiB) and a
-    # Llama-7B layer's gradients at 4 ranks one (two); each launch has a fixed cost of about 60 us
-    return int(float(os.environ.get("BITSCOM_SYMM_MB", "128")) * (1 << 20))
+    # 256 MiB per region (an eighth of it is kept for the small-bucket form): a 1 GB fp32 bucket
+    # at 8 ranks is one launch (three with 64 MiB) and a Llama-7B layer's gradients at 4 ranks
+    # one (two); each launch has a fixed cost of about 60 us
+    return int(float(os.environ.get("BITSCOM_SYMM_MB", "256")) * (1 << 20))
 
 
 def default_timeout_ms() -> float:
@@ -279,7 +280,7 @@ class FusedLowBitComm:
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle,
                                                  timeout_ms or default_timeout_ms())
         # BITSCOM_LL_MAX_MB: largest all-reduce (MiB of the tensor) that runs as one
-        # flag-in-data launch; unset: the library's default (32), 0: never
+        # flag-in-data launch, at four bytes per element; unset: the library's default (64), 0: never
         if os.environ.get("BITSCOM_LL_MAX_MB", "").strip():
             self.set_ll_max_bytes(int(float(os.environ["BITSCOM_LL_MAX_MB"]) * (1 << 20)))
         self.side_stream = torch.cuda.Stream(device=self.device)
@@ -398,7 +399,8 @@ class FusedLowBitComm:
         self.native.lib.bcom_comm_set_timeout_ms(self.native.handle, float(ms))
 
     def set_ll_max_bytes(self, nbytes: int) -> None:
-        """All-reduces of at most ``nbytes`` (4- or 8-bit codes, aligned tensors) run as ONE
+        """All-reduces of at most ``nbytes`` (counted at four bytes per element whatever the dtype;
+        4- or 8-bit codes, aligned tensors) run as ONE
         pass whose packed words carry their own arrival flags instead of as three phases with
         two flag handshakes; 0 switches that off.  Every rank of the group must use the same
         value (the two forms do not talk to each other)."""
@@ -514,7 +516,8 @@ class EmulatedWorld:
     def __init__(self, world: int, device="cuda:0", region_bytes: int = 8 << 20,
                  timeout_ms: float = 2000.0, ll_max_bytes: Optional[int] = None):
         """``ll_max_bytes``: largest all-reduce (bytes of the tensor) that runs as one
-        flag-in-data launch (``None``: the library's default, 32 MiB; 0: never)."""
+        flag-in-data launch, counted at four bytes per element (``None``: the library's default,
+        64 MiB = 16 Mi elements; 0: never)."""
         self.world = world
         self.device = torch.device(device)
         self.comms = [_NativeComm(r, world, region_bytes, self.device) for r in range(world)]
