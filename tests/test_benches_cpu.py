@@ -261,3 +261,31 @@ def test_resnet18_ddp_trainer_on_cpu_ranks(tmp_path):
     assert row["workload"] == "resnet18_cifar_ddp" and row["world"] == 2 and row["bitwidth"] == 2
     assert row["loss_last"] == row["loss_last"] and row["samples_per_s"] > 0
     assert os.path.exists(out)
+
+
+# ------------------------------------------------------------------ error-feedback benefit
+def test_error_feedback_benefit_and_training_curves(tmp_path, capsys):
+    """Both halves of the error-feedback comparison: the accumulated-error curve (error feedback
+    must win by an order of magnitude at 4 bit) and the small MLP trained through the quantizer
+    with and without residuals (same start, both learn, 8-bit runs indistinguishable); a CSV
+    and a PNG per curve."""
+    from bitscom_b200.bench import error_feedback_benefit as EF
+
+    EF.main(["--bits", "4", "8", "--steps", "40", "--vec-size", "32768", "--train-steps", "60",
+             "--out-dir", str(tmp_path)])
+    lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    curve4 = next(r for r in lines if r["bitwidth"] == 4 and "ef_rel_error" in r)
+    assert curve4["ef_rel_error"] < curve4["no_ef_rel_error"] / 3
+    for bits in (4, 8):
+        run = next(r for r in lines if r["bitwidth"] == bits and "train_steps" in r)
+        assert run["loss_no_ef_first"] == run["loss_ef_first"] > 1.5
+        assert run["loss_no_ef_last"] < 0.1 and run["loss_ef_last"] < 0.1
+        rows = list(csv.reader(open(tmp_path / f"ef_training_curve_bw{bits}.csv")))
+        assert rows[0] == ["step", "loss_noef", "loss_ef"] and len(rows) == 61
+        _assert_png(tmp_path / f"ef_training_curve_bw{bits}.png")
+        _assert_png(tmp_path / f"ef_comparison_bw{bits}.png")
+    run8 = next(r for r in lines if r["bitwidth"] == 8 and "train_steps" in r)
+    assert abs(run8["loss_no_ef_last"] - run8["loss_ef_last"]) < 1e-3
+    # the curves are deterministic
+    a = EF.ef_training_curve(4, steps=5, use_ef=True)
+    assert a == EF.ef_training_curve(4, steps=5, use_ef=True)
