@@ -14,6 +14,7 @@ import sys
 ENV_SWITCHES = [
     "BITSCOM_TIMING", "BITSCOM_TIMING_DIR", "BITSCOM_NVTX", "BITSCOM_COMM_DEBUG", "TRACE_EXPLAIN",
     "BITSCOM_UNSAFE_FULL_ASYNC_CHAIN", "BITSCOM_TIMEOUT_MS", "BITSCOM_MAX_CTAS", "BITSCOM_NVLS",
+    "BITSCOM_LL_MAX_MB", "BITSCOM_SYMM_MB", "BITSCOM_GEMM",
     "BITSCOM_ATTN_FWD", "BITSCOM_ATTN_BWD_DQ", "BITSCOM_CPU_CODEC", "BITSCOM_ALLOW_FALLBACK",
     "BITSCOM_NO_BUILD", "BITSCOM_NVCC", "BITSCOM_CUDA_COMPILER", "BITSCOM_RUN_PERF",
     "BITSCOM_EXPERIMENTAL",

@@ -436,6 +436,7 @@ class FusedLowBitComm:
                     self.native.handle, ctypes.byref(args), ctypes.c_void_p(stream.cuda_stream))
         if rc:
             check(rc, "bcom_collective")
+        _native.add_launches(1)   # at least one kernel (large buckets: one per chunk)
         self.launches += 1
         _timing.add("fused_launches")
         payload, wire = traffic_bytes(args, self.world)
