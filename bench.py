@@ -74,7 +74,14 @@ def run_ours(args):
     # the collective half of the metric, over all N GPUs, before the model takes the memory
     allreduce = None
     if world > 1 and cuda and args.impl == "ours" and not args.no_allreduce_block:
-        allreduce = allreduce_block(args)
+        try:
+            allreduce = allreduce_block(args)
+        except Exception as exc:  # the training half of the line is still worth reporting
+            allreduce = {"error": f"{type(exc).__name__}: {str(exc)[:300]}"}
+            import torch.distributed as _dist
+
+            if _dist.is_initialized():
+                _dist.barrier()
 
     trainer = LlamaTrainer(mcfg, tcfg)
     rank, dev = trainer.rank, trainer.device
