@@ -19,6 +19,11 @@
 // all-gather = phase 2 fed from `in` plus phase 3.  All three modes keep both flag
 // handshakes, which is what makes back-to-back calls safe without a separate barrier.
 //
+// Small all-reduces (up to 16 Mi elements, 4- or 8-bit codes) take a second form of the same
+// three phases, further down ("small buckets"): every packed word and every scale travels as
+// an 8-byte {word, epoch} pair that the consumer polls, so the two flag handshakes, the fence
+// and the arrival counters disappear and the launch is an ordinary one.  Same numerics.
+//
 // Synchronisation rules: the grid is launched cooperatively (all CTAs co-resident);
 // arrival counters live in the rank's control page and are re-armed by the kernel
 // itself; every wait is bounded by a wall-clock budget and, when it expires, the
