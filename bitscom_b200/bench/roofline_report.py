@@ -26,13 +26,14 @@ def _rows_of(rec: Dict) -> List[Dict]:
     tag = rec.get("peaks", "")
     case = rec.get("case", rec.get("workload", "?"))
     out = []
-    if case == "elementwise":
+    if case in ("elementwise", "norms_raw"):
         for k in rec.get("kernels", []):
             out.append({"kernel": k["name"], "workload": f"{rec.get('tokens')} tokens",
                         "time_ms": k["ms"], "achieved": f"{k['gbs']:.0f} GB/s",
                         "fraction": k["frac_hbm"], "of": f"HBM copy, {tag}"})
     elif case.startswith("gemm"):
-        out.append({"kernel": case, "workload": " x ".join(str(rec.get(d)) for d in "MNK"),
+        name = case + (f" ({rec['variant']})" if rec.get("variant") else "")
+        out.append({"kernel": name, "workload": " x ".join(str(rec.get(d)) for d in "MNK"),
                     "time_ms": rec.get("ms"), "achieved": f"{rec.get('tflops', 0):.0f} TFLOP/s",
                     "fraction": rec.get("frac_bf16_peak"), "of": f"cuBLAS bf16, {tag}"})
     elif case.startswith("attention"):
@@ -50,16 +51,20 @@ def _rows_of(rec: Dict) -> List[Dict]:
                         "achieved": f"{rec.get(d + '_gbs', 0):.0f} GB/s",
                         "fraction": rec.get(d + "_frac_hbm"), "of": f"HBM copy, {tag}"})
     elif case.startswith("fused"):
+        setting = (f", {rec['rounding']}" if rec.get("rounding") else "") + (
+            ", EF" if rec.get("ef") else ", no EF")
         out.append({"kernel": case, "workload": f"W{rec.get('world')} x {rec.get('elems')} "
-                    f"{rec.get('dtype')} {rec.get('bits')}-bit", "time_ms": rec.get("ms"),
+                    f"{rec.get('dtype')} {rec.get('bits')}-bit{setting}", "time_ms": rec.get("ms"),
                     "achieved": f"{rec.get('gbs', 0):.0f} GB/s", "fraction": rec.get("frac_hbm"),
                     "of": f"HBM copy, {tag}"})
     elif "roofline_frac" in rec:  # allreduce_sweep rows
         size = rec.get("bytes", 0) / (1 << 20)
         out.append({"kernel": f"low-bit all-reduce {rec.get('bits')}-bit",
-                    "workload": f"{rec.get('world')} GPUs, {size:g} MB {rec.get('dtype')}",
+                    "workload": f"{rec.get('world')} GPUs, {size:g} MB "
+                    f"{rec.get('bucket_dtype', rec.get('dtype'))}",
                     "time_ms": rec.get("lowbit_ms"),
-                    "achieved": f"{rec.get('lowbit_fp32eq_gbs', 0):.0f} GB/s fp32-equivalent",
+                    "achieved": f"{rec.get('lowbit_effective_gbs', rec.get('lowbit_fp32eq_gbs', 0)):.0f}"
+                    " GB/s fp32-equivalent",
                     "fraction": rec.get("roofline_frac"),
                     "of": f"max(HBM, NVLink) bound, {rec.get('peaks', tag)}"})
     return out
