@@ -42,10 +42,15 @@ def build_1f1b(stage: int, stages: int, microbatches: int) -> List[Action]:
     return actions
 
 
-def max_live_microbatches(actions: Sequence[Action]) -> int:
+def max_live_microbatches(actions: Sequence) -> int:
+    """Most forwards whose backward has not run yet, at any point of an action list (plain
+    ``(kind, mb)`` or interleaved ``(kind, mb, chunk)`` actions): the activation memory a rank
+    needs, in units of one micro-batch through one stage (plain) or one chunk (interleaved;
+    ``(P - rank - 1) * 2 + (chunks - 1) * P + 1`` chunk activations, each 1 / chunks of a
+    stage's)."""
     live = peak = 0
-    for kind, _ in actions:
-        live += 1 if kind == "F" else -1
+    for action in actions:
+        live += 1 if action[0] == "F" else -1
         peak = max(peak, live)
     return peak
 

@@ -158,6 +158,16 @@ def test_interleaved_bubble_matches_formula(stages, mbs, chunks):
     assert abs(t["efficiency"] - want) < 1e-9
 
 
+@pytest.mark.parametrize("stages,mbs,chunks", [(2, 8, 2), (2, 8, 4), (4, 8, 2), (4, 16, 2),
+                                               (8, 16, 2)])
+def test_interleaved_activation_memory(stages, mbs, chunks):
+    """Peak number of chunk activations alive on a rank: the warm-up depth plus one."""
+    for rank in range(stages):
+        acts = build_interleaved(rank, stages, mbs, chunks)
+        want = min((stages - rank - 1) * 2 + (chunks - 1) * stages + 1, mbs * chunks)
+        assert max_live_microbatches(acts) == want
+
+
 def test_interleaved_rejects_ragged_microbatches():
     with pytest.raises(ValueError):
         build_interleaved(0, 4, 6, 2)
